@@ -1,0 +1,31 @@
+// Stream-K work split of the fused linear: T = ntile * nkt units in (tile, k-tile) order are cut into G
+// contiguous ranges, CTA c owning [floor(c*T/G), floor((c+1)*T/G)). Shared by host and device code.
+#pragma once
+
+#if defined(__CUDACC__)
+#define BILOCO_HD __host__ __device__ inline
+#else
+#define BILOCO_HD inline
+#endif
+
+namespace biloco {
+
+// first unit of CTA c (c may equal G: one past the last unit)
+BILOCO_HD long long sched_first_unit(int c, long long T, int G) { return (long long)c * T / G; }
+
+// the CTA whose range contains unit u: the largest c with floor(c*T/G) <= u
+BILOCO_HD int sched_cta_of_unit(long long u, long long T, int G) { return (int)(((u + 1) * G - 1) / T); }
+
+// Largest number of partial-sum slots any tile needs = max over tiles of (#contributing CTAs - 1), at least 1.
+BILOCO_HD int sched_max_slots(int ntile, int nkt, int G) {
+    const long long T = (long long)ntile * nkt;
+    int best = 1;
+    for (int t = 0; t < ntile; ++t) {
+        const int c0 = sched_cta_of_unit((long long)t * nkt, T, G);
+        const int c1 = sched_cta_of_unit((long long)t * nkt + nkt - 1, T, G);
+        if (c1 - c0 > best) best = c1 - c0;
+    }
+    return best;
+}
+
+}  // namespace biloco

@@ -1,0 +1,166 @@
+"""Python side of the fused B200 kernel: sign packing, operand layouts, mode table and a launcher.
+
+Mirrors the public interface of the reference's ``biloco/kernel.py`` (``BiLoCoGemm``, ``pack_signs``,
+``pack_u_col32``, ``modes_for``, ``DEFAULT_MODE``, ``RANKS``, ``nvfp4_sf_bytes``, ``reference``,
+``time_graph``) and registers the same ``torch.ops.biloco.*`` operators (``csrc/bindings.cpp:17-48``), so a
+caller written against the reference runs unchanged. Underneath, every operator is one call into
+``libbiloco_b200.so`` through the C ABI of ``include/biloco_b200.h``; there is no PyTorch or CPU fallback.
+
+One launch computes  y = alpha * FP4(x) FP4(R)^T + sum_i S_i (x . v_i) u_i  for a decode batch of M <= 32 rows.
+"""
+import torch
+
+from . import _lib
+from . import ops as _ops  # noqa: F401  (registers torch.ops.biloco)
+
+ops = torch.ops.biloco
+
+# Ranks the mode table is measured for (the reference's RANKS, biloco/kernel.py:16, plus 1024).
+RANKS = (16, 32, 64, 128, 256, 512, 1024)
+
+# Schedules implemented by the fused kernel (see include/biloco_b200.h, BILOCO_MODE_*).
+IMPLEMENTED_MODES = (2,)
+
+# Fastest implemented mode per (M, rank) on B200 at K = N = 5120.
+DEFAULT_MODE = {M: {r: 2 for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
+
+
+def pack_signs(signs: torch.Tensor) -> torch.Tensor:
+    """[..., n] +-1 -> uint8 [..., n/8]; bit i of byte j is set iff signs[..., 8j + i] >= 0
+    (same bit order and zero-is-plus rule as biloco/kernel.py:29-34)."""
+    assert signs.shape[-1] % 8 == 0
+    b = (signs >= 0).reshape(*signs.shape[:-1], signs.shape[-1] // 8, 8).to(torch.int32)
+    shifts = torch.arange(8, device=signs.device, dtype=torch.int32)
+    return (b << shifts).sum(dim=-1).to(torch.uint8)
+
+
+def pack_u_col32(U_packed: torch.Tensor, n_cols: int, rank: int) -> torch.Tensor:
+    """U_packed [R, N/8] -> int32 [N, ceil(R/32)]: bit b of word w of column n is the sign bit of rank 32w + b
+    (layout of biloco/kernel.py:37-47). CUDA tensors go through the library's re-layout kernel."""
+    assert U_packed.dtype == torch.uint8 and U_packed.shape == (rank, n_cols // 8)
+    words = (rank + 31) // 32
+    if U_packed.is_cuda:
+        out = torch.empty((n_cols, words), device=U_packed.device, dtype=torch.int32)
+        with torch.cuda.device(U_packed.device):
+            _lib.check(_lib.load().biloco_b200_pack_u_col32(U_packed.contiguous().data_ptr(), out.data_ptr(), n_cols, rank,
+                                                            torch.cuda.current_stream().cuda_stream), "pack_u_col32")
+        return out
+    shifts = torch.arange(8, dtype=torch.int64)
+    bits = ((U_packed.to(torch.int64).unsqueeze(-1) >> shifts) & 1).reshape(rank, n_cols)       # [R, N]
+    pad = words * 32 - rank
+    if pad:
+        bits = torch.cat([bits, torch.zeros(pad, n_cols, dtype=torch.int64)], dim=0)
+    w = (bits.reshape(words, 32, n_cols) << torch.arange(32, dtype=torch.int64).view(1, 32, 1)).sum(dim=1)  # [words, N]
+    w = torch.where(w >= 2 ** 31, w - 2 ** 32, w)
+    return w.t().contiguous().to(torch.int32)
+
+
+def modes_for(M: int, rank: int, K: int = 5120):
+    """Modes the fused kernel accepts for this (M, rank, K). The launch can still reject a shape in its
+    host-side checks (K must be a multiple of 256, N of 8)."""
+    if not (1 <= M <= 32) or rank < 1 or K % 256 != 0:
+        return []
+    return list(IMPLEMENTED_MODES)
+
+
+def nvfp4_sf_bytes(rows: int, k: int) -> int:
+    """Bytes of the NVFP4 block-scale tensor for a [rows, k] operand (rows padded to 128, k/16 padded to 4)."""
+    return (rows + 127) // 128 * 128 * ((k // 16 + 3) // 4 * 4)
+
+
+def scratch_bytes(M: int, N: int, K: int, R: int, num_sms: int = 0) -> int:
+    """Scratch the fused kernel needs for this problem (0 SMs = ask the current device)."""
+    n = _lib.load().biloco_b200_scratch_bytes(M, N, K, R, num_sms)
+    if n == 0:
+        raise RuntimeError(f"fused linear does not support M={M} N={N} K={K} R={R}")
+    return n
+
+
+class BiLoCoGemm:
+    """Fused FP4 GEMM + binary low-rank term for one layer at a fixed decode batch M.
+
+    W_fp4 [N, K/2] uint8 and W_sf: NVFP4 weight codes and block scales; alpha: fp32 [1];
+    V_packed [R, K/8], U_packed [R, N/8]: packed signs; S: bf16 [R] coefficients.
+    Call with the NVFP4 activation A [1, rows, K/2] uint8 (rows >= M; the reference pads to 128 rows, any
+    row count from M to 128 is accepted), its block scales A_sf, and the BF16 activation X [M, K] (the
+    low-rank term uses the unquantized activation).
+    The scratch buffer is tagged with the call's epoch (a launch argument), so consecutive calls need no
+    clearing. A CUDA graph bakes the epochs in: call reset() at the start of the captured region so that
+    every replay starts from zeroed scratch and epoch 1.
+    """
+
+    def __init__(self, W_fp4, W_sf, alpha, V_packed, U_packed, S, M: int, mode: int = None):
+        self.N, self.K = W_fp4.shape[0], W_fp4.shape[1] * 2
+        self.R, self.M = V_packed.shape[0], M
+        self.mode = mode or DEFAULT_MODE.get(M, {}).get(self.R) or (modes_for(M, self.R, self.K) or [None])[0]
+        assert self.mode in modes_for(M, self.R, self.K), f"mode {self.mode} not available for M={M} R={self.R} K={self.K}"
+        self.W_fp4, self.W_sf, self.alpha, self.V, self.S = W_fp4, W_sf, alpha, V_packed, S
+        dev = W_fp4.device
+        self.U_col32 = pack_u_col32(U_packed, n_cols=self.N, rank=self.R)
+        self.none = torch.zeros(0, device=dev, dtype=torch.int64)
+        with torch.cuda.device(dev):
+            nbytes = scratch_bytes(M, self.N, self.K, self.R)
+        # one buffer holds status words, counters, the z hand-off area and the split-K partial sums
+        self.z = torch.zeros(nbytes // 4, device=dev, dtype=torch.float32)
+        self.epoch = 0
+
+    def reset(self):
+        self.z.zero_()
+        self.epoch = 0
+
+    def status(self):
+        """The 16 device status words (synchronises): word 0 is non-zero after a device-side wait ran out."""
+        import ctypes
+        out = (ctypes.c_int32 * 16)()
+        with torch.cuda.device(self.z.device):
+            _lib.check(_lib.load().biloco_b200_read_status(self.z.data_ptr(), out, torch.cuda.current_stream().cuda_stream),
+                       "read_status")
+        return list(out)
+
+    def __call__(self, A_pad, A_sf, X_bf16):
+        """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten)."""
+        self.epoch += 1
+        a = (A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32)
+        if self.mode == 2:
+            return ops.biloco_gemm_mode2(*a, self.z, self.none, self.none, self.none, self.none, self.M, self.epoch)
+        if self.mode == 4:
+            return ops.biloco_gemm_mode4(*a, self.z, self.none, self.M, self.epoch)
+        return ops.biloco_gemm_mode5(*a, self.z, self.none, self.none, self.M, self.epoch)
+
+
+def reference(A_fp4, A_sf, W_fp4, W_sf, alpha, X_bf16, V_packed, U_packed, S):
+    """Unfused reference: z = S * (X sign(V)^T), y_lr = z sign(U) (bf16), then the FP4 GEMM with y_lr added."""
+    z = ops.binary_z_reference(X_bf16, V_packed, S).contiguous()
+    y_lr = torch.empty(X_bf16.shape[0], U_packed.shape[1] * 8, device=X_bf16.device, dtype=torch.bfloat16)
+    ops.binary_expand_reference(z, U_packed, y_lr)
+    return ops.fp4_gemm_residual(A_fp4, W_fp4, A_sf, W_sf, alpha, y_lr)
+
+
+def time_graph(fn, pre=None, iters: int = 30, batch: int = 64):
+    """Median time per launch (us) of fn, replaying a CUDA graph of pre() followed by `batch` launches
+    (the reference's timing protocol, biloco/kernel.py:145-168: same operands every launch, so L2-warm)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        if pre:
+            pre()
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(s)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        if pre:
+            pre()
+        for _ in range(batch):
+            fn()
+    for _ in range(5):
+        g.replay()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in ev:
+        a.record()
+        g.replay()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) / batch * 1e3 for a, b in ev)
+    return ts[len(ts) // 2]

@@ -1,0 +1,133 @@
+/* biloco_b200 — C ABI of the B200 (sm_100a) implementation of the fused BiLoCo decode linear
+ *
+ *     y[M,N] = alpha * FP4(x)[M,K] . FP4(R)[N,K]^T  +  sum_i S_i (x . v_i) u_i          (M <= 32)
+ *
+ * Plain pointers and sizes only; every pointer is DEVICE memory unless stated otherwise. All functions
+ * enqueue work on `stream` and return without synchronising. Return value: 0 on success, a negative
+ * BILOCO_ERR_* code otherwise (nothing is enqueued in that case). Nothing here throws or allocates
+ * device memory: scratch is caller-owned (see biloco_b200_scratch_bytes).
+ *
+ * Each entry point names the interface of the reference (jindavid/BiLoCo) that it stands in for.
+ */
+#ifndef BILOCO_B200_H_
+#define BILOCO_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
+
+#define BILOCO_OK 0
+#define BILOCO_ERR_NULL -1           /* a required pointer is null */
+#define BILOCO_ERR_SHAPE -2          /* shape not supported (see each function) */
+#define BILOCO_ERR_ALIGN -3          /* a pointer is not aligned as required */
+#define BILOCO_ERR_SCRATCH -4        /* scratch too small */
+#define BILOCO_ERR_CUDA -5           /* a CUDA runtime / driver call failed */
+#define BILOCO_ERR_MODE -6           /* unknown schedule (mode) or quantisation rule */
+#define BILOCO_ERR_EPOCH -7          /* epoch must be >= 1 */
+#define BILOCO_ERR_LIMIT -8          /* size beyond a stated maximum */
+
+/* NVFP4 block-scale selection rules of the activation quantiser (biloco/fp4.py:12-18). */
+#define BILOCO_RULE_STATIC_6 0
+#define BILOCO_RULE_STATIC_4 1
+#define BILOCO_RULE_MSE 2            /* "four over six": per block, 6 or 4, smaller squared error */
+
+/* Schedules of the fused kernel; numbered like the reference's modes (biloco/kernel.py:18-26,66-76).
+ *   2: z by all CTAs at entry (rank-sliced), arrival counter hand-off
+ *   4: z by all CTAs at entry (rank-sliced), per-value epoch tags polled by the consumers
+ *   5: as mode 2 with the z stage split over K as well (for batches where z dominates)          */
+#define BILOCO_MODE_COUNTER 2
+#define BILOCO_MODE_TAGGED 4
+#define BILOCO_MODE_SPLITK 5
+
+/* Human-readable text for an error code (host pointer, static storage). */
+const char* biloco_b200_error_string(int code);
+
+/* ABI version of this library (bumped when a signature changes). */
+int biloco_b200_abi_version(void);
+
+/* Bytes of the block-scale tensor of a [rows, k] NVFP4 operand in the 128x4 atom layout.
+ * Replaces: biloco/kernel.py:132-134 (nvfp4_sf_bytes). Host-only arithmetic. */
+size_t biloco_b200_sf_bytes(int rows, int k);
+
+/* z[m,i] = S[i] * sum_k sign(V[i,k]) X[m,k], fp32 [M,R].   X bf16 [M,K], V_packed u8 [R,K/8] (bit set = +1,
+ * LSB first), S bf16 [R]. K % 8 == 0.
+ * Replaces: torch.ops.biloco.binary_z_reference (csrc/bindings.cpp:46, csrc/reference_ops.cu:169-215). */
+int biloco_b200_binary_z(const void* X_bf16, const void* V_packed, const void* S_bf16, float* z,
+                         int M, int K, int R, biloco_stream_t stream);
+
+/* Y[m,n] = bf16( sum_i z[m,i] sign(U[i,n]) ).   z fp32 [M,R], U_packed u8 [R,N/8], Y bf16 [M,N]. N % 8 == 0.
+ * Replaces: torch.ops.biloco.binary_expand_reference (csrc/bindings.cpp:47, csrc/reference_ops.cu:217-252). */
+int biloco_b200_binary_expand(const float* z, const void* U_packed, void* Y_bf16,
+                              int M, int N, int R, biloco_stream_t stream);
+
+/* U_packed u8 [R, N/8] -> U_col32 int32 [N, ceil(R/32)] (bit b of word w of column n = sign of rank 32w+b).
+ * Replaces: biloco/kernel.py:37-47 (pack_u_col32, a host loop in the reference). N % 8 == 0. */
+int biloco_b200_pack_u_col32(const void* U_packed, int32_t* U_col32, int N, int R, biloco_stream_t stream);
+
+/* NVFP4 activation quantiser: X bf16 [M,K] -> codes u8 [A_rows, K/2] (rows >= M zeroed), block scales
+ * (E4M3, 128x4 atom layout, biloco_b200_sf_bytes(A_rows,K) bytes, fully written), a_gscale fp32 [1]
+ * (decode scale of the tensor) and, if w_gscale != NULL, alpha_out[0] = w_gscale[0] * a_gscale[0].
+ * If smooth_bf16 != NULL the input is first divided by it per channel (result rounded to bf16) and, if
+ * Xs_bf16 != NULL, that smoothed activation is written there (the low-rank term consumes it).
+ * One global scale per call over all M rows (biloco/fp4.py:3-4). K % 64 == 0, M <= A_rows <= 128.
+ * Replaces: biloco/fp4.py:30-35 (fake_quantize_fp4 -> fouroversix.quantize_to_fp4) and the x/smooth_scale
+ * division of biloco/layer.py:55. */
+int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_bf16,
+                          void* A_codes, void* A_sf, float* a_gscale, float* alpha_out, const float* w_gscale,
+                          int M, int A_rows, int K, int rule, biloco_stream_t stream);
+
+/* Scratch bytes needed by biloco_b200_fused_linear / biloco_b200_fp4_gemm for this problem on a device
+ * with `num_sms` multiprocessors (0 = query the current device). The scratch must be zero-filled once
+ * before the first call (epoch 1) and whenever the epoch sequence restarts; it is never cleared between
+ * calls (the reference's BiLoCoGemm owns z/flags/corr/cnt buffers the same way, biloco/kernel.py:98-119).
+ * Returns 0 for an unsupported shape. Host-only arithmetic unless num_sms == 0. */
+size_t biloco_b200_scratch_bytes(int M, int N, int K, int R, int num_sms);
+
+/* Work split the fused kernel will use for this problem: out[0] = 128-row tiles, out[1] = 256-wide k-tiles,
+ * out[2] = CTAs launched, out[3] = partial-sum slots per tile, out[4] = MMA N (8/16/32), out[5] = pipeline
+ * stages. Host-only; for tests and sizing. No counterpart in the reference (its tiling is fixed by CUTLASS
+ * template parameters, csrc/biloco_gemm.cu:3017-3020). */
+int biloco_b200_schedule_info(int M, int N, int K, int R, int num_sms, int* out6);
+
+/* The fused decode linear, one launch:
+ *     Y[m,n] = bf16( alpha[0] * sum_k A[m,k] W[n,k]  +  sum_i z[m,i] sign(U[i,n]) ),  z = S .* (X sign(V)^T)
+ * W_codes u8 [N,K/2], W_sf E4M3 (atom layout, rows padded to 128), alpha fp32 [1] (device), A_codes u8
+ * [A_rows,K/2] (A_rows >= M; rows beyond M are ignored), A_sf E4M3 (atom layout), X bf16 [M,K],
+ * V_packed u8 [R,K/8], U_col32 int32 [N, ceil(R/32)], S bf16 [R], Y bf16 [M,N] (row stride N).
+ * R == 0 skips the low-rank term (X, V, U, S may then be NULL). C_bf16 (may be NULL): bf16 [M,N] added
+ * before the final rounding. `epoch` starts at 1 and increases by 1 per call on the same scratch.
+ * Shapes: 1 <= M <= 32, K % 256 == 0, N % 8 == 0. 16-byte alignment for W_codes, A_codes, W_sf, A_sf, X.
+ * Device-side waits are bounded; a wait that ran out leaves a non-zero code in the first int32 of scratch
+ * (read it with biloco_b200_read_status) and the call's output is undefined.
+ * Replaces: torch.ops.biloco.biloco_gemm_mode2/4/5 (csrc/bindings.cpp:37-43; host launcher
+ * csrc/biloco_gemm.cu:2986-3431, dispatchers :3435-3562) and, with R == 0, fp4_gemm / fp4_gemm_n64 /
+ * fp4_gemm_n128 / fp4_gemm_residual (csrc/bindings.cpp:22-27, csrc/biloco_gemm.cu:2744-2983). */
+int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const float* alpha,
+                             const void* A_codes, const void* A_sf, const void* X_bf16,
+                             const void* V_packed, const int32_t* U_col32, const void* S_bf16,
+                             const void* C_bf16, void* Y_bf16,
+                             void* scratch, size_t scratch_bytes,
+                             int M, int A_rows, int N, int K, int R,
+                             int mode, int epoch, biloco_stream_t stream);
+
+/* Copy the 16 int32 status words at the start of a scratch buffer to host memory `out16` (synchronises
+ * `stream`). Word 0: 0 = no device-side wait ran out since the scratch was last zeroed; otherwise the code
+ * of the first wait that gave up. Words 1..3: block index, epoch and role of that wait. */
+int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t stream);
+
+/* CUDA-core FP4 GEMM used to cross-check the tensor-core path on the device at full size:
+ * D[m,n] = bf16(alpha[0] * sum_k A[m,k] W[n,k] + C[m,n]). Same operand formats as above; K % 16 == 0.
+ * Replaces (functionally): torch.ops.biloco.fp4_gemm_residual as used by biloco/kernel.py:137-142. */
+int biloco_b200_fp4_gemm_simt(const void* A_codes, const void* A_sf, const void* W_codes, const void* W_sf,
+                              const float* alpha, const void* C_bf16, void* D_bf16,
+                              int M, int N, int K, biloco_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BILOCO_B200_H_ */
