@@ -1,0 +1,335 @@
+"""Benchmark of the fused BiLoCo decode linear on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--M 1] [--r 512]
+
+A *step* is one pass of the fused linear over ``--layers`` distinct synthetic layers (K = N = 5120 by default),
+i.e. ``--layers`` kernel launches that stream ``layers * bytes(K, N, r)`` algorithmic weight bytes; with the
+default 64 layers that is 986 MB per step, far larger than L2, so every launch streams its weights from HBM
+("inputs larger than L2"). One JSON line is printed by rank 0:
+
+  value         algorithmic GB/s of the whole job, operands resident in HBM, CUDA-graph replay of the step,
+                timed with CUDA events on the launching stream (max over ranks)
+  e2e           the same metric through the public Python API with HOST activations: per layer a pinned
+                host->device copy of x, the device NVFP4 quantiser, the fused linear, a device->host copy of y
+  roofline      achieved GB/s of the fused kernel vs the measured HBM copy peak (MEASURED_PEAKS.json)
+  cpu_baseline  the CPU oracle's fake-quant forward (biloco/layer.py:54-64 semantics) on the host cores,
+                bounded sample
+
+``--impl reference`` times that CPU forward alone and prints the same line shape with "impl": "reference".
+Multi-GPU (torchrun, one rank per GPU): every rank runs its own set of layers (the path shards by layer / by
+output columns with no exchange), so scaling is weak and no collective sits on the data path.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of fused_linear_kernel<8> at M=1, K=N=5120, r=512,
+# from the ncu capture summarised under profiles/ (None until a capture exists)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def algorithmic_bytes(K, N, r):
+    """E2M1 codes + E4M3 block scales of the residual + packed U and V sign bits."""
+    return N * K // 2 + N * K // 16 + N * r // 8 + K * r // 8
+
+
+def measured_hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.t0, self.t1 = index, None, None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu=timestamp,{self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                                         text=True)
+            time.sleep(0.15)
+        except Exception:
+            self.proc = None
+
+    def mark(self, which):
+        setattr(self, which, time.time())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        time.sleep(0.1)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        rows = []
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                ts = time.mktime(time.strptime(f[0].split(".")[0], "%Y/%m/%d %H:%M:%S")) + float("0." + f[0].split(".")[1])
+                rows.append((ts, float(f[1]), float(f[2]), f[4:8]))
+            except Exception:
+                continue
+        inside = [r for r in rows if self.t0 is not None and self.t0 - 0.05 <= r[0] <= (self.t1 or 1e18) + 0.05] or rows
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in inside for n, v in zip(names, r[3]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(r[1] for r in inside), "sm_max_mhz": inside[0][2], "reasons": reasons,
+                "samples": len(inside)}
+
+
+def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed):
+    """Synthetic layers in the construction of the reference's timing scripts (scripts/problem.py:7-27, random
+    block scales in [0.25, 2]), activations ~N(0,1) with 1 % outlier channels x20 quantised by the device quantiser."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    layers = []
+    for _ in range(L):
+        W = torch.randint(0, 256, (N, K // 2), device=dev, dtype=torch.uint8, generator=g)
+        W_sf = (torch.rand(kernel.nvfp4_sf_bytes(N, K), device=dev, generator=g) * 1.75 + 0.25).to(torch.float8_e4m3fn)
+        Vp = torch.randint(0, 256, (r, K // 8), device=dev, dtype=torch.uint8, generator=g)
+        Up = torch.randint(0, 256, (r, N // 8), device=dev, dtype=torch.uint8, generator=g)
+        S = (torch.randn(r, device=dev, generator=g) * 0.01).to(torch.bfloat16)
+        w_gs = torch.full((1,), 1e-3, device=dev)
+        x = torch.randn(M, K, device=dev, generator=g)
+        idx = torch.randperm(K, device=dev, generator=g)[: K // 100]
+        x[:, idx] *= 20
+        x = x.to(torch.bfloat16).contiguous()
+        q = fp4.quantize_activation(x, "mse", w_gscale=w_gs, rows=M)
+        gemm = kernel.BiLoCoGemm(W, W_sf, q["alpha"], Vp, Up, S, M=M)
+        layers.append(dict(gemm=gemm, q=q, x=x, w_gs=w_gs, x_host=x.cpu().pin_memory(),
+                           y_host=torch.empty(M, N, dtype=torch.bfloat16).pin_memory()))
+    return layers
+
+
+def cpu_forward_setup(M, K, N, r, seed=0):
+    """Operands of the reference's fake-quant forward for one synthetic layer (numpy, bf16-exact float32)."""
+    import numpy as np
+    from oracle import biloco_oracle as orc
+    rng = np.random.default_rng(seed)
+    V = np.where(rng.standard_normal((r, K)) >= 0, 1.0, -1.0).astype(np.float32)
+    U = np.where(rng.standard_normal((r, N)) >= 0, 1.0, -1.0).astype(np.float32)
+    S = orc.bf16_round(rng.standard_normal(r) * 0.01)
+    weight_fp4 = orc.bf16_round(orc.fake_quantize_fp4(orc.bf16_round(rng.standard_normal((N, K)) * 0.02), "static_6"))
+    x = orc.bf16_round(rng.standard_normal((M, K)))
+    x[:, rng.permutation(K)[: K // 100]] *= 20
+    return dict(x=x, smooth=np.ones(K, np.float32), V_scaled=orc.bf16_round(V * S[:, None]), U_T=U, weight_fp4=weight_fp4)
+
+
+def time_cpu_forward(M, K, N, r, calls, warm, budget_s):
+    """Median seconds per call of the oracle's torch-CPU forward (bf16 matmuls on all host threads, as the
+    reference module runs on a CPU); stops early when the time budget is used up."""
+    from oracle import biloco_oracle as orc
+    a = cpu_forward_setup(M, K, N, r)
+    layer = orc.TorchLayer(a["smooth"], a["V_scaled"], a["U_T"], a["weight_fp4"], None, "mse")
+    ts = []
+    t_start = time.time()
+    for i in range(warm + calls):
+        t0 = time.perf_counter()
+        layer(a["x"])
+        dt = time.perf_counter() - t0
+        if i >= warm:
+            ts.append(dt)
+        if time.time() - t_start > budget_s and len(ts) >= 3:
+            break
+    return statistics.median(ts), len(ts)
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    K, N, r, M = args.K, args.N, args.r, args.M
+    sec, n = time_cpu_forward(M, K, N, r, calls=max(args.steps, 3), warm=max(args.warmup, 3), budget_s=120)
+    gbs = algorithmic_bytes(K, N, r) / sec / 1e9
+    cores = os.cpu_count()
+    line = {
+        "impl": "reference", "metric": "fused BiLoCo linear algorithmic HBM GB/s", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": n, "warmup": max(args.warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 (+ f32 sign accumulate)", "data": "synthetic",
+        "config": workload_config(args, layers=1),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{n} calls of the fake-quant forward of one layer (M={M}, K={K}, N={N}, r={r}), median; "
+                                   f"numpy/BLAS threads = {torch.get_num_threads()}"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "us_per_call": sec * 1e6,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, layers):
+    return {"workload": f"configs[1] point M={args.M}, r={args.r}: fused BiLoCo linear K={args.K} N={args.N}, "
+                        f"{layers} distinct layers per step",
+            "M": args.M, "K": args.K, "N": args.N, "r": args.r, "layers_per_step": layers,
+            "l2_policy": "inputs larger than L2 (each step streams layers x weights from HBM)",
+            "algorithmic_bytes_per_call": algorithmic_bytes(args.K, args.N, args.r)}
+
+
+def run_ours(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    from biloco_b200 import fp4, kernel
+
+    K, N, r, M, L = args.K, args.N, args.r, args.M, args.layers
+    layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank)
+    bytes_call = algorithmic_bytes(K, N, r)
+
+    def step_device():
+        for ly in layers:
+            ly["out"] = ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], ly["x"])
+
+    # ---- device-resident arm: one CUDA graph per step -------------------------------------------------
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step_device()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        step_device()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    for ly in layers:
+        st = ly["gemm"].status()
+        assert st[0] == 0, f"device-side wait ran out during warm-up: {st[:4]}"
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.mark("t0")
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    barrier()
+    sampler.mark("t1")
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    for ly in layers:
+        st = ly["gemm"].status()
+        assert st[0] == 0, f"device-side wait ran out in the timed region: {st[:4]}"
+    ms_per_step = ms / args.steps
+    us_per_call = ms_per_step * 1e3 / L
+    value = world * L * bytes_call / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end-to-end arm: host activations in, host outputs back, through the Python API ----------------
+    def step_e2e():
+        for ly in layers:
+            ly["x"].copy_(ly["x_host"], non_blocking=True)
+            fp4.quantize_activation(ly["x"], "mse", w_gscale=ly["w_gs"], rows=M, out=ly["q"])
+            y = ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], ly["x"])
+            ly["y_host"].copy_(y.view(-1, N)[:M], non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_steps = max(3, min(args.steps, 50))
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        step_e2e()
+    barrier()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * L * bytes_call * e2e_steps / e2e_s / 1e9
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_hbm_peak()
+    achieved = bytes_call / (us_per_call * 1e-6) / 1e9
+    line = {
+        "metric": "fused BiLoCo linear algorithmic HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 (+ f32 sign accumulate)", "data": "synthetic",
+        "config": workload_config(args, L),
+        "us_per_call": us_per_call,
+        "gpu_launches": args.steps * L,
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": L * M * K * 2, "d2h_bytes_per_step": L * M * N * 2,
+                "steps": e2e_steps, "us_per_call": e2e_s / e2e_steps / L * 1e6},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"{peak_kind} (STREAM-style copy)",
+                     "kernel": "fused_linear_kernel", "algorithmic_bytes_per_launch": bytes_call},
+    }
+    if world == 1 and not args.no_cpu:
+        sec, n = time_cpu_forward(M, K, N, r, calls=200, warm=3, budget_s=args.cpu_budget)
+        line["cpu_baseline"] = {"value": bytes_call / sec / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                                "us_per_call": sec * 1e6,
+                                "sample": f"{n} calls of the CPU oracle's fake-quant forward of one layer "
+                                          f"(M={M}, K={K}, N={N}, r={r}), median; BLAS threads = {torch.get_num_threads()}"}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--M", type=int, default=1)
+    ap.add_argument("--K", type=int, default=5120)
+    ap.add_argument("--N", type=int, default=5120)
+    ap.add_argument("--r", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

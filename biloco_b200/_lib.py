@@ -24,6 +24,7 @@ SIGNATURES = {
     "biloco_b200_pack_u_col32": (_i, [_vp, _vp, _i, _i, _vp]),
     "biloco_b200_act_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "biloco_b200_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "biloco_b200_scratch_head_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "biloco_b200_schedule_info": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "biloco_b200_fused_linear": (_i, [_vp] * 12 + [_sz] + [_i] * 7 + [_vp]),
     "biloco_b200_read_status": (_i, [_vp, ctypes.POINTER(ctypes.c_int32), _vp]),

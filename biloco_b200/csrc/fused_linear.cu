@@ -22,7 +22,9 @@
 //    counter; the finisher adds them in slot order (deterministic), rounds and stores.
 //  * Low-rank term: at entry every CTA computes a slice of the ranks of z (all M rows) on CUDA cores from the
 //    bit-packed V and publishes it in scratch; an arrival counter (mode 2) tells the consumers that z is
-//    complete. Each contributor of a tile expands z through the packed U signs for its share of the rank words
+//    complete. Counters return to zero inside the launch (the finisher of a tile clears its counter, the last
+//    CTA past the z wait clears the z words), so launches on one scratch need no clearing in between and a
+//    captured CUDA graph can be replayed; launches that share a scratch must not overlap. Each contributor of a tile expands z through the packed U signs for its share of the rank words
 //    while its weight loads are in flight, and adds the result to the accumulators read back from TMEM.
 //  * Every wait (mbarrier, counter) is bounded by a %globaltimer budget; a wait that runs out records a code in
 //    the status words of the scratch, raises a CTA-wide abort flag, and the CTA leaves through the common exit
@@ -78,7 +80,7 @@ struct FusedParams {
     const __nv_bfloat16* C;
     __nv_bfloat16* Y;
     int32_t* status;
-    uint32_t* z_counter;
+    uint32_t* z_counter;      // [0] arrivals of z producers, [1] consumers that have seen it complete
     uint32_t* tile_cnt;
     float* zbuf;
     float* partials;
@@ -159,6 +161,26 @@ __device__ __forceinline__ void tmem_ld_acc(uint32_t taddr, float* v) {
     }
 }
 
+// Segments (maximal runs of units inside one tile) of the unit range [u0, u1), in PROCESSING order.
+// A range that ends inside a tile has a "head" segment whose tile is finished by a later CTA. It goes first:
+// its partial sum is then published before this CTA starts waiting for the partials of the tile it finishes
+// itself. (In natural order CTA c would publish for tile t+1 only after finishing tile t, which waits for CTA
+// c-1, which waits for CTA c-2, ...: a chain through every CTA of the grid.)
+// f(u_start, count) returns false to stop.
+template <class F>
+__device__ __forceinline__ void for_each_segment(long long u0, long long u1, int nkt, F&& f) {
+    const long long rem = u1 % nkt;
+    const long long head = (rem != 0 && u1 - rem > u0) ? (u1 - rem) : u1;   // == u1: no separate head segment
+    if (head < u1 && !f(head, (int)(u1 - head))) return;
+    for (long long u = u0; u < head;) {
+        const long long left = head - u;
+        const int in_tile = nkt - (int)(u % nkt);
+        const int cnt = (int)(in_tile < left ? in_tile : left);
+        if (!f(u, cnt)) return;
+        u += cnt;
+    }
+}
+
 enum : int {   // status codes of waits that ran out
     ST_EMPTY = 101, ST_FULL = 102, ST_ACC_EMPTY = 103, ST_ACC_FULL = 104, ST_Z = 105, ST_TILE = 106,
 };
@@ -209,38 +231,37 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         // ================= TMA producer =================
         if (lane == 0) {
             int i = 0;
-            for (long long u = u0; u < u1; ++u, ++i) {
-                const int s = i % C::STAGES;
-                const int use = i / C::STAGES;
-                if (use > 0 && !wait_bar(smem_u32(&ctrl->empty[s]), (use - 1) & 1, ctrl, p, ST_EMPTY, 4)) break;
-                const int t = (int)(u / p.nkt);
-                const int kt = (int)(u % p.nkt);
-                const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
-                const uint32_t bar = smem_u32(&ctrl->full[s]);
-                mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
-                tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
-                tma_load_2d(sbase + W_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
-                bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES,
-                          p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
-                bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES + SF_TILE_BYTES,
-                          p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
-            }
+            for_each_segment(u0, u1, p.nkt, [&](long long us, int cnt) {
+                for (long long u = us; u < us + cnt; ++u, ++i) {
+                    const int s = i % C::STAGES;
+                    const int use = i / C::STAGES;
+                    if (use > 0 && !wait_bar(smem_u32(&ctrl->empty[s]), (use - 1) & 1, ctrl, p, ST_EMPTY, 4)) return false;
+                    const int t = (int)(u / p.nkt);
+                    const int kt = (int)(u % p.nkt);
+                    const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
+                    const uint32_t bar = smem_u32(&ctrl->full[s]);
+                    mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
+                    tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
+                    tma_load_2d(sbase + W_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
+                    bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES,
+                              p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
+                    bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES + SF_TILE_BYTES,
+                              p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
+                }
+                return true;
+            });
         }
     } else if (warp == 5) {
         // ================= MMA issue =================
         constexpr uint32_t idesc = make_idesc_nvf4(TILE_N, MMA_N);
         int i = 0, seg = 0;
-        bool ok = true;
-        for (long long u = u0; u < u1 && ok; ++seg) {
-            const int k0 = (int)(u % p.nkt);
-            const long long rem = u1 - u;
-            const int cnt = (int)((p.nkt - k0) < rem ? (p.nkt - k0) : rem);
+        for_each_segment(u0, u1, p.nkt, [&](long long, int cnt) {
             const int buf = seg & 1;
-            if (seg >= 2 && !wait_bar(smem_u32(&ctrl->acc_empty[buf]), ((seg >> 1) - 1) & 1, ctrl, p, ST_ACC_EMPTY, 5)) break;
+            if (seg >= 2 && !wait_bar(smem_u32(&ctrl->acc_empty[buf]), ((seg >> 1) - 1) & 1, ctrl, p, ST_ACC_EMPTY, 5)) return false;
             tc_fence_after_sync();
             for (int j = 0; j < cnt; ++j, ++i) {
                 const int s = i % C::STAGES;
-                if (!wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p, ST_FULL, 5)) { ok = false; break; }
+                if (!wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p, ST_FULL, 5)) return false;
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
@@ -264,11 +285,11 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 }
                 __syncwarp();
             }
-            u += cnt;
-        }
+            ++seg;
+            return true;
+        });
     } else {
         // ================= z stage, expansion, epilogue (128 threads) =================
-        bool ok = true;
         const int Rpad = p.Rpad;
         float* zb = p.zbuf + (size_t)(p.epoch & 1u) * 32 * Rpad;
         if (p.R > 0) {
@@ -323,11 +344,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         bool z_ready = false;
         const float alpha = p.alpha[0];
         int seg = 0;
-        for (long long u = u0; u < u1 && ok; ++seg) {
+        for_each_segment(u0, u1, p.nkt, [&](long long u, int cnt) {
             const int t = (int)(u / p.nkt);
-            const int k0 = (int)(u % p.nkt);
-            const long long rem = u1 - u;
-            const int cnt = (int)((p.nkt - k0) < rem ? (p.nkt - k0) : rem);
             const int buf = seg & 1;
             const bool complete = (cnt == p.nkt);
             const int c_first = sched_cta_of_unit((long long)t * p.nkt, T, p.G);
@@ -342,8 +360,14 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             for (int m = 0; m < MMA_N; ++m) corr[m] = 0.f;
             if (p.R > 0) {
                 if (!z_ready) {
-                    if (tid == 0) wait_counter(p.z_counter, p.epoch * (uint32_t)p.G, ctrl, p, ST_Z);
-                    if (!epi_sync_ok(ctrl)) { ok = false; break; }
+                    if (tid == 0 && wait_counter(p.z_counter, (uint32_t)p.G, ctrl, p, ST_Z)) {
+                        // the last CTA to get here clears both words for the next launch on this scratch
+                        if (atomicAdd(p.z_counter + 1, 1u) == (uint32_t)p.G - 1u) {
+                            p.z_counter[0] = 0u;
+                            p.z_counter[1] = 0u;
+                        }
+                    }
+                    if (!epi_sync_ok(ctrl)) return false;
                     z_ready = true;
                 }
                 const int w0 = (int)((long long)slot * p.Rw / nc);
@@ -351,7 +375,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 const int32_t* ucol = p.Ucol + (size_t)(valid ? n : 0) * p.Rw;
                 for (int w = w0; w < w1; ++w) {
                     const uint32_t uw = valid ? (uint32_t)ucol[w] : 0u;
-#pragma unroll
+#pragma unroll (MMA_N <= 8 ? 8 : 2)
                     for (int b = 0; b < 32; b += 4) {
                         const float s0 = ((uw >> b) & 1u) ? 1.f : -1.f;
                         const float s1 = ((uw >> (b + 1)) & 1u) ? 1.f : -1.f;
@@ -369,8 +393,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             }
 
             // accumulators of this segment
-            if (!wait_bar(smem_u32(&ctrl->acc_full[buf]), (seg >> 1) & 1, ctrl, p, ST_ACC_FULL, warp)) ok = false;
-            if (!epi_sync_ok(ctrl)) { ok = false; break; }
+            wait_bar(smem_u32(&ctrl->acc_full[buf]), (seg >> 1) & 1, ctrl, p, ST_ACC_FULL, warp);
+            if (!epi_sync_ok(ctrl)) return false;
             tc_fence_after_sync();
             float acc[MMA_N];
             tmem_ld_acc<MMA_N>(tmem + ((uint32_t)(warp * 32) << 16) + buf * ACC_COL_STRIDE, acc);
@@ -394,8 +418,9 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             } else {
                 if (!complete) {
                     // finisher: wait for the nc-1 partials of this call, add them in slot order
-                    if (tid == 0) wait_counter(p.tile_cnt + t, p.epoch * (uint32_t)(nc - 1), ctrl, p, ST_TILE);
-                    if (!epi_sync_ok(ctrl)) { ok = false; break; }
+                    if (tid == 0 && wait_counter(p.tile_cnt + t, (uint32_t)(nc - 1), ctrl, p, ST_TILE))
+                        p.tile_cnt[t] = 0u;      // only this CTA reads it; ready for the next launch
+                    if (!epi_sync_ok(ctrl)) return false;
                     for (int sl = 0; sl < nc - 1; ++sl) {
                         const float* P = p.partials + ((size_t)t * p.max_slots + sl) * MMA_N * TILE_N;
 #pragma unroll
@@ -414,8 +439,9 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     }
                 }
             }
-            u += cnt;
-        }
+            ++seg;
+            return true;
+        });
     }
 
     // ---------------- common exit ----------------
@@ -550,6 +576,13 @@ extern "C" size_t biloco_b200_scratch_bytes(int M, int N, int K, int R, int num_
     ScratchLayout L;
     if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
     return L.total;
+}
+
+extern "C" size_t biloco_b200_scratch_head_bytes(int M, int N, int K, int R, int num_sms) {
+    if (num_sms == 0) num_sms = device_sm_count();
+    ScratchLayout L;
+    if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
+    return L.off_z;
 }
 
 extern "C" int biloco_b200_schedule_info(int M, int N, int K, int R, int num_sms, int* out6) {

@@ -84,9 +84,9 @@ class BiLoCoGemm:
     Call with the NVFP4 activation A [1, rows, K/2] uint8 (rows >= M; the reference pads to 128 rows, any
     row count from M to 128 is accepted), its block scales A_sf, and the BF16 activation X [M, K] (the
     low-rank term uses the unquantized activation).
-    The scratch buffer is tagged with the call's epoch (a launch argument), so consecutive calls need no
-    clearing. A CUDA graph bakes the epochs in: call reset() at the start of the captured region so that
-    every replay starts from zeroed scratch and epoch 1.
+    Consecutive calls need no clearing of the scratch buffer: the kernel returns its counters to zero before it
+    exits, so a CUDA graph containing calls can be replayed as is (calling reset() inside the captured region,
+    as the reference requires, stays valid).
     """
 
     def __init__(self, W_fp4, W_sf, alpha, V_packed, U_packed, S, M: int, mode: int = None):
@@ -100,12 +100,15 @@ class BiLoCoGemm:
         self.none = torch.zeros(0, device=dev, dtype=torch.int64)
         with torch.cuda.device(dev):
             nbytes = scratch_bytes(M, self.N, self.K, self.R)
+            self._head = _lib.load().biloco_b200_scratch_head_bytes(M, self.N, self.K, self.R, 0) // 4
         # one buffer holds status words, counters, the z hand-off area and the split-K partial sums
         self.z = torch.zeros(nbytes // 4, device=dev, dtype=torch.float32)
         self.epoch = 0
 
     def reset(self):
-        self.z.zero_()
+        """Clear the status words and counters (needed only after a launch whose status reported a failed wait;
+        harmless otherwise) and restart the epoch count."""
+        self.z[: self._head].zero_()
         self.epoch = 0
 
     def status(self):

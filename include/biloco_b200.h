@@ -81,12 +81,18 @@ int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_
                           void* A_codes, void* A_sf, float* a_gscale, float* alpha_out, const float* w_gscale,
                           int M, int A_rows, int K, int rule, biloco_stream_t stream);
 
-/* Scratch bytes needed by biloco_b200_fused_linear / biloco_b200_fp4_gemm for this problem on a device
+/* Scratch bytes needed by biloco_b200_fused_linear for this problem on a device
  * with `num_sms` multiprocessors (0 = query the current device). The scratch must be zero-filled once
- * before the first call (epoch 1) and whenever the epoch sequence restarts; it is never cleared between
- * calls (the reference's BiLoCoGemm owns z/flags/corr/cnt buffers the same way, biloco/kernel.py:98-119).
- * Returns 0 for an unsupported shape. Host-only arithmetic unless num_sms == 0. */
+ * before the first call; it needs no clearing between calls (the reference's BiLoCoGemm owns z/flags/corr/cnt
+ * buffers the same way, biloco/kernel.py:98-119). Its first biloco_b200_scratch_head_bytes() bytes hold the
+ * status words and counters: zero those again after a call whose status word reported a wait that ran out.
+ * Calls that share a scratch must not overlap on the device. Returns 0 for an unsupported shape. Host-only
+ * arithmetic unless num_sms == 0. */
 size_t biloco_b200_scratch_bytes(int M, int N, int K, int R, int num_sms);
+
+/* Bytes at the start of the scratch that hold status words and counters (what BiLoCoGemm.reset() clears,
+ * biloco/kernel.py:115-119). */
+size_t biloco_b200_scratch_head_bytes(int M, int N, int K, int R, int num_sms);
 
 /* Work split the fused kernel will use for this problem: out[0] = 128-row tiles, out[1] = 256-wide k-tiles,
  * out[2] = CTAs launched, out[3] = partial-sum slots per tile, out[4] = MMA N (8/16/32), out[5] = pipeline
@@ -100,7 +106,8 @@ int biloco_b200_schedule_info(int M, int N, int K, int R, int num_sms, int* out6
  * [A_rows,K/2] (A_rows >= M; rows beyond M are ignored), A_sf E4M3 (atom layout), X bf16 [M,K],
  * V_packed u8 [R,K/8], U_col32 int32 [N, ceil(R/32)], S bf16 [R], Y bf16 [M,N] (row stride N).
  * R == 0 skips the low-rank term (X, V, U, S may then be NULL). C_bf16 (may be NULL): bf16 [M,N] added
- * before the final rounding. `epoch` starts at 1 and increases by 1 per call on the same scratch.
+ * before the final rounding. `epoch` (>= 1) is the caller's launch count on this scratch (recorded in the status
+ * words when a wait gives up, and selecting one of two z buffers).
  * Shapes: 1 <= M <= 32, K % 256 == 0, N % 8 == 0. 16-byte alignment for W_codes, A_codes, W_sf, A_sf, X.
  * Device-side waits are bounded; a wait that ran out leaves a non-zero code in the first int32 of scratch
  * (read it with biloco_b200_read_status) and the call's output is undefined.

@@ -1,0 +1,164 @@
+"""GPU parity: every operator, called through the C ABI (via torch.ops.biloco / biloco_b200.kernel), against the CPU
+oracle on the same seeded inputs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import biloco_oracle as orc
+from tests.gpu_util import check_against_exact, check_against_unfused, dev_problem, oracle_outputs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def kernel():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    from biloco_b200 import kernel as k
+    return k
+
+
+@pytest.mark.parametrize("M,K,R", [(1, 64, 8), (3, 256, 20), (2, 5120, 512), (32, 1024, 64), (1, 72, 5)])
+def test_binary_z(kernel, M, K, R):
+    p = orc.random_problem(M, K, 128, R, seed=100 + M + R)
+    t = dev_problem(p)
+    z = kernel.ops.binary_z_reference(t["X"], t["V_packed"], t["S"]).cpu().numpy()
+    want = orc.binary_z(p["X"], p["V_packed"], p["S"])
+    assert z.shape == (M, R)
+    tol = 1e-5 * np.abs(p["S"])[None, :] * np.sum(np.abs(p["X"]), axis=1, keepdims=True) + 1e-12
+    assert np.all(np.abs(z - want) <= tol)
+
+
+@pytest.mark.parametrize("M,N,R", [(1, 128, 8), (3, 264, 40), (2, 5120, 512), (32, 1024, 64)])
+def test_binary_expand_and_u_col32(kernel, M, N, R):
+    p = orc.random_problem(M, 64, N, R, seed=200 + M + R)
+    t = dev_problem(p)
+    z = orc.binary_z(p["X"], p["V_packed"], p["S"])
+    Y = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    kernel.ops.binary_expand_reference(torch.from_numpy(z).cuda(), t["U_packed"], Y)
+    want = orc.binary_expand(z, p["U_packed"], True)
+    exact = orc.binary_expand(z, p["U_packed"], False)
+    y = Y.float().cpu().numpy()
+    # one bf16 ulp of slack for fp32 summation order at rounding boundaries
+    assert np.all(np.abs(y - want) <= 2.0 ** -7 * np.abs(exact) + 1e-6 * np.sum(np.abs(z), axis=1, keepdims=True))
+    col = kernel.pack_u_col32(t["U_packed"], N, R).cpu().numpy()
+    assert np.array_equal(col, orc.pack_u_col32(p["U_packed"], N, R))
+
+
+@pytest.mark.parametrize("rule", ["mse", "static_6", "static_4"])
+@pytest.mark.parametrize("M,K,rows,smooth", [(1, 5120, 128, False), (5, 256, 5, True), (32, 2560, 32, True), (8, 1024, 8, False)])
+def test_act_quant_bit_exact(kernel, rule, M, K, rows, smooth):
+    from biloco_b200 import fp4
+    rng = np.random.default_rng(1000 * M + K)
+    x = orc.bf16_round(rng.standard_normal((M, K)))
+    idx = rng.permutation(K)[: max(1, K // 100)]
+    x[:, idx] *= 20                                   # 1 % outlier channels x20
+    x = orc.bf16_round(x)
+    if M > 2:
+        x[1, :32] = 0.0                               # two all-zero blocks
+    s = orc.bf16_round(rng.random(K) * 3 + 0.25) if smooth else None
+    xs = orc.bf16_round(x / s) if smooth else x
+    codes, sf, gs = orc.nvfp4_quantize(xs, rule)
+    wg = torch.tensor([0.0123], device="cuda")
+    out = fp4.quantize_activation(torch.from_numpy(x).cuda().to(torch.bfloat16), rule,
+                                  smooth=torch.from_numpy(s).cuda().to(torch.bfloat16) if smooth else None,
+                                  w_gscale=wg, rows=rows)
+    assert np.float32(out["gscale"].item()) == gs
+    assert np.float32(out["alpha"].item()) == np.float32(np.float32(0.0123) * gs)
+    A = out["A"].cpu().numpy()[0]
+    assert np.array_equal(A[:M], codes) and not A[M:].any()
+    sf_dev = out["A_sf"].view(torch.uint8).cpu().numpy()
+    want_sf = np.zeros(orc.nvfp4_sf_bytes(rows, K), np.uint8)
+    want_sf[: orc.nvfp4_sf_bytes(M, K)] = orc.sf_swizzle(sf, K) if M <= 128 else 0
+    assert np.array_equal(sf_dev, want_sf)
+    if smooth:
+        assert np.array_equal(out["X"].float().cpu().numpy(), xs)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 128, 256), (4, 256, 1024), (3, 136, 512)])
+def test_fp4_gemm_simt(kernel, lib, M, N, K):
+    p = orc.random_problem(M, K, N, 8, scales="random", seed=7)
+    t = dev_problem(p)
+    D = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    rc = lib.biloco_b200_fp4_gemm_simt(t["A_pad"].data_ptr(), t["A_sf"].data_ptr(), t["W"].data_ptr(), t["W_sf"].data_ptr(),
+                                       t["alpha"].data_ptr(), None, D.data_ptr(), M, N, K, torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    want = orc.fp4_gemm(p["A_pad"], p["A_sf"], p["W"], p["W_sf"], 1.0, M=M)
+    check_against_unfused(D.float().cpu().numpy(), want, "simt gemm")
+
+
+# --- tensor-core GEMM alone (R = 0): single unit, several k-tiles split over CTAs, several tiles, ragged N ---
+@pytest.mark.parametrize("M,N,K", [(1, 128, 256), (1, 128, 512), (1, 256, 256), (4, 256, 1024), (8, 136, 768),
+                                   (16, 384, 2048), (32, 1024, 1024), (2, 2560, 9728)])
+def test_fp4_gemm_tensor_core(kernel, M, N, K):
+    p = orc.random_problem(M, K, N, 8, scales="random", seed=31 * M + N)
+    t = dev_problem(p)
+    alpha = torch.tensor([0.25], device="cuda")
+    for it in range(2):
+        D = kernel.ops.fp4_gemm(t["A"], t["W"], t["A_sf"], t["W_sf"], alpha)
+        assert D.shape == (1, M, N)
+        y = D.view(-1, N)[:M].float().cpu().numpy()
+        want = orc.fp4_gemm(p["A"], p["A_sf"], p["W"], p["W_sf"], 0.25, M=M)
+        exact = 0.25 * orc.fp4_gemm_acc(p["A"], p["A_sf"], p["W"], p["W_sf"], M=M)
+        check_against_unfused(y, want, f"fp4_gemm call {it}")
+        check_against_exact(y, exact, f"fp4_gemm call {it}")
+
+
+def test_fp4_gemm_residual_and_padded_rows(kernel):
+    M, N, K = 5, 256, 512
+    p = orc.random_problem(M, K, N, 8, scales="random", seed=77)
+    t = dev_problem(p)
+    C = orc.bf16_round(np.random.default_rng(0).standard_normal((M, N)) * 10)
+    D = kernel.ops.fp4_gemm_residual(t["A"], t["W"], t["A_sf"], t["W_sf"], t["alpha"], torch.from_numpy(C).cuda().to(torch.bfloat16))
+    want = orc.fp4_gemm(p["A"], p["A_sf"], p["W"], p["W_sf"], 1.0, C=C, M=M)
+    check_against_unfused(D.view(-1, N).float().cpu().numpy(), want, "residual")
+    # the reference's FP4-only baseline passes the activation zero-padded to 128 rows
+    D = kernel.ops.fp4_gemm_n64(t["A_pad"], t["W"], t["A_sf"], t["W_sf"], t["alpha"])
+    assert D.shape == (1, 128, N)
+    y = D.view(-1, N).float().cpu().numpy()
+    check_against_unfused(y[:M], orc.fp4_gemm(p["A"], p["A_sf"], p["W"], p["W_sf"], 1.0, M=M), "padded")
+    assert not y[M:].any()
+
+
+def _run_fused(kernel, p, M, N, launches=5):
+    t = dev_problem(p)
+    y_ref, y_exact = oracle_outputs(p, M)
+    # the unfused device path agrees with the oracle's unfused composition
+    y_unf = kernel.reference(t["A"], t["A_sf"], t["W"], t["W_sf"], t["alpha"], t["X"], t["V_packed"], t["U_packed"], t["S"])
+    check_against_unfused(y_unf.view(-1, N)[:M].float().cpu().numpy(), y_ref, "unfused device path")
+    R = p["V_packed"].shape[0]
+    for mode in kernel.modes_for(M, R, p["X"].shape[1]):
+        g = kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M, mode=mode)
+        for it in range(launches):                 # consecutive launches reuse the epoch-tagged scratch
+            y = g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].float()
+            torch.cuda.synchronize()
+            y = y.cpu().numpy()
+            check_against_unfused(y, y_ref, f"mode {mode} launch {it}")
+            check_against_exact(y, y_exact, f"mode {mode} launch {it}")
+        assert g.status()[0] == 0, f"device-side wait ran out: {g.status()[:4]}"
+        g.reset()
+        y = g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].float().cpu().numpy()
+        check_against_unfused(y, y_ref, f"mode {mode} after reset")
+
+
+@pytest.mark.parametrize("M,N,K,R", [(1, 128, 256, 32), (1, 256, 512, 16), (2, 384, 1024, 40), (8, 1024, 2560, 128),
+                                     (32, 640, 768, 64), (16, 136, 256, 256)])
+def test_fused_small_shapes_random_scales(kernel, M, N, K, R):
+    _run_fused(kernel, orc.random_problem(M, K, N, R, scales="random", seed=M * 7 + R), M, N)
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32])
+@pytest.mark.parametrize("r", [16, 32, 64, 128, 256, 512, 1024])
+def test_fused_reference_protocol(kernel, M, r):
+    """tests/run_tests.py:33-45 of the reference: K = N = 5120, zero block scales (isolates the low-rank term),
+    five consecutive launches per mode."""
+    _run_fused(kernel, orc.random_problem(M, 5120, 5120, r), M, 5120)
+
+
+@pytest.mark.parametrize("M,r", [(1, 512), (8, 128), (32, 512)])
+def test_fused_full_size_random_scales(kernel, M, r):
+    _run_fused(kernel, orc.random_problem(M, 5120, 5120, r, scales="random", seed=1000 * M + r), M, 5120, launches=2)
+
+
+@pytest.mark.parametrize("K,N", [(5120, 1024), (2560, 9728), (9728, 2560)])
+def test_fused_other_layer_shapes(kernel, K, N):
+    _run_fused(kernel, orc.random_problem(2, K, N, 256, scales="random", seed=K + N), 2, N, launches=2)

@@ -99,6 +99,14 @@ def test_layer_forward_matches_reference_layer(golden):
     assert np.linalg.norm(y - ref) <= 2e-3 * np.linalg.norm(ref)
 
 
+def test_torch_layer_matches_reference_layer(golden):
+    """The timed CPU baseline (torch bf16 matmuls) is the same computation."""
+    layer = orc.TorchLayer(golden["layer_smooth"], golden["layer_V_scaled"], golden["layer_U_T"], golden["layer_weight_fp4"],
+                           golden["layer_bias"], "mse")
+    y, ref = layer(golden["layer_x"]), golden["layer_y"]
+    assert np.max(np.abs(y - ref)) <= 2.0 ** -7 * np.max(np.abs(ref))
+
+
 def test_unfused_vs_exact_composition():
     p = orc.random_problem(3, 512, 256, 64, scales="random", seed=5)
     a = (p["A_pad"], p["A_sf"], p["W"], p["W_sf"], 0.37, p["X"], p["V_packed"], p["U_packed"], p["S"])
