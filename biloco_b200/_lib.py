@@ -27,6 +27,7 @@ SIGNATURES = {
     "biloco_b200_scratch_head_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "biloco_b200_schedule_info": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "biloco_b200_fused_linear": (_i, [_vp] * 12 + [_sz] + [_i] * 7 + [_vp]),
+    "biloco_b200_debug_stamps": (_i, [_vp, _sz]),
     "biloco_b200_read_status": (_i, [_vp, ctypes.POINTER(ctypes.c_int32), _vp]),
     "biloco_b200_fp4_gemm_simt": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
 }

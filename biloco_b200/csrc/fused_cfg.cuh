@@ -1,0 +1,177 @@
+// Configuration, parameter block, shared-memory control block and bounded-wait helpers of the fused linear.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "schedule.h"
+
+namespace biloco {
+
+constexpr int TILE_N = 128;                      // weight rows per tile = MMA M
+constexpr int KT = 256;                          // K elements per k-tile
+constexpr int KT_BYTES = KT / 2;                 // 128 B of codes per row = one 128-byte swizzle row
+constexpr int W_TILE_BYTES = TILE_N * KT_BYTES;  // 16384
+constexpr int SF_TILE_BYTES = 4 * 512;           // four 128x4 atoms
+constexpr int EPI_THREADS = 128;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 128;
+constexpr int ACC_COL_STRIDE = 32;               // accumulator buffer b starts at column 32*b
+constexpr int SFA_COL = 64;                      // 16 columns: 4 MMAs x 4
+constexpr int SFB_COL = 80;                      // 16 columns
+constexpr int CTRL_BYTES = 1024;
+constexpr int SMEM_BUDGET = 227 * 1024;
+constexpr uint64_t WAIT_BUDGET_NS = 200ull * 1000 * 1000;   // 200 ms per wait
+
+// CUDA-core work area in shared memory. During the z stage it holds a tile of the bf16 activation (XT_BYTES,
+// 16-byte chunks transposed so that a warp reads consecutive chunks) and the sign words of up to VT_RANKS ranks;
+// afterwards the same bytes hold the z values being expanded (ROWS x ZS_STRIDE floats).
+constexpr int XT_BYTES = 16384;
+constexpr int VT_RANKS = 8;
+constexpr int VT_BYTES = VT_RANKS * (XT_BYTES / 2 / 8);   // one bit per k of the widest activation tile (1 row)
+constexpr int WORK_BYTES = XT_BYTES + VT_BYTES;           // 24 KB
+constexpr int ZS_WORDS = 4;                      // rank words (32 ranks each) of z staged at a time
+constexpr int ZS_STRIDE = ZS_WORDS * 32 + 4;     // floats per staged row (+4: rows start in different banks)
+constexpr int STAMP_WORDS = 8;                   // uint64 time stamps per CTA when debug stamps are on
+static_assert(32 * ZS_STRIDE * 4 <= WORK_BYTES, "z staging must fit in the work area");
+
+template <int MMA_N>
+struct Cfg {
+    static constexpr int A_TILE_BYTES = MMA_N * KT_BYTES;
+    static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES + 2 * SF_TILE_BYTES;
+    static constexpr int STAGES = (SMEM_BUDGET - 1024 - CTRL_BYTES - WORK_BYTES) / STAGE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + CTRL_BYTES + WORK_BYTES;
+    static_assert(STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned for the 128-byte swizzle");
+    static_assert(STAGES >= 4 && STAGES <= 16, "stage count out of range");
+};
+
+struct FusedParams {
+    const uint8_t* W_sf;
+    const uint8_t* A_sf;
+    const float* alpha;
+    const __nv_bfloat16* X;
+    const uint8_t* Vp;
+    const int32_t* Ucol;
+    const __nv_bfloat16* S;
+    const __nv_bfloat16* C;
+    __nv_bfloat16* Y;
+    int32_t* status;
+    uint32_t* z_counter;      // [0] arrivals of z producers, [1] consumers that have seen it complete
+    uint32_t* tile_cnt;
+    float* zbuf;
+    float* partials;
+    int M, N, K, R, Rw, Rpad;
+    int ntile, nkt, G, max_slots;
+    uint32_t epoch;
+    int mode;
+    unsigned long long* stamps;   // debug: STAMP_WORDS %globaltimer values per CTA, or null
+};
+
+struct Ctrl {   // lives in shared memory after the stages
+    uint64_t full[16];
+    uint64_t empty[16];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    volatile int abort;
+};
+static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
+
+enum : int {   // status codes of waits that ran out
+    ST_EMPTY = 101, ST_FULL = 102, ST_ACC_EMPTY = 103, ST_ACC_FULL = 104, ST_Z = 105, ST_TILE = 106,
+};
+
+// The wait helpers are deliberately not inlined: the kernel's machine code is executed once, cold, per CTA, and
+// every kilobyte of it is an instruction fetch queued behind the weight stream.
+
+// Record the first failure and raise the CTA-wide abort flag.
+__device__ __noinline__ void fail(Ctrl* ctrl, int32_t* status, uint32_t epoch, int code, int role) {
+    ctrl->abort = 1;
+    if (atomicCAS(status, 0, code) == 0) {
+        status[1] = (int)blockIdx.x;
+        status[2] = (int)epoch;
+        status[3] = role;
+    }
+}
+
+// Bounded mbarrier wait. Returns false when the budget ran out or another role aborted.
+__device__ __noinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl* ctrl, int32_t* status, uint32_t epoch, int code,
+                                      int role) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 31u) == 31u) {
+            if (ctrl->abort) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, status, epoch, code, role); return false; }
+        }
+    }
+}
+
+// Bounded wait until *ctr >= target (acquire). One thread calls this.
+__device__ __noinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, Ctrl* ctrl, int32_t* status, uint32_t epoch,
+                                          int code) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if ((int32_t)(ld_acquire_u32(ctr) - target) >= 0) return true;
+        if ((it & 31u) == 31u) {
+            if (ctrl->abort) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, status, epoch, code, 0); return false; }
+        }
+    }
+}
+
+// Barrier over the 128 epilogue threads followed by a uniform look at the abort flag.
+__device__ __forceinline__ bool epi_sync_ok(Ctrl* ctrl) {
+    named_bar_sync(1, EPI_THREADS);
+    return ctrl->abort == 0;
+}
+
+__device__ __forceinline__ float signed_by_bit(float x, uint32_t word, int j) {
+    return __uint_as_float(__float_as_uint(x) ^ (((~word >> j) & 1u) << 31));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_wait_all() {
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// One segment = a maximal run of units inside one tile. SegWalk yields the segments of the unit range [u0, u1) in
+// PROCESSING order: a range that ends inside a tile has a "head" segment whose tile is finished by a later CTA, and
+// it goes first, so that its partial sum is published before this CTA starts waiting for the partials of the tile
+// it finishes itself. (In natural order CTA c would publish for tile t+1 only after finishing tile t, which waits
+// for CTA c-1, which waits for CTA c-2, ...: a chain through every CTA of the grid.)
+struct SegWalk {
+    int u0, head, u1, u;
+    int nkt;
+    bool in_head;
+    __device__ __forceinline__ SegWalk(int a, int b, int nkt_) : u0(a), u1(b), nkt(nkt_) {
+        const int rem = (int)((unsigned)b % (unsigned)nkt_);
+        head = (rem != 0 && b - rem > a) ? (b - rem) : b;   // == u1: no separate head segment
+        in_head = head < b;
+        u = in_head ? head : a;
+    }
+    __device__ __forceinline__ bool done() const { return !in_head && u >= head; }
+    // current segment: first unit and number of units
+    __device__ __forceinline__ int first() const { return u; }
+    __device__ __forceinline__ int count() const {
+        const int left = (in_head ? u1 : head) - u;
+        const int in_tile = nkt - (int)((unsigned)u % (unsigned)nkt);
+        return in_tile < left ? in_tile : left;
+    }
+    __device__ __forceinline__ void next() {
+        if (in_head) { in_head = false; u = u0; }
+        else u += count();
+    }
+};
+
+}  // namespace biloco

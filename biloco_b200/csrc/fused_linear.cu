@@ -10,7 +10,7 @@
 //    the activation and only M output rows are written.
 //  * Work unit = (128-row tile t, 256-wide k-tile kt): 16 KB of E2M1 codes + 2 KB of E4M3 scales. The
 //    T = ntile * nkt units are split evenly over all CTAs (one per SM) as contiguous ranges in (t, kt)
-//    order ("stream-K"), so every SM streams the same number of weight bytes whatever N is.
+//    order ("stream-K", schedule.h), so every SM streams the same number of weight bytes whatever N is.
 //  * Warp roles (192 threads): warps 0-3 = z stage, U expansion and epilogue (thread = TMEM lane = weight row);
 //    warp 4 = TMA producer; warp 5 = TMEM allocation + MMA issue.
 //  * Per stage: W codes by a 2-D TMA tile (128 rows x 128 B, 128-byte swizzle), activation codes by a 2-D TMA
@@ -22,13 +22,18 @@
 //    counter; the finisher adds them in slot order (deterministic), rounds and stores.
 //  * Low-rank term: at entry every CTA computes a slice of the ranks of z (all M rows) on CUDA cores from the
 //    bit-packed V and publishes it in scratch; an arrival counter (mode 2) tells the consumers that z is
-//    complete. Counters return to zero inside the launch (the finisher of a tile clears its counter, the last
-//    CTA past the z wait clears the z words), so launches on one scratch need no clearing in between and a
-//    captured CUDA graph can be replayed; launches that share a scratch must not overlap. Each contributor of a tile expands z through the packed U signs for its share of the rank words
+//    complete. Each contributor of a tile expands z through the packed U signs for its share of the rank words
 //    while its weight loads are in flight, and adds the result to the accumulators read back from TMEM.
+//    Counters return to zero inside the launch (the finisher of a tile clears its counter, the last CTA past
+//    the z wait clears the z words), so launches on one scratch need no clearing in between and a captured
+//    CUDA graph can be replayed; launches that share a scratch must not overlap.
 //  * Every wait (mbarrier, counter) is bounded by a %globaltimer budget; a wait that runs out records a code in
 //    the status words of the scratch, raises a CTA-wide abort flag, and the CTA leaves through the common exit
 //    (TMEM freed) instead of hanging.
+//  * The machine code is kept small on purpose (rolled loops, non-inlined wait helpers, one instantiation per
+//    row count): each CTA runs it once, cold, and instruction fetches queue behind the weight stream.
+//
+// Device code: fused_cfg.cuh (configuration, waits), fused_lowrank.cuh (z stage, expansion), fused_kernel.cuh.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -38,426 +43,9 @@
 #include <unordered_map>
 
 #include "../../include/biloco_b200.h"
-#include "ptx.cuh"
-#include "schedule.h"
+#include "fused_kernel.cuh"
 
 namespace biloco {
-
-constexpr int TILE_N = 128;                      // weight rows per tile = MMA M
-constexpr int KT = 256;                          // K elements per k-tile
-constexpr int KT_BYTES = KT / 2;                 // 128 B of codes per row = one 128-byte swizzle row
-constexpr int W_TILE_BYTES = TILE_N * KT_BYTES;  // 16384
-constexpr int SF_TILE_BYTES = 4 * 512;           // four 128x4 atoms
-constexpr int EPI_THREADS = 128;
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 128;
-constexpr int ACC_COL_STRIDE = 32;               // accumulator buffer b starts at column 32*b
-constexpr int SFA_COL = 64;                      // 16 columns: 4 MMAs x 4
-constexpr int SFB_COL = 80;                      // 16 columns
-constexpr int CTRL_BYTES = 1024;
-constexpr int SMEM_BUDGET = 227 * 1024;
-constexpr uint64_t WAIT_BUDGET_NS = 200ull * 1000 * 1000;   // 200 ms per wait
-constexpr int Z_CHUNK = 8;                       // ranks processed together in the z stage
-
-template <int MMA_N>
-struct Cfg {
-    static constexpr int A_TILE_BYTES = MMA_N * KT_BYTES;
-    static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES + 2 * SF_TILE_BYTES;
-    static constexpr int STAGES = (SMEM_BUDGET - 1024 - CTRL_BYTES) / STAGE_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + CTRL_BYTES;
-    static_assert(STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned for the 128-byte swizzle");
-    static_assert(STAGES >= 4, "too few stages");
-};
-
-struct FusedParams {
-    const uint8_t* W_sf;
-    const uint8_t* A_sf;
-    const float* alpha;
-    const __nv_bfloat16* X;
-    const uint8_t* Vp;
-    const int32_t* Ucol;
-    const __nv_bfloat16* S;
-    const __nv_bfloat16* C;
-    __nv_bfloat16* Y;
-    int32_t* status;
-    uint32_t* z_counter;      // [0] arrivals of z producers, [1] consumers that have seen it complete
-    uint32_t* tile_cnt;
-    float* zbuf;
-    float* partials;
-    int M, N, K, R, Rw, Rpad;
-    int ntile, nkt, G, max_slots;
-    uint32_t epoch;
-    int mode;
-};
-
-struct Ctrl {   // lives in shared memory after the stages
-    uint64_t full[16];
-    uint64_t empty[16];
-    uint64_t acc_full[2];
-    uint64_t acc_empty[2];
-    uint32_t tmem_base;
-    volatile int abort;
-    float red[4][Z_CHUNK];
-};
-static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
-
-// Record the first failure and raise the CTA-wide abort flag.
-__device__ __forceinline__ void fail(Ctrl* ctrl, const FusedParams& p, int code, int role) {
-    ctrl->abort = 1;
-    if (atomicCAS(p.status, 0, code) == 0) {
-        p.status[1] = (int)blockIdx.x;
-        p.status[2] = (int)p.epoch;
-        p.status[3] = role;
-    }
-}
-
-// Bounded mbarrier wait. Returns false when the budget ran out or another role aborted.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl* ctrl, const FusedParams& p, int code, int role) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 31u) == 31u) {
-            if (ctrl->abort) return false;
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, p, code, role); return false; }
-        }
-    }
-}
-
-// Bounded wait until *ctr >= target (acquire). One thread calls this.
-__device__ __forceinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, Ctrl* ctrl, const FusedParams& p, int code) {
-    uint64_t t0 = 0;
-    for (uint32_t it = 0;; ++it) {
-        if ((int32_t)(ld_acquire_u32(ctr) - target) >= 0) return true;
-        if ((it & 31u) == 31u) {
-            if (ctrl->abort) return false;
-            const uint64_t now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, p, code, 0); return false; }
-        }
-    }
-}
-
-// Barrier over the 128 epilogue threads followed by a uniform look at the abort flag.
-__device__ __forceinline__ bool epi_sync_ok(Ctrl* ctrl) {
-    named_bar_sync(1, EPI_THREADS);
-    return ctrl->abort == 0;
-}
-
-__device__ __forceinline__ float signed_by_bit(float x, uint32_t word, int j) {
-    return __uint_as_float(__float_as_uint(x) ^ (((~word >> j) & 1u) << 31));
-}
-
-template <int MMA_N>
-__device__ __forceinline__ void tmem_ld_acc(uint32_t taddr, float* v) {
-    if constexpr (MMA_N == 8) {
-        tmem_ld_x8(taddr, v);
-    } else if constexpr (MMA_N == 16) {
-        tmem_ld_x16(taddr, v);
-    } else {
-        tmem_ld_x16(taddr, v);
-        tmem_ld_x16(taddr + 16, v + 16);
-    }
-}
-
-// Segments (maximal runs of units inside one tile) of the unit range [u0, u1), in PROCESSING order.
-// A range that ends inside a tile has a "head" segment whose tile is finished by a later CTA. It goes first:
-// its partial sum is then published before this CTA starts waiting for the partials of the tile it finishes
-// itself. (In natural order CTA c would publish for tile t+1 only after finishing tile t, which waits for CTA
-// c-1, which waits for CTA c-2, ...: a chain through every CTA of the grid.)
-// f(u_start, count) returns false to stop.
-template <class F>
-__device__ __forceinline__ void for_each_segment(long long u0, long long u1, int nkt, F&& f) {
-    const long long rem = u1 % nkt;
-    const long long head = (rem != 0 && u1 - rem > u0) ? (u1 - rem) : u1;   // == u1: no separate head segment
-    if (head < u1 && !f(head, (int)(u1 - head))) return;
-    for (long long u = u0; u < head;) {
-        const long long left = head - u;
-        const int in_tile = nkt - (int)(u % nkt);
-        const int cnt = (int)(in_tile < left ? in_tile : left);
-        if (!f(u, cnt)) return;
-        u += cnt;
-    }
-}
-
-enum : int {   // status codes of waits that ran out
-    ST_EMPTY = 101, ST_FULL = 102, ST_ACC_EMPTY = 103, ST_ACC_FULL = 104, ST_Z = 105, ST_TILE = 106,
-};
-
-template <int MMA_N>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA, const FusedParams p) {
-    using C = Cfg<MMA_N>;
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t stage0 = (raw + 1023u) & ~1023u;                 // shared-window address of stage 0
-    Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem_raw + (stage0 - raw) + C::STAGES * C::STAGE_BYTES);
-
-    const int tid = threadIdx.x;
-    const int warp = tid >> 5;
-    const int lane = tid & 31;
-    const int cta = blockIdx.x;
-
-    const long long T = (long long)p.ntile * p.nkt;
-    const long long u0 = sched_first_unit(cta, T, p.G);
-    const long long u1 = sched_first_unit(cta + 1, T, p.G);
-
-    // ---------------- set-up ----------------
-    if (tid == 128) {
-        for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->full[s]), 1);
-            mbar_init(smem_u32(&ctrl->empty[s]), 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
-            mbar_init(smem_u32(&ctrl->acc_empty[b]), EPI_THREADS);
-        }
-        ctrl->abort = 0;
-        fence_mbar_init();
-        prefetch_tmap(&tmW);
-        prefetch_tmap(&tmA);
-    }
-    if (warp == 5) {
-        tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
-        tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const uint32_t tmem = ctrl->tmem_base;
-
-    if (warp == 4) {
-        // ================= TMA producer =================
-        if (lane == 0) {
-            int i = 0;
-            for_each_segment(u0, u1, p.nkt, [&](long long us, int cnt) {
-                for (long long u = us; u < us + cnt; ++u, ++i) {
-                    const int s = i % C::STAGES;
-                    const int use = i / C::STAGES;
-                    if (use > 0 && !wait_bar(smem_u32(&ctrl->empty[s]), (use - 1) & 1, ctrl, p, ST_EMPTY, 4)) return false;
-                    const int t = (int)(u / p.nkt);
-                    const int kt = (int)(u % p.nkt);
-                    const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
-                    const uint32_t bar = smem_u32(&ctrl->full[s]);
-                    mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
-                    tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
-                    tma_load_2d(sbase + W_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
-                    bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES,
-                              p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
-                    bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES + SF_TILE_BYTES,
-                              p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
-                }
-                return true;
-            });
-        }
-    } else if (warp == 5) {
-        // ================= MMA issue =================
-        constexpr uint32_t idesc = make_idesc_nvf4(TILE_N, MMA_N);
-        int i = 0, seg = 0;
-        for_each_segment(u0, u1, p.nkt, [&](long long, int cnt) {
-            const int buf = seg & 1;
-            if (seg >= 2 && !wait_bar(smem_u32(&ctrl->acc_empty[buf]), ((seg >> 1) - 1) & 1, ctrl, p, ST_ACC_EMPTY, 5)) return false;
-            tc_fence_after_sync();
-            for (int j = 0; j < cnt; ++j, ++i) {
-                const int s = i % C::STAGES;
-                if (!wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p, ST_FULL, 5)) return false;
-                tc_fence_after_sync();
-                if (lane == 0) {
-                    const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
-                    const uint32_t wsf = sbase + W_TILE_BYTES + C::A_TILE_BYTES;
-                    const uint32_t asf = wsf + SF_TILE_BYTES;
-#pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        tc_cp_32x128b_warpx4(tmem + SFA_COL + 4 * a, make_smem_desc(wsf + 512 * a, 128, 0));
-                        tc_cp_32x128b_warpx4(tmem + SFB_COL + 4 * a, make_smem_desc(asf + 512 * a, 128, 0));
-                    }
-                    const uint64_t wdesc = make_smem_desc(sbase, 1024, 2);
-                    const uint64_t adesc = make_smem_desc(sbase + W_TILE_BYTES, 1024, 2);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        // 64 K-elements = 32 B further along the swizzled row: +2 in the (address >> 4) field
-                        tc_mma_nvf4(tmem + buf * ACC_COL_STRIDE, wdesc + 2 * k, adesc + 2 * k, idesc,
-                                    tmem + SFA_COL + 4 * k, tmem + SFB_COL + 4 * k, (j > 0 || k > 0) ? 1u : 0u);
-                    }
-                    tc_commit(smem_u32(&ctrl->empty[s]));
-                    if (j == cnt - 1) tc_commit(smem_u32(&ctrl->acc_full[buf]));
-                }
-                __syncwarp();
-            }
-            ++seg;
-            return true;
-        });
-    } else {
-        // ================= z stage, expansion, epilogue (128 threads) =================
-        const int Rpad = p.Rpad;
-        float* zb = p.zbuf + (size_t)(p.epoch & 1u) * 32 * Rpad;
-        if (p.R > 0) {
-            const int i0 = (int)((long long)cta * p.R / p.G);
-            const int i1 = (int)((long long)(cta + 1) * p.R / p.G);
-            const int kbytes = p.K >> 3;
-            for (int ic = i0; ic < i1; ic += Z_CHUNK) {
-                const int nr = (i1 - ic) < Z_CHUNK ? (i1 - ic) : Z_CHUNK;
-                for (int m = 0; m < p.M; ++m) {
-                    float acc[Z_CHUNK];
-#pragma unroll
-                    for (int q = 0; q < Z_CHUNK; ++q) acc[q] = 0.f;
-                    const __nv_bfloat16* xrow = p.X + (size_t)m * p.K;
-                    for (int kb = tid; kb < kbytes; kb += EPI_THREADS) {
-                        const uint4 xp = *reinterpret_cast<const uint4*>(xrow + kb * 8);
-                        const uint32_t xw[4] = {xp.x, xp.y, xp.z, xp.w};
-                        float xf[8];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            xf[2 * e] = __uint_as_float(xw[e] << 16);
-                            xf[2 * e + 1] = __uint_as_float(xw[e] & 0xFFFF0000u);
-                        }
-#pragma unroll
-                        for (int q = 0; q < Z_CHUNK; ++q) {
-                            if (q < nr) {
-                                const uint32_t vb = p.Vp[(size_t)(ic + q) * kbytes + kb];
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) acc[q] += signed_by_bit(xf[j], vb, j);
-                            }
-                        }
-                    }
-#pragma unroll
-                    for (int q = 0; q < Z_CHUNK; ++q) {
-                        float v = acc[q];
-#pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                        if (lane == 0) ctrl->red[warp][q] = v;
-                    }
-                    named_bar_sync(1, EPI_THREADS);
-                    if (tid < nr) {
-                        const float v = (ctrl->red[0][tid] + ctrl->red[1][tid]) + (ctrl->red[2][tid] + ctrl->red[3][tid]);
-                        zb[(size_t)m * Rpad + ic + tid] = v * __bfloat162float(p.S[ic + tid]);
-                    }
-                    named_bar_sync(1, EPI_THREADS);
-                }
-            }
-            __threadfence();
-            named_bar_sync(1, EPI_THREADS);
-            if (tid == 0) red_release_add_u32(p.z_counter, 1u);
-        }
-
-        bool z_ready = false;
-        const float alpha = p.alpha[0];
-        int seg = 0;
-        for_each_segment(u0, u1, p.nkt, [&](long long u, int cnt) {
-            const int t = (int)(u / p.nkt);
-            const int buf = seg & 1;
-            const bool complete = (cnt == p.nkt);
-            const int c_first = sched_cta_of_unit((long long)t * p.nkt, T, p.G);
-            const int c_last = sched_cta_of_unit((long long)t * p.nkt + p.nkt - 1, T, p.G);
-            const int nc = c_last - c_first + 1;
-            const int slot = cta - c_first;
-            const int n = t * TILE_N + tid;
-            const bool valid = n < p.N;
-
-            float corr[MMA_N];
-#pragma unroll
-            for (int m = 0; m < MMA_N; ++m) corr[m] = 0.f;
-            if (p.R > 0) {
-                if (!z_ready) {
-                    if (tid == 0 && wait_counter(p.z_counter, (uint32_t)p.G, ctrl, p, ST_Z)) {
-                        // the last CTA to get here clears both words for the next launch on this scratch
-                        if (atomicAdd(p.z_counter + 1, 1u) == (uint32_t)p.G - 1u) {
-                            p.z_counter[0] = 0u;
-                            p.z_counter[1] = 0u;
-                        }
-                    }
-                    if (!epi_sync_ok(ctrl)) return false;
-                    z_ready = true;
-                }
-                const int w0 = (int)((long long)slot * p.Rw / nc);
-                const int w1 = (int)((long long)(slot + 1) * p.Rw / nc);
-                const int32_t* ucol = p.Ucol + (size_t)(valid ? n : 0) * p.Rw;
-                for (int w = w0; w < w1; ++w) {
-                    const uint32_t uw = valid ? (uint32_t)ucol[w] : 0u;
-#pragma unroll (MMA_N <= 8 ? 8 : 2)
-                    for (int b = 0; b < 32; b += 4) {
-                        const float s0 = ((uw >> b) & 1u) ? 1.f : -1.f;
-                        const float s1 = ((uw >> (b + 1)) & 1u) ? 1.f : -1.f;
-                        const float s2 = ((uw >> (b + 2)) & 1u) ? 1.f : -1.f;
-                        const float s3 = ((uw >> (b + 3)) & 1u) ? 1.f : -1.f;
-#pragma unroll
-                        for (int m = 0; m < MMA_N; ++m) {
-                            if (m < p.M) {
-                                const float4 zz = __ldcg(reinterpret_cast<const float4*>(zb + (size_t)m * Rpad + 32 * w + b));
-                                corr[m] += (s0 * zz.x + s1 * zz.y) + (s2 * zz.z + s3 * zz.w);
-                            }
-                        }
-                    }
-                }
-            }
-
-            // accumulators of this segment
-            wait_bar(smem_u32(&ctrl->acc_full[buf]), (seg >> 1) & 1, ctrl, p, ST_ACC_FULL, warp);
-            if (!epi_sync_ok(ctrl)) return false;
-            tc_fence_after_sync();
-            float acc[MMA_N];
-            tmem_ld_acc<MMA_N>(tmem + ((uint32_t)(warp * 32) << 16) + buf * ACC_COL_STRIDE, acc);
-            tc_wait_ld();
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctrl->acc_empty[buf]));
-
-            float v[MMA_N];
-#pragma unroll
-            for (int m = 0; m < MMA_N; ++m) v[m] = alpha * acc[m] + corr[m];
-
-            if (!complete && cta != c_last) {
-                // contributor: publish the fp32 partial
-                float* P = p.partials + ((size_t)t * p.max_slots + slot) * MMA_N * TILE_N;
-#pragma unroll
-                for (int m = 0; m < MMA_N; ++m)
-                    if (m < p.M) P[m * TILE_N + tid] = v[m];
-                __threadfence();
-                named_bar_sync(1, EPI_THREADS);
-                if (tid == 0) red_release_add_u32(p.tile_cnt + t, 1u);
-            } else {
-                if (!complete) {
-                    // finisher: wait for the nc-1 partials of this call, add them in slot order
-                    if (tid == 0 && wait_counter(p.tile_cnt + t, (uint32_t)(nc - 1), ctrl, p, ST_TILE))
-                        p.tile_cnt[t] = 0u;      // only this CTA reads it; ready for the next launch
-                    if (!epi_sync_ok(ctrl)) return false;
-                    for (int sl = 0; sl < nc - 1; ++sl) {
-                        const float* P = p.partials + ((size_t)t * p.max_slots + sl) * MMA_N * TILE_N;
-#pragma unroll
-                        for (int m = 0; m < MMA_N; ++m)
-                            if (m < p.M) v[m] += __ldcg(P + m * TILE_N + tid);
-                    }
-                }
-                if (valid) {
-#pragma unroll
-                    for (int m = 0; m < MMA_N; ++m) {
-                        if (m < p.M) {
-                            float o = v[m];
-                            if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
-                            p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
-                        }
-                    }
-                }
-            }
-            ++seg;
-            return true;
-        });
-    }
-
-    // ---------------- common exit ----------------
-    tc_fence_before_sync();
-    __syncthreads();
-    if (ctrl->abort) {
-        // give copies that may still be in flight time to land before the shared memory is released
-        const uint64_t t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 2000000ull) { }
-        __syncthreads();
-    }
-    if (warp == 5) {
-        tc_fence_after_sync();
-        tmem_dealloc(tmem, TMEM_COLS);
-    }
-}
 
 // -----------------------------------------------------------------------------------------------------------
 // Host side
@@ -526,6 +114,9 @@ static int device_sm_count() {
     return cached[dev];
 }
 
+static unsigned long long* g_stamps = nullptr;   // debug time-stamp buffer for subsequent launches (or null)
+static size_t g_stamps_bytes = 0;
+
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 
 struct ScratchLayout {
@@ -540,6 +131,7 @@ static bool make_layout(int M, int N, int K, int R, int num_sms, ScratchLayout* 
     L->nkt = K / KT;
     const long long T = (long long)L->ntile * L->nkt;
     L->G = (int)(T < num_sms ? T : num_sms);
+    if (!sched_fits_32bit(L->ntile, L->nkt, L->G) || (long long)R * (L->G + 1) >= (1ll << 31)) return false;
     L->max_slots = sched_max_slots(L->ntile, L->nkt, L->G);
     L->Rw = (R + 31) / 32;
     L->Rpad = L->Rw * 32;
@@ -552,18 +144,20 @@ static bool make_layout(int M, int N, int K, int R, int num_sms, ScratchLayout* 
     return true;
 }
 
-template <int MMA_N>
+static int rows_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : (M <= 16 ? 16 : 32)))); }
+
+template <int MMA_N, int ROWS>
 static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedParams& p, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(fused_linear_kernel<MMA_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<MMA_N>::SMEM_BYTES) !=
-            cudaSuccess)
+        if (cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Cfg<MMA_N>::SMEM_BYTES) != cudaSuccess)
             return BILOCO_ERR_CUDA;
         attr_set[dev] = true;
     }
-    fused_linear_kernel<MMA_N><<<p.G, NUM_THREADS, Cfg<MMA_N>::SMEM_BYTES, stream>>>(tmW, tmA, p);
+    fused_linear_kernel<MMA_N, ROWS><<<p.G, NUM_THREADS, Cfg<MMA_N>::SMEM_BYTES, stream>>>(tmW, tmA, p);
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
@@ -640,13 +234,23 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
     p.ntile = L.ntile; p.nkt = L.nkt; p.G = L.G; p.max_slots = L.max_slots;
     p.epoch = (uint32_t)epoch;
     p.mode = mode;
+    p.stamps = (g_stamps && g_stamps_bytes >= (size_t)L.G * STAMP_WORDS * 8) ? g_stamps : nullptr;
 
     cudaStream_t s = (cudaStream_t)stream;
-    switch (L.mma_n) {
-        case 8: return launch<8>(tmW, tmA, p, s);
-        case 16: return launch<16>(tmW, tmA, p, s);
-        default: return launch<32>(tmW, tmA, p, s);
+    switch (rows_for(M)) {
+        case 1: return launch<8, 1>(tmW, tmA, p, s);
+        case 2: return launch<8, 2>(tmW, tmA, p, s);
+        case 4: return launch<8, 4>(tmW, tmA, p, s);
+        case 8: return launch<8, 8>(tmW, tmA, p, s);
+        case 16: return launch<16, 16>(tmW, tmA, p, s);
+        default: return launch<32, 32>(tmW, tmA, p, s);
     }
+}
+
+extern "C" int biloco_b200_debug_stamps(void* device_buf, size_t bytes) {
+    g_stamps = (unsigned long long*)device_buf;
+    g_stamps_bytes = device_buf ? bytes : 0;
+    return BILOCO_OK;
 }
 
 extern "C" int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t stream) {

@@ -127,6 +127,12 @@ int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const float*
  * of the first wait that gave up. Words 1..3: block index, epoch and role of that wait. */
 int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t stream);
 
+/* Debug aid: while a device buffer is registered here, every fused launch of this process writes 8 uint64
+ * %globaltimer stamps per CTA into it (CTA c at words 8c..8c+7: 0 start, 1 z published, 2 z complete seen,
+ * 3 expansion done, 4 accumulators ready, 5/6 first/last segment stored). bytes >= 64 * CTAs; NULL turns it off.
+ * Counterpart in the reference: the optional Diag tensor (csrc/biloco_gemm.cu:313-317, 446-464). */
+int biloco_b200_debug_stamps(void* device_buf, size_t bytes);
+
 /* CUDA-core FP4 GEMM used to cross-check the tensor-core path on the device at full size:
  * D[m,n] = bf16(alpha[0] * sum_k A[m,k] W[n,k] + C[m,n]). Same operand formats as above; K % 16 == 0.
  * Replaces (functionally): torch.ops.biloco.fp4_gemm_residual as used by biloco/kernel.py:137-142. */
