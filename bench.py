@@ -99,7 +99,7 @@ class ClockSampler:
                 "samples": len(inside)}
 
 
-def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed):
+def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed, mode=None):
     """Synthetic layers in the construction of the reference's timing scripts (scripts/problem.py:7-27, random
     block scales in [0.25, 2]), activations ~N(0,1) with 1 % outlier channels x20 quantised by the device quantiser."""
     g = torch.Generator(device=dev).manual_seed(seed)
@@ -116,7 +116,7 @@ def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed):
         x[:, idx] *= 20
         x = x.to(torch.bfloat16).contiguous()
         q = fp4.quantize_activation(x, "mse", w_gscale=w_gs, rows=M)
-        gemm = kernel.BiLoCoGemm(W, W_sf, q["alpha"], Vp, Up, S, M=M)
+        gemm = kernel.BiLoCoGemm(W, W_sf, q["alpha"], Vp, Up, S, M=M, mode=mode)
         layers.append(dict(gemm=gemm, q=q, x=x, w_gs=w_gs, x_host=x.cpu().pin_memory(),
                            y_host=torch.empty(M, N, dtype=torch.bfloat16).pin_memory()))
     return layers
@@ -201,7 +201,7 @@ def run_ours(args):
     from biloco_b200 import fp4, kernel
 
     K, N, r, M, L = args.K, args.N, args.r, args.M, args.layers
-    layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank)
+    layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank, mode=args.mode)
     bytes_call = algorithmic_bytes(K, N, r)
 
     def step_device():
@@ -322,6 +322,7 @@ def main():
     ap.add_argument("--N", type=int, default=5120)
     ap.add_argument("--r", type=int, default=512)
     ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--mode", type=int, default=None, help="schedule of the fused kernel (default: the measured table)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")
     args = ap.parse_args()

@@ -16,11 +16,26 @@ constexpr int KT_BYTES = KT / 2;                 // 128 B of codes per row = one
 constexpr int W_TILE_BYTES = TILE_N * KT_BYTES;  // 16384
 constexpr int SF_TILE_BYTES = 4 * 512;           // four 128x4 atoms
 constexpr int EPI_THREADS = 128;
-constexpr int NUM_THREADS = 192;
-constexpr int TMEM_COLS = 128;
+// Warp roles: 0-3 z stage / expansion / epilogue, 4-7 weight producers, 8-11 activation producers, 12-15 scale-factor
+// movers (shared memory -> TMEM), 16 MMA issue.
+// Bulk copies issued by one thread complete one after the other (about 0.4 us each for anything up to 16 KB,
+// measured), copies issued by different warps overlap: several producer warps are what lets one CTA pull its
+// share of the weight stream at HBM speed.
+constexpr int W_PRODUCERS = 4;
+constexpr int A_PRODUCERS = 4;
+constexpr int FIRST_W_WARP = 4;
+constexpr int FIRST_A_WARP = FIRST_W_WARP + W_PRODUCERS;
+constexpr int FIRST_SF_WARP = FIRST_A_WARP + A_PRODUCERS;   // 4 warps, one per 32-lane TMEM quadrant (warp id % 4)
+constexpr int MMA_WARP = FIRST_SF_WARP + 4;
+constexpr int NUM_THREADS = (MMA_WARP + 1) * 32;
+static_assert(FIRST_SF_WARP % 4 == 0, "scale-factor warp q must own TMEM quadrant q");
+constexpr int START_BAR_THREADS = EPI_THREADS + 32 * (W_PRODUCERS + A_PRODUCERS);   // named barrier 2
+constexpr int TMEM_COLS = 256;
 constexpr int ACC_COL_STRIDE = 32;               // accumulator buffer b starts at column 32*b
-constexpr int SFA_COL = 64;                      // 16 columns: 4 MMAs x 4
-constexpr int SFB_COL = 80;                      // 16 columns
+constexpr int SF_SETS = 4;                       // scale-factor column sets, used round-robin by consecutive units
+constexpr int SFA_COL = 64;                      // set q: 16 columns (4 MMAs x 4) at SFA_COL + 32*q
+constexpr int SFB_COL = 80;                      // set q: 16 columns at SFB_COL + 32*q
+static_assert(SFA_COL + 32 * SF_SETS <= TMEM_COLS, "scale-factor sets exceed the TMEM allocation");
 constexpr int CTRL_BYTES = 1024;
 constexpr int SMEM_BUDGET = 227 * 1024;
 constexpr uint64_t WAIT_BUDGET_NS = 200ull * 1000 * 1000;   // 200 ms per wait
@@ -34,7 +49,7 @@ constexpr int VT_BYTES = VT_RANKS * (XT_BYTES / 2 / 8);   // one bit per k of th
 constexpr int WORK_BYTES = XT_BYTES + VT_BYTES;           // 24 KB
 constexpr int ZS_WORDS = 4;                      // rank words (32 ranks each) of z staged at a time
 constexpr int ZS_STRIDE = ZS_WORDS * 32 + 4;     // floats per staged row (+4: rows start in different banks)
-constexpr int STAMP_WORDS = 8;                   // uint64 time stamps per CTA when debug stamps are on
+constexpr int STAMP_WORDS = 16;                  // uint64 time stamps per CTA when debug stamps are on
 static_assert(32 * ZS_STRIDE * 4 <= WORK_BYTES, "z staging must fit in the work area");
 
 template <int MMA_N>
@@ -48,6 +63,7 @@ struct Cfg {
 };
 
 struct FusedParams {
+    const uint8_t* W_tiled;   // unit-contiguous weights (see biloco_b200_tile_weights) or null: row-major codes via TMA
     const uint8_t* W_sf;
     const uint8_t* A_sf;
     const float* alpha;
@@ -64,6 +80,7 @@ struct FusedParams {
     float* partials;
     int M, N, K, R, Rw, Rpad;
     int ntile, nkt, G, max_slots;
+    int z_consumers;          // CTAs that wait for z in this launch (all of them, or only those that finish a tile)
     uint32_t epoch;
     int mode;
     unsigned long long* stamps;   // debug: STAMP_WORDS %globaltimer values per CTA, or null
@@ -74,13 +91,16 @@ struct Ctrl {   // lives in shared memory after the stages
     uint64_t empty[16];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t sf_full[SF_SETS];    // scale factors of a unit are in TMEM set q (128 arrivals)
+    uint64_t sf_empty[SF_SETS];   // the MMAs that read set q have completed (tcgen05.commit)
     uint32_t tmem_base;
     volatile int abort;
 };
 static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
 
 enum : int {   // status codes of waits that ran out
-    ST_EMPTY = 101, ST_FULL = 102, ST_ACC_EMPTY = 103, ST_ACC_FULL = 104, ST_Z = 105, ST_TILE = 106,
+    ST_EMPTY = 101, ST_FULL = 102, ST_ACC_EMPTY = 103, ST_ACC_FULL = 104, ST_Z = 105, ST_TILE = 106, ST_SF_FULL = 107,
+    ST_SF_EMPTY = 108,
 };
 
 // The wait helpers are deliberately not inlined: the kernel's machine code is executed once, cold, per CTA, and
@@ -173,5 +193,31 @@ struct SegWalk {
         else u += count();
     }
 };
+
+// What a CTA does with one segment: the tile, its place among the tile's contributors, whether it finishes the tile,
+// and the rank words [w0, w1) of the low-rank term it expands. owner_mode: the finisher expands all ranks and the
+// other contributors none (their partial sums then do not wait for z); otherwise every contributor takes a share.
+struct SegInfo {
+    int t, nc, slot, w0, w1;
+    bool complete, finisher;
+};
+__device__ __forceinline__ SegInfo seg_info(const FusedParams& p, int T, int cta, int u, int cnt, bool owner_mode) {
+    SegInfo s;
+    s.t = (int)((unsigned)u / (unsigned)p.nkt);
+    const int c_first = sched_cta_of_unit(s.t * p.nkt, T, p.G);
+    const int c_last = sched_cta_of_unit(s.t * p.nkt + p.nkt - 1, T, p.G);
+    s.nc = c_last - c_first + 1;
+    s.slot = cta - c_first;
+    s.complete = (cnt == p.nkt);
+    s.finisher = s.complete || cta == c_last;
+    if (owner_mode) {
+        s.w0 = 0;
+        s.w1 = s.finisher ? p.Rw : 0;
+    } else {
+        s.w0 = s.slot * p.Rw / s.nc;
+        s.w1 = (s.slot + 1) * p.Rw / s.nc;
+    }
+    return s;
+}
 
 }  // namespace biloco

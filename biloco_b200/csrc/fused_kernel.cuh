@@ -42,10 +42,11 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const int u1 = sched_first_unit(cta + 1, T, p.G);
 
     // ---------------- set-up ----------------
-    if (tid == 128) {
+    if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 10] = globaltimer_ns();
+    if (tid == FIRST_W_WARP * 32) {
 #pragma unroll 1
         for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->full[s]), 1);
+            mbar_init(smem_u32(&ctrl->full[s]), 2);     // one weight producer + one activation producer
             mbar_init(smem_u32(&ctrl->empty[s]), 1);
         }
 #pragma unroll 1
@@ -53,12 +54,16 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             mbar_init(smem_u32(&ctrl->acc_full[b]), 1);
             mbar_init(smem_u32(&ctrl->acc_empty[b]), EPI_THREADS);
         }
+        for (int q = 0; q < SF_SETS; ++q) {
+            mbar_init(smem_u32(&ctrl->sf_full[q]), 128);
+            mbar_init(smem_u32(&ctrl->sf_empty[q]), 1);
+        }
         ctrl->abort = 0;
         fence_mbar_init();
         prefetch_tmap(&tmW);
         prefetch_tmap(&tmA);
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
         tmem_relinquish();
     }
@@ -68,12 +73,17 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const uint32_t tmem = ctrl->tmem_base;
     if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 0] = globaltimer_ns();
 
-    if (warp == 4) {
-        // ================= TMA producer =================
-        // wait until the epilogue threads have issued their first small loads (U words, V bits, x): those requests
-        // then sit ahead of the ~100 KB per SM of weight traffic issued next
-        asm volatile("bar.sync 2, %0;" ::"r"(EPI_THREADS + 32) : "memory");
+    if (warp >= FIRST_W_WARP && warp < FIRST_SF_WARP) {
+        // ================= producers =================
+        // Weight producer j issues the 18 KB weight record of units j, j+4, ... (in processing order), activation
+        // producer j the activation tile and its scales of the same units. All of them first wait until the
+        // epilogue threads' first small reads (U words, V bits, x) have landed: small requests issued while the
+        // weight stream is in flight wait microseconds in the memory system's queues.
+        asm volatile("bar.sync 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
         if (lane == 0) {
+            const bool is_w = warp < FIRST_A_WARP;
+            const int mine = is_w ? (warp - FIRST_W_WARP) : (warp - FIRST_A_WARP);
+            const int nprod = is_w ? W_PRODUCERS : A_PRODUCERS;
             int i = 0;
             bool ok = true;
 #pragma unroll 1
@@ -84,25 +94,71 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 int kt = us - t * p.nkt;
 #pragma unroll 1
                 for (int u = us; u < us + cnt; ++u, ++i, ++kt) {
+                    if (i % nprod != mine) continue;
                     const int s = i % C::STAGES;
                     const int use = i / C::STAGES;
-                    if (use > 0 && !wait_bar(smem_u32(&ctrl->empty[s]), (use - 1) & 1, ctrl, p.status, p.epoch, ST_EMPTY, 4)) {
+                    if (use > 0 && !wait_bar(smem_u32(&ctrl->empty[s]), (use - 1) & 1, ctrl, p.status, p.epoch, ST_EMPTY, warp)) {
                         ok = false;
                         break;
                     }
                     const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
                     const uint32_t bar = smem_u32(&ctrl->full[s]);
-                    mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
-                    tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
-                    tma_load_2d(sbase + W_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
-                    bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES,
-                              p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
-                    bulk_load(sbase + W_TILE_BYTES + C::A_TILE_BYTES + SF_TILE_BYTES,
-                              p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
+                    if (is_w) {
+                        mbar_arrive_expect_tx(bar, W_TILE_BYTES + SF_TILE_BYTES);
+                        if (p.W_tiled) {
+                            // one contiguous 18 KB record per unit: pre-swizzled codes followed by the scale atoms
+                            bulk_load(sbase, p.W_tiled + (size_t)u * (W_TILE_BYTES + SF_TILE_BYTES), W_TILE_BYTES + SF_TILE_BYTES, bar);
+                        } else {
+                            tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
+                            bulk_load(sbase + W_TILE_BYTES, p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
+                        }
+                    } else {
+                        mbar_arrive_expect_tx(bar, C::A_TILE_BYTES + SF_TILE_BYTES);
+                        tma_load_2d(sbase + W_TILE_BYTES + SF_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
+                        bulk_load(sbase + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES, p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
+                    }
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp >= FIRST_SF_WARP && warp < MMA_WARP) {
+        // ================= scale-factor movers =================
+        // The block-scaled MMA reads its scale factors from TMEM, lane l of every 32-lane quadrant holding rows
+        // l, l+32, l+64, l+96 of the 128x4 atom in four consecutive columns. tcgen05.cp can place an atom there, but
+        // eight of them per unit occupy the tensor pipe longer than the unit's four MMAs (measured); here warp q
+        // writes quadrant q from registers instead: per unit 8 x 128-bit shared loads and 2 x tcgen05.st per thread.
+        const uint32_t quad = (uint32_t)((warp & 3) * 32) << 16;
+        int i = 0;
+        bool ok = true;
+#pragma unroll 1
+        for (SegWalk sw(u0, u1, p.nkt); ok && !sw.done(); sw.next()) {
+            const int cnt = sw.count();
+#pragma unroll 1
+            for (int j = 0; j < cnt; ++j, ++i) {
+                const int s = i % C::STAGES;
+                const int q = i % SF_SETS;
+                bool ready = wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p.status, p.epoch, ST_FULL, warp);
+                if (ready && i >= SF_SETS)
+                    ready = wait_bar(smem_u32(&ctrl->sf_empty[q]), ((i / SF_SETS) - 1) & 1, ctrl, p.status, p.epoch, ST_SF_EMPTY, warp);
+                if (!__all_sync(0xffffffffu, ready)) { ok = false; break; }     // warp-uniform: the TMEM stores are warp-wide
+                tc_fence_after_sync();
+                const uint8_t* stage = smem_raw + (stage0 - raw) + s * C::STAGE_BYTES;
+                const uint4* wsf = reinterpret_cast<const uint4*>(stage + W_TILE_BYTES) + lane;
+                const uint4* asf = reinterpret_cast<const uint4*>(stage + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES) + lane;
+                uint32_t ra[16], rb[16];
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    const uint4 x = wsf[a * 32], y = asf[a * 32];       // atom a, row `lane`: 16 bytes = 4 columns
+                    ra[4 * a] = x.x; ra[4 * a + 1] = x.y; ra[4 * a + 2] = x.z; ra[4 * a + 3] = x.w;
+                    rb[4 * a] = y.x; rb[4 * a + 1] = y.y; rb[4 * a + 2] = y.z; rb[4 * a + 3] = y.w;
+                }
+                tmem_st_x16(tmem + quad + 32u * q + SFA_COL, ra);
+                tmem_st_x16(tmem + quad + 32u * q + SFB_COL, rb);
+                tc_wait_st();
+                tc_fence_before_sync();
+                mbar_arrive(smem_u32(&ctrl->sf_full[q]));
+            }
+        }
+    } else if (warp == MMA_WARP) {
         // ================= MMA issue =================
         constexpr uint32_t idesc = make_idesc_nvf4(TILE_N, MMA_N);
         int i = 0, seg = 0;
@@ -111,32 +167,28 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         for (SegWalk sw(u0, u1, p.nkt); ok && !sw.done(); sw.next(), ++seg) {
             const int cnt = sw.count();
             const int buf = seg & 1;
-            if (seg >= 2 && !wait_bar(smem_u32(&ctrl->acc_empty[buf]), ((seg >> 1) - 1) & 1, ctrl, p.status, p.epoch, ST_ACC_EMPTY, 5))
+            if (seg >= 2 && !wait_bar(smem_u32(&ctrl->acc_empty[buf]), ((seg >> 1) - 1) & 1, ctrl, p.status, p.epoch, ST_ACC_EMPTY, MMA_WARP))
                 break;
             tc_fence_after_sync();
 #pragma unroll 1
             for (int j = 0; j < cnt; ++j, ++i) {
                 const int s = i % C::STAGES;
-                if (!wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p.status, p.epoch, ST_FULL, 5)) { ok = false; break; }
+                if (!wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p.status, p.epoch, ST_FULL, MMA_WARP)) { ok = false; break; }
+                if (!wait_bar(smem_u32(&ctrl->sf_full[i % SF_SETS]), (i / SF_SETS) & 1, ctrl, p.status, p.epoch, ST_SF_FULL, MMA_WARP)) { ok = false; break; }
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
-                    const uint32_t wsf = sbase + W_TILE_BYTES + C::A_TILE_BYTES;
-                    const uint32_t asf = wsf + SF_TILE_BYTES;
-#pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        tc_cp_32x128b_warpx4(tmem + SFA_COL + 4 * a, make_smem_desc(wsf + 512 * a, 128, 0));
-                        tc_cp_32x128b_warpx4(tmem + SFB_COL + 4 * a, make_smem_desc(asf + 512 * a, 128, 0));
-                    }
+                    const uint32_t sfset = 32u * (uint32_t)(i % SF_SETS);
                     const uint64_t wdesc = make_smem_desc(sbase, 1024, 2);
-                    const uint64_t adesc = make_smem_desc(sbase + W_TILE_BYTES, 1024, 2);
+                    const uint64_t adesc = make_smem_desc(sbase + W_TILE_BYTES + SF_TILE_BYTES, 1024, 2);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         // 64 K-elements = 32 B further along the swizzled row: +2 in the (address >> 4) field
                         tc_mma_nvf4(tmem + buf * ACC_COL_STRIDE, wdesc + 2 * k, adesc + 2 * k, idesc,
-                                    tmem + SFA_COL + 4 * k, tmem + SFB_COL + 4 * k, (j > 0 || k > 0) ? 1u : 0u);
+                                    tmem + sfset + SFA_COL + 4 * k, tmem + sfset + SFB_COL + 4 * k, (j > 0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(smem_u32(&ctrl->empty[s]));
+                    tc_commit(smem_u32(&ctrl->sf_empty[i % SF_SETS]));
                     if (j == cnt - 1) tc_commit(smem_u32(&ctrl->acc_full[buf]));
                     if (p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 7] = globaltimer_ns();   // latest stage landed
                 }
@@ -148,6 +200,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         float* zb = p.zbuf + (size_t)(p.epoch & 1u) * 32 * p.Rpad;
         float* zs = reinterpret_cast<float*>(work);
         bool signal_pending = true;
+        const bool owner_mode = (p.mode & 0xff) == 4;
 
         // U words of the first chunk of the first two segments: requested before anything else, so that they do
         // not queue behind the weight stream later
@@ -161,22 +214,19 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
                 if (!sw.done()) {
-                    const int t = (int)((unsigned)sw.first() / (unsigned)p.nkt);
-                    const int c_first = sched_cta_of_unit(t * p.nkt, T, p.G);
-                    const int nc = sched_cta_of_unit(t * p.nkt + p.nkt - 1, T, p.G) - c_first + 1;
-                    const int w0 = (cta - c_first) * p.Rw / nc;
-                    const int w1 = (cta - c_first + 1) * p.Rw / nc;
-                    const int n = t * TILE_N + tid;
+                    const SegInfo si = seg_info(p, T, cta, sw.first(), sw.count(), owner_mode);
+                    const int n = si.t * TILE_N + tid;
                     const int32_t* ucol = p.Ucol + (size_t)(n < p.N ? n : 0) * p.Rw;
 #pragma unroll
-                    for (int w = 0; w < ZS_WORDS; ++w) uw_first[g][w] = (uint32_t)ucol[(w0 + w < w1) ? (w0 + w) : (w0 < w1 ? w0 : 0)];
+                    for (int w = 0; w < ZS_WORDS; ++w)
+                        uw_first[g][w] = (uint32_t)ucol[(si.w0 + w < si.w1) ? (si.w0 + w) : (si.w0 < si.w1 ? si.w0 : 0)];
                     sw.next();
                 }
             }
 
             z_stage<ROWS>(p, work, zb, cta, tid, signal_pending);
             if (signal_pending) {   // this CTA had no ranks to compute
-                asm volatile("bar.arrive 2, %0;" ::"r"(EPI_THREADS + 32) : "memory");
+                asm volatile("bar.arrive 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
                 signal_pending = false;
             }
             named_bar_sync(1, EPI_THREADS);    // orders every z store before thread 0's (cumulative) release
@@ -185,33 +235,30 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 if (p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 1] = globaltimer_ns();
             }
         }
-        if (signal_pending) asm volatile("bar.arrive 2, %0;" ::"r"(EPI_THREADS + 32) : "memory");
+        if (signal_pending) asm volatile("bar.arrive 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
 
         bool z_ready = false;
         const float alpha = p.alpha[0];
         int seg = 0;
 #pragma unroll 1
         for (SegWalk sw(u0, u1, p.nkt); !sw.done(); sw.next(), ++seg) {
-            const int u = sw.first();
-            const int cnt = sw.count();
-            const int t = (int)((unsigned)u / (unsigned)p.nkt);
+            const SegInfo si = seg_info(p, T, cta, sw.first(), sw.count(), owner_mode);
+            const int t = si.t, nc = si.nc, slot = si.slot;
             const int buf = seg & 1;
-            const bool complete = (cnt == p.nkt);
-            const int c_first = sched_cta_of_unit(t * p.nkt, T, p.G);
-            const int c_last = sched_cta_of_unit(t * p.nkt + p.nkt - 1, T, p.G);
-            const int nc = c_last - c_first + 1;
-            const int slot = cta - c_first;
+            const bool complete = si.complete;
             const int n = t * TILE_N + tid;
             const bool valid = n < p.N;
 
             float corr[ROWS];
 #pragma unroll
             for (int m = 0; m < ROWS; ++m) corr[m] = 0.f;
-            if (p.R > 0) {
+            // mode 2: every CTA passes the z wait once (the consumer count that re-arms the counter is the grid size),
+            // mode 4: only CTAs that finish a tile do
+            if (p.R > 0 && (!owner_mode || si.w0 < si.w1)) {
                 if (!z_ready) {
                     if (tid == 0 && wait_counter(p.z_counter, (uint32_t)p.G, ctrl, p.status, p.epoch, ST_Z)) {
-                        // the last CTA to get here clears both words for the next launch on this scratch
-                        if (atomicAdd(p.z_counter + 1, 1u) == (uint32_t)p.G - 1u) {
+                        // the last consumer to get here clears both words for the next launch on this scratch
+                        if (atomicAdd(p.z_counter + 1, 1u) == (uint32_t)p.z_consumers - 1u) {
                             p.z_counter[0] = 0u;
                             p.z_counter[1] = 0u;
                         }
@@ -220,8 +267,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     z_ready = true;
                     if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 2] = globaltimer_ns();
                 }
-                const int w0 = slot * p.Rw / nc;
-                const int w1 = (slot + 1) * p.Rw / nc;
+                const int w0 = si.w0, w1 = si.w1;
                 const int32_t* ucol = p.Ucol + (size_t)(valid ? n : 0) * p.Rw;
                 uint32_t uw_sel[ZS_WORDS];
 #pragma unroll
@@ -245,7 +291,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
             for (int m = 0; m < ROWS; ++m) v[m] = alpha * acc[m] + corr[m];
 
-            if (!complete && cta != c_last) {
+            if (!si.finisher) {
                 // contributor: publish the fp32 partial
                 float* P = p.partials + ((size_t)t * p.max_slots + slot) * MMA_N * TILE_N;
 #pragma unroll
@@ -292,7 +338,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         while (globaltimer_ns() - t0 < 2000000ull) { }
         __syncthreads();
     }
-    if (warp == 5) {
+    if (warp == MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, TMEM_COLS);
     }

@@ -144,6 +144,26 @@ static bool make_layout(int M, int N, int K, int R, int num_sms, ScratchLayout* 
     return true;
 }
 
+// Re-layout of the weights into the order the kernel streams them: record u = (tile t, k-tile kt) holds the 128 x 128 B
+// block of codes with the 128-byte swizzle already applied (16-byte chunk c of row r stored at chunk c ^ (r & 7)),
+// followed by the four 512-byte scale atoms of that block. Rows beyond N are zero.
+__global__ void tile_weights_kernel(const uint8_t* __restrict__ W, const uint8_t* __restrict__ W_sf, uint8_t* __restrict__ out,
+                                    int N, int K, int nkt) {
+    const int u = blockIdx.x;
+    const int t = u / nkt, kt = u - t * nkt;
+    uint8_t* rec = out + (size_t)u * (W_TILE_BYTES + SF_TILE_BYTES);
+    for (int i = threadIdx.x; i < W_TILE_BYTES / 16; i += blockDim.x) {
+        const int r = i >> 3, c = i & 7;
+        const int n = t * TILE_N + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (n < N) v = *reinterpret_cast<const uint4*>(W + (size_t)n * (K >> 1) + kt * KT_BYTES + c * 16);
+        *reinterpret_cast<uint4*>(rec + r * 128 + ((c ^ (r & 7)) * 16)) = v;
+    }
+    const uint8_t* sf = W_sf + ((size_t)t * (K >> 6) + (size_t)kt * 4) * 512;
+    for (int i = threadIdx.x; i < SF_TILE_BYTES / 16; i += blockDim.x)
+        *reinterpret_cast<uint4*>(rec + W_TILE_BYTES + i * 16) = *reinterpret_cast<const uint4*>(sf + i * 16);
+}
+
 static int rows_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : (M <= 16 ? 16 : 32)))); }
 
 template <int MMA_N, int ROWS>
@@ -189,14 +209,31 @@ extern "C" int biloco_b200_schedule_info(int M, int N, int K, int R, int num_sms
     return BILOCO_OK;
 }
 
-extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const float* alpha, const void* A_codes,
+extern "C" size_t biloco_b200_tiled_bytes(int N, int K) {
+    if (N < 1 || K < KT || (K % KT)) return 0;
+    return (size_t)((N + TILE_N - 1) / TILE_N) * (K / KT) * (W_TILE_BYTES + SF_TILE_BYTES);
+}
+
+extern "C" int biloco_b200_tile_weights(const void* W_codes, const void* W_sf, void* W_tiled, int N, int K, biloco_stream_t stream) {
+    if (!W_codes || !W_sf || !W_tiled) return BILOCO_ERR_NULL;
+    if (N < 1 || K < KT || (K % KT)) return BILOCO_ERR_SHAPE;
+    if (((uintptr_t)W_tiled & 15) || ((uintptr_t)W_codes & 15) || ((uintptr_t)W_sf & 15) || ((uintptr_t)W_tiled & 15)) return BILOCO_ERR_ALIGN;
+    const int nkt = K / KT;
+    const long long units = (long long)((N + TILE_N - 1) / TILE_N) * nkt;
+    if (units > 0x7fffffffll) return BILOCO_ERR_LIMIT;
+    tile_weights_kernel<<<(unsigned)units, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)W_codes, (const uint8_t*)W_sf,
+                                                                            (uint8_t*)W_tiled, N, K, nkt);
+    return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
+}
+
+extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha, const void* A_codes,
                                         const void* A_sf, const void* X_bf16, const void* V_packed, const int32_t* U_col32,
                                         const void* S_bf16, const void* C_bf16, void* Y_bf16, void* scratch,
                                         size_t scratch_bytes, int M, int A_rows, int N, int K, int R, int mode, int epoch,
                                         biloco_stream_t stream) {
-    if (!W_codes || !W_sf || !alpha || !A_codes || !A_sf || !Y_bf16 || !scratch) return BILOCO_ERR_NULL;
+    if ((!W_tiled && (!W_codes || !W_sf)) || !alpha || !A_codes || !A_sf || !Y_bf16 || !scratch) return BILOCO_ERR_NULL;
     if (R > 0 && (!X_bf16 || !V_packed || !U_col32 || !S_bf16)) return BILOCO_ERR_NULL;
-    if (mode != BILOCO_MODE_COUNTER) return BILOCO_ERR_MODE;
+    if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER) return BILOCO_ERR_MODE;
     if (epoch < 1) return BILOCO_ERR_EPOCH;
     if (A_rows < M || A_rows > 128) return BILOCO_ERR_SHAPE;
     const int sms = device_sm_count();
@@ -209,13 +246,15 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
         return BILOCO_ERR_ALIGN;
 
     CUtensorMap tmW, tmA;
-    int rc = get_tensor_map(W_codes, N, K / 2, TILE_N, &tmW);
+    int rc = get_tensor_map(A_codes, A_rows, K / 2, L.mma_n, &tmA);
     if (rc != BILOCO_OK) return rc;
-    rc = get_tensor_map(A_codes, A_rows, K / 2, L.mma_n, &tmA);
+    if (W_tiled) tmW = tmA;     // not used by the kernel on the tiled path
+    else rc = get_tensor_map(W_codes, N, K / 2, TILE_N, &tmW);
     if (rc != BILOCO_OK) return rc;
 
     uint8_t* sc = (uint8_t*)scratch;
     FusedParams p;
+    p.W_tiled = (const uint8_t*)W_tiled;
     p.W_sf = (const uint8_t*)W_sf;
     p.A_sf = (const uint8_t*)A_sf;
     p.alpha = alpha;
@@ -234,6 +273,16 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
     p.ntile = L.ntile; p.nkt = L.nkt; p.G = L.G; p.max_slots = L.max_slots;
     p.epoch = (uint32_t)epoch;
     p.mode = mode;
+    p.z_consumers = L.G;
+    if ((mode & 0xff) == BILOCO_MODE_OWNER) {   // only CTAs that finish a tile wait for z
+        int consumers = 0, prev = -1;
+        const int T = L.ntile * L.nkt;
+        for (int t = 0; t < L.ntile; ++t) {
+            const int c = sched_cta_of_unit(t * L.nkt + L.nkt - 1, T, L.G);
+            if (c != prev) { ++consumers; prev = c; }
+        }
+        p.z_consumers = consumers;
+    }
     p.stamps = (g_stamps && g_stamps_bytes >= (size_t)L.G * STAMP_WORDS * 8) ? g_stamps : nullptr;
 
     cudaStream_t s = (cudaStream_t)stream;

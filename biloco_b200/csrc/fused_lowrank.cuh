@@ -54,8 +54,9 @@ __device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, flo
                 }
                 cp_async_commit();
                 cp_async_wait_all();
+                if (tid == 0 && p.stamps && signal_pending) p.stamps[(size_t)cta * STAMP_WORDS + 8] = globaltimer_ns();
                 if (signal_pending) {   // the first small reads have landed: release the weight stream
-                    asm volatile("bar.arrive 2, %0;" ::"r"(EPI_THREADS + 32) : "memory");
+                    asm volatile("bar.arrive 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
                     signal_pending = false;
                 }
                 named_bar_sync(1, EPI_THREADS);
@@ -92,6 +93,7 @@ __device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, flo
                     }
                 }
             }
+            if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 9] = globaltimer_ns();
             if (lane < RP) {
                 if (warp < nr) zb[(size_t)(mg + lane) * p.Rpad + ic + warp] = zacc0 * __bfloat162float(p.S[ic + warp]);
                 if (warp + 4 < nr) zb[(size_t)(mg + lane) * p.Rpad + ic + warp + 4] = zacc1 * __bfloat162float(p.S[ic + warp + 4]);

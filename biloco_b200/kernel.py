@@ -19,7 +19,7 @@ ops = torch.ops.biloco
 RANKS = (16, 32, 64, 128, 256, 512, 1024)
 
 # Schedules implemented by the fused kernel (see include/biloco_b200.h, BILOCO_MODE_*).
-IMPLEMENTED_MODES = (2,)
+IMPLEMENTED_MODES = (2, 4)
 
 # Fastest implemented mode per (M, rank) on B200 at K = N = 5120.
 DEFAULT_MODE = {M: {r: 2 for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
@@ -84,12 +84,13 @@ class BiLoCoGemm:
     Call with the NVFP4 activation A [1, rows, K/2] uint8 (rows >= M; the reference pads to 128 rows, any
     row count from M to 128 is accepted), its block scales A_sf, and the BF16 activation X [M, K] (the
     low-rank term uses the unquantized activation).
+    tile_weights=False skips the unit-contiguous copy of the weight (saves its memory, streams slower).
     Consecutive calls need no clearing of the scratch buffer: the kernel returns its counters to zero before it
     exits, so a CUDA graph containing calls can be replayed as is (calling reset() inside the captured region,
     as the reference requires, stays valid).
     """
 
-    def __init__(self, W_fp4, W_sf, alpha, V_packed, U_packed, S, M: int, mode: int = None):
+    def __init__(self, W_fp4, W_sf, alpha, V_packed, U_packed, S, M: int, mode: int = None, tile_weights: bool = True):
         self.N, self.K = W_fp4.shape[0], W_fp4.shape[1] * 2
         self.R, self.M = V_packed.shape[0], M
         self.mode = mode or DEFAULT_MODE.get(M, {}).get(self.R) or (modes_for(M, self.R, self.K) or [None])[0]
@@ -98,6 +99,9 @@ class BiLoCoGemm:
         dev = W_fp4.device
         self.U_col32 = pack_u_col32(U_packed, n_cols=self.N, rank=self.R)
         self.none = torch.zeros(0, device=dev, dtype=torch.int64)
+        # unit-contiguous copy of the weight (the counterpart of the reference's V_perm / U_rw re-layouts): the
+        # kernel then reads sequential 18 KB records instead of 128 strided 128-byte rows per tile
+        self.W_tiled = _ops.tile_weights(W_fp4, W_sf) if tile_weights else self.none
         with torch.cuda.device(dev):
             nbytes = scratch_bytes(M, self.N, self.K, self.R)
             self._head = _lib.load().biloco_b200_scratch_head_bytes(M, self.N, self.K, self.R, 0) // 4
@@ -125,10 +129,10 @@ class BiLoCoGemm:
         self.epoch += 1
         a = (A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32)
         if self.mode == 2:
-            return ops.biloco_gemm_mode2(*a, self.z, self.none, self.none, self.none, self.none, self.M, self.epoch)
+            return ops.biloco_gemm_mode2(*a, self.z, self.none, self.none, self.W_tiled, self.none, self.M, self.epoch)
         if self.mode == 4:
-            return ops.biloco_gemm_mode4(*a, self.z, self.none, self.M, self.epoch)
-        return ops.biloco_gemm_mode5(*a, self.z, self.none, self.none, self.M, self.epoch)
+            return ops.biloco_gemm_mode4(*a, self.z, self.W_tiled, self.M, self.epoch)
+        return ops.biloco_gemm_mode5(*a, self.z, self.W_tiled, self.none, self.M, self.epoch)
 
 
 def reference(A_fp4, A_sf, W_fp4, W_sf, alpha, X_bf16, V_packed, U_packed, S):

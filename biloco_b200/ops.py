@@ -56,7 +56,7 @@ def _check_fp4_operands(A, B, A_sf, B_sf, alpha):
     return rows, N, K
 
 
-def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None):
+def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None, B_tiled=None):
     rows, N, K = _check_fp4_operands(A, B, A_sf, B_sf, alpha)
     _req(1 <= m_rows <= rows, "m_rows must be in [1, A.size(1)]")
     R = 0
@@ -70,10 +70,14 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
         _req(U_col32.dtype == torch.int32 and U_col32.is_contiguous() and U_col32.dim() == 2 and U_col32.size(0) == N
              and U_col32.size(1) == (R + 31) // 32, "U_col32 must be contiguous int32 [N, ceil(R/32)]")
     _req(scratch.is_cuda and scratch.is_contiguous(), "scratch must be a contiguous CUDA tensor")
+    if B_tiled is not None:
+        want = _lib.load().biloco_b200_tiled_bytes(N, K)
+        _req(B_tiled.is_cuda and B_tiled.is_contiguous() and B_tiled.dtype == torch.uint8 and B_tiled.numel() == want,
+             f"tiled weight copy must be a contiguous uint8 CUDA tensor of {want} bytes")
     D = out if out is not None else torch.empty((1, rows, N), device=A.device, dtype=torch.bfloat16)
     with torch.cuda.device(A.device):
         rc = _lib.load().biloco_b200_fused_linear(
-            B.data_ptr(), B_sf.data_ptr(), alpha.data_ptr(), A.data_ptr(), A_sf.data_ptr(),
+            B.data_ptr(), B_sf.data_ptr(), B_tiled.data_ptr() if B_tiled is not None else None, alpha.data_ptr(), A.data_ptr(), A_sf.data_ptr(),
             X.data_ptr() if R else None, V.data_ptr() if R else None, U_col32.data_ptr() if R else None,
             S.data_ptr() if R else None, C.data_ptr() if C is not None else None, D.data_ptr(),
             scratch.data_ptr(), scratch.numel() * scratch.element_size(),
@@ -82,17 +86,38 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
     return D
 
 
+def tile_weights(B, B_sf):
+    """Unit-contiguous copy of the NVFP4 weight (codes [N, K/2] + block scales) that the fused kernel streams fastest."""
+    N, K = B.size(0), B.size(1) * 2
+    lib = _lib.load()
+    nbytes = lib.biloco_b200_tiled_bytes(N, K)
+    _req(nbytes > 0, f"cannot tile a weight with N={N} K={K}")
+    out = torch.empty(nbytes, device=B.device, dtype=torch.uint8)
+    with torch.cuda.device(B.device):
+        _lib.check(lib.biloco_b200_tile_weights(B.data_ptr(), B_sf.data_ptr(), out.data_ptr(), N, K, _stream()), "tile_weights")
+    return out
+
+
+def _tiled_or_none(t):
+    # The schemas have no argument for the re-laid-out weight. BiLoCoGemm passes it in the slot of one of the
+    # reference's own internal-layout tensors (V_perm / Diag / Corr); an empty tensor there means "row-major only".
+    return t if (t is not None and t.numel() > 0 and t.dtype == torch.uint8) else None
+
+
 def biloco_gemm_mode2(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Z_scratch, Flags, Diag, V_perm, U_rw,
                       m_rows, epoch):
-    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Z_scratch, m_rows, epoch, _lib.MODE_COUNTER)
+    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Z_scratch, m_rows, epoch, _lib.MODE_COUNTER,
+                  B_tiled=_tiled_or_none(V_perm))
 
 
 def biloco_gemm_mode4(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Ztag, Diag, m_rows, epoch):
-    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Ztag, m_rows, epoch, _lib.MODE_TAGGED)
+    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Ztag, m_rows, epoch, _lib.MODE_OWNER,
+                  B_tiled=_tiled_or_none(Diag))
 
 
 def biloco_gemm_mode5(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, Corr, Cnt, m_rows, epoch):
-    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, m_rows, epoch, _lib.MODE_SPLITK)
+    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, m_rows, epoch, _lib.MODE_COUNTER,
+                  B_tiled=_tiled_or_none(Corr))
 
 
 # ---- FP4-only GEMMs (the reference's unfused path and its baselines) ---------------------------------------

@@ -37,12 +37,13 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
 #define BILOCO_RULE_MSE 2            /* "four over six": per block, 6 or 4, smaller squared error */
 
 /* Schedules of the fused kernel; numbered like the reference's modes (biloco/kernel.py:18-26,66-76).
- *   2: z by all CTAs at entry (rank-sliced), arrival counter hand-off
- *   4: z by all CTAs at entry (rank-sliced), per-value epoch tags polled by the consumers
- *   5: as mode 2 with the z stage split over K as well (for batches where z dominates)          */
+ *   2: every CTA that contributes to a tile expands z for a share of the ranks and adds it to its partial sum
+ *      (spreads the expansion over all SMs: for larger batches)
+ *   4: the CTA that finishes a tile expands z for all ranks; the other contributors publish their partial sums
+ *      without waiting for z (shortest dependency chain: for the smallest batches)
+ * In both, z is computed by all CTAs at entry (rank-sliced) and handed over through an arrival counter. */
 #define BILOCO_MODE_COUNTER 2
-#define BILOCO_MODE_TAGGED 4
-#define BILOCO_MODE_SPLITK 5
+#define BILOCO_MODE_OWNER 4
 
 /* Human-readable text for an error code (host pointer, static storage). */
 const char* biloco_b200_error_string(int code);
@@ -100,11 +101,24 @@ size_t biloco_b200_scratch_head_bytes(int M, int N, int K, int R, int num_sms);
  * template parameters, csrc/biloco_gemm.cu:3017-3020). */
 int biloco_b200_schedule_info(int M, int N, int K, int R, int num_sms, int* out6);
 
+/* Bytes of the unit-contiguous copy of an [N, K] NVFP4 weight (codes + block scales, N padded to 128). */
+size_t biloco_b200_tiled_bytes(int N, int K);
+
+/* Re-layout W_codes u8 [N,K/2] + W_sf (atom layout) into the order the fused kernel streams them: one contiguous
+ * 18 KB record per (128-row tile, 256-wide k-tile) = the 128x128 B block of codes with the shared-memory swizzle
+ * already applied, followed by its four 512 B scale atoms. Done once per layer; lets every weight read of the
+ * fused kernel be a sequential 18 KB burst instead of 128 strided 128 B pieces.
+ * Replaces: the operand re-layouts BiLoCoGemm.__init__ performs in the reference (pack_v_perm / U_rw,
+ * biloco/kernel.py:98-102). K % 256 == 0; 16-byte aligned pointers. */
+int biloco_b200_tile_weights(const void* W_codes, const void* W_sf, void* W_tiled, int N, int K, biloco_stream_t stream);
+
 /* The fused decode linear, one launch:
  *     Y[m,n] = bf16( alpha[0] * sum_k A[m,k] W[n,k]  +  sum_i z[m,i] sign(U[i,n]) ),  z = S .* (X sign(V)^T)
  * W_codes u8 [N,K/2], W_sf E4M3 (atom layout, rows padded to 128), alpha fp32 [1] (device), A_codes u8
  * [A_rows,K/2] (A_rows >= M; rows beyond M are ignored), A_sf E4M3 (atom layout), X bf16 [M,K],
  * V_packed u8 [R,K/8], U_col32 int32 [N, ceil(R/32)], S bf16 [R], Y bf16 [M,N] (row stride N).
+ * W_tiled (may be NULL): the copy made by biloco_b200_tile_weights; when given it is streamed instead of
+ * W_codes / W_sf (which may then be NULL).
  * R == 0 skips the low-rank term (X, V, U, S may then be NULL). C_bf16 (may be NULL): bf16 [M,N] added
  * before the final rounding. `epoch` (>= 1) is the caller's launch count on this scratch (recorded in the status
  * words when a wait gives up, and selecting one of two z buffers).
@@ -114,7 +128,7 @@ int biloco_b200_schedule_info(int M, int N, int K, int R, int num_sms, int* out6
  * Replaces: torch.ops.biloco.biloco_gemm_mode2/4/5 (csrc/bindings.cpp:37-43; host launcher
  * csrc/biloco_gemm.cu:2986-3431, dispatchers :3435-3562) and, with R == 0, fp4_gemm / fp4_gemm_n64 /
  * fp4_gemm_n128 / fp4_gemm_residual (csrc/bindings.cpp:22-27, csrc/biloco_gemm.cu:2744-2983). */
-int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const float* alpha,
+int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
                              const void* A_codes, const void* A_sf, const void* X_bf16,
                              const void* V_packed, const int32_t* U_col32, const void* S_bf16,
                              const void* C_bf16, void* Y_bf16,
@@ -127,9 +141,10 @@ int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const float*
  * of the first wait that gave up. Words 1..3: block index, epoch and role of that wait. */
 int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t stream);
 
-/* Debug aid: while a device buffer is registered here, every fused launch of this process writes 8 uint64
- * %globaltimer stamps per CTA into it (CTA c at words 8c..8c+7: 0 start, 1 z published, 2 z complete seen,
- * 3 expansion done, 4 accumulators ready, 5/6 first/last segment stored). bytes >= 64 * CTAs; NULL turns it off.
+/* Debug aid: while a device buffer is registered here, every fused launch of this process writes 16 uint64
+ * %globaltimer stamps per CTA into it (CTA c at words 16c..16c+15: 0 set-up done, 1 z published, 2 z complete seen,
+ * 3 expansion done, 4 accumulators ready, 5/6 first/last segment stored, 7 last stage consumed, 8 first z reads
+ * landed, 9 z computed, 10 CTA entry). bytes >= 128 * CTAs; NULL turns it off.
  * Counterpart in the reference: the optional Diag tensor (csrc/biloco_gemm.cu:313-317, 446-464). */
 int biloco_b200_debug_stamps(void* device_buf, size_t bytes);
 

@@ -92,7 +92,7 @@ def test_host_side_argument_checks(lib):
     # rejected before anything touches a device
     assert lib.biloco_b200_binary_z(None, None, None, None, 1, 64, 8, None) == -1
     assert lib.biloco_b200_act_quant(None, None, None, None, None, None, None, None, 1, 1, 64, 2, None) == -1
-    assert lib.biloco_b200_fused_linear(*([None] * 12), 0, 1, 1, 128, 256, 0, 2, 1, None) == -1
+    assert lib.biloco_b200_fused_linear(*([None] * 13), 0, 1, 1, 128, 256, 0, 2, 1, None) == -1
     assert lib.biloco_b200_scratch_bytes(33, 5120, 5120, 512, 148) == 0        # M > 32
     assert lib.biloco_b200_scratch_bytes(1, 5120, 5000, 512, 148) == 0         # K % 256 != 0
     assert lib.biloco_b200_scratch_bytes(1, 5128, 5120, 512, 148) > 0          # N % 8 == 0 is enough
