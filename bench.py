@@ -198,7 +198,9 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    from biloco_b200 import fp4, kernel
+    from biloco_b200 import _lib, fp4, kernel
+    if args.no_pdl:
+        _lib.load().biloco_b200_set_option(1, 0)
 
     K, N, r, M, L = args.K, args.N, args.r, args.M, args.layers
     layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank, mode=args.mode)
@@ -322,6 +324,7 @@ def main():
     ap.add_argument("--N", type=int, default=5120)
     ap.add_argument("--r", type=int, default=512)
     ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
     ap.add_argument("--mode", type=int, default=None, help="schedule of the fused kernel (default: the measured table)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")

@@ -29,7 +29,6 @@ constexpr int FIRST_SF_WARP = FIRST_A_WARP + A_PRODUCERS;   // 4 warps, one per 
 constexpr int MMA_WARP = FIRST_SF_WARP + 4;
 constexpr int NUM_THREADS = (MMA_WARP + 1) * 32;
 static_assert(FIRST_SF_WARP % 4 == 0, "scale-factor warp q must own TMEM quadrant q");
-constexpr int START_BAR_THREADS = EPI_THREADS + 32 * (W_PRODUCERS + A_PRODUCERS);   // named barrier 2
 constexpr int TMEM_COLS = 256;
 constexpr int ACC_COL_STRIDE = 32;               // accumulator buffer b starts at column 32*b
 constexpr int SF_SETS = 4;                       // scale-factor column sets, used round-robin by consecutive units

@@ -71,17 +71,17 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = ctrl->tmem_base;
+    griddep_launch_dependents();   // the next kernel of the stream may start its own set-up and weight prefetch
     if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 0] = globaltimer_ns();
 
     if (warp >= FIRST_W_WARP && warp < FIRST_SF_WARP) {
         // ================= producers =================
-        // Weight producer j issues the 18 KB weight record of units j, j+4, ... (in processing order), activation
-        // producer j the activation tile and its scales of the same units. All of them first wait until the
-        // epilogue threads' first small reads (U words, V bits, x) have landed: small requests issued while the
-        // weight stream is in flight wait microseconds in the memory system's queues.
-        asm volatile("bar.sync 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
+        // Weight producer j issues the 18 KB weight record of units j, j+W_PRODUCERS, ... (in processing order),
+        // activation producer j the activation tile and its scales of the same units. Weights do not depend on the
+        // previous kernel of the stream, so their copies start at once; activations are what that kernel produced.
         if (lane == 0) {
             const bool is_w = warp < FIRST_A_WARP;
+            if (!is_w) griddep_wait();
             const int mine = is_w ? (warp - FIRST_W_WARP) : (warp - FIRST_A_WARP);
             const int nprod = is_w ? W_PRODUCERS : A_PRODUCERS;
             int i = 0;
@@ -199,7 +199,6 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         // ================= z stage, expansion, epilogue (128 threads) =================
         float* zb = p.zbuf + (size_t)(p.epoch & 1u) * 32 * p.Rpad;
         float* zs = reinterpret_cast<float*>(work);
-        bool signal_pending = true;
         const bool owner_mode = (p.mode & 0xff) == 4;
 
         // U words of the first chunk of the first two segments: requested before anything else, so that they do
@@ -224,18 +223,17 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 }
             }
 
-            z_stage<ROWS>(p, work, zb, cta, tid, signal_pending);
-            if (signal_pending) {   // this CTA had no ranks to compute
-                asm volatile("bar.arrive 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
-                signal_pending = false;
-            }
+            z_prefetch_v<ROWS>(p, work, cta, tid);
+            griddep_wait();        // everything below reads what earlier kernels of the stream wrote (x, scratch)
+            if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 11] = globaltimer_ns();
+            z_stage<ROWS>(p, work, zb, cta, tid, true);
             named_bar_sync(1, EPI_THREADS);    // orders every z store before thread 0's (cumulative) release
             if (tid == 0) {
                 red_release_add_u32(p.z_counter, 1u);
                 if (p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 1] = globaltimer_ns();
             }
         }
-        if (signal_pending) asm volatile("bar.arrive 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
+        griddep_wait();            // (again, for the R == 0 path; a second wait returns at once)
 
         bool z_ready = false;
         const float alpha = p.alpha[0];

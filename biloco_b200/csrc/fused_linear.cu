@@ -114,6 +114,7 @@ static int device_sm_count() {
     return cached[dev];
 }
 
+static int g_use_pdl = 1;                        // launch with programmatic stream serialization
 static unsigned long long* g_stamps = nullptr;   // debug time-stamp buffer for subsequent launches (or null)
 static size_t g_stamps_bytes = 0;
 
@@ -177,8 +178,18 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
             return BILOCO_ERR_CUDA;
         attr_set[dev] = true;
     }
-    fused_linear_kernel<MMA_N, ROWS><<<p.G, NUM_THREADS, Cfg<MMA_N>::SMEM_BYTES, stream>>>(tmW, tmA, p);
-    return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)p.G);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Cfg<MMA_N>::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, fused_linear_kernel<MMA_N, ROWS>, tmW, tmA, p);
+    return e == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
 }  // namespace biloco
@@ -294,6 +305,11 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
         case 16: return launch<16, 16>(tmW, tmA, p, s);
         default: return launch<32, 32>(tmW, tmA, p, s);
     }
+}
+
+extern "C" int biloco_b200_set_option(int option, int value) {
+    if (option == BILOCO_OPT_PDL) { g_use_pdl = value ? 1 : 0; return BILOCO_OK; }
+    return BILOCO_ERR_MODE;
 }
 
 extern "C" int biloco_b200_debug_stamps(void* device_buf, size_t bytes) {

@@ -10,10 +10,10 @@ namespace biloco {
 // activation (RP rows x XK k) and the sign words of up to VT_RANKS ranks are copied to shared memory with one
 // batch of cp.async; then warp q accumulates rank q (and q+4): lane l owns the 32-bit sign words l, l+32, ... of
 // the tile and reads the matching 32 activations as four conflict-free 128-bit shared loads.
-// signal_pending: once the first batch of copies has landed the producer warp is released (named barrier 2): small
-// reads issued while ~15 MB of weight traffic is in flight wait microseconds in the memory system's queues.
+// The sign words of the very first pass are weights, not activations: the caller copies them (z_prefetch_v) before it
+// waits for the previous kernel of the stream, and passes v_preloaded = true.
 template <int ROWS>
-__device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, float* zb, int cta, int tid, bool& signal_pending) {
+__device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, float* zb, int cta, int tid, bool v_preloaded) {
     constexpr int RP = ROWS < 8 ? ROWS : 8;          // rows per pass
     constexpr int XK = XT_BYTES / 2 / RP;            // k per pass
     constexpr int XW = XK / 32;                      // sign words per rank per pass
@@ -36,7 +36,8 @@ __device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, flo
 #pragma unroll 1
             for (int k0 = 0; k0 < p.K; k0 += XK) {
                 const int kc = (p.K - k0) < XK ? (p.K - k0) : XK;     // multiple of 256
-                named_bar_sync(1, EPI_THREADS);                        // previous pass fully consumed
+                const bool v_here = v_preloaded && ic == i0 && mg == 0 && k0 == 0;
+                if (!v_here) named_bar_sync(1, EPI_THREADS);           // previous pass fully consumed
                 const int nchunk = kc >> 3;                            // 16-byte chunks per activation row
 #pragma unroll 1
                 for (int idx = tid; idx < RP * nchunk; idx += EPI_THREADS) {
@@ -47,18 +48,16 @@ __device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, flo
                                p.X + (size_t)row * p.K + k0 + c * 8);
                 }
                 const int vch = kc >> 7;                               // 16-byte chunks of sign bits per rank
+                if (!v_here) {
 #pragma unroll 1
-                for (int idx = tid; idx < nr * vch; idx += EPI_THREADS) {
-                    const int q = idx / vch, c = idx - q * vch;
-                    cp_async16(vt_s + q * (XK / 8) + c * 16, p.Vp + (size_t)(ic + q) * kbytes + (k0 >> 3) + c * 16);
+                    for (int idx = tid; idx < nr * vch; idx += EPI_THREADS) {
+                        const int q = idx / vch, c = idx - q * vch;
+                        cp_async16(vt_s + q * (XK / 8) + c * 16, p.Vp + (size_t)(ic + q) * kbytes + (k0 >> 3) + c * 16);
+                    }
                 }
                 cp_async_commit();
                 cp_async_wait_all();
-                if (tid == 0 && p.stamps && signal_pending) p.stamps[(size_t)cta * STAMP_WORDS + 8] = globaltimer_ns();
-                if (signal_pending) {   // the first small reads have landed: release the weight stream
-                    asm volatile("bar.arrive 2, %0;" ::"r"(START_BAR_THREADS) : "memory");
-                    signal_pending = false;
-                }
+                if (tid == 0 && p.stamps && v_here) p.stamps[(size_t)cta * STAMP_WORDS + 8] = globaltimer_ns();
                 named_bar_sync(1, EPI_THREADS);
                 const int nwords = kc >> 5;
 #pragma unroll
@@ -100,6 +99,25 @@ __device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, flo
             }
         }
     }
+}
+
+// Sign words of the first z pass of this CTA (ranks i0.., k = 0..XK) into the work area; no activation involved.
+template <int ROWS>
+__device__ __forceinline__ void z_prefetch_v(const FusedParams& p, uint8_t* work, int cta, int tid) {
+    constexpr int RP = ROWS < 8 ? ROWS : 8;
+    constexpr int XK = XT_BYTES / 2 / RP;
+    const int i0 = cta * p.R / p.G;
+    const int i1 = (cta + 1) * p.R / p.G;
+    const int nr = (i1 - i0) < VT_RANKS ? (i1 - i0) : VT_RANKS;
+    const int kc = p.K < XK ? p.K : XK;
+    const int vch = kc >> 7;
+    const uint32_t vt_s = smem_u32(work) + XT_BYTES;
+#pragma unroll 1
+    for (int idx = tid; idx < nr * vch; idx += EPI_THREADS) {
+        const int q = idx / vch, c = idx - q * vch;
+        cp_async16(vt_s + q * (XK / 8) + c * 16, p.Vp + (size_t)(i0 + q) * (p.K >> 3) + c * 16);
+    }
+    cp_async_commit();
 }
 
 // corr[m] += sum over rank words [w0, w1) of z[m, 32w+b] * sign(U bit b of word w of this thread's column).

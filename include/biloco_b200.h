@@ -141,10 +141,17 @@ int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const void* 
  * of the first wait that gave up. Words 1..3: block index, epoch and role of that wait. */
 int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t stream);
 
+/* Process-wide options. BILOCO_OPT_PDL (default 1): launch the fused kernel with programmatic stream
+ * serialization, so that its set-up and its weight prefetch overlap the tail of the previous kernel of the stream
+ * (the kernel itself waits for that kernel before it reads activations or touches scratch). 0 = plain launches.
+ * The reference launches with a "pdl" flag as well (csrc/biloco_gemm.cu:3421-3429). */
+#define BILOCO_OPT_PDL 1
+int biloco_b200_set_option(int option, int value);
+
 /* Debug aid: while a device buffer is registered here, every fused launch of this process writes 16 uint64
  * %globaltimer stamps per CTA into it (CTA c at words 16c..16c+15: 0 set-up done, 1 z published, 2 z complete seen,
  * 3 expansion done, 4 accumulators ready, 5/6 first/last segment stored, 7 last stage consumed, 8 first z reads
- * landed, 9 z computed, 10 CTA entry). bytes >= 128 * CTAs; NULL turns it off.
+ * landed, 9 z computed, 10 CTA entry, 11 previous kernel complete). bytes >= 128 * CTAs; NULL turns it off.
  * Counterpart in the reference: the optional Diag tensor (csrc/biloco_gemm.cu:313-317, 446-464). */
 int biloco_b200_debug_stamps(void* device_buf, size_t bytes);
 
