@@ -31,6 +31,8 @@ SIGNATURES = {
     "biloco_b200_fused_linear": (_i, [_vp] * 13 + [_sz] + [_i] * 7 + [_vp]),
     "biloco_b200_set_option": (_i, [_i, _i]),
     "biloco_b200_debug_stamps": (_i, [_vp, _sz]),
+    "biloco_b200_fused_linear_noalloc": (_i, [_vp] * 12 + [_i] * 6 + [_vp]),
+    "biloco_b200_noalloc_status": (_i, [ctypes.POINTER(ctypes.c_int32), _vp]),
     "biloco_b200_read_status": (_i, [_vp, ctypes.POINTER(ctypes.c_int32), _vp]),
     "biloco_b200_fp4_gemm_simt": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
 }

@@ -307,6 +307,118 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Entry point for callers that may not allocate device memory (see include/biloco_b200.h). Its scratch is the
+// file-scope array below: every GPU that loads this library holds BILOCO_NOALLOC_SCRATCH_BYTES for it until exit.
+// In host code the array's name is only a stand-in; the device address comes from cudaGetSymbolAddress.
+// ---------------------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[BILOCO_NOALLOC_SCRATCH_BYTES];
+static void* g_noalloc_ptr[64] = {nullptr};                 // per device, filled by the first call on that device
+static unsigned long long g_noalloc_shape[64] = {0};        // problem shape of the last call on that device
+
+extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                                const void* A_codes, const void* A_sf, const void* X_bf16,
+                                                const void* V_packed, const int32_t* U_col32, const void* S_bf16,
+                                                const void* C_bf16, void* Y_bf16, int M, int A_rows, int N, int K, int R,
+                                                int mode, biloco_stream_t stream) {
+    if ((!W_tiled && (!W_codes || !W_sf)) || !alpha || !A_codes || !A_sf || !Y_bf16) return BILOCO_ERR_NULL;
+    if (R > 0 && (!X_bf16 || !V_packed || !U_col32 || !S_bf16)) return BILOCO_ERR_NULL;
+    if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER) return BILOCO_ERR_MODE;
+    if (A_rows < M || A_rows > 128) return BILOCO_ERR_SHAPE;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BILOCO_ERR_CUDA;
+    const int sms = device_sm_count();
+    if (sms < 1) return BILOCO_ERR_CUDA;
+    ScratchLayout L;
+    if (!make_layout(M, N, K, R, sms, &L)) return BILOCO_ERR_SHAPE;
+    if (L.total > (size_t)BILOCO_NOALLOC_SCRATCH_BYTES) return BILOCO_ERR_LIMIT;     // beyond the built-in scratch
+    if (((uintptr_t)W_tiled & 15) || ((uintptr_t)W_codes & 15) || ((uintptr_t)A_codes & 15) || ((uintptr_t)W_sf & 15) ||
+        ((uintptr_t)A_sf & 15) || ((uintptr_t)X_bf16 & 15) || ((uintptr_t)U_col32 & 3))
+        return BILOCO_ERR_ALIGN;
+    cudaStream_t s = (cudaStream_t)stream;
+
+    // set-up, once per device with that device current: the array's device address
+    if (!g_noalloc_ptr[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) return BILOCO_ERR_CUDA;
+        g_noalloc_ptr[dev] = ptr;
+    }
+    uint8_t* sc = (uint8_t*)g_noalloc_ptr[dev];
+
+    // The array keeps what the last call left. Status words and counters must start at zero (they are zero after a
+    // call that ran to completion, but not after one whose wait gave up); the z area must be zero beyond rank R, which
+    // a previous problem with more ranks may have written.
+    const unsigned long long shape = ((unsigned long long)(unsigned)M << 48) ^ ((unsigned long long)(unsigned)N << 28) ^
+                                     ((unsigned long long)(unsigned)K << 12) ^ (unsigned long long)(unsigned)R;
+    const size_t clear = (g_noalloc_shape[dev] == shape) ? L.off_z : L.off_part;
+    if (cudaMemsetAsync(sc, 0, clear, s) != cudaSuccess) return BILOCO_ERR_CUDA;
+    g_noalloc_shape[dev] = shape;
+
+    // tensor maps are encoded on the stack for every call (the cache of the allocating entry point grows on the heap)
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return BILOCO_ERR_CUDA;
+    auto encode = [&](const void* ptr, int rows, int box_rows, CUtensorMap* out) -> bool {
+        const cuuint64_t gdim[2] = {(cuuint64_t)(K / 2), (cuuint64_t)rows};
+        const cuuint64_t gstride[1] = {(cuuint64_t)(K / 2)};
+        const cuuint32_t box[2] = {(cuuint32_t)KT_BYTES, (cuuint32_t)box_rows};
+        const cuuint32_t estr[2] = {1, 1};
+        return enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    CUtensorMap tmW, tmA;
+    if (!encode(A_codes, A_rows, L.mma_n, &tmA)) return BILOCO_ERR_CUDA;
+    if (W_tiled) tmW = tmA;
+    else if (!encode(W_codes, N, TILE_N, &tmW)) return BILOCO_ERR_CUDA;
+
+    FusedParams p;
+    p.W_tiled = (const uint8_t*)W_tiled;
+    p.W_sf = (const uint8_t*)W_sf;
+    p.A_sf = (const uint8_t*)A_sf;
+    p.alpha = alpha;
+    p.X = (const __nv_bfloat16*)X_bf16;
+    p.Vp = (const uint8_t*)V_packed;
+    p.Ucol = U_col32;
+    p.S = (const __nv_bfloat16*)S_bf16;
+    p.C = (const __nv_bfloat16*)C_bf16;
+    p.Y = (__nv_bfloat16*)Y_bf16;
+    p.status = (int32_t*)sc;
+    p.z_counter = (uint32_t*)(sc + L.off_zcnt);
+    p.tile_cnt = (uint32_t*)(sc + L.off_tilecnt);
+    p.zbuf = (float*)(sc + L.off_z);
+    p.partials = (float*)(sc + L.off_part);
+    p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = L.Rw; p.Rpad = L.Rpad;
+    p.ntile = L.ntile; p.nkt = L.nkt; p.G = L.G; p.max_slots = L.max_slots;
+    p.epoch = 1u;
+    p.mode = mode;
+    p.z_consumers = L.G;
+    if ((mode & 0xff) == BILOCO_MODE_OWNER) {
+        int consumers = 0, prev = -1;
+        const int T = L.ntile * L.nkt;
+        for (int t = 0; t < L.ntile; ++t) {
+            const int c = sched_cta_of_unit(t * L.nkt + L.nkt - 1, T, L.G);
+            if (c != prev) { ++consumers; prev = c; }
+        }
+        p.z_consumers = consumers;
+    }
+    p.stamps = nullptr;
+    switch (rows_for(M)) {
+        case 1: return launch<8, 1>(tmW, tmA, p, s);
+        case 2: return launch<8, 2>(tmW, tmA, p, s);
+        case 4: return launch<8, 4>(tmW, tmA, p, s);
+        case 8: return launch<8, 8>(tmW, tmA, p, s);
+        case 16: return launch<16, 16>(tmW, tmA, p, s);
+        default: return launch<32, 32>(tmW, tmA, p, s);
+    }
+}
+
+extern "C" int biloco_b200_noalloc_status(int32_t* out16, biloco_stream_t stream) {
+    int dev = 0;
+    if (!out16) return BILOCO_ERR_NULL;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_noalloc_ptr[dev]) return BILOCO_ERR_CUDA;
+    return biloco_b200_read_status(g_noalloc_ptr[dev], out16, stream);
+}
+
 extern "C" int biloco_b200_set_option(int option, int value) {
     if (option == BILOCO_OPT_PDL) { g_use_pdl = value ? 1 : 0; return BILOCO_OK; }
     return BILOCO_ERR_MODE;

@@ -136,6 +136,35 @@ int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const void* 
                              int M, int A_rows, int N, int K, int R,
                              int mode, int epoch, biloco_stream_t stream);
 
+/* The fused decode linear for callers that cannot allocate device memory.
+ *
+ * Some hosts of this library have no way to obtain scratch: code running inside another framework's stream-ordered
+ * or pooled allocator that must not be re-entered from a callback, inference servers that freeze their memory
+ * plan at start-up, plugins loaded into a process whose memory budget is fully handed out. biloco_b200_fused_linear
+ * asks such a caller for a scratch buffer it cannot provide. This variant takes none: its scratch is an array built
+ * into the library (BILOCO_NOALLOC_SCRATCH_BYTES of device memory on every GPU that loads the library, held until the
+ * process exits). It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are still
+ * the caller's. Same arithmetic and same results as biloco_b200_fused_linear (arguments as there, minus scratch and
+ * epoch).
+ *   - Limit: problems whose biloco_b200_scratch_bytes(M, N, K, R, 0) exceeds BILOCO_NOALLOC_SCRATCH_BYTES are rejected
+ *     with BILOCO_ERR_LIMIT (nothing is enqueued). K = N = 5120 needs 0.8 MB (M <= 8) to 2.8 MB (M = 32).
+ *   - The first call on a device looks up the array's device address (a set-up step of a few microseconds): make
+ *     that first call outside any stream capture.
+ *   - All calls on a device share the one array. It keeps what the previous call left; each call clears, on `stream`,
+ *     the words that have to start at zero. Two calls that overlap on the GPU (different streams without ordering)
+ *     race on it: keep calls to this entry point ordered.
+ * No counterpart in the reference (its scratch tensors are allocated by BiLoCoGemm through PyTorch). */
+#define BILOCO_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
+int biloco_b200_fused_linear_noalloc(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                     const void* A_codes, const void* A_sf, const void* X_bf16,
+                                     const void* V_packed, const int32_t* U_col32, const void* S_bf16,
+                                     const void* C_bf16, void* Y_bf16,
+                                     int M, int A_rows, int N, int K, int R, int mode, biloco_stream_t stream);
+
+/* Status words (as biloco_b200_read_status) of the built-in scratch of the current device; BILOCO_ERR_CUDA before the
+ * first biloco_b200_fused_linear_noalloc call on that device. No counterpart in the reference. */
+int biloco_b200_noalloc_status(int32_t* out16, biloco_stream_t stream);
+
 /* Copy the 16 int32 status words at the start of a scratch buffer to host memory `out16` (synchronises
  * `stream`). Word 0: 0 = no device-side wait ran out since the scratch was last zeroed; otherwise the code
  * of the first wait that gave up. Words 1..3: block index, epoch and role of that wait. */
