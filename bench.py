@@ -33,8 +33,8 @@ if ROOT not in sys.path:
 
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of fused_linear_kernel<8> at M=1, K=N=5120, r=512,
-# from the ncu capture summarised under profiles/ (None until a capture exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# from the ncu capture summarised in profiles/fused_linear_M1_K5120_N5120_r512.md (other shapes: null)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 15_530_000
 
 
 def algorithmic_bytes(K, N, r):
@@ -99,7 +99,7 @@ class ClockSampler:
                 "samples": len(inside)}
 
 
-def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed, mode=None):
+def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed, mode=None, share_act=False):
     """Synthetic layers in the construction of the reference's timing scripts (scripts/problem.py:7-27, random
     block scales in [0.25, 2]), activations ~N(0,1) with 1 % outlier channels x20 quantised by the device quantiser."""
     g = torch.Generator(device=dev).manual_seed(seed)
@@ -115,7 +115,10 @@ def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed, mode=None):
         idx = torch.randperm(K, device=dev, generator=g)[: K // 100]
         x[:, idx] *= 20
         x = x.to(torch.bfloat16).contiguous()
-        q = fp4.quantize_activation(x, "mse", w_gscale=w_gs, rows=M)
+        if share_act and layers:      # one activation buffer for every layer, as the hidden state of a decoder is
+            x, w_gs, q = layers[0]["x"], layers[0]["w_gs"], layers[0]["q"]
+        else:
+            q = fp4.quantize_activation(x, "mse", w_gscale=w_gs, rows=M)
         gemm = kernel.BiLoCoGemm(W, W_sf, q["alpha"], Vp, Up, S, M=M, mode=mode)
         layers.append(dict(gemm=gemm, q=q, x=x, w_gs=w_gs, x_host=x.cpu().pin_memory(),
                            y_host=torch.empty(M, N, dtype=torch.bfloat16).pin_memory()))
@@ -201,6 +204,8 @@ def run_ours(args):
     from biloco_b200 import _lib, fp4, kernel
     if args.no_pdl:
         _lib.load().biloco_b200_set_option(1, 0)
+    if args.ring:
+        _lib.load().biloco_b200_set_option(2, args.ring)
 
     K, N, r, M, L = args.K, args.N, args.r, args.M, args.layers
     layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank, mode=args.mode)
@@ -299,7 +304,7 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": L * M * K * 2, "d2h_bytes_per_step": L * M * N * 2,
                 "steps": e2e_steps, "us_per_call": e2e_s / e2e_steps / L * 1e6},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": f"{peak_kind} (STREAM-style copy)",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (M, K, N, r) == (1, 5120, 5120, 512) else None, "peak_source": f"{peak_kind} (STREAM-style copy)",
                      "kernel": "fused_linear_kernel", "algorithmic_bytes_per_launch": bytes_call},
     }
     if world == 1 and not args.no_cpu:
@@ -325,6 +330,7 @@ def main():
     ap.add_argument("--r", type=int, default=512)
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
+    ap.add_argument("--ring", type=int, default=0, help="pipeline stages in flight (0 = library default)")
     ap.add_argument("--mode", type=int, default=None, help="schedule of the fused kernel (default: the measured table)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")

@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(_HERE, "libbiloco_b200.so")
 
 OK = 0
 RULES = {"static_6": 0, "static_4": 1, "mse": 2}
-MODE_COUNTER, MODE_OWNER = 2, 4
+MODE_COUNTER, MODE_OWNER, MODE_CLUSTER = 2, 4, 5
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 
@@ -25,6 +25,7 @@ SIGNATURES = {
     "biloco_b200_act_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "biloco_b200_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "biloco_b200_scratch_head_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "biloco_b200_mode_supported": (_i, [_i, _i, _i, _i, _i, _i]),
     "biloco_b200_schedule_info": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "biloco_b200_tiled_bytes": (_sz, [_i, _i]),
     "biloco_b200_tile_weights": (_i, [_vp, _vp, _vp, _i, _i, _vp]),

@@ -50,6 +50,8 @@ constexpr int ZS_WORDS = 4;                      // rank words (32 ranks each) o
 constexpr int ZS_STRIDE = ZS_WORDS * 32 + 4;     // floats per staged row (+4: rows start in different banks)
 constexpr int STAMP_WORDS = 16;                  // uint64 time stamps per CTA when debug stamps are on
 static_assert(32 * ZS_STRIDE * 4 <= WORK_BYTES, "z staging must fit in the work area");
+constexpr int RED_OFF = 8 * ZS_STRIDE * 4 + 256;   // cluster mode (rows <= 8): partial sums of the peers start here,
+constexpr int RED_BYTES = WORK_BYTES - RED_OFF;    // after the z staging rows, [peer][row][128] floats
 
 template <int MMA_N>
 struct Cfg {
@@ -80,6 +82,10 @@ struct FusedParams {
     int M, N, K, R, Rw, Rpad;
     int ntile, nkt, G, max_slots;
     int z_consumers;          // CTAs that wait for z in this launch (all of them, or only those that finish a tile)
+    int ring;                 // pipeline stages in use (<= Cfg::STAGES). Every byte a CTA requests early is delivered
+                              // ahead of its later small reads (x, z, partial sums) on the SM's inbound path, so a
+                              // deep ring buys nothing for a short stream and delays the latency-critical reads
+    int cluster;              // > 1: a tile belongs to a cluster of this many CTAs (partial sums through DSMEM)
     uint32_t epoch;
     int mode;
     unsigned long long* stamps;   // debug: STAMP_WORDS %globaltimer values per CTA, or null
@@ -92,6 +98,8 @@ struct Ctrl {   // lives in shared memory after the stages
     uint64_t acc_empty[2];
     uint64_t sf_full[SF_SETS];    // scale factors of a unit are in TMEM set q (128 arrivals)
     uint64_t sf_empty[SF_SETS];   // the MMAs that read set q have completed (tcgen05.commit)
+    float zred[8][VT_RANKS];      // z stage: per-warp partial sums
+    uint64_t red_bar;             // cluster mode, finisher CTA: the other CTAs' partial sums are in this CTA's smem
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -99,7 +107,7 @@ static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
 
 enum : int {   // status codes of waits that ran out
     ST_EMPTY = 101, ST_FULL = 102, ST_ACC_EMPTY = 103, ST_ACC_FULL = 104, ST_Z = 105, ST_TILE = 106, ST_SF_FULL = 107,
-    ST_SF_EMPTY = 108,
+    ST_SF_EMPTY = 108, ST_CLUSTER = 109,
 };
 
 // The wait helpers are deliberately not inlined: the kernel's machine code is executed once, cold, per CTA, and
@@ -136,6 +144,19 @@ __device__ __noinline__ bool wait_counter(const uint32_t* ctr, uint32_t target, 
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if ((int32_t)(ld_acquire_u32(ctr) - target) >= 0) return true;
+        if ((it & 31u) == 31u) {
+            if (ctrl->abort) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, status, epoch, code, 0); return false; }
+        }
+    }
+}
+
+__device__ __noinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, Ctrl* ctrl, int32_t* status, uint32_t epoch, int code) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
         if ((it & 31u) == 31u) {
             if (ctrl->abort) return false;
             const uint64_t now = globaltimer_ns();
@@ -203,12 +224,18 @@ struct SegInfo {
 __device__ __forceinline__ SegInfo seg_info(const FusedParams& p, int T, int cta, int u, int cnt, bool owner_mode) {
     SegInfo s;
     s.t = (int)((unsigned)u / (unsigned)p.nkt);
-    const int c_first = sched_cta_of_unit(s.t * p.nkt, T, p.G);
-    const int c_last = sched_cta_of_unit(s.t * p.nkt + p.nkt - 1, T, p.G);
-    s.nc = c_last - c_first + 1;
-    s.slot = cta - c_first;
     s.complete = (cnt == p.nkt);
-    s.finisher = s.complete || cta == c_last;
+    if (p.cluster > 1) {
+        s.nc = p.cluster;
+        s.slot = cta - s.t * p.cluster;
+        s.finisher = s.slot == p.cluster - 1;
+    } else {
+        const int c_first = sched_cta_of_unit(s.t * p.nkt, T, p.G);
+        const int c_last = sched_cta_of_unit(s.t * p.nkt + p.nkt - 1, T, p.G);
+        s.nc = c_last - c_first + 1;
+        s.slot = cta - c_first;
+        s.finisher = s.complete || cta == c_last;
+    }
     if (owner_mode) {
         s.w0 = 0;
         s.w1 = s.finisher ? p.Rw : 0;

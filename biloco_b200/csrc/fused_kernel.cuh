@@ -37,9 +37,17 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const int lane = tid & 31;
     const int cta = blockIdx.x;
 
+    const int ring = p.ring < C::STAGES ? p.ring : C::STAGES;   // stages in use (see FusedParams::ring)
     const int T = p.ntile * p.nkt;
-    const int u0 = sched_first_unit(cta, T, p.G);
-    const int u1 = sched_first_unit(cta + 1, T, p.G);
+    int u0, u1;
+    if (p.cluster > 1) {      // CTA r of the cluster that owns tile t takes k-tiles [r*nkt/c, (r+1)*nkt/c)
+        const int t = cta / p.cluster, r = cta - t * p.cluster;
+        u0 = t * p.nkt + r * p.nkt / p.cluster;
+        u1 = t * p.nkt + (r + 1) * p.nkt / p.cluster;
+    } else {
+        u0 = sched_first_unit(cta, T, p.G);
+        u1 = sched_first_unit(cta + 1, T, p.G);
+    }
 
     // ---------------- set-up ----------------
     if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 10] = globaltimer_ns();
@@ -58,6 +66,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             mbar_init(smem_u32(&ctrl->sf_full[q]), 128);
             mbar_init(smem_u32(&ctrl->sf_empty[q]), 1);
         }
+        mbar_init(smem_u32(&ctrl->red_bar), p.cluster > 1 ? (uint32_t)(p.cluster - 1) : 1u);
         ctrl->abort = 0;
         fence_mbar_init();
         prefetch_tmap(&tmW);
@@ -70,6 +79,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    if (p.cluster > 1) cluster_sync_all();   // every CTA's barriers exist before a peer may arrive on them
     const uint32_t tmem = ctrl->tmem_base;
     griddep_launch_dependents();   // the next kernel of the stream may start its own set-up and weight prefetch
     if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 0] = globaltimer_ns();
@@ -95,8 +105,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll 1
                 for (int u = us; u < us + cnt; ++u, ++i, ++kt) {
                     if (i % nprod != mine) continue;
-                    const int s = i % C::STAGES;
-                    const int use = i / C::STAGES;
+                    const int s = i % ring;
+                    const int use = i / ring;
                     if (use > 0 && !wait_bar(smem_u32(&ctrl->empty[s]), (use - 1) & 1, ctrl, p.status, p.epoch, ST_EMPTY, warp)) {
                         ok = false;
                         break;
@@ -127,6 +137,15 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         // eight of them per unit occupy the tensor pipe longer than the unit's four MMAs (measured); here warp q
         // writes quadrant q from registers instead: per unit 8 x 128-bit shared loads and 2 x tcgen05.st per thread.
         const uint32_t quad = (uint32_t)((warp & 3) * 32) << 16;
+        if (p.R > 0) {
+            // until the first weights land these warps are idle: they are the second half of the z-stage threads
+            const int zt = EPI_THREADS + (tid - FIRST_SF_WARP * 32);
+            float* zb = p.zbuf + (size_t)(p.epoch & 1u) * 32 * p.Rpad;
+            z_prefetch_v<ROWS>(p, work, cta, zt);
+            griddep_wait();
+            z_stage<ROWS>(p, ctrl, work, zb, cta, zt, true);
+            named_bar_sync(3, Z_THREADS);      // every z store is ordered before the publishing thread's release
+        }
         int i = 0;
         bool ok = true;
 #pragma unroll 1
@@ -134,9 +153,9 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             const int cnt = sw.count();
 #pragma unroll 1
             for (int j = 0; j < cnt; ++j, ++i) {
-                const int s = i % C::STAGES;
+                const int s = i % ring;
                 const int q = i % SF_SETS;
-                bool ready = wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p.status, p.epoch, ST_FULL, warp);
+                bool ready = wait_bar(smem_u32(&ctrl->full[s]), (i / ring) & 1, ctrl, p.status, p.epoch, ST_FULL, warp);
                 if (ready && i >= SF_SETS)
                     ready = wait_bar(smem_u32(&ctrl->sf_empty[q]), ((i / SF_SETS) - 1) & 1, ctrl, p.status, p.epoch, ST_SF_EMPTY, warp);
                 if (!__all_sync(0xffffffffu, ready)) { ok = false; break; }     // warp-uniform: the TMEM stores are warp-wide
@@ -172,8 +191,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             tc_fence_after_sync();
 #pragma unroll 1
             for (int j = 0; j < cnt; ++j, ++i) {
-                const int s = i % C::STAGES;
-                if (!wait_bar(smem_u32(&ctrl->full[s]), (i / C::STAGES) & 1, ctrl, p.status, p.epoch, ST_FULL, MMA_WARP)) { ok = false; break; }
+                const int s = i % ring;
+                if (!wait_bar(smem_u32(&ctrl->full[s]), (i / ring) & 1, ctrl, p.status, p.epoch, ST_FULL, MMA_WARP)) { ok = false; break; }
                 if (!wait_bar(smem_u32(&ctrl->sf_full[i % SF_SETS]), (i / SF_SETS) & 1, ctrl, p.status, p.epoch, ST_SF_FULL, MMA_WARP)) { ok = false; break; }
                 tc_fence_after_sync();
                 if (lane == 0) {
@@ -190,7 +209,6 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     tc_commit(smem_u32(&ctrl->empty[s]));
                     tc_commit(smem_u32(&ctrl->sf_empty[i % SF_SETS]));
                     if (j == cnt - 1) tc_commit(smem_u32(&ctrl->acc_full[buf]));
-                    if (p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 7] = globaltimer_ns();   // latest stage landed
                 }
                 __syncwarp();
             }
@@ -225,9 +243,9 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
             z_prefetch_v<ROWS>(p, work, cta, tid);
             griddep_wait();        // everything below reads what earlier kernels of the stream wrote (x, scratch)
-            if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 11] = globaltimer_ns();
-            z_stage<ROWS>(p, work, zb, cta, tid, true);
-            named_bar_sync(1, EPI_THREADS);    // orders every z store before thread 0's (cumulative) release
+            if (tid == 0 && p.stamps) { p.stamps[(size_t)cta * STAMP_WORDS + 11] = globaltimer_ns(); p.stamps[(size_t)cta * STAMP_WORDS + 12] = clock64(); }
+            z_stage<ROWS>(p, ctrl, work, zb, cta, tid, true);
+            named_bar_sync(3, Z_THREADS);      // orders every z store before thread 0's (cumulative) release
             if (tid == 0) {
                 red_release_add_u32(p.z_counter, 1u);
                 if (p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 1] = globaltimer_ns();
@@ -289,7 +307,35 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll
             for (int m = 0; m < ROWS; ++m) v[m] = alpha * acc[m] + corr[m];
 
-            if (!si.finisher) {
+            if (p.cluster > 1) {
+                // ---- cluster mode: partial sums travel through the finisher's shared memory ----
+                const uint32_t red0 = smem_u32(work + RED_OFF);
+                if (!si.finisher) {
+                    const uint32_t dst = map_to_cta(red0 + (uint32_t)((slot * ROWS) * TILE_N + tid) * 4u, (uint32_t)(p.cluster - 1));
+#pragma unroll
+                    for (int m = 0; m < ROWS; ++m) st_cluster_f32(dst + (uint32_t)(m * TILE_N) * 4u, v[m]);
+                    named_bar_sync(1, EPI_THREADS);     // all 128 stores precede thread 0's (cumulative) release
+                    if (tid == 0) mbar_arrive_remote_release(map_to_cta(smem_u32(&ctrl->red_bar), (uint32_t)(p.cluster - 1)));
+                } else {
+                    wait_bar_cluster(smem_u32(&ctrl->red_bar), 0, ctrl, p.status, p.epoch, ST_CLUSTER);
+                    if (!epi_sync_ok(ctrl)) break;
+                    const float* red = reinterpret_cast<const float*>(work + RED_OFF);
+#pragma unroll 1
+                    for (int sl = 0; sl < nc - 1; ++sl)
+#pragma unroll
+                        for (int m = 0; m < ROWS; ++m) v[m] += red[(sl * ROWS + m) * TILE_N + tid];
+                    if (valid) {
+#pragma unroll
+                        for (int m = 0; m < ROWS; ++m) {
+                            if (m < p.M) {
+                                float o = v[m];
+                                if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
+                                p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
+                            }
+                        }
+                    }
+                }
+            } else if (!si.finisher) {
                 // contributor: publish the fp32 partial
                 float* P = p.partials + ((size_t)t * p.max_slots + slot) * MMA_N * TILE_N;
 #pragma unroll
@@ -336,6 +382,9 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         while (globaltimer_ns() - t0 < 2000000ull) { }
         __syncthreads();
     }
+    // cluster mode: no CTA leaves while a peer could still write into its shared memory (also on the failure path:
+    // every CTA gets here because every wait is bounded)
+    if (p.cluster > 1) cluster_sync_all();
     if (warp == MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, TMEM_COLS);

@@ -114,6 +114,7 @@ static int device_sm_count() {
     return cached[dev];
 }
 
+static int g_ring = 16;                          // pipeline stages in use (clamped to what fits)
 static int g_use_pdl = 1;                        // launch with programmatic stream serialization
 static unsigned long long* g_stamps = nullptr;   // debug time-stamp buffer for subsequent launches (or null)
 static size_t g_stamps_bytes = 0;
@@ -165,6 +166,21 @@ __global__ void tile_weights_kernel(const uint8_t* __restrict__ W, const uint8_t
         *reinterpret_cast<uint4*>(rec + W_TILE_BYTES + i * 16) = *reinterpret_cast<const uint4*>(sf + i * 16);
 }
 
+// Cluster mode: tile t is owned by a cluster of c CTAs that split its k-tiles; c = as many as fit on the device
+// (ntile * c <= SMs), at most 8, at most one per k-tile. 0 when the shape does not suit the mode: fewer than two
+// CTAs per tile, more than 8 rows (the peers' partial sums must fit the finisher's work area), or a grid that would
+// leave more than a third of the SMs idle.
+static int cluster_size_for(int M, int ntile, int nkt, int num_sms) {
+    if (M > 8) return 0;
+    int c = num_sms / ntile;
+    if (c > 8) c = 8;
+    if (c > nkt) c = nkt;
+    if (c < 2) return 0;
+    if ((c - 1) * 8 * TILE_N * 4 > RED_BYTES) return 0;
+    if (ntile * c * 3 < num_sms * 2) return 0;
+    return c;
+}
+
 static int rows_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : (M <= 16 ? 16 : 32)))); }
 
 template <int MMA_N, int ROWS>
@@ -183,11 +199,22 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = Cfg<MMA_N>::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (g_use_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (p.cluster > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)p.cluster;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    cfg.numAttrs = na;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, fused_linear_kernel<MMA_N, ROWS>, tmW, tmA, p);
     return e == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
@@ -208,6 +235,15 @@ extern "C" size_t biloco_b200_scratch_head_bytes(int M, int N, int K, int R, int
     ScratchLayout L;
     if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
     return L.off_z;
+}
+
+extern "C" int biloco_b200_mode_supported(int M, int N, int K, int R, int mode, int num_sms) {
+    if (num_sms == 0) num_sms = device_sm_count();
+    ScratchLayout L;
+    if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
+    if (mode == BILOCO_MODE_COUNTER || mode == BILOCO_MODE_OWNER) return 1;
+    if (mode == BILOCO_MODE_CLUSTER) return cluster_size_for(M, L.ntile, L.nkt, num_sms) >= 2 ? 1 : 0;
+    return 0;
 }
 
 extern "C" int biloco_b200_schedule_info(int M, int N, int K, int R, int num_sms, int* out6) {
@@ -244,7 +280,7 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
                                         biloco_stream_t stream) {
     if ((!W_tiled && (!W_codes || !W_sf)) || !alpha || !A_codes || !A_sf || !Y_bf16 || !scratch) return BILOCO_ERR_NULL;
     if (R > 0 && (!X_bf16 || !V_packed || !U_col32 || !S_bf16)) return BILOCO_ERR_NULL;
-    if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER) return BILOCO_ERR_MODE;
+    if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER && (mode & 0xff) != BILOCO_MODE_CLUSTER) return BILOCO_ERR_MODE;
     if (epoch < 1) return BILOCO_ERR_EPOCH;
     if (A_rows < M || A_rows > 128) return BILOCO_ERR_SHAPE;
     const int sms = device_sm_count();
@@ -284,7 +320,14 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
     p.ntile = L.ntile; p.nkt = L.nkt; p.G = L.G; p.max_slots = L.max_slots;
     p.epoch = (uint32_t)epoch;
     p.mode = mode;
-    p.z_consumers = L.G;
+    p.cluster = 0;
+    p.ring = g_ring;
+    if ((mode & 0xff) == BILOCO_MODE_CLUSTER) {
+        p.cluster = cluster_size_for(M, L.ntile, L.nkt, sms);
+        if (p.cluster < 2) return BILOCO_ERR_SHAPE;
+        p.G = L.ntile * p.cluster;
+    }
+    p.z_consumers = p.G;
     if ((mode & 0xff) == BILOCO_MODE_OWNER) {   // only CTAs that finish a tile wait for z
         int consumers = 0, prev = -1;
         const int T = L.ntile * L.nkt;
@@ -294,7 +337,7 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
         }
         p.z_consumers = consumers;
     }
-    p.stamps = (g_stamps && g_stamps_bytes >= (size_t)L.G * STAMP_WORDS * 8) ? g_stamps : nullptr;
+    p.stamps = (g_stamps && g_stamps_bytes >= (size_t)p.G * STAMP_WORDS * 8) ? g_stamps : nullptr;
 
     cudaStream_t s = (cudaStream_t)stream;
     switch (rows_for(M)) {
@@ -391,6 +434,8 @@ extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void*
     p.ntile = L.ntile; p.nkt = L.nkt; p.G = L.G; p.max_slots = L.max_slots;
     p.epoch = 1u;
     p.mode = mode;
+    p.cluster = 0;
+    p.ring = g_ring;
     p.z_consumers = L.G;
     if ((mode & 0xff) == BILOCO_MODE_OWNER) {
         int consumers = 0, prev = -1;
@@ -421,6 +466,7 @@ extern "C" int biloco_b200_noalloc_status(int32_t* out16, biloco_stream_t stream
 
 extern "C" int biloco_b200_set_option(int option, int value) {
     if (option == BILOCO_OPT_PDL) { g_use_pdl = value ? 1 : 0; return BILOCO_OK; }
+    if (option == BILOCO_OPT_RING) { g_ring = value < 2 ? 2 : value; return BILOCO_OK; }
     return BILOCO_ERR_MODE;
 }
 

@@ -6,118 +6,163 @@
 
 namespace biloco {
 
-// z stage, run by the 128 epilogue threads. CTA `cta` owns ranks [cta*R/G, (cta+1)*R/G). Per pass a tile of the
-// activation (RP rows x XK k) and the sign words of up to VT_RANKS ranks are copied to shared memory with one
-// batch of cp.async; then warp q accumulates rank q (and q+4): lane l owns the 32-bit sign words l, l+32, ... of
-// the tile and reads the matching 32 activations as four conflict-free 128-bit shared loads.
-// The sign words of the very first pass are weights, not activations: the caller copies them (z_prefetch_v) before it
-// waits for the previous kernel of the stream, and passes v_preloaded = true.
-template <int ROWS>
-__device__ __forceinline__ void z_stage(const FusedParams& p, uint8_t* work, float* zb, int cta, int tid, bool v_preloaded) {
-    constexpr int RP = ROWS < 8 ? ROWS : 8;          // rows per pass
-    constexpr int XK = XT_BYTES / 2 / RP;            // k per pass
-    constexpr int XW = XK / 32;                      // sign words per rank per pass
-    constexpr int JN = XW / 32;                      // sign words per lane per pass
-    static_assert(JN >= 1, "activation tile too small");
-    const int warp = tid >> 5, lane = tid & 31;
-    const int i0 = cta * p.R / p.G;
-    const int i1 = (cta + 1) * p.R / p.G;
-    const uint32_t xt_s = smem_u32(work);
-    const uint32_t vt_s = xt_s + XT_BYTES;
-    const uint32_t* vt = reinterpret_cast<const uint32_t*>(work + XT_BYTES);
-    const int kbytes = p.K >> 3;
+// z stage, run by Z_THREADS = 256 threads (the four epilogue warps and the four scale-factor warps, which have nothing
+// to move until the first weights land). CTA `cta` owns ranks [cta*R/G, (cta+1)*R/G), at most VT_RANKS at a time.
+// Per pass a tile of the activation (RP rows x XK k, 16-byte chunks transposed so that a warp reads consecutive
+// chunks) and the sign words of the CTA's ranks are copied to shared memory with one batch of cp.async. The eight
+// warps are arranged as RP rows x KW k-groups; a lane owns 32-bit sign words (32 consecutive k) of its k-group, unpacks
+// the 32 activations once and adds them into one accumulator per rank under a predicate taken from the sign bit.
+// Accumulators live in registers across all passes; one shuffle reduction and one shared-memory exchange at the end.
+// zt = index of the calling thread among the 256.
+// The sign words of the first pass are weights, not activations: z_prefetch_v copies them before the caller waits for
+// the previous kernel of the stream.
+constexpr int Z_THREADS = 256;
 
+template <int RP>
+__device__ __forceinline__ void z_issue_v(const FusedParams& p, uint8_t* work, int ic, int nr, int k0, int kc, int zt) {
+    constexpr int XK = XT_BYTES / 2 / RP;
+    const int vch = kc >> 7;                                 // 16-byte chunks of sign bits per rank
+    const uint32_t vt_s = smem_u32(work) + XT_BYTES;
 #pragma unroll 1
-    for (int ic = i0; ic < i1; ic += VT_RANKS) {
-        const int nr = (i1 - ic) < VT_RANKS ? (i1 - ic) : VT_RANKS;
-#pragma unroll 1
-        for (int mg = 0; mg < p.M; mg += RP) {       // rows beyond M inside a group repeat row M-1
-            float zacc0 = 0.f, zacc1 = 0.f;          // lane mm holds row mg+mm of rank slots warp, warp+4
-#pragma unroll 1
-            for (int k0 = 0; k0 < p.K; k0 += XK) {
-                const int kc = (p.K - k0) < XK ? (p.K - k0) : XK;     // multiple of 256
-                const bool v_here = v_preloaded && ic == i0 && mg == 0 && k0 == 0;
-                if (!v_here) named_bar_sync(1, EPI_THREADS);           // previous pass fully consumed
-                const int nchunk = kc >> 3;                            // 16-byte chunks per activation row
-#pragma unroll 1
-                for (int idx = tid; idx < RP * nchunk; idx += EPI_THREADS) {
-                    const int mm = idx / nchunk, c = idx - mm * nchunk;
-                    const int row = (mg + mm < p.M) ? (mg + mm) : (p.M - 1);
-                    const int w = c >> 2, v = c & 3;
-                    cp_async16(xt_s + mm * (XK * 2) + ((((w >> 5) * 4 + v) * 32) + (w & 31)) * 16,
-                               p.X + (size_t)row * p.K + k0 + c * 8);
-                }
-                const int vch = kc >> 7;                               // 16-byte chunks of sign bits per rank
-                if (!v_here) {
-#pragma unroll 1
-                    for (int idx = tid; idx < nr * vch; idx += EPI_THREADS) {
-                        const int q = idx / vch, c = idx - q * vch;
-                        cp_async16(vt_s + q * (XK / 8) + c * 16, p.Vp + (size_t)(ic + q) * kbytes + (k0 >> 3) + c * 16);
-                    }
-                }
-                cp_async_commit();
-                cp_async_wait_all();
-                if (tid == 0 && p.stamps && v_here) p.stamps[(size_t)cta * STAMP_WORDS + 8] = globaltimer_ns();
-                named_bar_sync(1, EPI_THREADS);
-                const int nwords = kc >> 5;
-#pragma unroll
-                for (int slot = 0; slot < 2; ++slot) {
-                    const int rq = warp + 4 * slot;
-                    if (rq < nr) {                                     // warp-uniform
-#pragma unroll 1
-                        for (int mm = 0; mm < RP; ++mm) {
-                            float a = 0.f;
-#pragma unroll 1
-                            for (int j = 0; j < JN; ++j) {
-                                const int w = j * 32 + lane;
-                                if (w < nwords) {
-                                    const uint32_t vw = vt[rq * XW + w];
-                                    const uint4* xs = reinterpret_cast<const uint4*>(work + mm * (XK * 2)) + (j * 4) * 32 + lane;
-#pragma unroll
-                                    for (int v = 0; v < 4; ++v) {
-                                        const uint4 xx = xs[v * 32];
-                                        const uint32_t xw[4] = {xx.x, xx.y, xx.z, xx.w};
-#pragma unroll
-                                        for (int e = 0; e < 4; ++e) {
-                                            a += signed_by_bit(__uint_as_float(xw[e] << 16), vw, 8 * v + 2 * e);
-                                            a += signed_by_bit(__uint_as_float(xw[e] & 0xFFFF0000u), vw, 8 * v + 2 * e + 1);
-                                        }
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-                            if (lane == mm) { if (slot == 0) zacc0 += a; else zacc1 += a; }
-                        }
-                    }
-                }
-            }
-            if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 9] = globaltimer_ns();
-            if (lane < RP) {
-                if (warp < nr) zb[(size_t)(mg + lane) * p.Rpad + ic + warp] = zacc0 * __bfloat162float(p.S[ic + warp]);
-                if (warp + 4 < nr) zb[(size_t)(mg + lane) * p.Rpad + ic + warp + 4] = zacc1 * __bfloat162float(p.S[ic + warp + 4]);
-            }
-        }
+    for (int idx = zt; idx < nr * vch; idx += Z_THREADS) {
+        const int q = idx / vch, c = idx - q * vch;
+        cp_async16(vt_s + q * (XK / 8) + c * 16, p.Vp + (size_t)(ic + q) * (p.K >> 3) + (k0 >> 3) + c * 16);
     }
 }
 
-// Sign words of the first z pass of this CTA (ranks i0.., k = 0..XK) into the work area; no activation involved.
 template <int ROWS>
-__device__ __forceinline__ void z_prefetch_v(const FusedParams& p, uint8_t* work, int cta, int tid) {
+__device__ __forceinline__ void z_prefetch_v(const FusedParams& p, uint8_t* work, int cta, int zt) {
     constexpr int RP = ROWS < 8 ? ROWS : 8;
     constexpr int XK = XT_BYTES / 2 / RP;
     const int i0 = cta * p.R / p.G;
     const int i1 = (cta + 1) * p.R / p.G;
     const int nr = (i1 - i0) < VT_RANKS ? (i1 - i0) : VT_RANKS;
-    const int kc = p.K < XK ? p.K : XK;
-    const int vch = kc >> 7;
-    const uint32_t vt_s = smem_u32(work) + XT_BYTES;
-#pragma unroll 1
-    for (int idx = tid; idx < nr * vch; idx += EPI_THREADS) {
-        const int q = idx / vch, c = idx - q * vch;
-        cp_async16(vt_s + q * (XK / 8) + c * 16, p.Vp + (size_t)(i0 + q) * (p.K >> 3) + c * 16);
-    }
+    z_issue_v<RP>(p, work, i0, nr, 0, p.K < XK ? p.K : XK, zt);
     cp_async_commit();
+}
+
+// Adds the 32 activations xf[] into acc[q] for the ranks whose sign bit is set, and keeps their plain sum in `all`
+// (sum_k s_k x_k = 2 * sum_{s_k = +1} x_k - sum_k x_k).
+template <int NQ>
+__device__ __forceinline__ void z_word(const float (&xf)[32], const uint32_t* vrow, int xw_stride, int nq, float (&acc)[NQ]) {
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        if (q < nq) {                                   // warp-uniform
+            const uint32_t vw = vrow[q * xw_stride];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (vw & (1u << j)) acc[q] += xf[j];
+        }
+    }
+}
+
+template <int ROWS>
+__device__ __forceinline__ void z_stage(const FusedParams& p, Ctrl* ctrl, uint8_t* work, float* zb, int cta, int zt, bool v_preloaded) {
+    constexpr int RP = ROWS < 8 ? ROWS : 8;          // rows per pass
+    constexpr int KW = 8 / RP;                       // k-groups (warps per row)
+    constexpr int XK = XT_BYTES / 2 / RP;            // k per pass
+    constexpr int XW = XK / 32;                      // sign words per rank per pass
+    const int zw = zt >> 5, lane = zt & 31;
+    const int row = zw % RP, kg = zw / RP;
+    const int i0 = cta * p.R / p.G;
+    const int i1 = (cta + 1) * p.R / p.G;
+    const uint32_t xt_s = smem_u32(work);
+    const uint32_t* vt = reinterpret_cast<const uint32_t*>(work + XT_BYTES);
+
+#pragma unroll 1
+    for (int ic = i0; ic < i1; ic += VT_RANKS) {
+        const int nr = (i1 - ic) < VT_RANKS ? (i1 - ic) : VT_RANKS;
+        // the coefficient this thread will need when it writes z: requested now, used after the reduction
+        float s_coef = 0.f;
+        if (zt < RP * VT_RANKS && (zt % VT_RANKS) < nr) s_coef = __bfloat162float(p.S[ic + (zt % VT_RANKS)]);
+#pragma unroll 1
+        for (int mg = 0; mg < p.M; mg += RP) {       // rows beyond M inside a group repeat row M-1
+            float acc[VT_RANKS];
+#pragma unroll
+            for (int q = 0; q < VT_RANKS; ++q) acc[q] = 0.f;
+            float all = 0.f;
+#pragma unroll 1
+            for (int k0 = 0; k0 < p.K; k0 += XK) {
+                const int kc = (p.K - k0) < XK ? (p.K - k0) : XK;     // multiple of 256
+                const bool v_here = v_preloaded && ic == i0 && mg == 0 && k0 == 0;
+                if (!v_here) named_bar_sync(3, Z_THREADS);             // previous pass fully consumed
+                const int nchunk = kc >> 3;                            // 16-byte chunks per activation row
+#pragma unroll 1
+                for (int idx = zt; idx < RP * nchunk; idx += Z_THREADS) {
+                    int mm = 0, c = idx;
+                    if (RP > 1) { mm = idx / nchunk; c = idx - mm * nchunk; }
+                    const int r = (mg + mm < p.M) ? (mg + mm) : (p.M - 1);
+                    const int w = c >> 2, v = c & 3;
+                    cp_async16(xt_s + mm * (XK * 2) + ((((w >> 5) * 4 + v) * 32) + (w & 31)) * 16,
+                               p.X + (size_t)r * p.K + k0 + c * 8);
+                }
+                if (!v_here) z_issue_v<RP>(p, work, ic, nr, k0, kc, zt);
+                cp_async_commit();
+                const int nwords = kc >> 5;
+                // The accumulation loop runs twice over the same instructions. The first time, while the copies are
+                // still in flight, it processes one word of whatever the work area holds and its result is thrown
+                // away: its purpose is to pull the loop's machine code into the instruction cache (each CTA executes
+                // this code once per launch, cold, and a cold instruction costs several times a warm one). The second
+                // time is the real pass.
+#pragma unroll 1
+                for (int pass = (k0 == 0 ? 0 : 1); pass < 2; ++pass) {
+                const bool dry = pass == 0;
+                if (!dry) {
+                    cp_async_wait_all();
+                    if (zt == 0 && p.stamps && v_here) p.stamps[(size_t)cta * STAMP_WORDS + 8] = globaltimer_ns();
+                    named_bar_sync(3, Z_THREADS);
+                }
+                const int w_end = dry ? min(nwords, kg * 32 + lane + 1) : nwords;
+#pragma unroll 1
+                for (int w = kg * 32 + lane; w < w_end; w += KW * 32) {
+                    const uint4* xs = reinterpret_cast<const uint4*>(work + row * (XK * 2)) + ((w >> 5) * 4) * 32 + (w & 31);
+                    float xf[32];
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const uint4 xx = xs[v * 32];
+                        const uint32_t xw[4] = {xx.x, xx.y, xx.z, xx.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            xf[8 * v + 2 * e] = __uint_as_float(xw[e] << 16);
+                            xf[8 * v + 2 * e + 1] = __uint_as_float(xw[e] & 0xFFFF0000u);
+                        }
+                    }
+                    float s = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) s += xf[j];
+                    all += s;
+                    z_word<VT_RANKS>(xf, vt + w, XW, nr, acc);
+                }
+                if (dry) {
+                    all = 0.f;
+#pragma unroll
+                    for (int q = 0; q < VT_RANKS; ++q) acc[q] = 0.f;
+                }
+                }
+            }
+            // z[row, rank] = S * (2 * sum_plus - sum_all), summed over the lanes and the k-groups
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) all += __shfl_xor_sync(0xffffffffu, all, o);
+#pragma unroll
+            for (int q = 0; q < VT_RANKS; ++q) {
+                float v = acc[q];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) ctrl->zred[zw][q] = 2.f * v - all;
+            }
+            named_bar_sync(3, Z_THREADS);
+            if (zt < RP * VT_RANKS) {
+                const int r = zt / VT_RANKS, q = zt - r * VT_RANKS;
+                if (q < nr) {
+                    float v = 0.f;
+#pragma unroll
+                    for (int g = 0; g < KW; ++g) v += ctrl->zred[g * RP + r][q];
+                    zb[(size_t)(mg + r) * p.Rpad + ic + q] = v * s_coef;
+                }
+            }
+            if (zt == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 9] = globaltimer_ns();
+        }
+    }
 }
 
 // corr[m] += sum over rank words [w0, w1) of z[m, 32w+b] * sign(U bit b of word w of this thread's column).

@@ -19,10 +19,11 @@ ops = torch.ops.biloco
 RANKS = (16, 32, 64, 128, 256, 512, 1024)
 
 # Schedules implemented by the fused kernel (see include/biloco_b200.h, BILOCO_MODE_*).
-IMPLEMENTED_MODES = (2, 4)
+IMPLEMENTED_MODES = (2, 4, 5)
 
-# Fastest implemented mode per (M, rank) on B200 at K = N = 5120.
-DEFAULT_MODE = {M: {r: 2 for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
+# Fastest implemented mode per (M, rank) on B200 at K = N = 5120 (bench.py --mode sweep, r = 512: mode 5 wins for
+# M <= 8 by 6-10 %, mode 4 loses everywhere; mode 5 does not take M > 8).
+DEFAULT_MODE = {M: {r: (5 if M <= 8 else 2) for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
 
 
 def pack_signs(signs: torch.Tensor) -> torch.Tensor:
@@ -60,7 +61,14 @@ def modes_for(M: int, rank: int, K: int = 5120):
     host-side checks (K must be a multiple of 256, N of 8)."""
     if not (1 <= M <= 32) or rank < 1 or K % 256 != 0:
         return []
-    return list(IMPLEMENTED_MODES)
+    return [m for m in IMPLEMENTED_MODES if m != 5 or M <= 8]
+
+
+def supported_modes(M: int, N: int, K: int, rank: int, num_sms: int = 0):
+    """Modes the launch accepts for this full problem shape (modes_for knows only M, rank and K; mode 5 also
+    depends on N and on the number of SMs). num_sms = 0 asks the current device."""
+    lib = _lib.load()
+    return [m for m in modes_for(M, rank, K) if lib.biloco_b200_mode_supported(M, N, K, rank, m, num_sms)]
 
 
 def nvfp4_sf_bytes(rows: int, k: int) -> int:
@@ -93,10 +101,15 @@ class BiLoCoGemm:
     def __init__(self, W_fp4, W_sf, alpha, V_packed, U_packed, S, M: int, mode: int = None, tile_weights: bool = True):
         self.N, self.K = W_fp4.shape[0], W_fp4.shape[1] * 2
         self.R, self.M = V_packed.shape[0], M
-        self.mode = mode or DEFAULT_MODE.get(M, {}).get(self.R) or (modes_for(M, self.R, self.K) or [None])[0]
-        assert self.mode in modes_for(M, self.R, self.K), f"mode {self.mode} not available for M={M} R={self.R} K={self.K}"
-        self.W_fp4, self.W_sf, self.alpha, self.V, self.S = W_fp4, W_sf, alpha, V_packed, S
         dev = W_fp4.device
+        with torch.cuda.device(dev):
+            ok = supported_modes(M, self.N, self.K, self.R)
+        if mode is None:      # the table's choice if this shape takes it, else the first mode that does
+            mode = DEFAULT_MODE.get(M, {}).get(self.R)
+            mode = mode if mode in ok else (ok or [None])[0]
+        self.mode = mode
+        assert self.mode in ok, f"mode {self.mode} not available for M={M} N={self.N} K={self.K} R={self.R}"
+        self.W_fp4, self.W_sf, self.alpha, self.V, self.S = W_fp4, W_sf, alpha, V_packed, S
         self.U_col32 = pack_u_col32(U_packed, n_cols=self.N, rank=self.R)
         self.none = torch.zeros(0, device=dev, dtype=torch.int64)
         # unit-contiguous copy of the weight (the counterpart of the reference's V_perm / U_rw re-layouts): the

@@ -116,7 +116,7 @@ def biloco_gemm_mode4(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zta
 
 
 def biloco_gemm_mode5(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, Corr, Cnt, m_rows, epoch):
-    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, m_rows, epoch, _lib.MODE_COUNTER,
+    return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, m_rows, epoch, _lib.MODE_CLUSTER,
                   B_tiled=_tiled_or_none(Corr))
 
 

@@ -41,9 +41,17 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
  *      (spreads the expansion over all SMs: for larger batches)
  *   4: the CTA that finishes a tile expands z for all ranks; the other contributors publish their partial sums
  *      without waiting for z (shortest dependency chain: for the smallest batches)
- * In both, z is computed by all CTAs at entry (rank-sliced) and handed over through an arrival counter. */
+ *   5: a tile belongs to a thread-block cluster of c CTAs (c = SMs / tiles, at most 8) that split its k-tiles; the
+ *      partial sums go to the finishing CTA through distributed shared memory instead of global memory (M <= 8 and
+ *      a tile count that lets tiles * c fill at least two thirds of the SMs; other shapes are refused)
+ * In all of them z is computed by all CTAs at entry (rank-sliced) and handed over through an arrival counter. */
 #define BILOCO_MODE_COUNTER 2
 #define BILOCO_MODE_OWNER 4
+#define BILOCO_MODE_CLUSTER 5
+
+/* 1 if biloco_b200_fused_linear accepts this problem in this mode on a device with num_sms multiprocessors
+ * (0 = the current device), else 0. Host-only. Counterpart: modes_for (biloco/kernel.py:66-76). */
+int biloco_b200_mode_supported(int M, int N, int K, int R, int mode, int num_sms);
 
 /* Human-readable text for an error code (host pointer, static storage). */
 const char* biloco_b200_error_string(int code);
@@ -175,6 +183,7 @@ int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t
  * (the kernel itself waits for that kernel before it reads activations or touches scratch). 0 = plain launches.
  * The reference launches with a "pdl" flag as well (csrc/biloco_gemm.cu:3421-3429). */
 #define BILOCO_OPT_PDL 1
+#define BILOCO_OPT_RING 2   /* pipeline stages the fused kernel keeps in flight (>= 2; clamped to what fits) */
 int biloco_b200_set_option(int option, int value);
 
 /* Debug aid: while a device buffer is registered here, every fused launch of this process writes 16 uint64

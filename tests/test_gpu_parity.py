@@ -126,7 +126,7 @@ def _run_fused(kernel, p, M, N, launches=5):
     y_unf = kernel.reference(t["A"], t["A_sf"], t["W"], t["W_sf"], t["alpha"], t["X"], t["V_packed"], t["U_packed"], t["S"])
     check_against_unfused(y_unf.view(-1, N)[:M].float().cpu().numpy(), y_ref, "unfused device path")
     R = p["V_packed"].shape[0]
-    for mode, tiled in [(m, tl) for m in kernel.modes_for(M, R, p["X"].shape[1]) for tl in (True, False)]:
+    for mode, tiled in [(m, tl) for m in kernel.supported_modes(M, N, p["X"].shape[1], R) for tl in (True, False)]:
         g = kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M, mode=mode,
                               tile_weights=tiled)
         mode = f"{mode}{'/tiled' if tiled else '/row-major'}"

@@ -32,8 +32,12 @@ def test_sf_bytes_and_mode_table(golden):
     # every (M, rank) of the reference's table has a default mode here, and it is an available one
     for M in (1, 2, 4, 8, 16, 32):
         for r in golden["ranks"]:
-            assert kernel.DEFAULT_MODE[M][int(r)] in kernel.modes_for(M, int(r), 5120)
+            assert kernel.DEFAULT_MODE[M][int(r)] in kernel.supported_modes(M, 5120, 5120, int(r), num_sms=148)
     assert kernel.modes_for(64, 512) == [] and kernel.modes_for(1, 512, K=5000) == []
+    # mode 5 (cluster per tile) needs few enough tiles for >= 2 CTAs each and at most 8 rows
+    assert kernel.supported_modes(1, 5120, 5120, 512, num_sms=148) == [2, 4, 5]
+    assert kernel.supported_modes(16, 5120, 5120, 512, num_sms=148) == [2, 4]
+    assert kernel.supported_modes(1, 28672, 8192, 512, num_sms=148) == [2, 4]
 
 
 def test_peel_matches_reference(golden):
