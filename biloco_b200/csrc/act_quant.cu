@@ -56,6 +56,11 @@ __global__ void __launch_bounds__(AMAX_THREADS) act_amax_kernel(const __nv_bfloa
     }
 }
 
+// tensor scale supplied by the caller (e.g. agreed between ranks that hold K-slices of one activation): only alpha
+__global__ void act_alpha_kernel(const float* __restrict__ a_gscale, float* __restrict__ alpha_out, const float* __restrict__ w_gscale) {
+    if (alpha_out && w_gscale) alpha_out[0] = __fmul_rn(w_gscale[0], a_gscale[0]);
+}
+
 __device__ __forceinline__ uint32_t e2m1_rn(float q) {
     const float a = fabsf(q);
     uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
@@ -182,13 +187,18 @@ extern "C" int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16
                                      int rule, biloco_stream_t stream) {
     if (!X_bf16 || !A_codes || !A_sf || !a_gscale) return BILOCO_ERR_NULL;
     if (M < 1 || A_rows < M || A_rows > 128 || K < 64 || (K % 64) != 0) return BILOCO_ERR_SHAPE;
+    const bool given_scale = (rule & BILOCO_RULE_GIVEN_SCALE) != 0;
+    rule &= ~BILOCO_RULE_GIVEN_SCALE;
     if (rule != BILOCO_RULE_STATIC_6 && rule != BILOCO_RULE_STATIC_4 && rule != BILOCO_RULE_MSE) return BILOCO_ERR_MODE;
     if (((uintptr_t)A_codes & 7) || ((uintptr_t)X_bf16 & 15) || ((uintptr_t)smooth_bf16 & 15) || ((uintptr_t)Xs_bf16 & 15))
         return BILOCO_ERR_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
     const float target = rule == BILOCO_RULE_STATIC_6 ? 448.0f : 256.0f;
-    act_amax_kernel<<<1, AMAX_THREADS, 0, s>>>((const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16, a_gscale,
-                                               alpha_out, w_gscale, M, K, target);
+    if (given_scale)
+        act_alpha_kernel<<<1, 1, 0, s>>>(a_gscale, alpha_out, w_gscale);
+    else
+        act_amax_kernel<<<1, AMAX_THREADS, 0, s>>>((const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16, a_gscale,
+                                                   alpha_out, w_gscale, M, K, target);
     const int rows_pad = (A_rows + 127) / 128 * 128;
     dim3 grid(((K >> 4) + Q_THREADS - 1) / Q_THREADS, rows_pad);
     act_quant_kernel<<<grid, Q_THREADS, 0, s>>>((const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16,

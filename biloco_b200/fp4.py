@@ -131,10 +131,19 @@ def fake_quantize_fp4(x: torch.Tensor, config=None) -> torch.Tensor:
 
 
 @torch.no_grad()
+def activation_scale_from_amax(amax: torch.Tensor, rule: str = None) -> torch.Tensor:
+    """Tensor scale the quantiser derives from max |x| (fp32 [1]); for callers that reduce amax across ranks."""
+    rule = CONFIG_X if rule is None else rule
+    target = 448.0 if rule == "static_6" else 256.0
+    amax = amax.to(torch.float32).reshape(1)
+    return torch.where(amax > 0, amax / (6.0 * target), torch.ones_like(amax))
+
+
 def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor = None, w_gscale: torch.Tensor = None,
-                        rows: int = None, out: dict = None):
+                        rows: int = None, out: dict = None, gscale: torch.Tensor = None):
     """bf16 CUDA activation [M, K] -> dict(A [1, rows, K/2] uint8, A_sf float8 (atom layout), gscale fp32 [1],
     alpha fp32 [1] (= w_gscale * gscale, when w_gscale is given), X bf16 [M, K] (x / smooth when smoothing)).
+    ``gscale`` (fp32 [1]) supplies the tensor scale instead of deriving it from this tensor's own maximum.
     Runs the library's quantiser on the current stream; nothing returns to the host. Pass ``out`` (a dict from
     an earlier call with the same shapes) to reuse its buffers, e.g. under CUDA-graph capture."""
     rule = CONFIG_X if rule is None else rule
@@ -150,12 +159,16 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
                    X=torch.empty_like(x) if smooth is not None else x)
     elif smooth is None:
         out["X"] = x
+    rule_id = _lib.RULES[rule]
+    if gscale is not None:          # tensor scale agreed elsewhere (tensor-parallel K-slices): do not recompute it
+        out["gscale"].copy_(gscale.reshape(1))
+        rule_id |= 0x100
     with torch.cuda.device(dev):
         rc = _lib.load().biloco_b200_act_quant(
             x.data_ptr(), smooth.data_ptr() if smooth is not None else None,
             out["X"].data_ptr() if smooth is not None else None, out["A"].data_ptr(), out["A_sf"].data_ptr(),
             out["gscale"].data_ptr(), out["alpha"].data_ptr() if w_gscale is not None else None,
-            w_gscale.data_ptr() if w_gscale is not None else None, M, rows, K, _lib.RULES[rule],
+            w_gscale.data_ptr() if w_gscale is not None else None, M, rows, K, rule_id,
             torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, f"act_quant (M={M}, K={K}, rule={rule})")
     return out

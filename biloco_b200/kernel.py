@@ -35,6 +35,13 @@ def pack_signs(signs: torch.Tensor) -> torch.Tensor:
     return (b << shifts).sum(dim=-1).to(torch.uint8)
 
 
+def unpack_signs(packed: torch.Tensor) -> torch.Tensor:
+    """uint8 [..., n/8] -> float32 [..., n] of +-1 (inverse of pack_signs)."""
+    shifts = torch.arange(8, device=packed.device, dtype=torch.int32)
+    bits = (packed.to(torch.int32).unsqueeze(-1) >> shifts) & 1
+    return bits.reshape(*packed.shape[:-1], packed.shape[-1] * 8).to(torch.float32) * 2.0 - 1.0
+
+
 def pack_u_col32(U_packed: torch.Tensor, n_cols: int, rank: int) -> torch.Tensor:
     """U_packed [R, N/8] -> int32 [N, ceil(R/32)]: bit b of word w of column n is the sign bit of rank 32w + b
     (layout of biloco/kernel.py:37-47). CUDA tensors go through the library's re-layout kernel."""
@@ -146,6 +153,26 @@ class BiLoCoGemm:
         if self.mode == 4:
             return ops.biloco_gemm_mode4(*a, self.z, self.W_tiled, self.M, self.epoch)
         return ops.biloco_gemm_mode5(*a, self.z, self.W_tiled, self.none, self.M, self.epoch)
+
+
+class _FP4Only:
+    """The NVFP4 GEMM alone (no low-rank term) with the launcher interface of BiLoCoGemm; used by BiLoCoLinear with
+    method "fp4" (the NVFP4-only baseline of the reference, biloco/layer.py:4-5)."""
+
+    def __init__(self, W_fp4, W_sf, alpha, M: int, tile_weights: bool = True):
+        self.N, self.K, self.M = W_fp4.shape[0], W_fp4.shape[1] * 2, M
+        self.W_fp4, self.W_sf, self.alpha = W_fp4, W_sf, alpha
+        dev = W_fp4.device
+        self.W_tiled = _ops.tile_weights(W_fp4, W_sf) if tile_weights else None
+        with torch.cuda.device(dev):
+            nbytes = scratch_bytes(M, self.N, self.K, 0)
+        self.z = torch.zeros(nbytes // 4, device=dev, dtype=torch.float32)
+        self.epoch = 0
+
+    def __call__(self, A, A_sf, X_bf16=None):
+        self.epoch += 1
+        return _ops._fused(A, self.W_fp4, A_sf, self.W_sf, self.alpha, None, None, None, None, self.z, self.M, self.epoch,
+                           _lib.MODE_COUNTER, B_tiled=self.W_tiled)
 
 
 def reference(A_fp4, A_sf, W_fp4, W_sf, alpha, X_bf16, V_packed, U_packed, S):

@@ -1,0 +1,129 @@
+"""BiLoCoLinear backed by the fused kernel: y = (x/s) V diag(alpha) U^T + FP4(x/s) FP4(R)^T + b.
+
+Same constructor, ``quantize`` and ``forward`` signatures as the reference module (``biloco/layer.py:16-64``), but
+``quantize`` keeps what the fused kernel streams — packed NVFP4 codes and block scales of the residual, bit-packed
+signs, bf16 coefficients — instead of dequantised bf16 copies, and ``forward`` is three enqueued device calls (the
+NVFP4 activation quantiser with the SmoothQuant division folded in, then the fused linear), with no host
+synchronisation. ``forward_fake_quant`` restates the reference's unfused bf16 forward on the same operands with
+plain torch ops; the tests use it as the device-side comparator.
+"""
+import torch
+import torch.nn as nn
+
+from . import fp4
+from .peel import decompose
+
+METHODS = ("biloco", "fp4")
+MAX_ROWS = 32     # activation rows per fused launch
+
+
+class BiLoCoLinear(nn.Module):
+    def __init__(self, linear: nn.Linear, rank: int, method: str = "biloco", smooth_factor: float = 0.5):
+        super().__init__()
+        assert method in METHODS, method
+        self.in_features, self.out_features = linear.in_features, linear.out_features
+        self.method = method
+        self.rank = rank if method != "fp4" else 0
+        self.smooth_factor = smooth_factor
+        dev = linear.weight.device
+        K, N, r = self.in_features, self.out_features, self.rank
+        # The original weight is consumed by quantize() and then freed.
+        self.weight = nn.Parameter(linear.weight.data.to(torch.bfloat16), requires_grad=False)
+        self.bias = None if linear.bias is None else nn.Parameter(linear.bias.data.to(torch.bfloat16), requires_grad=False)
+        self.register_buffer("smooth_scale", torch.ones(K, device=dev, dtype=torch.bfloat16))
+        self.register_buffer("V_packed", torch.zeros(r, K // 8, device=dev, dtype=torch.uint8))
+        self.register_buffer("U_packed", torch.zeros(r, N // 8, device=dev, dtype=torch.uint8))
+        self.register_buffer("S", torch.zeros(r, device=dev, dtype=torch.bfloat16))
+        self.register_buffer("W_codes", torch.zeros(N, K // 2, device=dev, dtype=torch.uint8))
+        self.register_buffer("W_sf", torch.zeros(fp4.nvfp4_sf_bytes(N, K), device=dev, dtype=torch.uint8))
+        self.register_buffer("w_gscale", torch.ones(1, device=dev, dtype=torch.float32))
+        self.smoothed = False
+        self._gemms = {}      # decode batch M -> BiLoCoGemm
+        self._acts = {}       # decode batch M -> reusable activation-quantiser outputs
+
+    # ------------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def quantize(self, act_col_max: torch.Tensor = None, T: int = 5, device=None):
+        """Smooth, split off the binary low-rank component, and pack the residual as NVFP4 (biloco/layer.py:34-52)."""
+        from .kernel import pack_signs
+        device = device or self.weight.device
+        W = self.weight.data.to(device=device, dtype=torch.float32)          # (out, in)
+        if act_col_max is not None:
+            a = act_col_max.to(device=device, dtype=torch.float32).clamp(min=1e-6)
+            w_col_max = W.abs().max(dim=0).values.clamp(min=1e-6)
+            s = (a ** self.smooth_factor) / (w_col_max ** (1 - self.smooth_factor))
+            self.smooth_scale.copy_(s.to(torch.bfloat16))
+            self.smoothed = True
+            W = W * s
+        if self.rank > 0:
+            U, V, alpha, R = decompose(W, r=self.rank, T=T)
+            self.V_packed.copy_(pack_signs(V.T.contiguous()))
+            self.U_packed.copy_(pack_signs(U.T.contiguous()))
+            self.S.copy_(alpha.to(torch.bfloat16))
+        else:
+            R = W
+        codes, sf, gs = fp4.quantize_nvfp4(R.to(torch.bfloat16).float(), fp4.CONFIG_W)
+        self.W_codes.copy_(codes)
+        self.W_sf.copy_(sf.view(torch.uint8))
+        self.w_gscale.copy_(gs)
+        self.weight = None
+        self._gemms.clear()
+
+    def export_operands(self):
+        """What the fused kernel consumes, as a dict of tensors (the packed counterpart of the reference's state dict)."""
+        return dict(W_codes=self.W_codes, W_sf=self.W_sf.view(torch.float8_e4m3fn), w_gscale=self.w_gscale,
+                    V_packed=self.V_packed, U_packed=self.U_packed, S=self.S, smooth_scale=self.smooth_scale,
+                    bias=self.bias)
+
+    # ------------------------------------------------------------------------------------------------------
+    def _gemm_for(self, M, alpha):
+        from .kernel import BiLoCoGemm, _FP4Only
+        g = self._gemms.get(M)
+        if g is None:
+            if self.rank > 0:
+                g = BiLoCoGemm(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), alpha, self.V_packed, self.U_packed, self.S, M=M)
+            else:
+                g = _FP4Only(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), alpha, M=M)
+            self._gemms[M] = g
+        return g
+
+    def _rows(self, x2):
+        M = x2.shape[0]
+        q = fp4.quantize_activation(x2, fp4.CONFIG_X, smooth=self.smooth_scale if self.smoothed else None,
+                                    w_gscale=self.w_gscale, rows=M, out=self._acts.get(M))
+        self._acts[M] = q
+        g = self._gemm_for(M, q["alpha"])
+        return g(q["A"], q["A_sf"], q["X"]).view(-1, self.out_features)[:M]
+
+    def forward(self, x):
+        assert self.weight is None, "call quantize() first"
+        shape = x.shape
+        x2 = x.to(torch.bfloat16).reshape(-1, self.in_features).contiguous()
+        if x2.shape[0] <= MAX_ROWS:
+            y = self._rows(x2)
+        else:   # longer inputs (prefill) go through in blocks of 32 rows; each block gets its own tensor scale
+            y = torch.cat([self._rows(x2[i:i + MAX_ROWS].contiguous()).clone() for i in range(0, x2.shape[0], MAX_ROWS)], dim=0)
+        if self.bias is not None:
+            y = y + self.bias
+        return y.reshape(*shape[:-1], self.out_features).to(torch.bfloat16)
+
+    # ------------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward_fake_quant(self, x):
+        """The reference's unfused forward (biloco/layer.py:54-64) on this module's operands, plain torch ops."""
+        from .kernel import unpack_signs
+        x_s = x.to(torch.bfloat16) / self.smooth_scale
+        y = torch.zeros((*x_s.shape[:-1], self.out_features), dtype=torch.bfloat16, device=x_s.device)
+        if self.rank > 0:
+            V_scaled = (unpack_signs(self.V_packed) * self.S.float().unsqueeze(1)).to(torch.bfloat16)    # [r, K]
+            U_T = unpack_signs(self.U_packed).to(torch.bfloat16)                                          # [r, N]
+            y = y + (x_s @ V_scaled.T) @ U_T
+        x_fq = fp4.fake_quantize_fp4(x_s.reshape(-1, self.in_features), fp4.CONFIG_X).reshape(x_s.shape)
+        weight_fp4 = fp4.dequantize_nvfp4(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), self.w_gscale).to(torch.bfloat16)
+        y = y + x_fq @ weight_fp4.T
+        if self.bias is not None:
+            y = y + self.bias
+        return y.to(torch.bfloat16)
+
+    def extra_repr(self):
+        return f"in={self.in_features}, out={self.out_features}, method={self.method}, rank={self.rank}"

@@ -1,0 +1,106 @@
+"""Tensor-parallel use of the fused linear on the GPUs of one box (one process per GPU, torch.distributed).
+
+The path shards without an exchange inside the kernel:
+
+  * column-parallel (N split): rank g keeps rows [g*N/G, (g+1)*N/G) of the residual (codes + block scales) and of U, the
+    whole of V and the coefficients. Outputs stay sharded; the z stage is recomputed identically on every rank.
+  * row-parallel (K split): rank g keeps columns [g*K/G, (g+1)*K/G) of the residual and rows of V, the whole of U. Each
+    rank's launch yields a partial y over all N (its K-slice of the FP4 product plus U . (S * V_g^T x_g), both linear
+    in the K-slice), and ONE all-reduce (NCCL over NVLink) of the [M, N] outputs finishes the layer.
+
+The NVFP4 tensor scale of an activation is defined over the whole [tokens, K] tensor; ranks that hold K-slices agree on
+it with a one-float max all-reduce before quantising (`agree_on_activation_scale`), so the codes equal the single-GPU
+ones. The reference has no distributed code; this is the N/K sharding that BASELINE configs 3 and 4 ask for.
+"""
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(n: int, world: int, rank: int, multiple: int):
+    """[lo, hi) of rank's equal share of n; n / world must be a multiple of `multiple`."""
+    assert n % world == 0 and (n // world) % multiple == 0, f"{n} does not split into {world} shards of a multiple of {multiple}"
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+def _sf_view(W_sf, N, K):
+    """Block scales in the 128x4 atom layout as [N/128, K/64, 32, 4, 4] = (row block, k atom, row%32, row/32%4, kblock%4)."""
+    return W_sf.view(torch.uint8).reshape(-1)[: ((N + 127) // 128 * 128) * (K // 16)].view((N + 127) // 128, K // 64, 32, 4, 4)
+
+
+def shard_column_parallel(ops: dict, world: int, rank: int):
+    """Operands of rank's N-shard. ops: W_codes [N,K/2], W_sf (atom layout), w_gscale, V_packed [r,K/8], U_packed [r,N/8],
+    S [r], smooth_scale [K], bias [N] or None."""
+    N, K = ops["W_codes"].shape[0], ops["W_codes"].shape[1] * 2
+    lo, hi = shard_bounds(N, world, rank, 128)
+    sf = _sf_view(ops["W_sf"], N, K)[lo // 128: hi // 128].contiguous().reshape(-1)
+    out = dict(ops)
+    out.update(W_codes=ops["W_codes"][lo:hi].contiguous(), W_sf=sf.view(ops["W_sf"].dtype),
+               U_packed=ops["U_packed"][:, lo // 8: hi // 8].contiguous(),
+               bias=None if ops.get("bias") is None else ops["bias"][lo:hi].contiguous())
+    return out
+
+
+def shard_row_parallel(ops: dict, world: int, rank: int):
+    """Operands of rank's K-shard (the bias stays with rank 0 so that the all-reduce adds it once)."""
+    N, K = ops["W_codes"].shape[0], ops["W_codes"].shape[1] * 2
+    lo, hi = shard_bounds(K, world, rank, 256)
+    sf = _sf_view(ops["W_sf"], N, K)[:, lo // 64: hi // 64].contiguous().reshape(-1)
+    out = dict(ops)
+    out.update(W_codes=ops["W_codes"][:, lo // 2: hi // 2].contiguous(), W_sf=sf.view(ops["W_sf"].dtype),
+               V_packed=ops["V_packed"][:, lo // 8: hi // 8].contiguous(),
+               smooth_scale=ops["smooth_scale"][lo:hi].contiguous(),
+               bias=ops.get("bias") if rank == 0 else None)
+    return out
+
+
+def agree_on_activation_scale(x_local: torch.Tensor, smooth_local: torch.Tensor = None, rule: str = None, group=None):
+    """fp32 [1] tensor scale of the full activation whose K-slice this rank holds (max all-reduce of one float)."""
+    from . import fp4
+    xs = x_local.to(torch.bfloat16)
+    if smooth_local is not None:
+        xs = xs / smooth_local
+    amax = xs.float().abs().max().reshape(1)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    return fp4.activation_scale_from_amax(amax, rule)
+
+
+class ShardedBiLoCoLinear:
+    """One rank's shard of a quantised layer, run through the fused kernel.
+
+    kind = "column": forward(x [M, K]) -> y [M, N/G] (local columns).
+    kind = "row":    forward(x_local [M, K/G]) -> y [M, N], all-reduced over the group.
+    """
+
+    def __init__(self, ops: dict, kind: str, M: int, group=None):
+        from .kernel import BiLoCoGemm
+        assert kind in ("column", "row")
+        self.kind, self.M, self.group = kind, M, group
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.ops = (shard_column_parallel if kind == "column" else shard_row_parallel)(ops, world, rank)
+        o = self.ops
+        self.N, self.K = o["W_codes"].shape[0], o["W_codes"].shape[1] * 2
+        dev = o["W_codes"].device
+        self.alpha = torch.zeros(1, device=dev, dtype=torch.float32)
+        self.gemm = BiLoCoGemm(o["W_codes"], o["W_sf"].view(torch.float8_e4m3fn), self.alpha, o["V_packed"], o["U_packed"], o["S"], M=M)
+        self._act = None
+
+    def forward(self, x):
+        from . import fp4
+        o = self.ops
+        x = x.to(torch.bfloat16).contiguous()
+        gscale = agree_on_activation_scale(x, o["smooth_scale"], group=self.group) if self.kind == "row" else None
+        q = fp4.quantize_activation(x, smooth=o["smooth_scale"], w_gscale=o["w_gscale"], rows=self.M, out=self._act, gscale=gscale)
+        self._act = q
+        self.alpha.copy_(q["alpha"])
+        y = self.gemm(q["A"], q["A_sf"], q["X"]).view(-1, self.N)[: self.M]
+        if o.get("bias") is not None:
+            y = y + o["bias"]
+        if self.kind == "row" and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            y = y.contiguous()
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y
+
+    __call__ = forward

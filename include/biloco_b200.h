@@ -35,6 +35,7 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
 #define BILOCO_RULE_STATIC_6 0
 #define BILOCO_RULE_STATIC_4 1
 #define BILOCO_RULE_MSE 2            /* "four over six": per block, 6 or 4, smaller squared error */
+#define BILOCO_RULE_GIVEN_SCALE 0x100 /* OR-ed to a rule: a_gscale[0] already holds the tensor scale (not recomputed) */
 
 /* Schedules of the fused kernel; numbered like the reference's modes (biloco/kernel.py:18-26,66-76).
  *   2: every CTA that contributes to a tile expands z for a share of the ranks and adds it to its partial sum
@@ -84,6 +85,8 @@ int biloco_b200_pack_u_col32(const void* U_packed, int32_t* U_col32, int N, int 
  * If smooth_bf16 != NULL the input is first divided by it per channel (result rounded to bf16) and, if
  * Xs_bf16 != NULL, that smoothed activation is written there (the low-rank term consumes it).
  * One global scale per call over all M rows (biloco/fp4.py:3-4). K % 64 == 0, M <= A_rows <= 128.
+ * With BILOCO_RULE_GIVEN_SCALE the scale is an input: ranks that each hold a K-slice of one activation first agree on
+ * amax (a one-float max all-reduce) and so quantise exactly as a single device would.
  * Replaces: biloco/fp4.py:30-35 (fake_quantize_fp4 -> fouroversix.quantize_to_fp4) and the x/smooth_scale
  * division of biloco/layer.py:55. */
 int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_bf16,

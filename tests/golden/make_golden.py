@@ -148,6 +148,8 @@ def main():
     x[:, idx] *= 20
     x = x.to(torch.bfloat16)
     y = bl(x)
+    out["layer_W"] = lin.weight.detach().float().numpy()
+    out["layer_act_max"] = act_max.numpy()
     out["layer_x"] = x.float().numpy()
     out["layer_y"] = y.float().numpy()
     out["layer_smooth"] = bl.smooth_scale.float().numpy()

@@ -1,0 +1,124 @@
+"""Kernel-backed BiLoCoLinear / model-level PTQ: host logic on CPU, kernel forward on GPU."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from biloco_b200 import fp4, kernel, peel
+from biloco_b200.layer import BiLoCoLinear
+from biloco_b200.model import load_quantized, quantize_model, replace_linears, save_quantized
+from oracle import biloco_oracle as orc
+
+
+def _golden_layer(golden, device="cpu"):
+    K, N = golden["layer_W"].shape[1], golden["layer_W"].shape[0]
+    lin = nn.Linear(K, N, bias=True)
+    with torch.no_grad():
+        lin.weight.copy_(torch.from_numpy(golden["layer_W"]))
+        lin.bias.copy_(torch.from_numpy(golden["layer_bias"]))
+    peel.set_peel_seed(42)
+    fp4.set_scale_rules("mse", "mse")
+    bl = BiLoCoLinear(lin, rank=32)
+    bl.quantize(act_col_max=torch.from_numpy(golden["layer_act_max"]), T=5, device="cpu")   # CPU: same RNG stream as the golden run
+    return bl.to(device)
+
+
+def test_quantize_reproduces_reference_layer(golden):
+    """quantize() on CPU gives the factors the reference's BiLoCoLinear produced (V_scaled = diag(alpha) V^T in bf16,
+    U^T signs, smoothing vector) and a residual that dequantises to the reference's weight_fp4."""
+    bl = _golden_layer(golden)
+    assert np.array_equal(bl.smooth_scale.float().numpy(), golden["layer_smooth"])
+    V_scaled = (kernel.unpack_signs(bl.V_packed) * bl.S.float().unsqueeze(1)).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(kernel.unpack_signs(bl.U_packed).numpy(), golden["layer_U_T"])
+    assert np.array_equal(np.sign(V_scaled), np.sign(golden["layer_V_scaled"]))
+    # the reference rounds alpha * v to bf16 per element, the kernel operand keeps alpha in bf16: same up to 1 bf16 ulp
+    assert np.allclose(V_scaled, golden["layer_V_scaled"], rtol=2.0 ** -7, atol=0)
+    w = fp4.dequantize_nvfp4(bl.W_codes, bl.W_sf.view(torch.float8_e4m3fn), bl.w_gscale).to(torch.bfloat16).float().numpy()
+    assert np.array_equal(w, golden["layer_weight_fp4"])
+    # and the unfused forward restated in torch agrees with the reference module's output
+    y = bl.forward_fake_quant(torch.from_numpy(golden["layer_x"]).to(torch.bfloat16)).float().numpy()
+    ref = golden["layer_y"]
+    assert np.max(np.abs(y - ref)) <= 2.0 ** -6 * np.max(np.abs(ref))
+
+
+class _Tiny(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.a = nn.Linear(256, 512, bias=False)
+        self.block = nn.Sequential(nn.Linear(512, 256, bias=True), nn.ReLU())
+        self.lm_head = nn.Linear(256, 128, bias=False)
+
+    def forward(self, x):
+        return self.lm_head(self.block(self.a(x)))
+
+
+def test_model_api_and_checkpoint_roundtrip(tmp_path):
+    torch.manual_seed(0)
+    model = _Tiny()
+    ref = copy.deepcopy(model)
+    batches = [torch.randn(4, 256) for _ in range(3)]
+    quantize_model(model, ref_model=ref, batches=batches, rank=16, T=2, device="cpu", calib_batches=2)
+    layers = {n: m for n, m in model.named_modules() if isinstance(m, BiLoCoLinear)}
+    assert set(layers) == {"a", "block.0", "lm_head"}          # every nn.Linear, lm_head included
+    assert all(m.weight is None and m.smoothed for m in layers.values())
+    path = str(tmp_path / "q.pt")
+    save_quantized(model, path, manifest={"rank": 16})
+    fresh = _Tiny()
+    assert load_quantized(fresh, path, rank=16) == {"rank": 16}
+    for n, m in layers.items():
+        f = dict(fresh.named_modules())[n]
+        for k in ("smooth_scale", "V_packed", "U_packed", "S", "W_codes", "W_sf", "w_gscale"):
+            assert torch.equal(getattr(f, k), getattr(m, k)), (n, k)
+        assert f.smoothed and f.weight is None
+    x = torch.randn(2, 256).to(torch.bfloat16)
+    ya = layers["a"].forward_fake_quant(x)
+    yb = dict(fresh.named_modules())["a"].forward_fake_quant(x)
+    assert torch.equal(ya, yb)
+    # method "fp4" keeps no low-rank factors
+    m2 = _Tiny()
+    replace_linears(m2, rank=16, method="fp4")
+    assert m2.a.rank == 0 and m2.a.V_packed.numel() == 0
+
+
+@pytest.mark.gpu
+def test_layer_forward_on_kernel_matches_reference_layer(golden):
+    from tests.gpu_util import check_against_unfused
+    bl = _golden_layer(golden, "cuda")
+    x = torch.from_numpy(golden["layer_x"]).cuda().to(torch.bfloat16)
+    for _ in range(2):
+        y = bl(x).float().cpu().numpy()
+        check_against_unfused(y, golden["layer_y"], "kernel forward vs reference module output")
+    y_fq = bl.forward_fake_quant(x).float().cpu().numpy()
+    check_against_unfused(y, y_fq, "kernel forward vs unfused forward on the device")
+    # a leading batch dimension and more than 32 rows
+    xb = torch.randn(2, 24, 256, device="cuda").to(torch.bfloat16)
+    yb = bl(xb)
+    assert yb.shape == (2, 24, 128) and torch.isfinite(yb.float()).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [1, 8])
+def test_config0_layer(M):
+    """BASELINE config 0: W fp32 ~ N(0, 0.02^2) 5120 x 5120 (seed 0), decompose(r = 512, T = 5) with peel seed 42, NVFP4
+    residual, x bf16 ~ N(0,1) with 1 % outlier channels x20; fused output vs the unfused fake-quant forward."""
+    from tests.gpu_util import check_against_unfused
+    torch.manual_seed(0)
+    lin = nn.Linear(5120, 5120, bias=False)
+    with torch.no_grad():
+        lin.weight.copy_(0.02 * torch.randn(5120, 5120))
+    lin = lin.cuda()
+    peel.set_peel_seed(42)
+    bl = BiLoCoLinear(lin, rank=512)
+    bl.quantize(T=5, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(M, 5120, device="cuda", generator=g)
+    x[:, torch.randperm(5120, device="cuda", generator=g)[:51]] *= 20
+    x = x.to(torch.bfloat16)
+    y = bl(x).float().cpu().numpy()
+    y_ref = bl.forward_fake_quant(x).float().cpu().numpy()
+    check_against_unfused(y, y_ref, f"config 0, M={M}")
+    # the low-rank term matters: dropping it changes the output by much more than the tolerance
+    z = kernel.ops.binary_z_reference(x, bl.V_packed, bl.S)
+    assert float(z.abs().max()) > 0

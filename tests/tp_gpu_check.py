@@ -1,0 +1,67 @@
+"""Tensor-parallel check on real GPUs (one process per GPU, NCCL). Launched by tests/test_gpu_tp.py or by hand:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 tests/tp_gpu_check.py
+
+Every rank builds the same layer, runs its column-parallel and row-parallel shard through the fused kernel, and compares
+with the whole layer run on its own GPU: column shards must equal the matching columns bit for bit (same arithmetic per
+column), the all-reduced row-parallel output must match within the suite's tolerances."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    world, rank = dist.get_world_size(), dist.get_rank()
+    from biloco_b200 import fp4, kernel, parallel
+    from tests.gpu_util import check_against_unfused
+
+    M, K, N, R = 4, 2048, 2048, 128
+    g = torch.Generator(device=dev).manual_seed(7)        # same operands on every rank
+    W = (torch.randn(N, K, device=dev, generator=g) * 0.02).to(torch.bfloat16).float()
+    codes, sf, gs = fp4.quantize_nvfp4(W, "mse")
+    V = torch.where(torch.randn(R, K, device=dev, generator=g) >= 0, 1.0, -1.0)
+    U = torch.where(torch.randn(R, N, device=dev, generator=g) >= 0, 1.0, -1.0)
+    ops = dict(W_codes=codes, W_sf=sf.view(torch.uint8), w_gscale=gs, V_packed=kernel.pack_signs(V), U_packed=kernel.pack_signs(U),
+               S=(torch.randn(R, device=dev, generator=g) * 0.01).to(torch.bfloat16),
+               smooth_scale=(torch.rand(K, device=dev, generator=g) * 2 + 0.5).to(torch.bfloat16), bias=None)
+    x = torch.randn(M, K, device=dev, generator=g)
+    x[:, torch.randperm(K, device=dev, generator=g)[: K // 100]] *= 20
+    x = x.to(torch.bfloat16)
+
+    # whole layer on this GPU
+    q = fp4.quantize_activation(x, smooth=ops["smooth_scale"], w_gscale=gs, rows=M)
+    full = kernel.BiLoCoGemm(codes, sf, q["alpha"], ops["V_packed"], ops["U_packed"], ops["S"], M=M)
+    y_full = full(q["A"], q["A_sf"], q["X"]).view(-1, N)[:M].clone()
+
+    col = parallel.ShardedBiLoCoLinear(ops, "column", M)
+    lo, hi = parallel.shard_bounds(N, world, rank, 128)
+    y_col = col(x)
+    torch.cuda.synchronize()
+    assert torch.equal(y_col.view(torch.int16), y_full[:, lo:hi].contiguous().view(torch.int16)), "column shard differs"
+
+    row = parallel.ShardedBiLoCoLinear(ops, "row", M)
+    klo, khi = parallel.shard_bounds(K, world, rank, 256)
+    for _ in range(2):
+        y_row = row(x[:, klo:khi].contiguous())
+    torch.cuda.synchronize()
+    # each rank rounds its partial to bf16 before the all-reduce: within the suite's tolerance of the single-GPU result
+    check_against_unfused(y_row.float().cpu().numpy(), y_full.float().cpu().numpy(), f"row-parallel, rank {rank}")
+    assert row.gemm.status()[0] == 0 and col.gemm.status()[0] == 0
+    dist.barrier()
+    if rank == 0:
+        print(f"tensor-parallel check ok on {world} GPUs", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
