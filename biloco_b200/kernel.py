@@ -128,6 +128,7 @@ class BiLoCoGemm:
         # one buffer holds status words, counters, the z hand-off area and the split-K partial sums
         self.z = torch.zeros(nbytes // 4, device=dev, dtype=torch.float32)
         self.epoch = 0
+        self.residual = None      # optional bf16 [M, N] added before the single final rounding (e.g. a broadcast bias)
 
     def reset(self):
         """Clear the status words and counters (needed only after a launch whose status reported a failed wait;
@@ -147,6 +148,10 @@ class BiLoCoGemm:
     def __call__(self, A_pad, A_sf, X_bf16):
         """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten)."""
         self.epoch += 1
+        if self.residual is not None:   # the operator schemas carry no residual: call the library entry point directly
+            return _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32, self.z,
+                               self.M, self.epoch, self.mode, C=self.residual,
+                               B_tiled=self.W_tiled if self.W_tiled.numel() else None)
         a = (A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32)
         if self.mode == 2:
             return ops.biloco_gemm_mode2(*a, self.z, self.none, self.none, self.W_tiled, self.none, self.M, self.epoch)
@@ -168,11 +173,12 @@ class _FP4Only:
             nbytes = scratch_bytes(M, self.N, self.K, 0)
         self.z = torch.zeros(nbytes // 4, device=dev, dtype=torch.float32)
         self.epoch = 0
+        self.residual = None
 
     def __call__(self, A, A_sf, X_bf16=None):
         self.epoch += 1
         return _ops._fused(A, self.W_fp4, A_sf, self.W_sf, self.alpha, None, None, None, None, self.z, self.M, self.epoch,
-                           _lib.MODE_COUNTER, B_tiled=self.W_tiled)
+                           _lib.MODE_COUNTER, C=self.residual, B_tiled=self.W_tiled)
 
 
 def reference(A_fp4, A_sf, W_fp4, W_sf, alpha, X_bf16, V_packed, U_packed, S):

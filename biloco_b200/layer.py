@@ -84,6 +84,8 @@ class BiLoCoLinear(nn.Module):
                 g = BiLoCoGemm(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), alpha, self.V_packed, self.U_packed, self.S, M=M)
             else:
                 g = _FP4Only(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), alpha, M=M)
+            if self.bias is not None:     # added inside the kernel, before its single bf16 rounding
+                g.residual = self.bias.detach().to(torch.bfloat16).unsqueeze(0).expand(M, self.out_features).contiguous()
             self._gemms[M] = g
         return g
 
@@ -103,8 +105,6 @@ class BiLoCoLinear(nn.Module):
             y = self._rows(x2)
         else:   # longer inputs (prefill) go through in blocks of 32 rows; each block gets its own tensor scale
             y = torch.cat([self._rows(x2[i:i + MAX_ROWS].contiguous()).clone() for i in range(0, x2.shape[0], MAX_ROWS)], dim=0)
-        if self.bias is not None:
-            y = y + self.bias
         return y.reshape(*shape[:-1], self.out_features).to(torch.bfloat16)
 
     # ------------------------------------------------------------------------------------------------------
