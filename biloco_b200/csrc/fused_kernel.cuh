@@ -330,7 +330,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                             if (m < p.M) {
                                 float o = v[m];
                                 if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
-                                p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
+                                if (p.mode & 0x400) reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
+                                else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
                             }
                         }
                     }
@@ -364,7 +365,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                         if (m < p.M) {
                             float o = v[m];
                             if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
-                            p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
+                            if (p.mode & 0x400) reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
+                                else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
                         }
                     }
                 }

@@ -129,6 +129,7 @@ class BiLoCoGemm:
         self.z = torch.zeros(nbytes // 4, device=dev, dtype=torch.float32)
         self.epoch = 0
         self.residual = None      # optional bf16 [M, N] added before the single final rounding (e.g. a broadcast bias)
+        self.fp32_out = False     # True: return the unrounded fp32 sum (partial outputs reduced across devices)
 
     def reset(self):
         """Clear the status words and counters (needed only after a launch whose status reported a failed wait;
@@ -148,10 +149,10 @@ class BiLoCoGemm:
     def __call__(self, A_pad, A_sf, X_bf16):
         """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten)."""
         self.epoch += 1
-        if self.residual is not None:   # the operator schemas carry no residual: call the library entry point directly
+        if self.residual is not None or self.fp32_out:   # not expressible in the operator schemas: call the library directly
             return _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32, self.z,
                                self.M, self.epoch, self.mode, C=self.residual,
-                               B_tiled=self.W_tiled if self.W_tiled.numel() else None)
+                               B_tiled=self.W_tiled if self.W_tiled.numel() else None, fp32_out=self.fp32_out)
         a = (A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32)
         if self.mode == 2:
             return ops.biloco_gemm_mode2(*a, self.z, self.none, self.none, self.W_tiled, self.none, self.M, self.epoch)

@@ -56,7 +56,7 @@ def _check_fp4_operands(A, B, A_sf, B_sf, alpha):
     return rows, N, K
 
 
-def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None, B_tiled=None):
+def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None, B_tiled=None, fp32_out=False):
     rows, N, K = _check_fp4_operands(A, B, A_sf, B_sf, alpha)
     _req(1 <= m_rows <= rows, "m_rows must be in [1, A.size(1)]")
     R = 0
@@ -74,7 +74,10 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
         want = _lib.load().biloco_b200_tiled_bytes(N, K)
         _req(B_tiled.is_cuda and B_tiled.is_contiguous() and B_tiled.dtype == torch.uint8 and B_tiled.numel() == want,
              f"tiled weight copy must be a contiguous uint8 CUDA tensor of {want} bytes")
-    D = out if out is not None else torch.empty((1, rows, N), device=A.device, dtype=torch.bfloat16)
+    D = out if out is not None else torch.empty((1, rows, N), device=A.device, dtype=torch.float32 if fp32_out else torch.bfloat16)
+    if fp32_out:
+        _req(D.dtype == torch.float32, "fp32 output buffer expected")
+        mode |= 0x400
     with torch.cuda.device(A.device):
         rc = _lib.load().biloco_b200_fused_linear(
             B.data_ptr(), B_sf.data_ptr(), B_tiled.data_ptr() if B_tiled is not None else None, alpha.data_ptr(), A.data_ptr(), A_sf.data_ptr(),

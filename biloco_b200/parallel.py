@@ -85,6 +85,9 @@ class ShardedBiLoCoLinear:
         dev = o["W_codes"].device
         self.alpha = torch.zeros(1, device=dev, dtype=torch.float32)
         self.gemm = BiLoCoGemm(o["W_codes"], o["W_sf"].view(torch.float8_e4m3fn), self.alpha, o["V_packed"], o["U_packed"], o["S"], M=M)
+        self.gemm.fp32_out = kind == "row"     # partial sums are reduced in fp32; one bf16 rounding after the all-reduce
+        if o.get("bias") is not None:
+            self.gemm.residual = o["bias"].to(torch.bfloat16).unsqueeze(0).expand(M, self.N).contiguous()
         self._act = None
 
     def forward(self, x):
@@ -96,11 +99,11 @@ class ShardedBiLoCoLinear:
         self._act = q
         self.alpha.copy_(q["alpha"])
         y = self.gemm(q["A"], q["A_sf"], q["X"]).view(-1, self.N)[: self.M]
-        if o.get("bias") is not None:
-            y = y + o["bias"]
-        if self.kind == "row" and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+        if self.kind == "row":
             y = y.contiguous()
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)      # fp32 [M, N] over NVLink
+            y = y.to(torch.bfloat16)
         return y
 
     __call__ = forward

@@ -50,6 +50,10 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
 #define BILOCO_MODE_OWNER 4
 #define BILOCO_MODE_CLUSTER 5
 
+/* OR-ed to the mode: Y is fp32 [M,N] instead of bf16 (the unrounded sum). For partial outputs that are reduced across
+ * devices before the single bf16 rounding (row-parallel shards). No counterpart in the reference (single GPU). */
+#define BILOCO_OUT_FP32 0x400
+
 /* 1 if biloco_b200_fused_linear accepts this problem in this mode on a device with num_sms multiprocessors
  * (0 = the current device), else 0. Host-only. Counterpart: modes_for (biloco/kernel.py:66-76). */
 int biloco_b200_mode_supported(int M, int N, int K, int R, int mode, int num_sms);
