@@ -16,17 +16,16 @@ constexpr int KT_BYTES = KT / 2;                 // 128 B of codes per row = one
 constexpr int W_TILE_BYTES = TILE_N * KT_BYTES;  // 16384
 constexpr int SF_TILE_BYTES = 4 * 512;           // four 128x4 atoms
 constexpr int EPI_THREADS = 128;
-// Warp roles: 0-3 z stage / expansion / epilogue, 4-7 weight producers, 8-11 activation producers, 12-15 scale-factor
-// movers (shared memory -> TMEM), 16 MMA issue.
+// Warp roles: 0-3 z stage / expansion / epilogue; 4-7 feeders: lane 0 of each requests the weight and activation
+// copies of every fourth unit, and the whole warp moves the scale factors of every unit from shared memory into its
+// 32-lane TMEM quadrant; 8-11 second half of the z stage; 12 MMA issue.
 // Bulk copies issued by one thread complete one after the other (about 0.4 us each for anything up to 16 KB,
-// measured), copies issued by different warps overlap: several producer warps are what lets one CTA pull its
+// measured), copies issued by different warps overlap: several requesting warps are what lets one CTA pull its
 // share of the weight stream at HBM speed.
-constexpr int W_PRODUCERS = 4;
-constexpr int A_PRODUCERS = 4;
-constexpr int FIRST_W_WARP = 4;
-constexpr int FIRST_A_WARP = FIRST_W_WARP + W_PRODUCERS;
-constexpr int FIRST_SF_WARP = FIRST_A_WARP + A_PRODUCERS;   // 4 warps, one per 32-lane TMEM quadrant (warp id % 4)
-constexpr int MMA_WARP = FIRST_SF_WARP + 4;
+constexpr int PRODUCERS = 4;
+constexpr int FIRST_SF_WARP = 4;                 // 4 warps, one per 32-lane TMEM quadrant (warp id % 4)
+constexpr int FIRST_Z_WARP = 8;                  // 4 warps that only take part in the z stage
+constexpr int MMA_WARP = 12;
 constexpr int NUM_THREADS = (MMA_WARP + 1) * 32;
 static_assert(FIRST_SF_WARP % 4 == 0, "scale-factor warp q must own TMEM quadrant q");
 constexpr int TMEM_COLS = 256;
@@ -35,32 +34,50 @@ constexpr int SF_SETS = 4;                       // scale-factor column sets, us
 constexpr int SFA_COL = 64;                      // set q: 16 columns (4 MMAs x 4) at SFA_COL + 32*q
 constexpr int SFB_COL = 80;                      // set q: 16 columns at SFB_COL + 32*q
 static_assert(SFA_COL + 32 * SF_SETS <= TMEM_COLS, "scale-factor sets exceed the TMEM allocation");
-constexpr int CTRL_BYTES = 1024;
+constexpr int CTRL_BYTES = 3072;
 constexpr int SMEM_BUDGET = 227 * 1024;
 constexpr uint64_t WAIT_BUDGET_NS = 200ull * 1000 * 1000;   // 200 ms per wait
 
-// CUDA-core work area in shared memory. During the z stage it holds a tile of the bf16 activation (XT_BYTES,
-// 16-byte chunks transposed so that a warp reads consecutive chunks) and the sign words of up to VT_RANKS ranks;
-// afterwards the same bytes hold the z values being expanded (ROWS x ZS_STRIDE floats).
+// CUDA-core work area in shared memory. During the z stage it holds one pass of one bf16 activation row (XT_BYTES,
+// 16-byte chunks transposed so that a warp reads consecutive chunks) followed by the sign words of the ranks the CTA
+// computes (vt_bytes, chosen by the host: at least VT_MIN_BYTES); afterwards the same bytes hold the z values being
+// expanded and, in cluster mode, the partial sums of the other CTAs of the cluster.
 constexpr int XT_BYTES = 16384;
-constexpr int VT_RANKS = 8;
-constexpr int VT_BYTES = VT_RANKS * (XT_BYTES / 2 / 8);   // one bit per k of the widest activation tile (1 row)
-constexpr int WORK_BYTES = XT_BYTES + VT_BYTES;           // 24 KB
-constexpr int ZS_WORDS = 4;                      // rank words (32 ranks each) of z staged at a time
-constexpr int ZS_STRIDE = ZS_WORDS * 32 + 4;     // floats per staged row (+4: rows start in different banks)
+constexpr int XK = XT_BYTES / 2;                 // k per pass of the z stage
+constexpr int VT_MIN_BYTES = 8192;
+constexpr int VT_MAX_BYTES = 65536;
+constexpr int WORK_BYTES = XT_BYTES + VT_MIN_BYTES;       // 24 KB: the smallest work area
+constexpr int ZR_MAX = 64;                       // ranks per chunk of the z stage (partial sums per warp in Ctrl)
+constexpr int ZS_FIRST = 4;                      // U words per segment fetched ahead of the dependency wait
+// z is staged for the expansion in chunks of zs_words(ROWS) rank words (32 ranks each): ROWS x (32*words + 4) floats
+// (+4: rows start in different banks), at most ZS_BYTES.
+__host__ __device__ constexpr int zs_words(int rows) { return rows <= 8 ? 8 : 4; }
+__host__ __device__ constexpr int zs_stride(int rows) { return zs_words(rows) * 32 + 4; }
+constexpr int ZS_BYTES_SMALL = 8320;             // rows <= 8:  8 * 260 * 4
 constexpr int STAMP_WORDS = 16;                  // uint64 time stamps per CTA when debug stamps are on
-static_assert(32 * ZS_STRIDE * 4 <= WORK_BYTES, "z staging must fit in the work area");
-constexpr int RED_OFF = 8 * ZS_STRIDE * 4 + 256;   // cluster mode (rows <= 8): partial sums of the peers start here,
+static_assert(32 * zs_stride(32) * 4 <= WORK_BYTES && 16 * zs_stride(16) * 4 <= WORK_BYTES, "z staging must fit in the work area");
+static_assert(8 * zs_stride(8) * 4 <= ZS_BYTES_SMALL && 4 * zs_stride(4) * 4 <= ZS_BYTES_SMALL, "z staging (rows <= 8)");
+constexpr int RED_OFF = ZS_BYTES_SMALL + 128;      // cluster mode (rows <= 8): partial sums of the peers start here,
 constexpr int RED_BYTES = WORK_BYTES - RED_OFF;    // after the z staging rows, [peer][row][128] floats
 
+// Rows <= 8 (MMA_N == 8): two CTAs fit on one SM (registers, shared memory and TMEM are all sized for it), so that
+// with programmatic dependent launch the next kernel of the stream is resident beside this one and has its first
+// weights in shared memory before this one has finished its dependent tail. More rows: one CTA per SM, deeper ring.
+constexpr int CORESIDENT_SMEM = 113 * 1024;      // 2 x (113 KB + 1 KB reserved) = 228 KB, the SM's shared memory
 template <int MMA_N>
 struct Cfg {
     static constexpr int A_TILE_BYTES = MMA_N * KT_BYTES;
     static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES + 2 * SF_TILE_BYTES;
-    static constexpr int STAGES = (SMEM_BUDGET - 1024 - CTRL_BYTES - WORK_BYTES) / STAGE_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + CTRL_BYTES + WORK_BYTES;
+    static constexpr int CTAS_PER_SM = MMA_N == 8 ? 2 : 1;
+    static constexpr int fixed_bytes(int vt_bytes) { return 1024 + CTRL_BYTES + XT_BYTES + vt_bytes; }
+    static constexpr int stages_alone(int vt_bytes) { return (SMEM_BUDGET - fixed_bytes(vt_bytes)) / STAGE_BYTES; }
+    static constexpr int stages_shared(int vt_bytes) { return (CORESIDENT_SMEM - fixed_bytes(vt_bytes)) / STAGE_BYTES; }
+    static constexpr int smem_bytes(int ring, int vt_bytes) { return ring * STAGE_BYTES + fixed_bytes(vt_bytes); }
+    static constexpr int STAGES = stages_alone(VT_MIN_BYTES);          // the deepest ring
     static_assert(STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned for the 128-byte swizzle");
     static_assert(STAGES >= 4 && STAGES <= 16, "stage count out of range");
+    static_assert(stages_alone(VT_MAX_BYTES) >= SF_SETS, "the ring must not be shorter than the scale-factor sets");
+    static_assert(stages_shared(VT_MIN_BYTES) >= SF_SETS || CTAS_PER_SM == 1, "the ring must not be shorter than the scale-factor sets");
 };
 
 struct FusedParams {
@@ -75,16 +92,20 @@ struct FusedParams {
     const __nv_bfloat16* C;
     __nv_bfloat16* Y;
     int32_t* status;
-    uint32_t* z_counter;      // [0] arrivals of z producers, [1] consumers that have seen it complete
+    uint32_t* z_counter;      // [0] number of launches completed on this scratch (gives the z validity bit),
+                              // [1] CTAs of the current launch that have finished
     uint32_t* tile_cnt;
     float* zbuf;
     float* partials;
     int M, N, K, R, Rw, Rpad;
     int ntile, nkt, G, max_slots;
-    int z_consumers;          // CTAs that wait for z in this launch (all of them, or only those that finish a tile)
-    int ring;                 // pipeline stages in use (<= Cfg::STAGES). Every byte a CTA requests early is delivered
-                              // ahead of its later small reads (x, z, partial sums) on the SM's inbound path, so a
-                              // deep ring buys nothing for a short stream and delays the latency-critical reads
+    int ring;                 // pipeline stages (<= Cfg::STAGES); the shared-memory layout follows it
+    int trigger;              // where the CTA lets the next kernel of the stream start: 0 after set-up, 4 after its own
+                              // dependency wait, 3 once its activation row has landed, 1 after its z stage, 2 after
+                              // its first expansion (an exiting CTA counts as having done so)
+    int vt_bytes;             // shared memory for the z stage's sign words (VT_MIN_BYTES .. VT_MAX_BYTES)
+    int nsl;                  // z stage: rank slices per activation row; work item (row m, slice s) = m*nsl + s goes to
+                              // CTA (m*nsl + s) % G
     int cluster;              // > 1: a tile belongs to a cluster of this many CTAs (partial sums through DSMEM)
     uint32_t epoch;
     int mode;
@@ -98,8 +119,11 @@ struct Ctrl {   // lives in shared memory after the stages
     uint64_t acc_empty[2];
     uint64_t sf_full[SF_SETS];    // scale factors of a unit are in TMEM set q (128 arrivals)
     uint64_t sf_empty[SF_SETS];   // the MMAs that read set q have completed (tcgen05.commit)
-    float zred[8][VT_RANKS];      // z stage: per-warp partial sums
+    float zred[8][ZR_MAX];        // z stage: per-warp partial sums of sum_{sign = +1} x, per rank of the chunk
+    float zall[8];                // z stage: per-warp partial sums of sum x
     uint64_t red_bar;             // cluster mode, finisher CTA: the other CTAs' partial sums are in this CTA's smem
+    uint64_t x_bar;               // z stage: the activation row has landed (bulk copy)
+    uint64_t red_free;            // cluster mode, other CTAs: the finisher's z stage is over, its work area may be written
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -129,7 +153,7 @@ __device__ __noinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl* ctrl,
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 31u) == 31u) {
+        if ((it & 3u) == 3u) {          // (a try may have been parked for up to a millisecond)
             if (ctrl->abort) return false;
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
@@ -157,7 +181,7 @@ __device__ __noinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, Ctr
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait_cluster(bar, parity)) return true;
-        if ((it & 31u) == 31u) {
+        if ((it & 3u) == 3u) {
             if (ctrl->abort) return false;
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;

@@ -20,7 +20,7 @@ __device__ __forceinline__ void tmem_ld_acc(uint32_t taddr, float* v) {
 }
 
 template <int MMA_N, int ROWS>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, Cfg<MMA_N>::CTAS_PER_SM)
 fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ FusedParams p) {
     static_assert(ROWS <= MMA_N, "the tensor-core tile must cover the rows");
@@ -28,7 +28,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t stage0 = (raw + 1023u) & ~1023u;                 // shared-window address of stage 0
-    uint8_t* after_stages = smem_raw + (stage0 - raw) + C::STAGES * C::STAGE_BYTES;
+    const int ring = p.ring;                                        // stages in use; the host sized the allocation for it
+    uint8_t* after_stages = smem_raw + (stage0 - raw) + ring * C::STAGE_BYTES;
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(after_stages);
     uint8_t* work = after_stages + CTRL_BYTES;                       // WORK_BYTES, 1024-byte aligned
 
@@ -37,7 +38,6 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     const int lane = tid & 31;
     const int cta = blockIdx.x;
 
-    const int ring = p.ring < C::STAGES ? p.ring : C::STAGES;   // stages in use (see FusedParams::ring)
     const int T = p.ntile * p.nkt;
     int u0, u1;
     if (p.cluster > 1) {      // CTA r of the cluster that owns tile t takes k-tiles [r*nkt/c, (r+1)*nkt/c)
@@ -49,12 +49,14 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         u1 = sched_first_unit(cta + 1, T, p.G);
     }
 
+    uint32_t seq = 0;         // (thread 0) launches completed on this scratch before this one
+
     // ---------------- set-up ----------------
-    if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 10] = globaltimer_ns();
-    if (tid == FIRST_W_WARP * 32) {
+    if (tid == 0 && p.stamps) { p.stamps[(size_t)cta * STAMP_WORDS + 10] = globaltimer_ns(); p.stamps[(size_t)cta * STAMP_WORDS + 1] = clock64(); }
+    if (tid == FIRST_SF_WARP * 32) {
 #pragma unroll 1
-        for (int s = 0; s < C::STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->full[s]), 2);     // one weight producer + one activation producer
+        for (int s = 0; s < ring; ++s) {
+            mbar_init(smem_u32(&ctrl->full[s]), 1);     // the stage's producer; the copies complete the byte count
             mbar_init(smem_u32(&ctrl->empty[s]), 1);
         }
 #pragma unroll 1
@@ -67,6 +69,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             mbar_init(smem_u32(&ctrl->sf_empty[q]), 1);
         }
         mbar_init(smem_u32(&ctrl->red_bar), p.cluster > 1 ? (uint32_t)(p.cluster - 1) : 1u);
+        mbar_init(smem_u32(&ctrl->red_free), 1);
+        mbar_init(smem_u32(&ctrl->x_bar), 1);
         ctrl->abort = 0;
         fence_mbar_init();
         prefetch_tmap(&tmW);
@@ -81,101 +85,96 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     tc_fence_after_sync();
     if (p.cluster > 1) cluster_sync_all();   // every CTA's barriers exist before a peer may arrive on them
     const uint32_t tmem = ctrl->tmem_base;
-    griddep_launch_dependents();   // the next kernel of the stream may start its own set-up and weight prefetch
+    if (p.trigger == 0) griddep_launch_dependents();   // the next kernel of the stream may start its set-up and weight prefetch
     if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 0] = globaltimer_ns();
 
-    if (warp >= FIRST_W_WARP && warp < FIRST_SF_WARP) {
-        // ================= producers =================
-        // Weight producer j issues the 18 KB weight record of units j, j+W_PRODUCERS, ... (in processing order),
-        // activation producer j the activation tile and its scales of the same units. Weights do not depend on the
-        // previous kernel of the stream, so their copies start at once; activations are what that kernel produced.
-        if (lane == 0) {
-            const bool is_w = warp < FIRST_A_WARP;
-            if (!is_w) griddep_wait();
-            const int mine = is_w ? (warp - FIRST_W_WARP) : (warp - FIRST_A_WARP);
-            const int nprod = is_w ? W_PRODUCERS : A_PRODUCERS;
-            int i = 0;
-            bool ok = true;
-#pragma unroll 1
-            for (SegWalk sw(u0, u1, p.nkt); ok && !sw.done(); sw.next()) {
-                const int us = sw.first();
-                const int cnt = sw.count();
-                int t = (int)((unsigned)us / (unsigned)p.nkt);
-                int kt = us - t * p.nkt;
-#pragma unroll 1
-                for (int u = us; u < us + cnt; ++u, ++i, ++kt) {
-                    if (i % nprod != mine) continue;
-                    const int s = i % ring;
-                    const int use = i / ring;
-                    if (use > 0 && !wait_bar(smem_u32(&ctrl->empty[s]), (use - 1) & 1, ctrl, p.status, p.epoch, ST_EMPTY, warp)) {
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t sbase = stage0 + s * C::STAGE_BYTES;
-                    const uint32_t bar = smem_u32(&ctrl->full[s]);
-                    if (is_w) {
-                        mbar_arrive_expect_tx(bar, W_TILE_BYTES + SF_TILE_BYTES);
-                        if (p.W_tiled) {
-                            // one contiguous 18 KB record per unit: pre-swizzled codes followed by the scale atoms
-                            bulk_load(sbase, p.W_tiled + (size_t)u * (W_TILE_BYTES + SF_TILE_BYTES), W_TILE_BYTES + SF_TILE_BYTES, bar);
-                        } else {
-                            tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
-                            bulk_load(sbase + W_TILE_BYTES, p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
-                        }
-                    } else {
-                        mbar_arrive_expect_tx(bar, C::A_TILE_BYTES + SF_TILE_BYTES);
-                        tma_load_2d(sbase + W_TILE_BYTES + SF_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
-                        bulk_load(sbase + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES, p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
-                    }
-                }
-            }
+    if (warp >= FIRST_Z_WARP && warp < MMA_WARP) {
+        // ================= z warps: second half of the z stage =================
+        if (p.R > 0) {
+            const int zt = EPI_THREADS + (tid - FIRST_Z_WARP * 32);
+            uint32_t seq_unused;
+            z_stage(p, ctrl, work, p.zbuf, cta, zt, &seq_unused);     // (contains the dependency wait)
+            named_bar_sync(3, Z_THREADS);      // the work area is free for the expansion
         }
-    } else if (warp >= FIRST_SF_WARP && warp < MMA_WARP) {
-        // ================= scale-factor movers =================
+    } else if (warp >= FIRST_SF_WARP && warp < FIRST_Z_WARP) {
+        // ================= feeders: copy requests + scale-factor moves =================
+        // Lane 0 of feeder j requests the copies of units j, j+PRODUCERS, ... (in processing order). Weights do not
+        // depend on the previous kernel of the stream: the first ring of weight records is requested at once, before
+        // the dependency wait; activations are what that kernel produced and follow the wait. Later units are
+        // requested from inside the scale-factor loop, as their stages come free.
+        const int mine = warp - FIRST_SF_WARP;
+        const int nunits = u1 - u0;
+        const int head = SegWalk(u0, u1, p.nkt).head;     // units [head, u1) are processed first, then [u0, head)
+        const int nhead = u1 - head;
+        auto issue_w = [&](int i) {
+            const int u = i < nhead ? head + i : u0 + (i - nhead);
+            const uint32_t sbase = stage0 + (i % ring) * C::STAGE_BYTES;
+            const uint32_t bar = smem_u32(&ctrl->full[i % ring]);
+            mbar_arrive_expect_tx(bar, W_TILE_BYTES + C::A_TILE_BYTES + 2 * SF_TILE_BYTES);
+            if (p.W_tiled) {
+                // one contiguous 18 KB record per unit: pre-swizzled codes followed by the scale atoms
+                bulk_load(sbase, p.W_tiled + (size_t)u * (W_TILE_BYTES + SF_TILE_BYTES), W_TILE_BYTES + SF_TILE_BYTES, bar);
+            } else {
+                const int t = (int)((unsigned)u / (unsigned)p.nkt), kt = u - t * p.nkt;
+                tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
+                bulk_load(sbase + W_TILE_BYTES, p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
+            }
+        };
+        auto issue_a = [&](int i) {
+            const int u = i < nhead ? head + i : u0 + (i - nhead);
+            const int kt = (int)((unsigned)u % (unsigned)p.nkt);
+            const uint32_t sbase = stage0 + (i % ring) * C::STAGE_BYTES;
+            const uint32_t bar = smem_u32(&ctrl->full[i % ring]);
+            tma_load_2d(sbase + W_TILE_BYTES + SF_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
+            bulk_load(sbase + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES, p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
+        };
+        if (lane == 0) {
+#pragma unroll 1
+            for (int i = mine; i < nunits && i < ring; i += PRODUCERS) issue_w(i);
+            griddep_wait();
+#pragma unroll 1
+            for (int i = mine; i < nunits && i < ring; i += PRODUCERS) issue_a(i);
+        }
+        __syncwarp();
+
         // The block-scaled MMA reads its scale factors from TMEM, lane l of every 32-lane quadrant holding rows
         // l, l+32, l+64, l+96 of the 128x4 atom in four consecutive columns. tcgen05.cp can place an atom there, but
         // eight of them per unit occupy the tensor pipe longer than the unit's four MMAs (measured); here warp q
         // writes quadrant q from registers instead: per unit 8 x 128-bit shared loads and 2 x tcgen05.st per thread.
         const uint32_t quad = (uint32_t)((warp & 3) * 32) << 16;
-        if (p.R > 0) {
-            // until the first weights land these warps are idle: they are the second half of the z-stage threads
-            const int zt = EPI_THREADS + (tid - FIRST_SF_WARP * 32);
-            float* zb = p.zbuf + (size_t)(p.epoch & 1u) * 32 * p.Rpad;
-            z_prefetch_v<ROWS>(p, work, cta, zt);
-            griddep_wait();
-            z_stage<ROWS>(p, ctrl, work, zb, cta, zt, true);
-            named_bar_sync(3, Z_THREADS);      // every z store is ordered before the publishing thread's release
-        }
-        int i = 0;
-        bool ok = true;
 #pragma unroll 1
-        for (SegWalk sw(u0, u1, p.nkt); ok && !sw.done(); sw.next()) {
-            const int cnt = sw.count();
-#pragma unroll 1
-            for (int j = 0; j < cnt; ++j, ++i) {
-                const int s = i % ring;
-                const int q = i % SF_SETS;
-                bool ready = wait_bar(smem_u32(&ctrl->full[s]), (i / ring) & 1, ctrl, p.status, p.epoch, ST_FULL, warp);
-                if (ready && i >= SF_SETS)
-                    ready = wait_bar(smem_u32(&ctrl->sf_empty[q]), ((i / SF_SETS) - 1) & 1, ctrl, p.status, p.epoch, ST_SF_EMPTY, warp);
-                if (!__all_sync(0xffffffffu, ready)) { ok = false; break; }     // warp-uniform: the TMEM stores are warp-wide
-                tc_fence_after_sync();
-                const uint8_t* stage = smem_raw + (stage0 - raw) + s * C::STAGE_BYTES;
-                const uint4* wsf = reinterpret_cast<const uint4*>(stage + W_TILE_BYTES) + lane;
-                const uint4* asf = reinterpret_cast<const uint4*>(stage + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES) + lane;
-                uint32_t ra[16], rb[16];
+        for (int i = 0; i < nunits; ++i) {
+            const int s = i % ring;
+            const int q = i % SF_SETS;
+            bool ready = wait_bar(smem_u32(&ctrl->full[s]), (i / ring) & 1, ctrl, p.status, p.epoch, ST_FULL, warp);
+            if (ready && i >= SF_SETS)
+                ready = wait_bar(smem_u32(&ctrl->sf_empty[q]), ((i / SF_SETS) - 1) & 1, ctrl, p.status, p.epoch, ST_SF_EMPTY, warp);
+            if (!__all_sync(0xffffffffu, ready)) break;     // warp-uniform: the TMEM stores are warp-wide
+            tc_fence_after_sync();
+            const uint8_t* stage = smem_raw + (stage0 - raw) + s * C::STAGE_BYTES;
+            const uint4* wsf = reinterpret_cast<const uint4*>(stage + W_TILE_BYTES) + lane;
+            const uint4* asf = reinterpret_cast<const uint4*>(stage + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES) + lane;
+            uint32_t ra[16], rb[16];
 #pragma unroll
-                for (int a = 0; a < 4; ++a) {
-                    const uint4 x = wsf[a * 32], y = asf[a * 32];       // atom a, row `lane`: 16 bytes = 4 columns
-                    ra[4 * a] = x.x; ra[4 * a + 1] = x.y; ra[4 * a + 2] = x.z; ra[4 * a + 3] = x.w;
-                    rb[4 * a] = y.x; rb[4 * a + 1] = y.y; rb[4 * a + 2] = y.z; rb[4 * a + 3] = y.w;
-                }
-                tmem_st_x16(tmem + quad + 32u * q + SFA_COL, ra);
-                tmem_st_x16(tmem + quad + 32u * q + SFB_COL, rb);
-                tc_wait_st();
-                tc_fence_before_sync();
-                mbar_arrive(smem_u32(&ctrl->sf_full[q]));
+            for (int a = 0; a < 4; ++a) {
+                const uint4 x = wsf[a * 32], y = asf[a * 32];       // atom a, row `lane`: 16 bytes = 4 columns
+                ra[4 * a] = x.x; ra[4 * a + 1] = x.y; ra[4 * a + 2] = x.z; ra[4 * a + 3] = x.w;
+                rb[4 * a] = y.x; rb[4 * a + 1] = y.y; rb[4 * a + 2] = y.z; rb[4 * a + 3] = y.w;
             }
+            tmem_st_x16(tmem + quad + 32u * q + SFA_COL, ra);
+            tmem_st_x16(tmem + quad + 32u * q + SFB_COL, rb);
+            tc_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&ctrl->sf_full[q]));
+            // refill: the stage of unit i-1 is the stage of unit j = i-1+ring; its feeder requests the copies as soon
+            // as the MMAs of unit i-1 have completed
+            const int j = i - 1 + ring;
+            bool fed = true;
+            if (i >= 1 && j < nunits && (j % PRODUCERS) == mine && lane == 0) {
+                fed = wait_bar(smem_u32(&ctrl->empty[j % ring]), ((j / ring) - 1) & 1, ctrl, p.status, p.epoch, ST_EMPTY, warp);
+                if (fed) { issue_w(j); issue_a(j); }
+            }
+            if (!__all_sync(0xffffffffu, fed)) break;
         }
     } else if (warp == MMA_WARP) {
         // ================= MMA issue =================
@@ -215,17 +214,17 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
     } else {
         // ================= z stage, expansion, epilogue (128 threads) =================
-        float* zb = p.zbuf + (size_t)(p.epoch & 1u) * 32 * p.Rpad;
         float* zs = reinterpret_cast<float*>(work);
         const bool owner_mode = (p.mode & 0xff) == 4;
 
-        // U words of the first chunk of the first two segments: requested before anything else, so that they do
-        // not queue behind the weight stream later
-        uint32_t uw_first[2][ZS_WORDS];
+        // U words of the first two segments' first ranks: requested before anything else, so that they do not queue
+        // behind the weight stream later
+        uint32_t uw_first[2][ZS_FIRST];
 #pragma unroll
         for (int g = 0; g < 2; ++g)
 #pragma unroll
-            for (int w = 0; w < ZS_WORDS; ++w) uw_first[g][w] = 0u;
+            for (int w = 0; w < ZS_FIRST; ++w) uw_first[g][w] = 0u;
+        uint32_t phase = 0;
         if (p.R > 0) {
             SegWalk sw(u0, u1, p.nkt);
 #pragma unroll
@@ -235,25 +234,24 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     const int n = si.t * TILE_N + tid;
                     const int32_t* ucol = p.Ucol + (size_t)(n < p.N ? n : 0) * p.Rw;
 #pragma unroll
-                    for (int w = 0; w < ZS_WORDS; ++w)
+                    for (int w = 0; w < ZS_FIRST; ++w)
                         uw_first[g][w] = (uint32_t)ucol[(si.w0 + w < si.w1) ? (si.w0 + w) : (si.w0 < si.w1 ? si.w0 : 0)];
                     sw.next();
                 }
             }
 
-            z_prefetch_v<ROWS>(p, work, cta, tid);
-            griddep_wait();        // everything below reads what earlier kernels of the stream wrote (x, scratch)
-            if (tid == 0 && p.stamps) { p.stamps[(size_t)cta * STAMP_WORDS + 11] = globaltimer_ns(); p.stamps[(size_t)cta * STAMP_WORDS + 12] = clock64(); }
-            z_stage<ROWS>(p, ctrl, work, zb, cta, tid, true);
-            named_bar_sync(3, Z_THREADS);      // orders every z store before thread 0's (cumulative) release
-            if (tid == 0) {
-                red_release_add_u32(p.z_counter, 1u);
-                if (p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 1] = globaltimer_ns();
-            }
+            // (contains the dependency wait; also reads the number of launches completed on this scratch so far: its
+            // parity is the validity mark of this launch's z values)
+            phase = z_stage(p, ctrl, work, p.zbuf, cta, tid, &seq);
+            named_bar_sync(3, Z_THREADS);      // the work area is free for the expansion
         }
+        if (p.trigger == 1 && tid == 0) griddep_launch_dependents();
         griddep_wait();            // (again, for the R == 0 path; a second wait returns at once)
+        // Cluster mode: the other CTAs of the cluster deposit their partial sums in this (the finishing) CTA's work
+        // area, which its z stage has been using until now: tell them it is free.
+        if (p.cluster > 1 && (cta % p.cluster) == p.cluster - 1 && tid < p.cluster - 1)
+            mbar_arrive_remote_release(map_to_cta(smem_u32(&ctrl->red_free), (uint32_t)tid));
 
-        bool z_ready = false;
         const float alpha = p.alpha[0];
         int seg = 0;
 #pragma unroll 1
@@ -268,29 +266,16 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             float corr[ROWS];
 #pragma unroll
             for (int m = 0; m < ROWS; ++m) corr[m] = 0.f;
-            // mode 2: every CTA passes the z wait once (the consumer count that re-arms the counter is the grid size),
-            // mode 4: only CTAs that finish a tile do
-            if (p.R > 0 && (!owner_mode || si.w0 < si.w1)) {
-                if (!z_ready) {
-                    if (tid == 0 && wait_counter(p.z_counter, (uint32_t)p.G, ctrl, p.status, p.epoch, ST_Z)) {
-                        // the last consumer to get here clears both words for the next launch on this scratch
-                        if (atomicAdd(p.z_counter + 1, 1u) == (uint32_t)p.z_consumers - 1u) {
-                            p.z_counter[0] = 0u;
-                            p.z_counter[1] = 0u;
-                        }
-                    }
-                    if (!epi_sync_ok(ctrl)) break;
-                    z_ready = true;
-                    if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 2] = globaltimer_ns();
-                }
-                const int w0 = si.w0, w1 = si.w1;
+            // every contributor of a tile expands its share of the ranks (mode 4: the finisher expands them all)
+            if (p.R > 0 && si.w0 < si.w1) {
                 const int32_t* ucol = p.Ucol + (size_t)(valid ? n : 0) * p.Rw;
-                uint32_t uw_sel[ZS_WORDS];
+                uint32_t uw_sel[ZS_FIRST];
 #pragma unroll
-                for (int w = 0; w < ZS_WORDS; ++w) uw_sel[w] = (seg & 1) ? uw_first[1][w] : uw_first[0][w];
-                expand_z<ROWS>(corr, zb, p.Rpad, ucol, w0, w1, zs, tid, uw_sel, seg < 2);
+                for (int w = 0; w < ZS_FIRST; ++w) uw_sel[w] = (seg & 1) ? uw_first[1][w] : uw_first[0][w];
+                if (!expand_z<ROWS>(corr, p, ctrl, p.zbuf, ucol, si.w0, si.w1, zs, tid, uw_sel, seg < 2, phase)) break;
                 if (tid == 0 && p.stamps && seg == 0) p.stamps[(size_t)cta * STAMP_WORDS + 3] = globaltimer_ns();
             }
+            if (p.trigger == 2 && tid == 0 && seg == 0) griddep_launch_dependents();
 
             // accumulators of this segment
             wait_bar(smem_u32(&ctrl->acc_full[buf]), (seg >> 1) & 1, ctrl, p.status, p.epoch, ST_ACC_FULL, warp);
@@ -311,6 +296,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 // ---- cluster mode: partial sums travel through the finisher's shared memory ----
                 const uint32_t red0 = smem_u32(work + RED_OFF);
                 if (!si.finisher) {
+                    wait_bar_cluster(smem_u32(&ctrl->red_free), 0, ctrl, p.status, p.epoch, ST_CLUSTER);
+                    if (!epi_sync_ok(ctrl)) break;
                     const uint32_t dst = map_to_cta(red0 + (uint32_t)((slot * ROWS) * TILE_N + tid) * 4u, (uint32_t)(p.cluster - 1));
 #pragma unroll
                     for (int m = 0; m < ROWS; ++m) st_cluster_f32(dst + (uint32_t)(m * TILE_N) * 4u, v[m]);
@@ -371,18 +358,27 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                     }
                 }
             }
-            if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 5 + (seg > 0 ? 1 : 0)] = globaltimer_ns();
+            if (tid == 0 && p.stamps && seg == 0) p.stamps[(size_t)cta * STAMP_WORDS + 5] = globaltimer_ns();
         }
     }
 
     // ---------------- common exit ----------------
     tc_fence_before_sync();
     __syncthreads();
+    if (tid == 0 && p.stamps) { p.stamps[(size_t)cta * STAMP_WORDS + 13] = globaltimer_ns(); p.stamps[(size_t)cta * STAMP_WORDS + 6] = clock64(); }
     if (ctrl->abort) {
         // give copies that may still be in flight time to land before the shared memory is released
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 2000000ull) { }
         __syncthreads();
+    }
+    // The last CTA to get here advances the scratch's launch count, which flips the validity mark of z for the next
+    // launch (whose reads of the count follow the completion of this grid).
+    if (tid == 0 && p.R > 0) {
+        if (atomicAdd(p.z_counter + 1, 1u) == (uint32_t)p.G - 1u) {
+            p.z_counter[1] = 0u;
+            p.z_counter[0] = seq + 1u;
+        }
     }
     // cluster mode: no CTA leaves while a peer could still write into its shared memory (also on the failure path:
     // every CTA gets here because every wait is bounded)

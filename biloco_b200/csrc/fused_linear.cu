@@ -21,12 +21,13 @@
 //    others store fp32 partials (alpha*acc + their slice of the low-rank term) to scratch and bump the tile's
 //    counter; the finisher adds them in slot order (deterministic), rounds and stores.
 //  * Low-rank term: at entry every CTA computes a slice of the ranks of z (all M rows) on CUDA cores from the
-//    bit-packed V and publishes it in scratch; an arrival counter (mode 2) tells the consumers that z is
-//    complete. Each contributor of a tile expands z through the packed U signs for its share of the rank words
-//    while its weight loads are in flight, and adds the result to the accumulators read back from TMEM.
-//    Counters return to zero inside the launch (the finisher of a tile clears its counter, the last CTA past
-//    the z wait clears the z words), so launches on one scratch need no clearing in between and a captured
-//    CUDA graph can be replayed; launches that share a scratch must not overlap.
+//    bit-packed V and publishes it in scratch. There is no completion flag: each published value carries a
+//    validity mark in its lowest mantissa bit that flips from launch to launch, and the consumers poll the
+//    values themselves. Each contributor of a tile expands z through the packed U signs for its share of the
+//    rank words and adds the result to the accumulators read back from TMEM.
+//    Tile counters return to zero inside the launch and the last CTA to leave advances the scratch's launch
+//    count, so launches on one scratch need no clearing in between and a captured CUDA graph can be replayed;
+//    launches that share a scratch must not overlap.
 //  * Every wait (mbarrier, counter) is bounded by a %globaltimer budget; a wait that runs out records a code in
 //    the status words of the scratch, raises a CTA-wide abort flag, and the CTA leaves through the common exit
 //    (TMEM freed) instead of hanging.
@@ -114,10 +115,12 @@ static int device_sm_count() {
     return cached[dev];
 }
 
-static int g_ring = 16;                          // pipeline stages in use (clamped to what fits)
+static int g_ring = 0;                           // pipeline stages: 0 = chosen per kernel, else clamped to what fits
 static int g_use_pdl = 1;                        // launch with programmatic stream serialization
 static unsigned long long* g_stamps = nullptr;   // debug time-stamp buffer for subsequent launches (or null)
 static size_t g_stamps_bytes = 0;
+static size_t g_stamps_seq = 0;
+static int g_trigger = -1;                        // < 0: chosen per launch (see launch())
 
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 
@@ -175,8 +178,9 @@ static int cluster_size_for(int M, int ntile, int nkt, int num_sms) {
     int c = num_sms / ntile;
     if (c > 8) c = 8;
     if (c > nkt) c = nkt;
+    const int rows = M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
+    while (c >= 2 && (c - 1) * rows * TILE_N * 4 > RED_BYTES) --c;     // the peers' partial sums must fit beside the staged z
     if (c < 2) return 0;
-    if ((c - 1) * 8 * TILE_N * 4 > RED_BYTES) return 0;
     if (ntile * c * 3 < num_sms * 2) return 0;
     return c;
 }
@@ -184,20 +188,43 @@ static int cluster_size_for(int M, int ntile, int nkt, int num_sms) {
 static int rows_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : (M <= 16 ? 16 : 32)))); }
 
 template <int MMA_N, int ROWS>
-static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedParams& p, cudaStream_t stream) {
+static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedParams& p_in, cudaStream_t stream) {
+    using C = Cfg<MMA_N>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 Cfg<MMA_N>::SMEM_BYTES) != cudaSuccess)
+                                 SMEM_BUDGET) != cudaSuccess)
             return BILOCO_ERR_CUDA;
         attr_set[dev] = true;
     }
+    // z stage geometry: nsl rank slices per activation row, and shared memory for the sign words of one slice
+    FusedParams p = p_in;
+    p.nsl = p.G / p.M > 1 ? p.G / p.M : 1;
+    int vt = VT_MIN_BYTES;
+    if (p.R > 0) {
+        const int ranks = (p.R + p.nsl - 1) / p.nsl;
+        const int kc = p.K < XK ? p.K : XK;
+        vt = (ranks * (kc / 8) + 1023) & ~1023;
+        if (vt < VT_MIN_BYTES) vt = VT_MIN_BYTES;
+        if (vt > VT_MAX_BYTES) vt = VT_MAX_BYTES;
+    }
+    p.vt_bytes = vt;
+    // where a CTA lets the next launch of the stream start (measured at K = N = 5120: once the activation row has
+    // landed for the cluster schedule, straight after set-up otherwise)
+    p.trigger = g_trigger >= 0 ? g_trigger : (p.cluster > 1 ? 3 : 0);
+    // Ring depth decides how many CTAs share an SM: with the short ring the next launch of the stream moves in beside
+    // this one (only useful when launches overlap, i.e. with programmatic dependent launch).
+    int ring = C::stages_alone(vt);
+    if (g_ring) ring = g_ring < ring ? g_ring : ring;
+    else if (C::CTAS_PER_SM == 2 && g_use_pdl && C::stages_shared(vt) >= SF_SETS) ring = C::stages_shared(vt);
+    if (ring < SF_SETS) ring = SF_SETS;
+    p.ring = ring;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.G);
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = Cfg<MMA_N>::SMEM_BYTES;
+    cfg.dynamicSmemBytes = (size_t)C::smem_bytes(ring, vt);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -327,17 +354,11 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
         if (p.cluster < 2) return BILOCO_ERR_SHAPE;
         p.G = L.ntile * p.cluster;
     }
-    p.z_consumers = p.G;
-    if ((mode & 0xff) == BILOCO_MODE_OWNER) {   // only CTAs that finish a tile wait for z
-        int consumers = 0, prev = -1;
-        const int T = L.ntile * L.nkt;
-        for (int t = 0; t < L.ntile; ++t) {
-            const int c = sched_cta_of_unit(t * L.nkt + L.nkt - 1, T, L.G);
-            if (c != prev) { ++consumers; prev = c; }
-        }
-        p.z_consumers = consumers;
+    p.stamps = nullptr;
+    if (g_stamps && g_stamps_bytes >= (size_t)p.G * STAMP_WORDS * 8) {     // consecutive launches rotate through the buffer
+        const size_t per = (size_t)p.G * STAMP_WORDS, slots = g_stamps_bytes / (per * 8);
+        p.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
     }
-    p.stamps = (g_stamps && g_stamps_bytes >= (size_t)p.G * STAMP_WORDS * 8) ? g_stamps : nullptr;
 
     cudaStream_t s = (cudaStream_t)stream;
     switch (rows_for(M)) {
@@ -357,7 +378,6 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
 // ---------------------------------------------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_noalloc_scratch[BILOCO_NOALLOC_SCRATCH_BYTES];
 static void* g_noalloc_ptr[64] = {nullptr};                 // per device, filled by the first call on that device
-static unsigned long long g_noalloc_shape[64] = {0};        // problem shape of the last call on that device
 
 extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
                                                 const void* A_codes, const void* A_sf, const void* X_bf16,
@@ -388,14 +408,11 @@ extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void*
     }
     uint8_t* sc = (uint8_t*)g_noalloc_ptr[dev];
 
-    // The array keeps what the last call left. Status words and counters must start at zero (they are zero after a
-    // call that ran to completion, but not after one whose wait gave up); the z area must be zero beyond rank R, which
-    // a previous problem with more ranks may have written.
-    const unsigned long long shape = ((unsigned long long)(unsigned)M << 48) ^ ((unsigned long long)(unsigned)N << 28) ^
-                                     ((unsigned long long)(unsigned)K << 12) ^ (unsigned long long)(unsigned)R;
-    const size_t clear = (g_noalloc_shape[dev] == shape) ? L.off_z : L.off_part;
+    // The array keeps what the last call left, possibly from another problem shape or from a call whose wait gave up:
+    // status words, launch count, tile counters and the z area all restart from zero on every call (the z values'
+    // validity marks are relative to the launch count).
+    const size_t clear = L.off_part;
     if (cudaMemsetAsync(sc, 0, clear, s) != cudaSuccess) return BILOCO_ERR_CUDA;
-    g_noalloc_shape[dev] = shape;
 
     // tensor maps are encoded on the stack for every call (the cache of the allocating entry point grows on the heap)
     EncodeTiledFn enc = get_encode_fn();
@@ -436,16 +453,6 @@ extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void*
     p.mode = mode;
     p.cluster = 0;
     p.ring = g_ring;
-    p.z_consumers = L.G;
-    if ((mode & 0xff) == BILOCO_MODE_OWNER) {
-        int consumers = 0, prev = -1;
-        const int T = L.ntile * L.nkt;
-        for (int t = 0; t < L.ntile; ++t) {
-            const int c = sched_cta_of_unit(t * L.nkt + L.nkt - 1, T, L.G);
-            if (c != prev) { ++consumers; prev = c; }
-        }
-        p.z_consumers = consumers;
-    }
     p.stamps = nullptr;
     switch (rows_for(M)) {
         case 1: return launch<8, 1>(tmW, tmA, p, s);
@@ -466,13 +473,15 @@ extern "C" int biloco_b200_noalloc_status(int32_t* out16, biloco_stream_t stream
 
 extern "C" int biloco_b200_set_option(int option, int value) {
     if (option == BILOCO_OPT_PDL) { g_use_pdl = value ? 1 : 0; return BILOCO_OK; }
-    if (option == BILOCO_OPT_RING) { g_ring = value < 2 ? 2 : value; return BILOCO_OK; }
+    if (option == BILOCO_OPT_TRIGGER) { g_trigger = value; return BILOCO_OK; }
+    if (option == BILOCO_OPT_RING) { g_ring = value <= 0 ? 0 : value; return BILOCO_OK; }
     return BILOCO_ERR_MODE;
 }
 
 extern "C" int biloco_b200_debug_stamps(void* device_buf, size_t bytes) {
     g_stamps = (unsigned long long*)device_buf;
     g_stamps_bytes = device_buf ? bytes : 0;
+    g_stamps_seq = 0;
     return BILOCO_OK;
 }
 

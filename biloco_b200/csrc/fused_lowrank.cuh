@@ -6,120 +6,184 @@
 
 namespace biloco {
 
-// z stage, run by Z_THREADS = 256 threads (the four epilogue warps and the four scale-factor warps, which have nothing
-// to move until the first weights land). CTA `cta` owns ranks [cta*R/G, (cta+1)*R/G), at most VT_RANKS at a time.
-// Per pass a tile of the activation (RP rows x XK k, 16-byte chunks transposed so that a warp reads consecutive
-// chunks) and the sign words of the CTA's ranks are copied to shared memory with one batch of cp.async. The eight
-// warps are arranged as RP rows x KW k-groups; a lane owns 32-bit sign words (32 consecutive k) of its k-group, unpacks
-// the 32 activations once and adds them into one accumulator per rank under a predicate taken from the sign bit.
-// Accumulators live in registers across all passes; one shuffle reduction and one shared-memory exchange at the end.
+// z stage, run by Z_THREADS = 256 threads (the four epilogue warps and the four z warps).
+//
+// Work is cut into items (activation row m, rank slice s): nsl slices per row, item m*nsl + s belongs to CTA
+// (m*nsl + s) % G, so with G >= M every CTA reads ONE activation row (K * 2 bytes, the only read of the stage that
+// depends on the previous kernel of the stream) and the sign words of its R*M/G ranks. Ranks are processed in chunks
+// of what the sign-word area holds (at most ZR_MAX), k in passes of XK.
+// Everything that does not depend on the previous kernel happens before the dependency wait, which is inside this
+// function: the work split, the coefficients, the sign words of the first chunk (cp.async, made visible with a
+// barrier). After the wait one thread requests the activation row with a single bulk copy and all threads wait on its
+// mbarrier; nothing else stands between the wait and the arithmetic.
+// Arithmetic: warp w takes the w-th eighth of the pass's 32-bit sign words, one word per lane; a lane unpacks the 32
+// activations of its word once and, for every rank, adds them under predicates taken from the sign bits (four
+// independent accumulators in flight). One shuffle reduction per group of ZG ranks (see z_reduce8), per-warp partial
+// sums in shared memory, one combine per chunk: z = S * (2 * sum_{sign=+1} x - sum x).
+// The CUDA-core code here is bound by instruction issue, not by latency (measured: the same cycles cold and warm,
+// alone or beside spinning warps), so what matters is the instruction count per element and an even spread over warps.
 // zt = index of the calling thread among the 256.
-// The sign words of the first pass are weights, not activations: z_prefetch_v copies them before the caller waits for
-// the previous kernel of the stream.
 constexpr int Z_THREADS = 256;
+constexpr int Z_WARPS = Z_THREADS / 32;
+constexpr int ZG = 8;                            // ranks per reduction group
 
-template <int RP>
-__device__ __forceinline__ void z_issue_v(const FusedParams& p, uint8_t* work, int ic, int nr, int k0, int kc, int zt) {
-    constexpr int XK = XT_BYTES / 2 / RP;
+struct ZItem { int m, ra, rb; };
+__device__ __forceinline__ ZItem z_item(const FusedParams& p, int it) {
+    ZItem z;
+    z.m = it / p.nsl;
+    const int sl = it - z.m * p.nsl;
+    z.ra = sl * p.R / p.nsl;
+    z.rb = (sl + 1) * p.R / p.nsl;
+    return z;
+}
+// ranks per chunk when a pass covers kc k
+__device__ __forceinline__ int z_chunk_ranks(const FusedParams& p, int kc) {
+    const int c = p.vt_bytes / (kc >> 3);
+    return c < ZR_MAX ? c : ZR_MAX;
+}
+
+__device__ __forceinline__ void z_issue_v(const FusedParams& p, uint8_t* work, int r0, int nr, int k0, int kc, int zt) {
     const int vch = kc >> 7;                                 // 16-byte chunks of sign bits per rank
     const uint32_t vt_s = smem_u32(work) + XT_BYTES;
 #pragma unroll 1
     for (int idx = zt; idx < nr * vch; idx += Z_THREADS) {
         const int q = idx / vch, c = idx - q * vch;
-        cp_async16(vt_s + q * (XK / 8) + c * 16, p.Vp + (size_t)(ic + q) * (p.K >> 3) + (k0 >> 3) + c * 16);
+        cp_async16(vt_s + q * (kc >> 3) + c * 16, p.Vp + (size_t)(r0 + q) * (p.K >> 3) + (k0 >> 3) + c * 16);
     }
 }
 
-template <int ROWS>
-__device__ __forceinline__ void z_prefetch_v(const FusedParams& p, uint8_t* work, int cta, int zt) {
-    constexpr int RP = ROWS < 8 ? ROWS : 8;
-    constexpr int XK = XT_BYTES / 2 / RP;
-    const int i0 = cta * p.R / p.G;
-    const int i1 = (cta + 1) * p.R / p.G;
-    const int nr = (i1 - i0) < VT_RANKS ? (i1 - i0) : VT_RANKS;
-    z_issue_v<RP>(p, work, i0, nr, 0, p.K < XK ? p.K : XK, zt);
-    cp_async_commit();
-}
-
-// Adds the 32 activations xf[] into acc[q] for the ranks whose sign bit is set, and keeps their plain sum in `all`
-// (sum_k s_k x_k = 2 * sum_{s_k = +1} x_k - sum_k x_k).
-template <int NQ>
-__device__ __forceinline__ void z_word(const float (&xf)[32], const uint32_t* vrow, int xw_stride, int nq, float (&acc)[NQ]) {
+// acc[q] += sum of the activations xf[] whose sign bit in rank q's word is set, q < NQ: an add under a predicate taken
+// from the sign bit, two accumulators per rank (even and odd k), the element loop outermost so that consecutive adds
+// go to different accumulators. Measured on this part, cycles per (warp, element) with two warps per scheduler:
+// 4.0 for this form with NQ = 4; 4.8 with one accumulator per rank; 5.2 with NQ = 2; 7.6 for sign flips by XOR; 9.7
+// for multiplications by +-1. The predicate is spelled out in PTX so that it cannot turn into a branch.
+template <int NQ, int OFF>
+__device__ __forceinline__ void z_word_n(const float (&xf)[32], const uint32_t* vrow, int xw_stride, float (&accs)[ZG]) {
+    uint32_t vw[NQ];
+    float acc[NQ], a1[NQ];
 #pragma unroll
-    for (int q = 0; q < NQ; ++q) {
-        if (q < nq) {                                   // warp-uniform
-            const uint32_t vw = vrow[q * xw_stride];
+    for (int q = 0; q < NQ; ++q) { vw[q] = vrow[(OFF + q) * xw_stride]; acc[q] = 0.f; a1[q] = 0.f; }
+#define BILOCO_PADD(accv, vwv, bit, xv)                                                                              \
+    asm("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %1, %2;\n\tsetp.ne.u32 p, t, 0;\n\t@p add.f32 %0, %0, %3;\n\t}" \
+        : "+f"(accv) : "r"(vwv), "r"(bit), "f"(xv))
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-                if (vw & (1u << j)) acc[q] += xf[j];
+    for (int j = 0; j < 32; j += 2)
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            BILOCO_PADD(acc[q], vw[q], 1u << j, xf[j]);
+            BILOCO_PADD(a1[q], vw[q], 2u << j, xf[j + 1]);
         }
+#undef BILOCO_PADD
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) accs[OFF + q] += acc[q] + a1[q];
+}
+
+// The same for nq <= ZG ranks, in runs of at most four (5 = 3 + 2, 6 = 3 + 3, 7 = 4 + 3, 8 = 4 + 4); nq is warp-uniform.
+__device__ __forceinline__ void z_word(const float (&xf)[32], const uint32_t* vrow, int xw_stride, int nq, float (&acc)[ZG]) {
+    if (nq <= 4) {
+        if (nq == 1) z_word_n<1, 0>(xf, vrow, xw_stride, acc);
+        else if (nq == 2) z_word_n<2, 0>(xf, vrow, xw_stride, acc);
+        else if (nq == 3) z_word_n<3, 0>(xf, vrow, xw_stride, acc);
+        else z_word_n<4, 0>(xf, vrow, xw_stride, acc);
+    } else if (nq <= 6) {
+        z_word_n<3, 0>(xf, vrow, xw_stride, acc);
+        if (nq == 5) z_word_n<2, 3>(xf, vrow, xw_stride, acc);
+        else z_word_n<3, 3>(xf, vrow, xw_stride, acc);
+    } else {
+        z_word_n<4, 0>(xf, vrow, xw_stride, acc);
+        if (nq == 7) z_word_n<3, 4>(xf, vrow, xw_stride, acc);
+        else z_word_n<4, 4>(xf, vrow, xw_stride, acc);
     }
 }
 
-template <int ROWS>
-__device__ __forceinline__ void z_stage(const FusedParams& p, Ctrl* ctrl, uint8_t* work, float* zb, int cta, int zt, bool v_preloaded) {
-    constexpr int RP = ROWS < 8 ? ROWS : 8;          // rows per pass
-    constexpr int KW = 8 / RP;                       // k-groups (warps per row)
-    constexpr int XK = XT_BYTES / 2 / RP;            // k per pass
-    constexpr int XW = XK / 32;                      // sign words per rank per pass
+// Sum of acc[q] over the 32 lanes for all ZG ranks at once: a lane gives away half of its values at every step, so the
+// eight sums cost 4 + 2 + 1 + 2 shuffles instead of 8 x 5. On return lane l holds the total of rank ((l>>4)&1)*4 +
+// ((l>>3)&1)*2 + ((l>>2)&1).
+__device__ __forceinline__ float z_reduce8(float (&acc)[ZG], int lane) {
+    static_assert(ZG == 8, "written for eight ranks");
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+    float a[4], b[2], c;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {        // lanes with bit 4 set keep ranks 4-7, the others ranks 0-3
+        const float give = h16 ? acc[i] : acc[i + 4], keep = h16 ? acc[i + 4] : acc[i];
+        a[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float give = h8 ? a[i] : a[i + 2], keep = h8 ? a[i + 2] : a[i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+    }
+    {
+        const float give = h4 ? b[0] : b[1], keep = h4 ? b[1] : b[0];
+        c = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+    }
+    c += __shfl_xor_sync(0xffffffffu, c, 2);
+    c += __shfl_xor_sync(0xffffffffu, c, 1);
+    return c;
+}
+
+// Contains the dependency wait (griddepcontrol.wait). Returns the validity mark of this launch's z values: the parity
+// of the scratch's launch count, which is read behind the activation request so that its latency is hidden.
+__device__ __forceinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8_t* work, float* zb, int cta, int zt, uint32_t* seq_out) {
     const int zw = zt >> 5, lane = zt & 31;
-    const int row = zw % RP, kg = zw / RP;
-    const int i0 = cta * p.R / p.G;
-    const int i1 = (cta + 1) * p.R / p.G;
-    const uint32_t xt_s = smem_u32(work);
+    const int nitems = p.M * p.nsl;
     const uint32_t* vt = reinterpret_cast<const uint32_t*>(work + XT_BYTES);
+    const uint32_t x_bar = smem_u32(&ctrl->x_bar);
+    const int kc0 = p.K < XK ? p.K : XK;
+    const int cap = z_chunk_ranks(p, kc0);
+    bool waited = false;
+    uint32_t x_parity = 0, seq = 0;
 
 #pragma unroll 1
-    for (int ic = i0; ic < i1; ic += VT_RANKS) {
-        const int nr = (i1 - ic) < VT_RANKS ? (i1 - ic) : VT_RANKS;
-        // the coefficient this thread will need when it writes z: requested now, used after the reduction
-        float s_coef = 0.f;
-        if (zt < RP * VT_RANKS && (zt % VT_RANKS) < nr) s_coef = __bfloat162float(p.S[ic + (zt % VT_RANKS)]);
+    for (int item = cta; item < nitems; item += p.G) {
+        const ZItem it = z_item(p, item);
 #pragma unroll 1
-        for (int mg = 0; mg < p.M; mg += RP) {       // rows beyond M inside a group repeat row M-1
-            float acc[VT_RANKS];
-#pragma unroll
-            for (int q = 0; q < VT_RANKS; ++q) acc[q] = 0.f;
-            float all = 0.f;
+        for (int c0 = it.ra; c0 < it.rb;) {
+            const int nrc = (it.rb - c0) < cap ? (it.rb - c0) : cap;
+            const int ngroups = (nrc + ZG - 1) / ZG;
+            // this warp's partial sums start at zero; the coefficient this thread needs at the end is requested now
+            for (int q = lane; q < nrc; q += 32) ctrl->zred[zw][q] = 0.f;
+            if (lane == 0) ctrl->zall[zw] = 0.f;
+            float s_coef = 0.f;
+            if (zt < nrc) s_coef = __bfloat162float(p.S[c0 + zt]);
 #pragma unroll 1
             for (int k0 = 0; k0 < p.K; k0 += XK) {
-                const int kc = (p.K - k0) < XK ? (p.K - k0) : XK;     // multiple of 256
-                const bool v_here = v_preloaded && ic == i0 && mg == 0 && k0 == 0;
-                if (!v_here) named_bar_sync(3, Z_THREADS);             // previous pass fully consumed
-                const int nchunk = kc >> 3;                            // 16-byte chunks per activation row
-#pragma unroll 1
-                for (int idx = zt; idx < RP * nchunk; idx += Z_THREADS) {
-                    int mm = 0, c = idx;
-                    if (RP > 1) { mm = idx / nchunk; c = idx - mm * nchunk; }
-                    const int r = (mg + mm < p.M) ? (mg + mm) : (p.M - 1);
-                    const int w = c >> 2, v = c & 3;
-                    cp_async16(xt_s + mm * (XK * 2) + ((((w >> 5) * 4 + v) * 32) + (w & 31)) * 16,
-                               p.X + (size_t)r * p.K + k0 + c * 8);
+                const int kc = (p.K - k0) < XK ? (p.K - k0) : XK;       // multiple of 256
+                const int words = kc >> 5, wpw = (words + Z_WARPS - 1) / Z_WARPS;     // at most 32 words per warp
+                if (waited) named_bar_sync(3, Z_THREADS);               // the previous pass has been consumed
+                z_issue_v(p, work, c0, nrc, k0, kc, zt);
+                cp_async_commit_wait_all();
+                named_bar_sync(3, Z_THREADS);                           // sign words (and cleared sums) visible to all
+                if (!waited) {
+                    griddep_wait();             // everything below reads what earlier kernels of the stream wrote
+                    waited = true;
+                    if (p.trigger == 4 && zt == 0) griddep_launch_dependents();
+                    if (zt == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 11] = globaltimer_ns();
                 }
-                if (!v_here) z_issue_v<RP>(p, work, ic, nr, k0, kc, zt);
-                cp_async_commit();
-                const int nwords = kc >> 5;
-                // The accumulation loop runs twice over the same instructions. The first time, while the copies are
-                // still in flight, it processes one word of whatever the work area holds and its result is thrown
-                // away: its purpose is to pull the loop's machine code into the instruction cache (each CTA executes
-                // this code once per launch, cold, and a cold instruction costs several times a warm one). The second
-                // time is the real pass.
-#pragma unroll 1
-                for (int pass = (k0 == 0 ? 0 : 1); pass < 2; ++pass) {
-                const bool dry = pass == 0;
-                if (!dry) {
-                    cp_async_wait_all();
-                    if (zt == 0 && p.stamps && v_here) p.stamps[(size_t)cta * STAMP_WORDS + 8] = globaltimer_ns();
-                    named_bar_sync(3, Z_THREADS);
+                const bool load_x = !(p.K <= XK && c0 > it.ra);         // (a single-pass row stays in place)
+                if (load_x && zt == 0) {
+                    mbar_arrive_expect_tx(x_bar, (uint32_t)kc * 2u);
+                    bulk_load(smem_u32(work), p.X + (size_t)it.m * p.K + k0, (uint32_t)kc * 2u, x_bar);
                 }
-                const int w_end = dry ? min(nwords, kg * 32 + lane + 1) : nwords;
-#pragma unroll 1
-                for (int w = kg * 32 + lane; w < w_end; w += KW * 32) {
-                    const uint4* xs = reinterpret_cast<const uint4*>(work + row * (XK * 2)) + ((w >> 5) * 4) * 32 + (w & 31);
-                    float xf[32];
+                if (zt == 0 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 14] = globaltimer_ns();
+                if (item == cta && c0 == it.ra && k0 == 0) seq = ld_volatile_u32(p.z_counter);
+                if (load_x) {
+                    wait_bar(x_bar, x_parity, ctrl, p.status, p.epoch, ST_Z, 0);       // (on failure: status set, carry on)
+                    x_parity ^= 1u;
+                }
+                if (zt == 0 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 8] = globaltimer_ns();
+                if (p.trigger == 3 && zt == 0) griddep_launch_dependents();
+
+                if (zt == 224 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 2] = globaltimer_ns();
+                const int w = zw * wpw + lane;
+                const bool active = lane < wpw && w < words;
+                float xf[32];
+                float sm = 0.f;
+                if (active) {
+                    const uint4* xs = reinterpret_cast<const uint4*>(work) + w * 4;     // 64 bytes = 32 bf16 of word w
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
-                        const uint4 xx = xs[v * 32];
+                        const uint4 xx = xs[v];
                         const uint32_t xw[4] = {xx.x, xx.y, xx.z, xx.w};
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
@@ -127,92 +191,164 @@ __device__ __forceinline__ void z_stage(const FusedParams& p, Ctrl* ctrl, uint8_
                             xf[8 * v + 2 * e + 1] = __uint_as_float(xw[e] & 0xFFFF0000u);
                         }
                     }
-                    float s = 0.f;
+                    float t[16];                                         // plain sum of the word, as a tree
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) s += xf[j];
-                    all += s;
-                    z_word<VT_RANKS>(xf, vt + w, XW, nr, acc);
+                    for (int j = 0; j < 16; ++j) t[j] = xf[j] + xf[j + 16];
+#pragma unroll
+                    for (int h = 8; h > 0; h >>= 1)
+#pragma unroll
+                        for (int j = 0; j < h; ++j) t[j] += t[j + h];
+                    sm = t[0];
                 }
-                if (dry) {
-                    all = 0.f;
 #pragma unroll
-                    for (int q = 0; q < VT_RANKS; ++q) acc[q] = 0.f;
+                for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+                if (lane == 0) ctrl->zall[zw] += sm;
+#pragma unroll 1
+                for (int g = 0; g < ngroups; ++g) {
+                    float acc[ZG];
+#pragma unroll
+                    for (int q = 0; q < ZG; ++q) acc[q] = 0.f;
+                    if (active) {
+                        const int nq = (nrc - g * ZG) < ZG ? (nrc - g * ZG) : ZG;
+                        z_word(xf, vt + (size_t)(g * ZG) * words + w, words, nq, acc);
+                    }
+                    const float tot = z_reduce8(acc, lane);
+                    const int rq = g * ZG + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                    if ((lane & 3) == 0 && rq < nrc) ctrl->zred[zw][rq] += tot;
                 }
-                }
-            }
-            // z[row, rank] = S * (2 * sum_plus - sum_all), summed over the lanes and the k-groups
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) all += __shfl_xor_sync(0xffffffffu, all, o);
-#pragma unroll
-            for (int q = 0; q < VT_RANKS; ++q) {
-                float v = acc[q];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) ctrl->zred[zw][q] = 2.f * v - all;
+                if (zt == 224 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 7] = globaltimer_ns();
+                if (zt == 0 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 12] = globaltimer_ns();
             }
             named_bar_sync(3, Z_THREADS);
-            if (zt < RP * VT_RANKS) {
-                const int r = zt / VT_RANKS, q = zt - r * VT_RANKS;
-                if (q < nr) {
-                    float v = 0.f;
+            if (zt < nrc) {
+                float v = 0.f, a = 0.f;
 #pragma unroll
-                    for (int g = 0; g < KW; ++g) v += ctrl->zred[g * RP + r][q];
-                    zb[(size_t)(mg + r) * p.Rpad + ic + q] = v * s_coef;
-                }
+                for (int g = 0; g < Z_WARPS; ++g) { v += ctrl->zred[g][zt]; a += ctrl->zall[g]; }
+                // the lowest mantissa bit is the validity mark the consumers poll on (see expand_z)
+                zb[(size_t)it.m * p.Rpad + c0 + zt] = __uint_as_float((__float_as_uint((2.f * v - a) * s_coef) & ~1u) | ((seq & 1u) ^ 1u));
             }
             if (zt == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 9] = globaltimer_ns();
+            named_bar_sync(3, Z_THREADS);              // the partial sums may be cleared for the next chunk
+            c0 += nrc;
         }
     }
+    if (!waited) {                                     // a CTA without a z item
+        griddep_wait();
+        if (zt == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 11] = globaltimer_ns();
+        seq = ld_volatile_u32(p.z_counter);
+    }
+    *seq_out = seq;
+    return (seq & 1u) ^ 1u;
 }
 
 // corr[m] += sum over rank words [w0, w1) of z[m, 32w+b] * sign(U bit b of word w of this thread's column).
-// z comes from the scratch buffer in global memory and is staged ZS_WORDS words at a time in shared memory (one
-// batch of coalesced 128-bit loads per chunk); uw_first holds this thread's U words of the first chunk when they
-// were fetched ahead of time (use_first).
+//
+// z comes from the scratch buffer in global memory, where the z stages of all CTAs of this launch publish it, and
+// there is no separate "z is complete" flag: every value is its own flag. The lowest mantissa bit of a published
+// value equals `phase`, and phase flips with every launch that completes on the scratch (launch counter in the
+// scratch head, bumped by the last CTA to leave), so a value left by the previous launch reads as "not yet there".
+// The consumers load the values they need straight away, 128 bits at a time, and reload until all four marks match:
+// one memory round trip after the last producer's store instead of three (counter, then poll, then data). The mark
+// costs one unit in the last place of an fp32 z value. Ranks >= R (padding of the last rank word) are never written
+// and read as zero; rows >= M of the staging area are left as they are (their sums are never stored). Values are staged zs_words(ROWS) rank words at a time in shared memory.
+// uw_first holds this thread's first ZS_FIRST U words when they were fetched ahead of time (use_first).
+// Returns false when the poll ran out of time (status set, abort raised).
 template <int ROWS>
-__device__ __forceinline__ void expand_z(float (&corr)[ROWS], const float* zb, int Rpad, const int32_t* ucol, int w0, int w1,
-                                         float* zs, int tid, const uint32_t* uw_first, bool use_first) {
+__device__ __forceinline__ bool expand_z(float (&corr)[ROWS], const FusedParams& p, Ctrl* ctrl, const float* zb, const int32_t* ucol,
+                                         int w0, int w1, float* zs, int tid, const uint32_t* uw_first, bool use_first, uint32_t phase) {
+    constexpr int ZW = zs_words(ROWS);
+    constexpr int ZSTR = zs_stride(ROWS);
+    constexpr int NPT = (ROWS * ZW * 8 + EPI_THREADS - 1) / EPI_THREADS;     // 128-bit loads per thread per chunk
+    bool good = true;
 #pragma unroll 1
-    for (int c0 = w0; c0 < w1; c0 += ZS_WORDS) {
-        const int cw = (w1 - c0) < ZS_WORDS ? (w1 - c0) : ZS_WORDS;
-        uint32_t uwv[ZS_WORDS];
-        if (use_first && c0 == w0) {
+    for (int c0 = w0; c0 < w1 && good; c0 += ZW) {
+        const int cw = (w1 - c0) < ZW ? (w1 - c0) : ZW;
+        uint32_t uwv[ZW];
 #pragma unroll
-            for (int w = 0; w < ZS_WORDS; ++w) uwv[w] = uw_first[w];
-        } else {
-#pragma unroll
-            for (int w = 0; w < ZS_WORDS; ++w) uwv[w] = (uint32_t)ucol[(w < cw) ? (c0 + w) : c0];
+        for (int w = 0; w < ZW; ++w) {
+            if (w < ZS_FIRST && use_first && c0 == w0) uwv[w] = uw_first[w];
+            else uwv[w] = (uint32_t)ucol[(w < cw) ? (c0 + w) : c0];
         }
-        named_bar_sync(1, EPI_THREADS);                      // zs free again
         const int per_row = 8 * cw;
-#pragma unroll 1
-        for (int idx = tid; idx < ROWS * per_row; idx += EPI_THREADS) {
+        const int total = ROWS * per_row;
+        int goff[NPT], soff[NPT];
+#pragma unroll
+        for (int q = 0; q < NPT; ++q) {
+            const int idx = tid + q * EPI_THREADS;
             const int m = idx / per_row, j = idx - m * per_row;
-            const float4 zz = __ldcg(reinterpret_cast<const float4*>(zb + (size_t)m * Rpad + 32 * c0) + j);
-            *reinterpret_cast<float4*>(zs + m * ZS_STRIDE + 4 * j) = zz;
+            goff[q] = (idx < total && m < p.M) ? (m * p.Rpad + 32 * c0 + 4 * j) : -1;     // rows >= M: nothing to wait for
+            soff[q] = m * ZSTR + 4 * j;
+        }
+        uint4 v[NPT];
+        uint64_t t0 = 0;
+#pragma unroll 1
+        for (uint32_t it = 0;; ++it) {
+#pragma unroll
+            for (int q = 0; q < NPT; ++q)
+                if (goff[q] >= 0) v[q] = ld_volatile_v4(zb + goff[q]);
+            uint32_t bad = 0;
+#pragma unroll
+            for (int q = 0; q < NPT; ++q) {
+                if (goff[q] >= 0) {
+                    const int e = 32 * c0 + (soff[q] % ZSTR);           // rank of v[q].x
+                    bad |= (e + 0 < p.R ? (v[q].x ^ phase) : 0u) | (e + 1 < p.R ? (v[q].y ^ phase) : 0u) |
+                           (e + 2 < p.R ? (v[q].z ^ phase) : 0u) | (e + 3 < p.R ? (v[q].w ^ phase) : 0u);
+                }
+            }
+            if (!(bad & 1u)) break;
+            if ((it & 15u) == 15u) {
+                if (ctrl->abort) { good = false; break; }
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, p.status, p.epoch, ST_Z, 0); good = false; break; }
+            }
+        }
+        named_bar_sync(1, EPI_THREADS);                      // zs free again (the previous chunk has been consumed)
+#pragma unroll
+        for (int q = 0; q < NPT; ++q) {
+            if (goff[q] >= 0) {
+                const int e = 32 * c0 + (soff[q] % ZSTR);
+                float4 zz;
+                zz.x = e + 0 < p.R ? __uint_as_float(v[q].x) : 0.f;
+                zz.y = e + 1 < p.R ? __uint_as_float(v[q].y) : 0.f;
+                zz.z = e + 2 < p.R ? __uint_as_float(v[q].z) : 0.f;
+                zz.w = e + 3 < p.R ? __uint_as_float(v[q].w) : 0.f;
+                *reinterpret_cast<float4*>(zs + soff[q]) = zz;
+            }
         }
         named_bar_sync(1, EPI_THREADS);
+        if (ctrl->abort) { good = false; break; }           // uniform: written before the barrier, read after it
+        // UNR groups of four ranks are in flight at a time: with one warp per scheduler nothing else hides the
+        // shared-memory latency of the z values
+        constexpr int UNR = ROWS >= 8 ? 1 : 8 / ROWS;
 #pragma unroll 1
         for (int w = 0; w < cw; ++w) {
             const uint32_t uw = uwv[0];
 #pragma unroll
-            for (int q = 0; q + 1 < ZS_WORDS; ++q) uwv[q] = uwv[q + 1];
+            for (int q = 0; q + 1 < ZW; ++q) uwv[q] = uwv[q + 1];
 #pragma unroll 1
-            for (int b = 0; b < 32; b += 4) {
-                const uint32_t nib = uw >> b;
-                const float s0 = (nib & 1u) ? 1.f : -1.f;
-                const float s1 = (nib & 2u) ? 1.f : -1.f;
-                const float s2 = (nib & 4u) ? 1.f : -1.f;
-                const float s3 = (nib & 8u) ? 1.f : -1.f;
-                const float* zrow = zs + 32 * w + b;
+            for (int b0 = 0; b0 < 32; b0 += 4 * UNR) {
+                const float* zrow = zs + 32 * w + b0;
+                float4 zz[UNR][ROWS];
 #pragma unroll
-                for (int m = 0; m < ROWS; ++m) {
-                    const float4 zz = *reinterpret_cast<const float4*>(zrow + m * ZS_STRIDE);
-                    corr[m] += (s0 * zz.x + s1 * zz.y) + (s2 * zz.z + s3 * zz.w);
+                for (int u = 0; u < UNR; ++u)
+#pragma unroll
+                    for (int m = 0; m < ROWS; ++m) zz[u][m] = *reinterpret_cast<const float4*>(zrow + 4 * u + m * ZSTR);
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const uint32_t nib = uw >> (b0 + 4 * u);
+                    const float s0 = (nib & 1u) ? 1.f : -1.f;
+                    const float s1 = (nib & 2u) ? 1.f : -1.f;
+                    const float s2 = (nib & 4u) ? 1.f : -1.f;
+                    const float s3 = (nib & 8u) ? 1.f : -1.f;
+#pragma unroll
+                    for (int m = 0; m < ROWS; ++m)
+                        corr[m] += (s0 * zz[u][m].x + s1 * zz[u][m].y) + (s2 * zz[u][m].z + s3 * zz[u][m].w);
                 }
             }
         }
     }
+    return good;
 }
 
 }  // namespace biloco

@@ -190,13 +190,22 @@ int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t
  * (the kernel itself waits for that kernel before it reads activations or touches scratch). 0 = plain launches.
  * The reference launches with a "pdl" flag as well (csrc/biloco_gemm.cu:3421-3429). */
 #define BILOCO_OPT_PDL 1
-#define BILOCO_OPT_RING 2   /* pipeline stages the fused kernel keeps in flight (>= 2; clamped to what fits) */
+/* Pipeline stages the fused kernel keeps in flight. 0 (default): chosen by the library - for M <= 8 with dependent
+ * launch on, a ring of 4 stages so that two consecutive launches are resident on an SM at the same time (the second
+ * one's first weights are in shared memory before the first has finished); otherwise all the stages that fit.
+ * Other values are clamped to [4, what fits]. */
+#define BILOCO_OPT_RING 2
+/* Where a CTA of the fused kernel allows the next kernel of the stream to start (programmatic dependent launch):
+ * -1 (default) chosen by the library, 0 after set-up, 4 after its dependency wait, 3 once its activation row has
+ * landed, 1 after its z stage, 2 after its first expansion. Tuning aid. */
+#define BILOCO_OPT_TRIGGER 3
 int biloco_b200_set_option(int option, int value);
 
 /* Debug aid: while a device buffer is registered here, every fused launch of this process writes 16 uint64
  * %globaltimer stamps per CTA into it (CTA c at words 16c..16c+15: 0 set-up done, 1 z published, 2 z complete seen,
  * 3 expansion done, 4 accumulators ready, 5/6 first/last segment stored, 7 last stage consumed, 8 first z reads
- * landed, 9 z computed, 10 CTA entry, 11 previous kernel complete). bytes >= 128 * CTAs; NULL turns it off.
+ * landed, 9 z computed, 10 CTA entry, 11 previous kernel complete, 13 CTA exit). bytes >= 128 * CTAs; a larger
+ * buffer is used as consecutive slots of 128 * CTAs bytes by consecutive launches, round-robin; NULL turns it off.
  * Counterpart in the reference: the optional Diag tensor (csrc/biloco_gemm.cu:313-317, 446-464). */
 int biloco_b200_debug_stamps(void* device_buf, size_t bytes);
 
