@@ -18,14 +18,13 @@ namespace biloco {
 // mbarrier; nothing else stands between the wait and the arithmetic.
 // Arithmetic: warp w takes the w-th eighth of the pass's 32-bit sign words, one word per lane; a lane unpacks the 32
 // activations of its word once and, for every rank, adds them under predicates taken from the sign bits (four
-// independent accumulators in flight). One shuffle reduction per group of ZG ranks (see z_reduce8), per-warp partial
+// independent accumulators in flight). One shuffle reduction per run of four ranks (see z_reduce4), per-warp partial
 // sums in shared memory, one combine per chunk: z = S * (2 * sum_{sign=+1} x - sum x).
 // The CUDA-core code here is bound by instruction issue, not by latency (measured: the same cycles cold and warm,
 // alone or beside spinning warps), so what matters is the instruction count per element and an even spread over warps.
 // zt = index of the calling thread among the 256.
 constexpr int Z_THREADS = 256;
 constexpr int Z_WARPS = Z_THREADS / 32;
-constexpr int ZG = 8;                            // ranks per reduction group
 
 struct ZItem { int m, ra, rb; };
 __device__ __forceinline__ ZItem z_item(const FusedParams& p, int it) {
@@ -52,71 +51,62 @@ __device__ __forceinline__ void z_issue_v(const FusedParams& p, uint8_t* work, i
     }
 }
 
-// acc[q] += sum of the activations xf[] whose sign bit in rank q's word is set, q < NQ: an add under a predicate taken
-// from the sign bit, two accumulators per rank (even and odd k), the element loop outermost so that consecutive adds
-// go to different accumulators. Measured on this part, cycles per (warp, element) with two warps per scheduler:
-// 4.0 for this form with NQ = 4; 4.8 with one accumulator per rank; 5.2 with NQ = 2; 7.6 for sign flips by XOR; 9.7
-// for multiplications by +-1. The predicate is spelled out in PTX so that it cannot turn into a branch.
-template <int NQ, int OFF>
-__device__ __forceinline__ void z_word_n(const float (&xf)[32], const uint32_t* vrow, int xw_stride, float (&accs)[ZG]) {
-    uint32_t vw[NQ];
-    float acc[NQ], a1[NQ];
-#pragma unroll
-    for (int q = 0; q < NQ; ++q) { vw[q] = vrow[(OFF + q) * xw_stride]; acc[q] = 0.f; a1[q] = 0.f; }
+// One 32-bit sign word (32 consecutive k) of NQ ranks: sums[q] = sum of the word's activations whose sign bit in rank
+// q's word is set; plain = sum of all 32. An add under a predicate taken from the sign bit (spelled out in PTX so that
+// it cannot turn into a branch or a select), two accumulators per rank, eight activations per trip of a rolled loop.
+// Measured in isolation (cycles per warp and element, two warps per scheduler): this form with 8 add chains 4.0; with
+// 4 chains 5.2; sign flips by XOR 7.6; multiplications by +-1 9.7. The loops are kept rolled on purpose: the kernel's
+// code runs once per CTA and launch, and instruction fetch was the largest stall after barriers in the profile
+// (4.1 stalled warp-cycles per issued instruction with everything unrolled).
 #define BILOCO_PADD(accv, vwv, bit, xv)                                                                              \
     asm("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %1, %2;\n\tsetp.ne.u32 p, t, 0;\n\t@p add.f32 %0, %0, %3;\n\t}" \
         : "+f"(accv) : "r"(vwv), "r"(bit), "f"(xv))
+template <int NQ>
+__device__ __forceinline__ void z_word_n(const uint4* xs, const uint32_t* vrow, int xw_stride, int nq, float (&sums)[4], float& plain) {
+    uint32_t vw[NQ];
+    float a0[NQ], a1[NQ];
 #pragma unroll
-    for (int j = 0; j < 32; j += 2)
+    for (int q = 0; q < NQ; ++q) { vw[q] = q < nq ? vrow[q * xw_stride] : 0u; a0[q] = 0.f; a1[q] = 0.f; }
+    float ps = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+        const uint4 xx = xs[c];
+        const uint32_t xw[4] = {xx.x, xx.y, xx.z, xx.w};
+        float xf[8];
 #pragma unroll
-        for (int q = 0; q < NQ; ++q) {
-            BILOCO_PADD(acc[q], vw[q], 1u << j, xf[j]);
-            BILOCO_PADD(a1[q], vw[q], 2u << j, xf[j + 1]);
+        for (int e = 0; e < 4; ++e) {
+            xf[2 * e] = __uint_as_float(xw[e] << 16);
+            xf[2 * e + 1] = __uint_as_float(xw[e] & 0xFFFF0000u);
         }
-#undef BILOCO_PADD
 #pragma unroll
-    for (int q = 0; q < NQ; ++q) accs[OFF + q] += acc[q] + a1[q];
-}
-
-// The same for nq <= ZG ranks, in runs of at most four (5 = 3 + 2, 6 = 3 + 3, 7 = 4 + 3, 8 = 4 + 4); nq is warp-uniform.
-__device__ __forceinline__ void z_word(const float (&xf)[32], const uint32_t* vrow, int xw_stride, int nq, float (&acc)[ZG]) {
-    if (nq <= 4) {
-        if (nq == 1) z_word_n<1, 0>(xf, vrow, xw_stride, acc);
-        else if (nq == 2) z_word_n<2, 0>(xf, vrow, xw_stride, acc);
-        else if (nq == 3) z_word_n<3, 0>(xf, vrow, xw_stride, acc);
-        else z_word_n<4, 0>(xf, vrow, xw_stride, acc);
-    } else if (nq <= 6) {
-        z_word_n<3, 0>(xf, vrow, xw_stride, acc);
-        if (nq == 5) z_word_n<2, 3>(xf, vrow, xw_stride, acc);
-        else z_word_n<3, 3>(xf, vrow, xw_stride, acc);
-    } else {
-        z_word_n<4, 0>(xf, vrow, xw_stride, acc);
-        if (nq == 7) z_word_n<3, 4>(xf, vrow, xw_stride, acc);
-        else z_word_n<4, 4>(xf, vrow, xw_stride, acc);
+        for (int j = 0; j < 8; j += 2)
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) {
+                BILOCO_PADD(a0[q], vw[q], 1u << j, xf[j]);
+                BILOCO_PADD(a1[q], vw[q], 2u << j, xf[j + 1]);
+            }
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) vw[q] >>= 8;
+        ps += ((xf[0] + xf[1]) + (xf[2] + xf[3])) + ((xf[4] + xf[5]) + (xf[6] + xf[7]));
     }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) sums[q] = q < NQ ? a0[q < NQ ? q : 0] + a1[q < NQ ? q : 0] : 0.f;
+    plain = ps;
 }
 
-// Sum of acc[q] over the 32 lanes for all ZG ranks at once: a lane gives away half of its values at every step, so the
-// eight sums cost 4 + 2 + 1 + 2 shuffles instead of 8 x 5. On return lane l holds the total of rank ((l>>4)&1)*4 +
-// ((l>>3)&1)*2 + ((l>>2)&1).
-__device__ __forceinline__ float z_reduce8(float (&acc)[ZG], int lane) {
-    static_assert(ZG == 8, "written for eight ranks");
-    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
-    float a[4], b[2], c;
+// Sum of v[q] over the 32 lanes for four ranks at once: a lane gives away half of its values at every step (2 + 1 + 3
+// shuffles instead of 4 x 5). On return lane l holds the total of rank ((l >> 4) & 1) * 2 + ((l >> 3) & 1).
+__device__ __forceinline__ float z_reduce4(const float (&v)[4], int lane) {
+    const bool h16 = lane & 16, h8 = lane & 8;
+    float a[2];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {        // lanes with bit 4 set keep ranks 4-7, the others ranks 0-3
-        const float give = h16 ? acc[i] : acc[i + 4], keep = h16 ? acc[i + 4] : acc[i];
+    for (int i = 0; i < 2; ++i) {        // lanes with bit 4 set keep ranks 2-3, the others ranks 0-1
+        const float give = h16 ? v[i] : v[i + 2], keep = h16 ? v[i + 2] : v[i];
         a[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
     }
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const float give = h8 ? a[i] : a[i + 2], keep = h8 ? a[i + 2] : a[i];
-        b[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
-    }
-    {
-        const float give = h4 ? b[0] : b[1], keep = h4 ? b[1] : b[0];
-        c = keep + __shfl_xor_sync(0xffffffffu, give, 4);
-    }
+    const float give = h8 ? a[0] : a[1], keep = h8 ? a[1] : a[0];
+    float c = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+    c += __shfl_xor_sync(0xffffffffu, c, 4);
     c += __shfl_xor_sync(0xffffffffu, c, 2);
     c += __shfl_xor_sync(0xffffffffu, c, 1);
     return c;
@@ -124,7 +114,8 @@ __device__ __forceinline__ float z_reduce8(float (&acc)[ZG], int lane) {
 
 // Contains the dependency wait (griddepcontrol.wait). Returns the validity mark of this launch's z values: the parity
 // of the scratch's launch count, which is read behind the activation request so that its latency is hidden.
-__device__ __forceinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8_t* work, float* zb, int cta, int zt, uint32_t* seq_out) {
+// Not inlined: the epilogue warps and the z warps call it from two places and share one copy of the code.
+__device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8_t* work, float* zb, int cta, int zt, uint32_t* seq_out) {
     const int zw = zt >> 5, lane = zt & 31;
     const int nitems = p.M * p.nsl;
     const uint32_t* vt = reinterpret_cast<const uint32_t*>(work + XT_BYTES);
@@ -140,7 +131,6 @@ __device__ __forceinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, ui
 #pragma unroll 1
         for (int c0 = it.ra; c0 < it.rb;) {
             const int nrc = (it.rb - c0) < cap ? (it.rb - c0) : cap;
-            const int ngroups = (nrc + ZG - 1) / ZG;
             // this warp's partial sums start at zero; the coefficient this thread needs at the end is requested now
             for (int q = lane; q < nrc; q += 32) ctrl->zred[zw][q] = 0.f;
             if (lane == 0) ctrl->zall[zw] = 0.f;
@@ -177,44 +167,25 @@ __device__ __forceinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, ui
                 if (zt == 224 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 2] = globaltimer_ns();
                 const int w = zw * wpw + lane;
                 const bool active = lane < wpw && w < words;
-                float xf[32];
-                float sm = 0.f;
-                if (active) {
-                    const uint4* xs = reinterpret_cast<const uint4*>(work) + w * 4;     // 64 bytes = 32 bf16 of word w
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const uint4 xx = xs[v];
-                        const uint32_t xw[4] = {xx.x, xx.y, xx.z, xx.w};
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            xf[8 * v + 2 * e] = __uint_as_float(xw[e] << 16);
-                            xf[8 * v + 2 * e + 1] = __uint_as_float(xw[e] & 0xFFFF0000u);
-                        }
-                    }
-                    float t[16];                                         // plain sum of the word, as a tree
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) t[j] = xf[j] + xf[j + 16];
-#pragma unroll
-                    for (int h = 8; h > 0; h >>= 1)
-#pragma unroll
-                        for (int j = 0; j < h; ++j) t[j] += t[j + h];
-                    sm = t[0];
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
-                if (lane == 0) ctrl->zall[zw] += sm;
+                const uint4* xs = reinterpret_cast<const uint4*>(work) + (active ? w : 0) * 4;     // 64 bytes = 32 bf16 of word w
 #pragma unroll 1
-                for (int g = 0; g < ngroups; ++g) {
-                    float acc[ZG];
-#pragma unroll
-                    for (int q = 0; q < ZG; ++q) acc[q] = 0.f;
+                for (int q0 = 0; q0 < nrc; q0 += 4) {                   // runs of four ranks
+                    const int nq = nrc - q0;
+                    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+                    float plain = 0.f;
                     if (active) {
-                        const int nq = (nrc - g * ZG) < ZG ? (nrc - g * ZG) : ZG;
-                        z_word(xf, vt + (size_t)(g * ZG) * words + w, words, nq, acc);
+                        const uint32_t* vrow = vt + (size_t)q0 * words + w;
+                        if (nq <= 2) z_word_n<2>(xs, vrow, words, nq, sums, plain);
+                        else z_word_n<4>(xs, vrow, words, nq, sums, plain);
                     }
-                    const float tot = z_reduce8(acc, lane);
-                    const int rq = g * ZG + ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                    if ((lane & 3) == 0 && rq < nrc) ctrl->zred[zw][rq] += tot;
+                    const float tot = z_reduce4(sums, lane);
+                    const int rq = q0 + ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1);
+                    if ((lane & 7) == 0 && rq < nrc) ctrl->zred[zw][rq] += tot;
+                    if (q0 == 0) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
+                        if (lane == 0) ctrl->zall[zw] += plain;
+                    }
                 }
                 if (zt == 224 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 7] = globaltimer_ns();
                 if (zt == 0 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 12] = globaltimer_ns();
@@ -303,6 +274,7 @@ __device__ __forceinline__ bool expand_z(float (&corr)[ROWS], const FusedParams&
                 else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, p.status, p.epoch, ST_Z, 0); good = false; break; }
             }
         }
+        if (tid == 0 && p.stamps && c0 == w0) p.stamps[(size_t)blockIdx.x * STAMP_WORDS + 15] = globaltimer_ns();
         named_bar_sync(1, EPI_THREADS);                      // zs free again (the previous chunk has been consumed)
 #pragma unroll
         for (int q = 0; q < NPT; ++q) {
@@ -318,6 +290,8 @@ __device__ __forceinline__ bool expand_z(float (&corr)[ROWS], const FusedParams&
         }
         named_bar_sync(1, EPI_THREADS);
         if (ctrl->abort) { good = false; break; }           // uniform: written before the barrier, read after it
+        // Signs as +-1.0 multipliers shared by the rows. (Adds under a predicate with a separate plain row sum, the
+        // form the z stage uses, measured slower here from 4 rows up and no faster below.)
         // UNR groups of four ranks are in flight at a time: with one warp per scheduler nothing else hides the
         // shared-memory latency of the z values
         constexpr int UNR = ROWS >= 8 ? 1 : 8 / ROWS;

@@ -98,6 +98,7 @@ def test_layer_forward_on_kernel_matches_reference_layer(golden):
     ref = golden["layer_y"]
     for _ in range(2):
         y = bl(x).float().cpu().numpy()
+        assert all(g.status()[0] == 0 for g in bl._gemms.values()), "a device-side wait ran out"
         # against the exact value: the suite's bounds
         check_against_unfused(y, y_exact, "kernel forward vs exact value")
         # against the reference module's own output: its bf16 matmuls round z, alpha*v and every partial result to bf16,
