@@ -9,8 +9,10 @@ default 64 layers that is 986 MB per step, far larger than L2, so every launch s
 
   value         algorithmic GB/s of the whole job, operands resident in HBM, CUDA-graph replay of the step,
                 timed with CUDA events on the launching stream (max over ranks)
-  e2e           the same metric through the public Python API with HOST activations: per layer a pinned
-                host->device copy of x, the device NVFP4 quantiser, the fused linear, a device->host copy of y
+  e2e           the same metric through the public Python API with HOST activations: per step one pinned
+                host->device copy of the step's bf16 activations, per layer the device NVFP4 quantiser and the
+                fused linear, one device->host copy of the outputs; the step is captured in a CUDA graph once and a
+                replay plus a synchronisation is timed (wall clock)
   roofline      achieved GB/s of the fused kernel vs the measured HBM copy peak (MEASURED_PEAKS.json)
   cpu_baseline  the CPU oracle's fake-quant forward (biloco/layer.py:54-64 semantics) on the host cores,
                 bounded sample
@@ -120,8 +122,7 @@ def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed, mode=None, share_a
         else:
             q = fp4.quantize_activation(x, "mse", w_gscale=w_gs, rows=M)
         gemm = kernel.BiLoCoGemm(W, W_sf, q["alpha"], Vp, Up, S, M=M, mode=mode)
-        layers.append(dict(gemm=gemm, q=q, x=x, w_gs=w_gs, x_host=x.cpu().pin_memory(),
-                           y_host=torch.empty(M, N, dtype=torch.bfloat16).pin_memory()))
+        layers.append(dict(gemm=gemm, q=q, x=x, w_gs=w_gs))
     return layers
 
 
@@ -265,17 +266,41 @@ def run_ours(args):
     value = world * L * bytes_call / (ms_per_step * 1e-3) / 1e9
 
     # ---- end-to-end arm: host activations in, host outputs back, through the Python API ----------------
+    # One step = what a decode step of a host program does: the step's bf16 activations (all layers, one pinned host
+    # buffer) are copied to the device, every layer runs the public calls (activation quantiser, fused linear), and the
+    # outputs (one device buffer) are copied back to pinned host memory. The step is captured once in a CUDA graph, as
+    # a serving loop would do; a replay plus a synchronisation is timed.
+    x_host = torch.empty(L, M, K, dtype=torch.bfloat16).pin_memory()
+    for i, ly in enumerate(layers):
+        x_host[i].copy_(ly["x"].cpu())
+    x_dev = torch.empty(L, M, K, device=dev, dtype=torch.bfloat16)
+    y_dev = torch.empty(L, M, N, device=dev, dtype=torch.bfloat16)
+    y_host = torch.empty(L, M, N, dtype=torch.bfloat16).pin_memory()
+
+    def step_e2e_body():
+        x_dev.copy_(x_host, non_blocking=True)
+        for i, ly in enumerate(layers):
+            fp4.quantize_activation(x_dev[i], "mse", w_gscale=ly["w_gs"], rows=M, out=ly["q"])
+            ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], x_dev[i], out=y_dev[i])
+        y_host.copy_(y_dev, non_blocking=True)
+
+    with torch.cuda.stream(side):
+        step_e2e_body()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    y_check = y_host.clone()
+    graph_e2e = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph_e2e, stream=side):
+        step_e2e_body()
+
     def step_e2e():
-        for ly in layers:
-            ly["x"].copy_(ly["x_host"], non_blocking=True)
-            fp4.quantize_activation(ly["x"], "mse", w_gscale=ly["w_gs"], rows=M, out=ly["q"])
-            y = ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], ly["x"])
-            ly["y_host"].copy_(y.view(-1, N)[:M], non_blocking=True)
+        graph_e2e.replay()
         torch.cuda.synchronize()
 
     e2e_steps = max(3, min(args.steps, 50))
     for _ in range(3):
         step_e2e()
+    assert torch.equal(y_host, y_check), "graph replay of the end-to-end step changed the outputs"
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):

@@ -11,55 +11,22 @@
 //     code = e2m1_rn(xs / d)                round-to-nearest-even on {0,.5,1,1.5,2,3,4,6}, saturating; 0 if d == 0
 //     mse rule: err_D = sum_{j=0..15} (xs_j - value(code_j) * d)^2 in index order (separate mul and add);
 //               the block takes D = 4 iff err_4 < err_6.
-// Two launches: a single-CTA reduction that writes the scales, then a grid that writes codes and block scales.
+// One launch: every CTA first reduces the whole activation to its maximum (redundantly: M*K*2 bytes from L2, no
+// grid-wide synchronisation needed), then the CTAs share the 16-element blocks and the zero padding between them.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
 #include "../../include/biloco_b200.h"
+#include "ptx.cuh"
+
+extern "C" int biloco_internal_use_pdl();
 
 namespace {
 
-__device__ __forceinline__ float load_smoothed(const __nv_bfloat16* X, const __nv_bfloat16* smooth, size_t row_off, int k) {
-    float v = __bfloat162float(X[row_off + k]);
-    if (smooth) v = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v, __bfloat162float(smooth[k]))));
-    return v;
-}
-
-constexpr int AMAX_THREADS = 1024;
-
-__global__ void __launch_bounds__(AMAX_THREADS) act_amax_kernel(const __nv_bfloat16* __restrict__ X,
-                                                                const __nv_bfloat16* __restrict__ smooth,
-                                                                float* __restrict__ a_gscale, float* __restrict__ alpha_out,
-                                                                const float* __restrict__ w_gscale, int M, int K, float target) {
-    float amax = 0.f;
-    const size_t total = (size_t)M * K;
-    for (size_t i = threadIdx.x; i < total; i += AMAX_THREADS) {
-        const int k = (int)(i % K);
-        amax = fmaxf(amax, fabsf(load_smoothed(X, smooth, i - k, k)));
-    }
-    __shared__ float red[AMAX_THREADS / 32];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        float v = red[threadIdx.x];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-        if (threadIdx.x == 0) {
-            const float gs = v > 0.f ? __fdiv_rn(v, 6.0f * target) : 1.0f;
-            a_gscale[0] = gs;
-            if (alpha_out && w_gscale) alpha_out[0] = __fmul_rn(w_gscale[0], gs);
-        }
-    }
-}
-
-// tensor scale supplied by the caller (e.g. agreed between ranks that hold K-slices of one activation): only alpha
-__global__ void act_alpha_kernel(const float* __restrict__ a_gscale, float* __restrict__ alpha_out, const float* __restrict__ w_gscale) {
-    if (alpha_out && w_gscale) alpha_out[0] = __fmul_rn(w_gscale[0], a_gscale[0]);
-}
+// Small CTAs: with programmatic dependent launch the quantiser runs on SMs that already hold a CTA of the fused kernel.
+constexpr int Q_THREADS = 128;
 
 __device__ __forceinline__ uint32_t e2m1_rn(float q) {
     const float a = fabsf(q);
@@ -100,24 +67,81 @@ __device__ __forceinline__ float quant_block(const float* x, float t, float D, f
     return err;
 }
 
-constexpr int Q_THREADS = 128;
+// bf16 pair -> two floats, optionally divided by the smoothing pair and rounded back to bf16
+__device__ __forceinline__ void unpack_smoothed(uint32_t w, uint32_t sm, bool smooth, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xFFFF0000u);
+    if (smooth) {
+        lo = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(lo, __uint_as_float(sm << 16))));
+        hi = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(hi, __uint_as_float(sm & 0xFFFF0000u))));
+    }
+}
 
-// One thread per 16-element block of a row (rows up to the 128-padded count so that every scale byte is written).
 __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat16* __restrict__ X,
                                                               const __nv_bfloat16* __restrict__ smooth,
                                                               __nv_bfloat16* __restrict__ Xs, uint8_t* __restrict__ codes,
-                                                              uint8_t* __restrict__ sf, const float* __restrict__ a_gscale,
-                                                              int M, int A_rows, int K, int rule) {
+                                                              uint8_t* __restrict__ sf, float* __restrict__ a_gscale,
+                                                              float* __restrict__ alpha_out, const float* __restrict__ w_gscale,
+                                                              int M, int A_rows, int K, int rule, int given_scale, float target) {
     const int kblocks = K >> 4;
-    const int row = blockIdx.y;
-    const int kb = blockIdx.x * Q_THREADS + threadIdx.x;
-    if (kb >= kblocks) return;
-    const size_t sf_off = ((size_t)(row >> 7) * (kblocks >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
-    if (row >= M) {
-        sf[sf_off] = 0;
-        if (row < A_rows) *reinterpret_cast<uint2*>(codes + (size_t)row * (K >> 1) + kb * 8) = make_uint2(0u, 0u);
-        return;
+    __shared__ float red[Q_THREADS / 32];
+    __shared__ float gs_sh;
+    // Programmatic dependent launch: the kernel that consumes these outputs may start its own preamble (weight
+    // prefetch) now; this kernel reads nothing before the previous kernel of the stream has completed.
+    biloco::griddep_launch_dependents();
+    biloco::griddep_wait();
+    // ---- tensor scale: maximum of the (smoothed) activation, every CTA for itself ----
+    if (!given_scale) {
+        float amax = 0.f;
+        const int nvec = (M * K) >> 3, kvec = K >> 3;                    // 128-bit vectors of 8 elements
+        for (int i = threadIdx.x; i < nvec; i += Q_THREADS) {
+            const uint4 a = reinterpret_cast<const uint4*>(X)[i];
+            uint4 c = make_uint4(0u, 0u, 0u, 0u);
+            if (smooth) c = reinterpret_cast<const uint4*>(smooth)[i % kvec];
+            const uint32_t w[4] = {a.x, a.y, a.z, a.w}, v[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float lo, hi;
+                unpack_smoothed(w[e], v[e], smooth != nullptr, lo, hi);
+                amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float v = threadIdx.x < Q_THREADS / 32 ? red[threadIdx.x] : 0.f;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+            if (threadIdx.x == 0) gs_sh = v > 0.f ? __fdiv_rn(v, 6.0f * target) : 1.0f;
+        }
+    } else if (threadIdx.x == 0) {
+        gs_sh = a_gscale[0];
     }
+    __syncthreads();
+    const float gs = gs_sh;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        if (!given_scale) a_gscale[0] = gs;
+        if (alpha_out && w_gscale) alpha_out[0] = __fmul_rn(w_gscale[0], gs);
+    }
+    // ---- zero padding: block scales of rows M .. 128-padded row count, codes of rows M .. A_rows ----
+    {
+        const int rows_pad = (A_rows + 127) & ~127;
+        const int kgroups = kblocks >> 2;                                // the four scales of a row's k-group are adjacent
+        const int npad = (rows_pad - M) * kgroups;
+        for (int i = blockIdx.x * Q_THREADS + threadIdx.x; i < npad; i += gridDim.x * Q_THREADS) {
+            const int row = M + i / kgroups, kg = i % kgroups;
+            *reinterpret_cast<uint32_t*>(sf + ((size_t)(row >> 7) * kgroups + kg) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4) = 0u;
+        }
+        const int ncode = (A_rows - M) * (K >> 4);                       // 64-bit vectors of codes
+        uint2* cz = reinterpret_cast<uint2*>(codes + (size_t)M * (K >> 1));
+        for (int i = blockIdx.x * Q_THREADS + threadIdx.x; i < ncode; i += gridDim.x * Q_THREADS) cz[i] = make_uint2(0u, 0u);
+    }
+    // ---- one thread per 16-element block ----
+    for (int id = blockIdx.x * Q_THREADS + threadIdx.x; id < M * kblocks; id += gridDim.x * Q_THREADS) {
+    const int row = id / kblocks, kb = id - row * kblocks;
+    const size_t sf_off = ((size_t)(row >> 7) * (kblocks >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
     float x[16];
     const size_t roff = (size_t)row * K;
     {   // two 128-bit loads per operand (K % 16 == 0 and 16-byte aligned bases keep them aligned)
@@ -151,7 +175,6 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
     float bmax = 0.f;
 #pragma unroll
     for (int j = 0; j < 16; ++j) bmax = fmaxf(bmax, fabsf(x[j]));
-    const float gs = a_gscale[0];
     const float t = __fdiv_rn(bmax, gs);
     uint32_t c[16];
     uint8_t s;
@@ -178,6 +201,7 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
     }
     *reinterpret_cast<uint2*>(codes + (size_t)row * (K >> 1) + kb * 8) = make_uint2(lo, hi);
     sf[sf_off] = s;
+    }
 }
 
 }  // namespace
@@ -194,15 +218,20 @@ extern "C" int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16
         return BILOCO_ERR_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
     const float target = rule == BILOCO_RULE_STATIC_6 ? 448.0f : 256.0f;
-    if (given_scale)
-        act_alpha_kernel<<<1, 1, 0, s>>>(a_gscale, alpha_out, w_gscale);
-    else
-        act_amax_kernel<<<1, AMAX_THREADS, 0, s>>>((const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16, a_gscale,
-                                                   alpha_out, w_gscale, M, K, target);
-    const int rows_pad = (A_rows + 127) / 128 * 128;
-    dim3 grid(((K >> 4) + Q_THREADS - 1) / Q_THREADS, rows_pad);
-    act_quant_kernel<<<grid, Q_THREADS, 0, s>>>((const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16,
-                                                (__nv_bfloat16*)Xs_bf16, (uint8_t*)A_codes, (uint8_t*)A_sf, a_gscale, M,
-                                                A_rows, K, rule);
+    int nblk = (M * (K >> 4) + Q_THREADS - 1) / Q_THREADS;
+    if (nblk > 96) nblk = 96;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)nblk);
+    cfg.blockDim = dim3(Q_THREADS);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = biloco_internal_use_pdl() ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, act_quant_kernel, (const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16,
+                           (__nv_bfloat16*)Xs_bf16, (uint8_t*)A_codes, (uint8_t*)A_sf, a_gscale, alpha_out, w_gscale, M, A_rows, K,
+                           rule, given_scale ? 1 : 0, target) != cudaSuccess)
+        return BILOCO_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }

@@ -132,6 +132,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 #pragma unroll 1
             for (int i = mine; i < nunits && i < ring; i += PRODUCERS) issue_w(i);
             griddep_wait();
+            fence_proxy_async_global();       // the activation was written by ordinary stores of the previous kernel
 #pragma unroll 1
             for (int i = mine; i < nunits && i < ring; i += PRODUCERS) issue_a(i);
         }

@@ -117,6 +117,7 @@ static int device_sm_count() {
 
 static int g_ring = 0;                           // pipeline stages: 0 = chosen per kernel, else clamped to what fits
 static int g_use_pdl = 1;                        // launch with programmatic stream serialization
+
 static unsigned long long* g_stamps = nullptr;   // debug time-stamp buffer for subsequent launches (or null)
 static size_t g_stamps_bytes = 0;
 static size_t g_stamps_seq = 0;
@@ -470,6 +471,9 @@ extern "C" int biloco_b200_noalloc_status(int32_t* out16, biloco_stream_t stream
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || !g_noalloc_ptr[dev]) return BILOCO_ERR_CUDA;
     return biloco_b200_read_status(g_noalloc_ptr[dev], out16, stream);
 }
+
+// (shared with the activation quantiser's launcher; not part of the public interface)
+extern "C" int biloco_internal_use_pdl() { return g_use_pdl; }
 
 extern "C" int biloco_b200_set_option(int option, int value) {
     if (option == BILOCO_OPT_PDL) { g_use_pdl = value ? 1 : 0; return BILOCO_OK; }

@@ -146,6 +146,7 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
                 named_bar_sync(3, Z_THREADS);                           // sign words (and cleared sums) visible to all
                 if (!waited) {
                     griddep_wait();             // everything below reads what earlier kernels of the stream wrote
+                    fence_proxy_async_global(); // (the bulk copy below reads through the async proxy)
                     waited = true;
                     if (p.trigger == 4 && zt == 0) griddep_launch_dependents();
                     if (zt == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 11] = globaltimer_ns();
@@ -281,10 +282,11 @@ __device__ __forceinline__ bool expand_z(float (&corr)[ROWS], const FusedParams&
             if (goff[q] >= 0) {
                 const int e = 32 * c0 + (soff[q] % ZSTR);
                 float4 zz;
-                zz.x = e + 0 < p.R ? __uint_as_float(v[q].x) : 0.f;
-                zz.y = e + 1 < p.R ? __uint_as_float(v[q].y) : 0.f;
-                zz.z = e + 2 < p.R ? __uint_as_float(v[q].z) : 0.f;
-                zz.w = e + 3 < p.R ? __uint_as_float(v[q].w) : 0.f;
+                // (the mark is cleared, so that the result does not depend on the launch count's parity)
+                zz.x = e + 0 < p.R ? __uint_as_float(v[q].x & ~1u) : 0.f;
+                zz.y = e + 1 < p.R ? __uint_as_float(v[q].y & ~1u) : 0.f;
+                zz.z = e + 2 < p.R ? __uint_as_float(v[q].z & ~1u) : 0.f;
+                zz.w = e + 3 < p.R ? __uint_as_float(v[q].w & ~1u) : 0.f;
                 *reinterpret_cast<float4*>(zs + soff[q]) = zz;
             }
         }

@@ -225,6 +225,9 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 // Programmatic dependent launch: wait for the grids this one depends on / allow dependents to start.
+// Orders earlier generic-proxy writes (here: of the previous kernel, made visible by the dependency wait) before
+// this thread's later async-proxy reads of global memory (TMA and bulk copies).
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -146,12 +146,13 @@ class BiLoCoGemm:
                        "read_status")
         return list(out)
 
-    def __call__(self, A_pad, A_sf, X_bf16):
-        """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten)."""
+    def __call__(self, A_pad, A_sf, X_bf16, out=None):
+        """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten). ``out`` (not in the reference's signature):
+        a [rows, N] tensor to write into instead of a fresh one, e.g. a slice of a buffer that is read back in one copy."""
         self.epoch += 1
-        if self.residual is not None or self.fp32_out:   # not expressible in the operator schemas: call the library directly
+        if self.residual is not None or self.fp32_out or out is not None:   # not expressible in the operator schemas
             return _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32, self.z,
-                               self.M, self.epoch, self.mode, C=self.residual,
+                               self.M, self.epoch, self.mode, C=self.residual, out=out,
                                B_tiled=self.W_tiled if self.W_tiled.numel() else None, fp32_out=self.fp32_out)
         a = (A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32)
         if self.mode == 2:

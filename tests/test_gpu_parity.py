@@ -130,12 +130,16 @@ def _run_fused(kernel, p, M, N, launches=5):
         g = kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M, mode=mode,
                               tile_weights=tiled)
         mode = f"{mode}{'/tiled' if tiled else '/row-major'}"
+        y_first = None
         for it in range(launches):                 # consecutive launches reuse the scratch without clearing
             y = g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].float()
             torch.cuda.synchronize()
             y = y.cpu().numpy()
             check_against_unfused(y, y_ref, f"mode {mode} launch {it}")
             check_against_exact(y, y_exact, f"mode {mode} launch {it}")
+            if y_first is None:
+                y_first = y
+            assert np.array_equal(y, y_first), f"mode {mode}: launch {it} is not bit-identical to launch 0"
         assert g.status()[0] == 0, f"device-side wait ran out: {g.status()[:4]}"
         g.reset()
         y = g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].float().cpu().numpy()
