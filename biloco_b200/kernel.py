@@ -21,10 +21,15 @@ RANKS = (16, 32, 64, 128, 256, 512, 1024)
 # Schedules implemented by the fused kernel (see include/biloco_b200.h, BILOCO_MODE_*).
 IMPLEMENTED_MODES = (2, 4, 5)
 
-# Fastest implemented mode per (M, rank) on B200 at K = N = 5120 (bench.py --mode sweep, r = 512: mode 5 wins for
-# M <= 8 by 6-10 %, mode 4 loses everywhere; mode 5 does not take M > 8).
-DEFAULT_MODE = {M: {r: (5 if M <= 8 else 2) for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
-
+# Fastest implemented mode per (M, rank) on B200 at K = N = 5120, from `bench.py --M .. --r .. --mode ..` (us per call,
+# 64 distinct layers per step, mode 2 / mode 5):
+#   r = 128 : M=1 10.7/9.1   M=2 11.5/9.4   M=4 12.1/10.3  M=8 16.6/14.5
+#   r = 256 : M=1 11.3/9.2   M=2 12.5/10.8  M=4 13.9/12.1  M=8 21.4/20.5
+#   r = 512 : M=1 12.3/10.7  M=2 15.0/12.9  M=4 16.8/17.5  M=8 30.7/28.3
+#   r = 1024: M=1 14.7/13.7  M=2 18.4/19.8  M=4 23.5/24.6  M=8 48.3/47.2
+# Mode 5 does not take M > 8; mode 4 loses everywhere. Ranks below 128 were not measured and follow r = 128.
+_MODE2_WINS = {(4, 512), (2, 1024), (4, 1024)}
+DEFAULT_MODE = {M: {r: (2 if (M > 8 or (M, r) in _MODE2_WINS) else 5) for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
 
 def pack_signs(signs: torch.Tensor) -> torch.Tensor:
     """[..., n] +-1 -> uint8 [..., n/8]; bit i of byte j is set iff signs[..., 8j + i] >= 0
