@@ -12,7 +12,8 @@
 //     mse rule: err_D = sum_{j=0..15} (xs_j - value(code_j) * d)^2 in index order (separate mul and add);
 //               the block takes D = 4 iff err_4 < err_6.
 // One launch: every CTA first reduces the whole activation to its maximum (redundantly: M*K*2 bytes from L2, no
-// grid-wide synchronisation needed), then the CTAs share the 16-element blocks and the zero padding between them.
+// grid-wide synchronisation needed), then the CTAs share the elements (one lane each, sixteen lanes per block, the
+// block-wide steps through shuffles) and the zero padding between them.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -26,7 +27,8 @@ extern "C" int biloco_internal_use_pdl();
 namespace {
 
 // Small CTAs: with programmatic dependent launch the quantiser runs on SMs that already hold a CTA of the fused kernel.
-constexpr int Q_THREADS = 128;
+constexpr int Q_THREADS = 256;
+constexpr int Q_MAX_CLUSTER = 8;
 
 __device__ __forceinline__ uint32_t e2m1_rn(float q) {
     const float a = fabsf(q);
@@ -47,26 +49,6 @@ __device__ __forceinline__ uint8_t float_to_e4m3_sat(float v) {
     return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
-// quantise one block with divisor D; returns the squared error (only when want_err)
-__device__ __forceinline__ float quant_block(const float* x, float t, float D, float gs, uint8_t* sf_out, uint32_t* codes,
-                                             bool want_err) {
-    const uint8_t sf = float_to_e4m3_sat(__fdiv_rn(t, D));
-    const float d = __fmul_rn(e4m3_to_float(sf), gs);
-    *sf_out = sf;
-    float err = 0.f;
-    const bool live = d > 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-        const uint32_t c = live ? e2m1_rn(__fdiv_rn(x[j], d)) : 0u;
-        codes[j] = c;
-        if (want_err) {
-            const float diff = __fsub_rn(x[j], __fmul_rn(e2m1_value(c), d));
-            err = __fadd_rn(err, __fmul_rn(diff, diff));
-        }
-    }
-    return err;
-}
-
 // bf16 pair -> two floats, optionally divided by the smoothing pair and rounded back to bf16
 __device__ __forceinline__ void unpack_smoothed(uint32_t w, uint32_t sm, bool smooth, float& lo, float& hi) {
     lo = __uint_as_float(w << 16);
@@ -82,7 +64,8 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
                                                               __nv_bfloat16* __restrict__ Xs, uint8_t* __restrict__ codes,
                                                               uint8_t* __restrict__ sf, float* __restrict__ a_gscale,
                                                               float* __restrict__ alpha_out, const float* __restrict__ w_gscale,
-                                                              int M, int A_rows, int K, int rule, int given_scale, float target) {
+                                                              int M, int A_rows, int K, int rule, int given_scale, float target,
+                                                              int csize) {
     const int kblocks = K >> 4;
     __shared__ float red[Q_THREADS / 32];
     __shared__ float gs_sh;
@@ -90,11 +73,16 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
     // prefetch) now; this kernel reads nothing before the previous kernel of the stream has completed.
     biloco::griddep_launch_dependents();
     biloco::griddep_wait();
-    // ---- tensor scale: maximum of the (smoothed) activation, every CTA for itself ----
+    // ---- tensor scale: maximum of the (smoothed) activation. Every cluster of `csize` CTAs computes it for itself (no
+    //      grid-wide synchronisation): a CTA reduces its share of the 128-bit vectors, the CTAs of the cluster exchange
+    //      their maxima through distributed shared memory ----
+    __shared__ float cl_red[Q_MAX_CLUSTER];
+    const int crank = csize > 1 ? (int)(blockIdx.x % (unsigned)csize) : 0;
     if (!given_scale) {
         float amax = 0.f;
         const int nvec = (M * K) >> 3, kvec = K >> 3;                    // 128-bit vectors of 8 elements
-        for (int i = threadIdx.x; i < nvec; i += Q_THREADS) {
+#pragma unroll 4
+        for (int i = crank * Q_THREADS + threadIdx.x; i < nvec; i += csize * Q_THREADS) {
             const uint4 a = reinterpret_cast<const uint4*>(X)[i];
             uint4 c = make_uint4(0u, 0u, 0u, 0u);
             if (smooth) c = reinterpret_cast<const uint4*>(smooth)[i % kvec];
@@ -114,7 +102,19 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
             float v = threadIdx.x < Q_THREADS / 32 ? red[threadIdx.x] : 0.f;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-            if (threadIdx.x == 0) gs_sh = v > 0.f ? __fdiv_rn(v, 6.0f * target) : 1.0f;
+            if (csize > 1) {       // lane r hands this CTA's maximum to CTA r of the cluster
+                if (threadIdx.x < csize)
+                    biloco::st_cluster_f32(biloco::map_to_cta(biloco::smem_u32(&cl_red[crank]), (uint32_t)threadIdx.x), v);
+            } else if (threadIdx.x == 0) {
+                cl_red[0] = v;
+            }
+        }
+        if (csize > 1) biloco::cluster_sync_all();      // (release/acquire: the peers' values are in cl_red)
+        else __syncthreads();
+        if (threadIdx.x == 0) {
+            float v = 0.f;
+            for (int r = 0; r < csize; ++r) v = fmaxf(v, cl_red[r]);
+            gs_sh = v > 0.f ? __fdiv_rn(v, 6.0f * target) : 1.0f;
         }
     } else if (threadIdx.x == 0) {
         gs_sh = a_gscale[0];
@@ -138,69 +138,53 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
         uint2* cz = reinterpret_cast<uint2*>(codes + (size_t)M * (K >> 1));
         for (int i = blockIdx.x * Q_THREADS + threadIdx.x; i < ncode; i += gridDim.x * Q_THREADS) cz[i] = make_uint2(0u, 0u);
     }
-    // ---- one thread per 16-element block ----
-    for (int id = blockIdx.x * Q_THREADS + threadIdx.x; id < M * kblocks; id += gridDim.x * Q_THREADS) {
-    const int row = id / kblocks, kb = id - row * kblocks;
-    const size_t sf_off = ((size_t)(row >> 7) * (kblocks >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3);
-    float x[16];
-    const size_t roff = (size_t)row * K;
-    {   // two 128-bit loads per operand (K % 16 == 0 and 16-byte aligned bases keep them aligned)
-        const uint4* px = reinterpret_cast<const uint4*>(X + roff + kb * 16);
-        const uint4 a = px[0], b = px[1];
-        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    // ---- one lane per element, sixteen lanes per block: a lane's code is a handful of instructions, the block-wide
+    //      steps (maximum, the squared errors summed in index order, packing) go through shuffles ----
+    const int total = M * K;                                   // multiple of 64, so whole warps stay together
+    for (int e0 = blockIdx.x * Q_THREADS; e0 < total; e0 += gridDim.x * Q_THREADS) {
+        const int e = e0 + threadIdx.x;                        // (total % Q_THREADS may be 64: the upper half-CTA idles)
+        if (e >= total) break;
+        const int row = e / K, k = e - row * K;
+        const int kb = k >> 4, j = k & 15;
+        const int lane = threadIdx.x & 31, base = lane & 16;  // first lane of this block's group
+        float x = __bfloat162float(X[e]);
+        if (smooth) x = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(x, __bfloat162float(smooth[k]))));
+        if (Xs) Xs[e] = __float2bfloat16_rn(x);                // (exact: x is a bf16 value)
+        float bmax = fabsf(x);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            x[2 * e] = __uint_as_float(w[e] << 16);
-            x[2 * e + 1] = __uint_as_float(w[e] & 0xFFFF0000u);
-        }
-        if (smooth) {
-            const uint4* ps = reinterpret_cast<const uint4*>(smooth + kb * 16);
-            const uint4 c = ps[0], d = ps[1];
-            const uint32_t v[8] = {c.x, c.y, c.z, c.w, d.x, d.y, d.z, d.w};
+        for (int o = 8; o > 0; o >>= 1) bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, o));
+        const float t = __fdiv_rn(bmax, gs);
+        uint32_t code = 0;
+        uint8_t sfb = 0;
+        float e6 = 0.f, e4 = 0.f;
+        uint32_t c6 = 0, c4 = 0;
+        uint8_t s6 = 0, s4 = 0;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                x[2 * e] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(x[2 * e], __uint_as_float(v[e] << 16))));
-                x[2 * e + 1] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(x[2 * e + 1], __uint_as_float(v[e] & 0xFFFF0000u))));
+        for (int cand = 0; cand < 2; ++cand) {
+            const float D = cand == 0 ? 6.0f : 4.0f;
+            if (cand == 0 && rule == BILOCO_RULE_STATIC_4) continue;
+            if (cand == 1 && rule == BILOCO_RULE_STATIC_6) continue;
+            const uint8_t sfv = float_to_e4m3_sat(__fdiv_rn(t, D));
+            const float d = __fmul_rn(e4m3_to_float(sfv), gs);
+            const uint32_t c = d > 0.f ? e2m1_rn(__fdiv_rn(x, d)) : 0u;
+            float err = 0.f;
+            if (rule == BILOCO_RULE_MSE) {
+                const float diff = __fsub_rn(x, __fmul_rn(e2m1_value(c), d));
+                const float sq = __fmul_rn(diff, diff);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) err = __fadd_rn(err, __shfl_sync(0xffffffffu, sq, base + i));   // index order
             }
+            if (cand == 0) { c6 = c; s6 = sfv; e6 = err; } else { c4 = c; s4 = sfv; e4 = err; }
         }
-    }
-    if (Xs) {
-        uint32_t o[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = (__float_as_uint(x[2 * e]) >> 16) | (__float_as_uint(x[2 * e + 1]) & 0xFFFF0000u);
-        uint4* po = reinterpret_cast<uint4*>(Xs + roff + kb * 16);
-        po[0] = make_uint4(o[0], o[1], o[2], o[3]);
-        po[1] = make_uint4(o[4], o[5], o[6], o[7]);
-    }
-    float bmax = 0.f;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) bmax = fmaxf(bmax, fabsf(x[j]));
-    const float t = __fdiv_rn(bmax, gs);
-    uint32_t c[16];
-    uint8_t s;
-    if (rule == BILOCO_RULE_STATIC_6) {
-        quant_block(x, t, 6.0f, gs, &s, c, false);
-    } else if (rule == BILOCO_RULE_STATIC_4) {
-        quant_block(x, t, 4.0f, gs, &s, c, false);
-    } else {
-        uint32_t c4[16];
-        uint8_t s4;
-        const float e6 = quant_block(x, t, 6.0f, gs, &s, c, true);
-        const float e4 = quant_block(x, t, 4.0f, gs, &s4, c4, true);
-        if (e4 < e6) {
-            s = s4;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) c[j] = c4[j];
-        }
-    }
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        lo |= c[j] << (4 * j);
-        hi |= c[8 + j] << (4 * j);
-    }
-    *reinterpret_cast<uint2*>(codes + (size_t)row * (K >> 1) + kb * 8) = make_uint2(lo, hi);
-    sf[sf_off] = s;
+        if (rule == BILOCO_RULE_STATIC_6 || (rule == BILOCO_RULE_MSE && !(e4 < e6))) { code = c6; sfb = s6; }
+        else { code = c4; sfb = s4; }
+        // pack: two codes per byte (element 2i in bits 0-3), four bytes per word; lanes 0 and 8 of the group store
+        uint32_t w = code | (__shfl_down_sync(0xffffffffu, code, 1) << 4);
+        w |= (__shfl_down_sync(0xffffffffu, w, 2) << 8) | (__shfl_down_sync(0xffffffffu, w, 4) << 16) |
+             (__shfl_down_sync(0xffffffffu, w, 6) << 24);
+        if ((j & 7) == 0) *reinterpret_cast<uint32_t*>(codes + (size_t)row * (K >> 1) + kb * 8 + (j >> 3) * 4) = w;
+        if (j == 0)
+            sf[((size_t)(row >> 7) * (kblocks >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3)] = sfb;
     }
 }
 
@@ -218,20 +202,35 @@ extern "C" int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16
         return BILOCO_ERR_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
     const float target = rule == BILOCO_RULE_STATIC_6 ? 448.0f : 256.0f;
-    int nblk = (M * (K >> 4) + Q_THREADS - 1) / Q_THREADS;
-    if (nblk > 96) nblk = 96;
+    // cluster size: at most about ten 128-bit loads per thread in the maximum phase; CTAs: one element per lane up to 128 CTAs
+    int csize = 1;
+    while (csize < Q_MAX_CLUSTER && (M * K / 8) > csize * Q_THREADS * 10) csize *= 2;
+    int nblk = (M * K + Q_THREADS - 1) / Q_THREADS;
+    if (nblk > 128) nblk = 128;
+    nblk = (nblk + csize - 1) / csize * csize;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)nblk);
     cfg.blockDim = dim3(Q_THREADS);
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (biloco_internal_use_pdl()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (csize > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)csize;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = biloco_internal_use_pdl() ? 1 : 0;
+    cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, act_quant_kernel, (const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16,
                            (__nv_bfloat16*)Xs_bf16, (uint8_t*)A_codes, (uint8_t*)A_sf, a_gscale, alpha_out, w_gscale, M, A_rows, K,
-                           rule, given_scale ? 1 : 0, target) != cudaSuccess)
+                           rule, given_scale ? 1 : 0, target, csize) != cudaSuccess)
         return BILOCO_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
