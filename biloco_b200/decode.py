@@ -1,0 +1,240 @@
+"""Greedy decode of a Llama/Qwen-shaped decoder whose linears are kernel-backed BiLoCoLinear layers.
+
+The decoder is an ordinary ``nn.Module`` built from ``nn.Linear`` layers (q/k/v/o, gate/up/down, lm_head), so the
+model-level entry points apply to it unchanged (``biloco_b200.model.quantize_model`` / ``replace_linears``); for
+throughput measurements ``synthetic_quantize`` swaps in layers with random packed operands instead of decomposing
+random weights. Everything between the linears (embedding, RMSNorm, rotary embedding, attention over a static KV
+cache, argmax) is plain torch. One decode step is captured in a CUDA graph and replayed for the prompt and the
+generated tokens with no host interaction in between.
+
+    python -m biloco_b200.decode --model qwen3-4b --M 1 --prompt 128 --steps 256
+
+prints one JSON line: tokens/s, ms per step, the linears' algorithmic bytes per step and the fraction of the measured
+HBM peak they correspond to (the decode regime streams every weight once per step).
+"""
+import argparse
+import json
+import math
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .layer import BiLoCoLinear
+
+
+@dataclass
+class DecoderConfig:
+    layers: int
+    hidden: int
+    intermediate: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    vocab: int
+    qk_norm: bool = False
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+
+
+PRESETS = {
+    # shapes of the configurations named in the baseline; random initialisation, no checkpoint involved
+    "qwen3-4b": DecoderConfig(36, 2560, 9728, 32, 8, 128, 151936, qk_norm=True),
+    "llama3-70b": DecoderConfig(80, 8192, 28672, 64, 8, 128, 128256, rope_theta=5e5, eps=1e-5),
+    "tiny": DecoderConfig(2, 256, 512, 4, 2, 64, 512, qk_norm=True),
+}
+
+
+def _rms(x, w, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+class Block(nn.Module):
+    def __init__(self, c: DecoderConfig, device, dtype):
+        super().__init__()
+        kw = dict(bias=False, device=device, dtype=dtype)
+        self.q_proj = nn.Linear(c.hidden, c.heads * c.head_dim, **kw)
+        self.k_proj = nn.Linear(c.hidden, c.kv_heads * c.head_dim, **kw)
+        self.v_proj = nn.Linear(c.hidden, c.kv_heads * c.head_dim, **kw)
+        self.o_proj = nn.Linear(c.heads * c.head_dim, c.hidden, **kw)
+        self.gate_proj = nn.Linear(c.hidden, c.intermediate, **kw)
+        self.up_proj = nn.Linear(c.hidden, c.intermediate, **kw)
+        self.down_proj = nn.Linear(c.intermediate, c.hidden, **kw)
+        self.input_norm = nn.Parameter(torch.ones(c.hidden, device=device, dtype=dtype))
+        self.post_norm = nn.Parameter(torch.ones(c.hidden, device=device, dtype=dtype))
+        if c.qk_norm:
+            self.q_norm = nn.Parameter(torch.ones(c.head_dim, device=device, dtype=dtype))
+            self.k_norm = nn.Parameter(torch.ones(c.head_dim, device=device, dtype=dtype))
+
+
+class Decoder(nn.Module):
+    """Decoder-only transformer for single-token steps over a static KV cache. ``meta=True`` builds the linears without
+    storage (their weights are about to be replaced by synthetic quantised layers)."""
+
+    def __init__(self, c: DecoderConfig, device="cuda", dtype=torch.bfloat16, meta=False, std=0.02):
+        super().__init__()
+        self.c = c
+        lin_dev = "meta" if meta else device
+        self.embed = nn.Embedding(c.vocab, c.hidden, device=device, dtype=dtype)
+        self.blocks = nn.ModuleList(Block(c, lin_dev, dtype) for _ in range(c.layers))
+        if meta:      # norm weights are real even when the linears are placeholders
+            for b in self.blocks:
+                for n in ("input_norm", "post_norm", "q_norm", "k_norm"):
+                    if hasattr(b, n):
+                        setattr(b, n, nn.Parameter(torch.ones(getattr(b, n).shape, device=device, dtype=dtype)))
+        self.norm = nn.Parameter(torch.ones(c.hidden, device=device, dtype=dtype))
+        self.lm_head = nn.Linear(c.hidden, c.vocab, bias=False, device=lin_dev, dtype=dtype)
+        if not meta:
+            for m in self.modules():
+                if isinstance(m, (nn.Linear, nn.Embedding)):
+                    nn.init.normal_(m.weight, std=std)
+        else:
+            nn.init.normal_(self.embed.weight, std=std)
+
+    def new_cache(self, M, max_len, device=None, dtype=torch.bfloat16):
+        c = self.c
+        device = device or self.embed.weight.device
+        kv = [(torch.zeros(M, c.kv_heads, max_len, c.head_dim, device=device, dtype=dtype),
+               torch.zeros(M, c.kv_heads, max_len, c.head_dim, device=device, dtype=dtype)) for _ in range(c.layers)]
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=device, dtype=torch.float32) / c.head_dim))
+        ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+        return dict(kv=kv, cos=ang.cos(), sin=ang.sin(), positions=torch.arange(max_len, device=device))
+
+    @staticmethod
+    def _rope(x, cos, sin):                  # x [M, H, D]; cos/sin [1, D/2]
+        x1, x2 = x[..., : x.shape[-1] // 2].float(), x[..., x.shape[-1] // 2:].float()
+        return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1).to(x.dtype)
+
+    def step(self, tokens, pos, cache):
+        """tokens int64 [M], pos int64 device tensor [1] (the position being written), cache from new_cache().
+        Returns the logits [M, vocab] of the next token."""
+        c = self.c
+        M = tokens.shape[0]
+        h = self.embed(tokens)
+        cos = cache["cos"].index_select(0, pos)
+        sin = cache["sin"].index_select(0, pos)
+        mask = (cache["positions"] <= pos)[None, None, None, :]
+        for b, (kc, vc) in zip(self.blocks, cache["kv"]):
+            x = _rms(h, b.input_norm, c.eps)
+            q = b.q_proj(x).view(M, c.heads, c.head_dim)
+            k = b.k_proj(x).view(M, c.kv_heads, c.head_dim)
+            v = b.v_proj(x).view(M, c.kv_heads, c.head_dim)
+            if c.qk_norm:
+                q, k = _rms(q, b.q_norm, c.eps), _rms(k, b.k_norm, c.eps)
+            q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
+            kc.index_copy_(2, pos, k.unsqueeze(2).to(kc.dtype))
+            vc.index_copy_(2, pos, v.unsqueeze(2).to(vc.dtype))
+            a = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, attn_mask=mask, enable_gqa=True)
+            h = h + b.o_proj(a.reshape(M, c.heads * c.head_dim))
+            x = _rms(h, b.post_norm, c.eps)
+            h = h + b.down_proj(F.silu(b.gate_proj(x)) * b.up_proj(x))
+        return self.lm_head(_rms(h, self.norm, c.eps))
+
+
+def synthetic_quantize(model: Decoder, rank: int, seed: int = 0):
+    """Replace every nn.Linear of the decoder (lm_head included) by a BiLoCoLinear with random packed operands."""
+    dev = model.embed.weight.device
+    n = 0
+    for parent in list(model.modules()):
+        for name, child in list(parent.named_children()):
+            if isinstance(child, nn.Linear):
+                setattr(parent, name, BiLoCoLinear.synthetic(child.in_features, child.out_features, rank, dev, seed=seed + n))
+                n += 1
+    return n
+
+
+def linear_bytes(model: nn.Module):
+    """Algorithmic bytes one decode step streams through the linears: codes + block scales + packed U and V signs."""
+    total = 0
+    for m in model.modules():
+        if isinstance(m, BiLoCoLinear):
+            K, N, r = m.in_features, m.out_features, m.rank
+            total += N * K // 2 + N * K // 16 + N * r // 8 + K * r // 8
+    return total
+
+
+@torch.no_grad()
+def greedy_decode(model: Decoder, prompt: torch.Tensor, steps: int, use_graph: bool = True):
+    """prompt int64 [M, P] on the model's device. Feeds the prompt one position at a time (filling the cache), then
+    generates `steps` tokens greedily. Returns (tokens [M, steps], seconds spent on the generated steps)."""
+    dev = prompt.device
+    M, P = prompt.shape
+    cache = model.new_cache(M, P + steps)
+    pos = torch.zeros(1, device=dev, dtype=torch.long)
+    nxt = torch.zeros(M, device=dev, dtype=torch.long)
+    out = torch.zeros(M, P + steps, device=dev, dtype=torch.long)
+
+    def one_step():
+        # the token at position pos: from the prompt while inside it, else the previous step's argmax
+        tok = torch.where(pos < P, prompt.index_select(1, pos.clamp(max=P - 1)).squeeze(1), nxt)
+        logits = model.step(tok, pos, cache)
+        nxt.copy_(logits.float().argmax(dim=-1))
+        out.index_copy_(1, pos, nxt.unsqueeze(1))
+        pos.add_(1)
+
+    run = one_step
+    if use_graph:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            one_step()                       # warm-up outside capture (lazy allocations, kernel launch set-up)
+            torch.cuda.synchronize()
+            pos.zero_()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=s):
+                one_step()
+        torch.cuda.current_stream().wait_stream(s)
+        pos.zero_()
+        run = g.replay
+    for _ in range(P - 1):                   # positions 0 .. P-2: prompt tokens in, predictions discarded
+        run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):                   # position P-1 predicts the first generated token, and so on
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    return out[:, P - 1:P - 1 + steps].clone(), e0.elapsed_time(e1) * 1e-3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="qwen3-4b", choices=sorted(PRESETS))
+    ap.add_argument("--M", type=int, default=1, help="sequences decoded together (<= 32)")
+    ap.add_argument("--rank", type=int, default=512)
+    ap.add_argument("--prompt", type=int, default=128)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the preset's)")
+    ap.add_argument("--seed", type=int, default=0)
+    args = ap.parse_args()
+    assert torch.cuda.is_available(), "decode needs a CUDA device (there is no CPU path)"
+    c = PRESETS[args.model]
+    if args.layers:
+        c = DecoderConfig(**{**c.__dict__, "layers": args.layers})
+    dev = torch.device("cuda")
+    torch.manual_seed(args.seed)
+    model = Decoder(c, device=dev, meta=True)
+    nlin = synthetic_quantize(model, args.rank, seed=args.seed)
+    g = torch.Generator(device=dev).manual_seed(args.seed)
+    prompt = torch.randint(0, c.vocab, (args.M, args.prompt), device=dev, generator=g)
+    toks, sec = greedy_decode(model, prompt, args.steps)
+    nbytes = linear_bytes(model)
+    peak = None
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        peak = json.load(open(path)).get("hbm_gbs")
+    gbs = nbytes * args.steps / sec / 1e9
+    print(json.dumps({
+        "metric": "decode tokens/s", "value": args.M * args.steps / sec, "unit": "tokens/s", "M": args.M,
+        "ms_per_step": sec / args.steps * 1e3, "model": args.model, "layers": c.layers, "linears": nlin, "rank": args.rank,
+        "prompt": args.prompt, "steps": args.steps, "data": "synthetic (random packed operands, random prompt)",
+        "linear_bytes_per_step": nbytes, "linear_GBps": gbs, "hbm_peak_GBps": peak,
+        "roofline_frac": (gbs / peak) if peak else None, "finite": bool(torch.isfinite(toks.float()).all())}))
+
+
+if __name__ == "__main__":
+    main()

@@ -41,6 +41,29 @@ class BiLoCoLinear(nn.Module):
         self._gemms = {}      # decode batch M -> BiLoCoGemm
         self._acts = {}       # decode batch M -> reusable activation-quantiser outputs
 
+    @classmethod
+    def synthetic(cls, in_features: int, out_features: int, rank: int, device, seed: int = 0):
+        """A quantised layer with random operands (random codes, block scales in [0.25, 2], random signs, coefficients
+        ~ N(0, 0.01^2)), in the construction of the reference's timing scripts (scripts/problem.py:7-27): the same
+        bytes and arithmetic as a decomposed layer without the decomposition. For throughput measurements."""
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        K, N, r = in_features, out_features, rank
+        self.in_features, self.out_features, self.method, self.rank, self.smooth_factor = K, N, "biloco", r, 0.5
+        g = torch.Generator(device=device).manual_seed(seed)
+        self.weight, self.bias = None, None
+        self.register_buffer("smooth_scale", torch.ones(K, device=device, dtype=torch.bfloat16))
+        self.register_buffer("V_packed", torch.randint(0, 256, (r, K // 8), device=device, dtype=torch.uint8, generator=g))
+        self.register_buffer("U_packed", torch.randint(0, 256, (r, N // 8), device=device, dtype=torch.uint8, generator=g))
+        self.register_buffer("S", (torch.randn(r, device=device, generator=g) * 0.01).to(torch.bfloat16))
+        self.register_buffer("W_codes", torch.randint(0, 256, (N, K // 2), device=device, dtype=torch.uint8, generator=g))
+        sf = (torch.rand(fp4.nvfp4_sf_bytes(N, K), device=device, generator=g) * 1.75 + 0.25).to(torch.float8_e4m3fn)
+        self.register_buffer("W_sf", sf.view(torch.uint8))
+        self.register_buffer("w_gscale", torch.full((1,), 1e-3, device=device, dtype=torch.float32))
+        self.smoothed = False
+        self._gemms, self._acts = {}, {}
+        return self
+
     # ------------------------------------------------------------------------------------------------------
     @torch.no_grad()
     def quantize(self, act_col_max: torch.Tensor = None, T: int = 5, device=None):
