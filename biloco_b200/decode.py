@@ -8,6 +8,7 @@ cache, argmax) is plain torch. One decode step is captured in a CUDA graph and r
 generated tokens with no host interaction in between.
 
     python -m biloco_b200.decode --model qwen3-4b --M 1 --prompt 128 --steps 256
+    torchrun --nproc-per-node 8 -m biloco_b200.decode --model llama3-70b --M 1 --prompt 512 --steps 128     # tensor parallel
 
 prints one JSON line: tokens/s, ms per step, the linears' algorithmic bytes per step and the fraction of the measured
 HBM peak they correspond to (the decode regime streams every weight once per step).
@@ -19,6 +20,7 @@ import os
 from dataclasses import dataclass
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
@@ -44,6 +46,7 @@ PRESETS = {
     "qwen3-4b": DecoderConfig(36, 2560, 9728, 32, 8, 128, 151936, qk_norm=True),
     "llama3-70b": DecoderConfig(80, 8192, 28672, 64, 8, 128, 128256, rope_theta=5e5, eps=1e-5),
     "tiny": DecoderConfig(2, 256, 512, 4, 2, 64, 512, qk_norm=True),
+    "tiny-tp": DecoderConfig(2, 256, 1024, 8, 2, 64, 512, qk_norm=True),      # splits over 2 ranks (K shards of 256)
 }
 
 
@@ -52,17 +55,35 @@ def _rms(x, w, eps):
     return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
 
 
+class RowParallel(nn.Module):
+    """A K-shard of a quantised linear: the local launch returns an fp32 partial sum over all N, one NCCL all-reduce adds
+    the ranks' partials, and the sum is rounded to bf16 once (biloco_b200.parallel.ShardedBiLoCoLinear)."""
+
+    def __init__(self, shard: BiLoCoLinear, group=None):
+        super().__init__()
+        self.shard, self.group, self._impl = shard, group, {}
+
+    def forward(self, x):
+        from .parallel import ShardedBiLoCoLinear
+        x2 = x.reshape(-1, self.shard.in_features)
+        M = x2.shape[0]
+        if M not in self._impl:
+            self._impl[M] = ShardedBiLoCoLinear(self.shard.export_operands(), "row", M, group=self.group, presharded=True)
+        return self._impl[M](x2).reshape(*x.shape[:-1], self.shard.out_features)
+
+
 class Block(nn.Module):
-    def __init__(self, c: DecoderConfig, device, dtype):
+    def __init__(self, c: DecoderConfig, device, dtype, tp: int = 1):
         super().__init__()
         kw = dict(bias=False, device=device, dtype=dtype)
-        self.q_proj = nn.Linear(c.hidden, c.heads * c.head_dim, **kw)
-        self.k_proj = nn.Linear(c.hidden, c.kv_heads * c.head_dim, **kw)
-        self.v_proj = nn.Linear(c.hidden, c.kv_heads * c.head_dim, **kw)
-        self.o_proj = nn.Linear(c.heads * c.head_dim, c.hidden, **kw)
-        self.gate_proj = nn.Linear(c.hidden, c.intermediate, **kw)
-        self.up_proj = nn.Linear(c.hidden, c.intermediate, **kw)
-        self.down_proj = nn.Linear(c.intermediate, c.hidden, **kw)
+        # tensor parallel over `tp` ranks: q/k/v/gate/up keep N/tp output columns, o/down keep K/tp input columns
+        self.q_proj = nn.Linear(c.hidden, c.heads * c.head_dim // tp, **kw)
+        self.k_proj = nn.Linear(c.hidden, c.kv_heads * c.head_dim // tp, **kw)
+        self.v_proj = nn.Linear(c.hidden, c.kv_heads * c.head_dim // tp, **kw)
+        self.o_proj = nn.Linear(c.heads * c.head_dim // tp, c.hidden, **kw)
+        self.gate_proj = nn.Linear(c.hidden, c.intermediate // tp, **kw)
+        self.up_proj = nn.Linear(c.hidden, c.intermediate // tp, **kw)
+        self.down_proj = nn.Linear(c.intermediate // tp, c.hidden, **kw)
         self.input_norm = nn.Parameter(torch.ones(c.hidden, device=device, dtype=dtype))
         self.post_norm = nn.Parameter(torch.ones(c.hidden, device=device, dtype=dtype))
         if c.qk_norm:
@@ -74,19 +95,20 @@ class Decoder(nn.Module):
     """Decoder-only transformer for single-token steps over a static KV cache. ``meta=True`` builds the linears without
     storage (their weights are about to be replaced by synthetic quantised layers)."""
 
-    def __init__(self, c: DecoderConfig, device="cuda", dtype=torch.bfloat16, meta=False, std=0.02):
+    def __init__(self, c: DecoderConfig, device="cuda", dtype=torch.bfloat16, meta=False, std=0.02, tp: int = 1, group=None):
         super().__init__()
-        self.c = c
+        assert c.heads % tp == 0 and c.kv_heads % tp == 0 and c.intermediate % (256 * tp) == 0 and c.vocab % (8 * tp) == 0
+        self.c, self.tp, self.group = c, tp, group
         lin_dev = "meta" if meta else device
         self.embed = nn.Embedding(c.vocab, c.hidden, device=device, dtype=dtype)
-        self.blocks = nn.ModuleList(Block(c, lin_dev, dtype) for _ in range(c.layers))
+        self.blocks = nn.ModuleList(Block(c, lin_dev, dtype, tp) for _ in range(c.layers))
         if meta:      # norm weights are real even when the linears are placeholders
             for b in self.blocks:
                 for n in ("input_norm", "post_norm", "q_norm", "k_norm"):
                     if hasattr(b, n):
                         setattr(b, n, nn.Parameter(torch.ones(getattr(b, n).shape, device=device, dtype=dtype)))
         self.norm = nn.Parameter(torch.ones(c.hidden, device=device, dtype=dtype))
-        self.lm_head = nn.Linear(c.hidden, c.vocab, bias=False, device=lin_dev, dtype=dtype)
+        self.lm_head = nn.Linear(c.hidden, c.vocab // tp, bias=False, device=lin_dev, dtype=dtype)     # vocabulary-parallel
         if not meta:
             for m in self.modules():
                 if isinstance(m, (nn.Linear, nn.Embedding)):
@@ -97,8 +119,9 @@ class Decoder(nn.Module):
     def new_cache(self, M, max_len, device=None, dtype=torch.bfloat16):
         c = self.c
         device = device or self.embed.weight.device
-        kv = [(torch.zeros(M, c.kv_heads, max_len, c.head_dim, device=device, dtype=dtype),
-               torch.zeros(M, c.kv_heads, max_len, c.head_dim, device=device, dtype=dtype)) for _ in range(c.layers)]
+        kvh = c.kv_heads // self.tp
+        kv = [(torch.zeros(M, kvh, max_len, c.head_dim, device=device, dtype=dtype),
+               torch.zeros(M, kvh, max_len, c.head_dim, device=device, dtype=dtype)) for _ in range(c.layers)]
         inv = 1.0 / (c.rope_theta ** (torch.arange(0, c.head_dim, 2, device=device, dtype=torch.float32) / c.head_dim))
         ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
         return dict(kv=kv, cos=ang.cos(), sin=ang.sin(), positions=torch.arange(max_len, device=device))
@@ -113,25 +136,31 @@ class Decoder(nn.Module):
         Returns the logits [M, vocab] of the next token."""
         c = self.c
         M = tokens.shape[0]
+        heads, kv_heads = c.heads // self.tp, c.kv_heads // self.tp
         h = self.embed(tokens)
         cos = cache["cos"].index_select(0, pos)
         sin = cache["sin"].index_select(0, pos)
         mask = (cache["positions"] <= pos)[None, None, None, :]
         for b, (kc, vc) in zip(self.blocks, cache["kv"]):
             x = _rms(h, b.input_norm, c.eps)
-            q = b.q_proj(x).view(M, c.heads, c.head_dim)
-            k = b.k_proj(x).view(M, c.kv_heads, c.head_dim)
-            v = b.v_proj(x).view(M, c.kv_heads, c.head_dim)
+            q = b.q_proj(x).view(M, heads, c.head_dim)
+            k = b.k_proj(x).view(M, kv_heads, c.head_dim)
+            v = b.v_proj(x).view(M, kv_heads, c.head_dim)
             if c.qk_norm:
                 q, k = _rms(q, b.q_norm, c.eps), _rms(k, b.k_norm, c.eps)
             q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
             kc.index_copy_(2, pos, k.unsqueeze(2).to(kc.dtype))
             vc.index_copy_(2, pos, v.unsqueeze(2).to(vc.dtype))
             a = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, attn_mask=mask, enable_gqa=True)
-            h = h + b.o_proj(a.reshape(M, c.heads * c.head_dim))
+            h = h + b.o_proj(a.reshape(M, heads * c.head_dim))
             x = _rms(h, b.post_norm, c.eps)
             h = h + b.down_proj(F.silu(b.gate_proj(x)) * b.up_proj(x))
-        return self.lm_head(_rms(h, self.norm, c.eps))
+        logits = self.lm_head(_rms(h, self.norm, c.eps))
+        if self.tp > 1:         # every rank gets the whole vocabulary (and takes the same argmax)
+            parts = [torch.empty_like(logits) for _ in range(self.tp)]
+            dist.all_gather(parts, logits.contiguous(), group=self.group)
+            logits = torch.cat(parts, dim=-1)
+        return logits
 
 
 def synthetic_quantize(model: Decoder, rank: int, seed: int = 0):
@@ -141,7 +170,10 @@ def synthetic_quantize(model: Decoder, rank: int, seed: int = 0):
     for parent in list(model.modules()):
         for name, child in list(parent.named_children()):
             if isinstance(child, nn.Linear):
-                setattr(parent, name, BiLoCoLinear.synthetic(child.in_features, child.out_features, rank, dev, seed=seed + n))
+                layer = BiLoCoLinear.synthetic(child.in_features, child.out_features, rank, dev, seed=seed + n)
+                if model.tp > 1 and name in ("o_proj", "down_proj"):
+                    layer = RowParallel(layer, model.group)
+                setattr(parent, name, layer)
                 n += 1
     return n
 
@@ -210,30 +242,49 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the preset's)")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a captured step")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "decode needs a CUDA device (there is no CPU path)"
     c = PRESETS[args.model]
     if args.layers:
         c = DecoderConfig(**{**c.__dict__, "layers": args.layers})
-    dev = torch.device("cuda")
+    # tensor parallel when launched by torchrun: one rank per GPU, q/k/v/gate/up/lm_head column-parallel, o/down
+    # row-parallel with an NCCL all-reduce of the fp32 partial sums
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(args.seed)
-    model = Decoder(c, device=dev, meta=True)
-    nlin = synthetic_quantize(model, args.rank, seed=args.seed)
-    g = torch.Generator(device=dev).manual_seed(args.seed)
+    model = Decoder(c, device=dev, meta=True, tp=world)
+    nlin = synthetic_quantize(model, args.rank, seed=args.seed + 1000 * rank)
+    g = torch.Generator(device=dev).manual_seed(args.seed)           # (same prompt on every rank)
     prompt = torch.randint(0, c.vocab, (args.M, args.prompt), device=dev, generator=g)
-    toks, sec = greedy_decode(model, prompt, args.steps)
-    nbytes = linear_bytes(model)
+    toks, sec = greedy_decode(model, prompt, args.steps, use_graph=not args.no_graph)
+    nbytes = linear_bytes(model) * world
+    if world > 1:
+        t = torch.tensor([sec], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+        same = toks.clone()
+        dist.broadcast(same, src=0)
+        assert torch.equal(same, toks), "ranks disagree on the generated tokens"
+        if rank != 0:
+            dist.destroy_process_group()
+            return
     peak = None
     path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(path):
         peak = json.load(open(path)).get("hbm_gbs")
     gbs = nbytes * args.steps / sec / 1e9
     print(json.dumps({
-        "metric": "decode tokens/s", "value": args.M * args.steps / sec, "unit": "tokens/s", "M": args.M,
+        "metric": "decode tokens/s", "value": args.M * args.steps / sec, "unit": "tokens/s", "M": args.M, "n_gpus": world,
         "ms_per_step": sec / args.steps * 1e3, "model": args.model, "layers": c.layers, "linears": nlin, "rank": args.rank,
         "prompt": args.prompt, "steps": args.steps, "data": "synthetic (random packed operands, random prompt)",
         "linear_bytes_per_step": nbytes, "linear_GBps": gbs, "hbm_peak_GBps": peak,
-        "roofline_frac": (gbs / peak) if peak else None, "finite": bool(torch.isfinite(toks.float()).all())}))
+        "roofline_frac": (gbs / (peak * world)) if peak else None, "finite": bool(torch.isfinite(toks.float()).all())}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

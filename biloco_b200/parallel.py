@@ -73,13 +73,14 @@ class ShardedBiLoCoLinear:
     kind = "row":    forward(x_local [M, K/G]) -> y [M, N], all-reduced over the group.
     """
 
-    def __init__(self, ops: dict, kind: str, M: int, group=None):
+    def __init__(self, ops: dict, kind: str, M: int, group=None, presharded: bool = False):
+        """ops: the operands of the whole layer (sharded here), or with presharded=True this rank's shard as it is."""
         from .kernel import BiLoCoGemm
         assert kind in ("column", "row")
         self.kind, self.M, self.group = kind, M, group
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.ops = (shard_column_parallel if kind == "column" else shard_row_parallel)(ops, world, rank)
+        self.ops = dict(ops) if presharded else (shard_column_parallel if kind == "column" else shard_row_parallel)(ops, world, rank)
         o = self.ops
         self.N, self.K = o["W_codes"].shape[0], o["W_codes"].shape[1] * 2
         dev = o["W_codes"].device
