@@ -18,7 +18,7 @@ namespace biloco {
 // mbarrier; nothing else stands between the wait and the arithmetic.
 // Arithmetic: warp w takes the w-th eighth of the pass's 32-bit sign words, one word per lane; a lane unpacks the 32
 // activations of its word once and, for every rank, adds them under predicates taken from the sign bits (four
-// independent accumulators in flight). One shuffle reduction per run of four ranks (see z_reduce4), per-warp partial
+// independent accumulators in flight). One shuffle reduction per run of up to six ranks (z_reduce_run), per-warp partial
 // sums in shared memory, one combine per chunk: z = S * (2 * sum_{sign=+1} x - sum x).
 // The CUDA-core code here is bound by instruction issue, not by latency (measured: the same cycles cold and warm,
 // alone or beside spinning warps), so what matters is the instruction count per element and an even spread over warps.
@@ -58,11 +58,12 @@ __device__ __forceinline__ void z_issue_v(const FusedParams& p, uint8_t* work, i
 // 4 chains 5.2; sign flips by XOR 7.6; multiplications by +-1 9.7. The loops are kept rolled on purpose: the kernel's
 // code runs once per CTA and launch, and instruction fetch was the largest stall after barriers in the profile
 // (4.1 stalled warp-cycles per issued instruction with everything unrolled).
+constexpr int ZRUN = 6;                          // ranks per run of the z stage's inner loop (4.27 ranks per CTA at M = 1, r = 512, 120 CTAs: one run)
 #define BILOCO_PADD(accv, vwv, bit, xv)                                                                              \
     asm("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %1, %2;\n\tsetp.ne.u32 p, t, 0;\n\t@p add.f32 %0, %0, %3;\n\t}" \
         : "+f"(accv) : "r"(vwv), "r"(bit), "f"(xv))
 template <int NQ>
-__device__ __forceinline__ void z_word_n(const uint4* xs, const uint32_t* vrow, int xw_stride, int nq, float (&sums)[4], float& plain) {
+__device__ __forceinline__ void z_word_n(const uint4* xs, const uint32_t* vrow, int xw_stride, int nq, float (&sums)[ZRUN], float& plain) {
     uint32_t vw[NQ];
     float a0[NQ], a1[NQ];
 #pragma unroll
@@ -90,23 +91,33 @@ __device__ __forceinline__ void z_word_n(const uint4* xs, const uint32_t* vrow, 
         ps += ((xf[0] + xf[1]) + (xf[2] + xf[3])) + ((xf[4] + xf[5]) + (xf[6] + xf[7]));
     }
 #pragma unroll
-    for (int q = 0; q < 4; ++q) sums[q] = q < NQ ? a0[q < NQ ? q : 0] + a1[q < NQ ? q : 0] : 0.f;
+    for (int q = 0; q < ZRUN; ++q) sums[q] = q < NQ ? a0[q < NQ ? q : 0] + a1[q < NQ ? q : 0] : 0.f;
     plain = ps;
 }
 
-// Sum of v[q] over the 32 lanes for four ranks at once: a lane gives away half of its values at every step (2 + 1 + 3
-// shuffles instead of 4 x 5). On return lane l holds the total of rank ((l >> 4) & 1) * 2 + ((l >> 3) & 1).
-__device__ __forceinline__ float z_reduce4(const float (&v)[4], int lane) {
-    const bool h16 = lane & 16, h8 = lane & 8;
-    float a[2];
+// Sum of v[q] over the 32 lanes for up to eight ranks at once: a lane gives away half of its values at every step
+// (4 + 2 + 1 + 2 shuffles instead of 8 x 5). On return lane l holds the total of rank ((l >> 4) & 1) * 4 +
+// ((l >> 3) & 1) * 2 + ((l >> 2) & 1); ranks >= ZRUN are zero.
+__device__ __forceinline__ float z_reduce_run(const float (&v)[ZRUN], int lane) {
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4;
+    float w[8];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {        // lanes with bit 4 set keep ranks 2-3, the others ranks 0-1
-        const float give = h16 ? v[i] : v[i + 2], keep = h16 ? v[i + 2] : v[i];
+    for (int i = 0; i < 8; ++i) w[i] = i < ZRUN ? v[i < ZRUN ? i : 0] : 0.f;
+    float a[4], b[2], c;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {        // lanes with bit 4 set keep ranks 4-7, the others ranks 0-3
+        const float give = h16 ? w[i] : w[i + 4], keep = h16 ? w[i + 4] : w[i];
         a[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
     }
-    const float give = h8 ? a[0] : a[1], keep = h8 ? a[1] : a[0];
-    float c = keep + __shfl_xor_sync(0xffffffffu, give, 8);
-    c += __shfl_xor_sync(0xffffffffu, c, 4);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float give = h8 ? a[i] : a[i + 2], keep = h8 ? a[i + 2] : a[i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+    }
+    {
+        const float give = h4 ? b[0] : b[1], keep = h4 ? b[1] : b[0];
+        c = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+    }
     c += __shfl_xor_sync(0xffffffffu, c, 2);
     c += __shfl_xor_sync(0xffffffffu, c, 1);
     return c;
@@ -170,18 +181,22 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
                 const bool active = lane < wpw && w < words;
                 const uint4* xs = reinterpret_cast<const uint4*>(work) + (active ? w : 0) * 4;     // 64 bytes = 32 bf16 of word w
 #pragma unroll 1
-                for (int q0 = 0; q0 < nrc; q0 += 4) {                   // runs of four ranks
+                for (int q0 = 0; q0 < nrc; q0 += ZRUN) {                // runs of up to six ranks
                     const int nq = nrc - q0;
-                    float sums[4] = {0.f, 0.f, 0.f, 0.f};
+                    float sums[ZRUN];
+#pragma unroll
+                    for (int q = 0; q < ZRUN; ++q) sums[q] = 0.f;
                     float plain = 0.f;
                     if (active) {
                         const uint32_t* vrow = vt + (size_t)q0 * words + w;
                         if (nq <= 2) z_word_n<2>(xs, vrow, words, nq, sums, plain);
-                        else z_word_n<4>(xs, vrow, words, nq, sums, plain);
+                        else if (nq <= 4) z_word_n<4>(xs, vrow, words, nq, sums, plain);
+                        else if (nq == 5) z_word_n<5>(xs, vrow, words, nq, sums, plain);
+                        else z_word_n<6>(xs, vrow, words, nq, sums, plain);
                     }
-                    const float tot = z_reduce4(sums, lane);
-                    const int rq = q0 + ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1);
-                    if ((lane & 7) == 0 && rq < nrc) ctrl->zred[zw][rq] += tot;
+                    const float tot = z_reduce_run(sums, lane);
+                    const int rl = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                    if ((lane & 3) == 0 && rl < ZRUN && q0 + rl < nrc) ctrl->zred[zw][q0 + rl] += tot;
                     if (q0 == 0) {
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
