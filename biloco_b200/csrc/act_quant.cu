@@ -59,13 +59,12 @@ __device__ __forceinline__ void unpack_smoothed(uint32_t w, uint32_t sm, bool sm
     }
 }
 
-__global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat16* __restrict__ X,
-                                                              const __nv_bfloat16* __restrict__ smooth,
-                                                              __nv_bfloat16* __restrict__ Xs, uint8_t* __restrict__ codes,
+__global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat16* X, const __nv_bfloat16* smooth,
+                                                              __nv_bfloat16* Xs, uint8_t* __restrict__ codes,
                                                               uint8_t* __restrict__ sf, float* __restrict__ a_gscale,
                                                               float* __restrict__ alpha_out, const float* __restrict__ w_gscale,
                                                               int M, int A_rows, int K, int rule, int given_scale, float target,
-                                                              int csize) {
+                                                              int csize, const __nv_bfloat16* __restrict__ norm_w, float eps, int n_alpha) {
     const int kblocks = K >> 4;
     __shared__ float red[Q_THREADS / 32];
     __shared__ float gs_sh;
@@ -73,6 +72,64 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
     // prefetch) now; this kernel reads nothing before the previous kernel of the stream has completed.
     biloco::griddep_launch_dependents();
     biloco::griddep_wait();
+    // ---- optional RMSNorm in front (per row: x * rsqrt(mean(x^2) + eps), rounded to bf16, times the bf16 weight, rounded
+    //      to bf16; then the smoothing division): CTA r of the cluster takes rows r, r + csize, ..., two passes over a
+    //      row (sum of squares, then normalise and store); every cluster does all rows (same values), and after the
+    //      cluster barrier the rest of the kernel reads the normalised activation it has just written ----
+    if (norm_w) {
+        const int kvec = K >> 3;
+        for (int row = csize > 1 ? (int)(blockIdx.x % (unsigned)csize) : 0; row < M; row += csize) {
+            const uint4* xr = reinterpret_cast<const uint4*>(X + (size_t)row * K);
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < kvec; i += Q_THREADS) {
+                const uint4 a = xr[i];
+                const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
+                    ss = fmaf(lo, lo, ss);
+                    ss = fmaf(hi, hi, ss);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            __syncthreads();                                  // (red is reused from the previous row)
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+            __syncthreads();
+            float tot = 0.f;
+#pragma unroll
+            for (int i = 0; i < Q_THREADS / 32; ++i) tot += red[i];
+            const float inv = rsqrtf(tot / (float)K + eps);
+            uint4* xo = reinterpret_cast<uint4*>(Xs + (size_t)row * K);
+            for (int i = threadIdx.x; i < kvec; i += Q_THREADS) {
+                const uint4 a = xr[i], g = reinterpret_cast<const uint4*>(norm_w)[i];
+                uint4 c = make_uint4(0u, 0u, 0u, 0u);
+                if (smooth) c = reinterpret_cast<const uint4*>(smooth)[i];
+                const uint32_t w[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w}, sw[4] = {c.x, c.y, c.z, c.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v[2] = {__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xFFFF0000u)};
+                    const float gv[2] = {__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xFFFF0000u)};
+                    const float sv[2] = {__uint_as_float(sw[e] << 16), __uint_as_float(sw[e] & 0xFFFF0000u)};
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        v[h] = __bfloat162float(__float2bfloat16_rn(v[h] * inv));
+                        v[h] = __bfloat162float(__float2bfloat16_rn(v[h] * gv[h]));
+                        if (smooth) v[h] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v[h], sv[h])));
+                    }
+                    o[e] = (__float_as_uint(v[0]) >> 16) | (__float_as_uint(v[1]) & 0xFFFF0000u);
+                }
+                xo[i] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        __threadfence();
+        if (csize > 1) biloco::cluster_sync_all();
+        else __syncthreads();
+        X = Xs;                 // from here on: an already normalised and smoothed activation, nothing left to write back
+        smooth = nullptr;
+        Xs = nullptr;
+    }
     // ---- tensor scale: maximum of the (smoothed) activation. Every cluster of `csize` CTAs computes it for itself (no
     //      grid-wide synchronisation): a CTA reduces its share of the 128-bit vectors, the CTAs of the cluster exchange
     //      their maxima through distributed shared memory ----
@@ -123,7 +180,8 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
     const float gs = gs_sh;
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         if (!given_scale) a_gscale[0] = gs;
-        if (alpha_out && w_gscale) alpha_out[0] = __fmul_rn(w_gscale[0], gs);
+        if (alpha_out && w_gscale)
+            for (int i = 0; i < n_alpha; ++i) alpha_out[i] = __fmul_rn(w_gscale[i], gs);     // one per consumer of this activation
     }
     // ---- zero padding: block scales of rows M .. 128-padded row count, codes of rows M .. A_rows ----
     {
@@ -190,10 +248,13 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
 
 }  // namespace
 
-extern "C" int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_bf16, void* A_codes, void* A_sf,
-                                     float* a_gscale, float* alpha_out, const float* w_gscale, int M, int A_rows, int K,
-                                     int rule, biloco_stream_t stream) {
+static int launch_act_quant(const void* X_bf16, const void* norm_w, float eps, const void* smooth_bf16, void* Xs_bf16, void* A_codes,
+                            void* A_sf, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M, int A_rows,
+                            int K, int rule, biloco_stream_t stream) {
     if (!X_bf16 || !A_codes || !A_sf || !a_gscale) return BILOCO_ERR_NULL;
+    if (norm_w && !Xs_bf16) return BILOCO_ERR_NULL;
+    if (n_alpha < 1 || n_alpha > 16) return BILOCO_ERR_SHAPE;
+    if ((uintptr_t)norm_w & 15) return BILOCO_ERR_ALIGN;
     if (M < 1 || A_rows < M || A_rows > 128 || K < 64 || (K % 64) != 0) return BILOCO_ERR_SHAPE;
     const bool given_scale = (rule & BILOCO_RULE_GIVEN_SCALE) != 0;
     rule &= ~BILOCO_RULE_GIVEN_SCALE;
@@ -230,7 +291,22 @@ extern "C" int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16
     cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, act_quant_kernel, (const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16,
                            (__nv_bfloat16*)Xs_bf16, (uint8_t*)A_codes, (uint8_t*)A_sf, a_gscale, alpha_out, w_gscale, M, A_rows, K,
-                           rule, given_scale ? 1 : 0, target, csize) != cudaSuccess)
+                           rule, given_scale ? 1 : 0, target, csize, (const __nv_bfloat16*)norm_w, eps, n_alpha) != cudaSuccess)
         return BILOCO_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
+}
+
+extern "C" int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_bf16, void* A_codes, void* A_sf,
+                                     float* a_gscale, float* alpha_out, const float* w_gscale, int M, int A_rows, int K,
+                                     int rule, biloco_stream_t stream) {
+    return launch_act_quant(X_bf16, nullptr, 0.f, smooth_bf16, Xs_bf16, A_codes, A_sf, a_gscale, alpha_out, w_gscale, 1, M, A_rows, K,
+                            rule, stream);
+}
+
+extern "C" int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_weight_bf16, float eps, const void* smooth_bf16,
+                                          void* Xn_bf16, void* A_codes, void* A_sf, float* a_gscale, float* alpha_out,
+                                          const float* w_gscale, int n_alpha, int M, int A_rows, int K, int rule,
+                                          biloco_stream_t stream) {
+    return launch_act_quant(X_bf16, norm_weight_bf16, eps, smooth_bf16, Xn_bf16, A_codes, A_sf, a_gscale, alpha_out, w_gscale, n_alpha,
+                            M, A_rows, K, rule, stream);
 }

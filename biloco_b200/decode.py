@@ -99,6 +99,7 @@ class Decoder(nn.Module):
         super().__init__()
         assert c.heads % tp == 0 and c.kv_heads % tp == 0 and c.intermediate % (256 * tp) == 0 and c.vocab % (8 * tp) == 0
         self.c, self.tp, self.group = c, tp, group
+        self.fuse_norm_quant, self._shared = True, {}     # (see _normed_linears)
         lin_dev = "meta" if meta else device
         self.embed = nn.Embedding(c.vocab, c.hidden, device=device, dtype=dtype)
         self.blocks = nn.ModuleList(Block(c, lin_dev, dtype, tp) for _ in range(c.layers))
@@ -126,6 +127,26 @@ class Decoder(nn.Module):
         ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
         return dict(kv=kv, cos=ang.cos(), sin=ang.sin(), positions=torch.arange(max_len, device=device))
 
+    def _normed_linears(self, h, norm_w, layers, key):
+        """[layer(rmsnorm(h) * norm_w) for layer in layers]. When the layers are unsmoothed kernel-backed BiLoCo layers
+        the norm, the NVFP4 quantisation and one decode scale per layer come from ONE launch (the activation is the
+        same for all of them), followed by one fused linear per layer; otherwise the plain composition."""
+        from . import fp4
+        M = h.shape[0]
+        fusable = self.fuse_norm_quant and M <= 32 and all(isinstance(l, BiLoCoLinear) and l.weight is None and not l.smoothed
+                                                           and l.rank > 0 for l in layers)
+        if not fusable:
+            x = _rms(h, norm_w, self.c.eps)
+            return [l(x) for l in layers]
+        st = self._shared.get((key, M))
+        if st is None:
+            st = dict(w_gs=torch.cat([l.w_gscale.reshape(1) for l in layers]).contiguous(), q=None)
+            self._shared[(key, M)] = st
+        q = fp4.quantize_activation(h.contiguous(), fp4.CONFIG_X, w_gscale=st["w_gs"], rows=M, out=st["q"],
+                                    norm_weight=norm_w, eps=self.c.eps)
+        st["q"] = q
+        return [l.forward_quantized(q, q["alpha"][i:i + 1]) for i, l in enumerate(layers)]
+
     @staticmethod
     def _rope(x, cos, sin):                  # x [M, H, D]; cos/sin [1, D/2]
         x1, x2 = x[..., : x.shape[-1] // 2].float(), x[..., x.shape[-1] // 2:].float()
@@ -141,11 +162,9 @@ class Decoder(nn.Module):
         cos = cache["cos"].index_select(0, pos)
         sin = cache["sin"].index_select(0, pos)
         mask = (cache["positions"] <= pos)[None, None, None, :]
-        for b, (kc, vc) in zip(self.blocks, cache["kv"]):
-            x = _rms(h, b.input_norm, c.eps)
-            q = b.q_proj(x).view(M, heads, c.head_dim)
-            k = b.k_proj(x).view(M, kv_heads, c.head_dim)
-            v = b.v_proj(x).view(M, kv_heads, c.head_dim)
+        for li, (b, (kc, vc)) in enumerate(zip(self.blocks, cache["kv"])):
+            q, k, v = self._normed_linears(h, b.input_norm, [b.q_proj, b.k_proj, b.v_proj], (li, "qkv"))
+            q, k, v = q.view(M, heads, c.head_dim), k.view(M, kv_heads, c.head_dim), v.view(M, kv_heads, c.head_dim)
             if c.qk_norm:
                 q, k = _rms(q, b.q_norm, c.eps), _rms(k, b.k_norm, c.eps)
             q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
@@ -153,9 +172,9 @@ class Decoder(nn.Module):
             vc.index_copy_(2, pos, v.unsqueeze(2).to(vc.dtype))
             a = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, attn_mask=mask, enable_gqa=True)
             h = h + b.o_proj(a.reshape(M, heads * c.head_dim))
-            x = _rms(h, b.post_norm, c.eps)
-            h = h + b.down_proj(F.silu(b.gate_proj(x)) * b.up_proj(x))
-        logits = self.lm_head(_rms(h, self.norm, c.eps))
+            gate, up = self._normed_linears(h, b.post_norm, [b.gate_proj, b.up_proj], (li, "mlp"))
+            h = h + b.down_proj(F.silu(gate) * up)
+        logits, = self._normed_linears(h, self.norm, [self.lm_head], (-1, "head"))
         if self.tp > 1:         # every rank gets the whole vocabulary (and takes the same argmax)
             parts = [torch.empty_like(logits) for _ in range(self.tp)]
             dist.all_gather(parts, logits.contiguous(), group=self.group)
@@ -243,6 +262,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the preset's)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a captured step")
+    ap.add_argument("--no-fuse", action="store_true", help="separate RMSNorm kernels and one quantiser launch per linear")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "decode needs a CUDA device (there is no CPU path)"
     c = PRESETS[args.model]
@@ -257,6 +277,7 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(args.seed)
     model = Decoder(c, device=dev, meta=True, tp=world)
+    model.fuse_norm_quant = not args.no_fuse
     nlin = synthetic_quantize(model, args.rank, seed=args.seed + 1000 * rank)
     g = torch.Generator(device=dev).manual_seed(args.seed)           # (same prompt on every rank)
     prompt = torch.randint(0, c.vocab, (args.M, args.prompt), device=dev, generator=g)
@@ -280,7 +301,7 @@ def main():
     print(json.dumps({
         "metric": "decode tokens/s", "value": args.M * args.steps / sec, "unit": "tokens/s", "M": args.M, "n_gpus": world,
         "ms_per_step": sec / args.steps * 1e3, "model": args.model, "layers": c.layers, "linears": nlin, "rank": args.rank,
-        "prompt": args.prompt, "steps": args.steps, "data": "synthetic (random packed operands, random prompt)",
+        "prompt": args.prompt, "steps": args.steps, "fused_norm_quant": model.fuse_norm_quant, "data": "synthetic (random packed operands, random prompt)",
         "linear_bytes_per_step": nbytes, "linear_GBps": gbs, "hbm_peak_GBps": peak,
         "roofline_frac": (gbs / (peak * world)) if peak else None, "finite": bool(torch.isfinite(toks.float()).all())}))
     if world > 1:

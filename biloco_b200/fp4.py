@@ -140,12 +140,16 @@ def activation_scale_from_amax(amax: torch.Tensor, rule: str = None) -> torch.Te
 
 
 def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor = None, w_gscale: torch.Tensor = None,
-                        rows: int = None, out: dict = None, gscale: torch.Tensor = None):
+                        rows: int = None, out: dict = None, gscale: torch.Tensor = None, norm_weight: torch.Tensor = None,
+                        eps: float = 1e-6):
     """bf16 CUDA activation [M, K] -> dict(A [1, rows, K/2] uint8, A_sf float8 (atom layout), gscale fp32 [1],
     alpha fp32 [1] (= w_gscale * gscale, when w_gscale is given), X bf16 [M, K] (x / smooth when smoothing)).
     ``gscale`` (fp32 [1]) supplies the tensor scale instead of deriving it from this tensor's own maximum.
     Runs the library's quantiser on the current stream; nothing returns to the host. Pass ``out`` (a dict from
-    an earlier call with the same shapes) to reuse its buffers, e.g. under CUDA-graph capture."""
+    an earlier call with the same shapes) to reuse its buffers, e.g. under CUDA-graph capture.
+    ``norm_weight`` (bf16 [K]): RMS-normalise every row first (x * rsqrt(mean(x^2) + eps) -> bf16, * weight -> bf16) inside
+    the same launch; X is then the normalised activation. ``w_gscale`` may hold n scales (fp32 [n]): alpha gets one entry
+    per linear that consumes this activation."""
     rule = CONFIG_X if rule is None else rule
     assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     M, K = x.shape
@@ -155,20 +159,33 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
         out = dict(A=torch.empty((1, rows, K // 2), device=dev, dtype=torch.uint8),
                    A_sf=torch.empty(nvfp4_sf_bytes(rows, K), device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn),
                    gscale=torch.empty(1, device=dev, dtype=torch.float32),
-                   alpha=torch.empty(1, device=dev, dtype=torch.float32) if w_gscale is not None else None,
-                   X=torch.empty_like(x) if smooth is not None else x)
-    elif smooth is None:
+                   alpha=torch.empty(w_gscale.numel(), device=dev, dtype=torch.float32) if w_gscale is not None else None,
+                   X=torch.empty_like(x) if (smooth is not None or norm_weight is not None) else x)
+    elif smooth is None and norm_weight is None:
         out["X"] = x
     rule_id = _lib.RULES[rule]
     if gscale is not None:          # tensor scale agreed elsewhere (tensor-parallel K-slices): do not recompute it
         out["gscale"].copy_(gscale.reshape(1))
         rule_id |= 0x100
+    n_alpha = w_gscale.numel() if w_gscale is not None else 1
     with torch.cuda.device(dev):
-        rc = _lib.load().biloco_b200_act_quant(
-            x.data_ptr(), smooth.data_ptr() if smooth is not None else None,
-            out["X"].data_ptr() if smooth is not None else None, out["A"].data_ptr(), out["A_sf"].data_ptr(),
-            out["gscale"].data_ptr(), out["alpha"].data_ptr() if w_gscale is not None else None,
-            w_gscale.data_ptr() if w_gscale is not None else None, M, rows, K, rule_id,
-            torch.cuda.current_stream().cuda_stream)
+        if norm_weight is None and n_alpha == 1:
+            rc = _lib.load().biloco_b200_act_quant(
+                x.data_ptr(), smooth.data_ptr() if smooth is not None else None,
+                out["X"].data_ptr() if smooth is not None else None, out["A"].data_ptr(), out["A_sf"].data_ptr(),
+                out["gscale"].data_ptr(), out["alpha"].data_ptr() if w_gscale is not None else None,
+                w_gscale.data_ptr() if w_gscale is not None else None, M, rows, K, rule_id,
+                torch.cuda.current_stream().cuda_stream)
+        else:
+            if norm_weight is not None:
+                assert norm_weight.dtype == torch.bfloat16 and norm_weight.numel() == K and norm_weight.is_contiguous()
+            rc = _lib.load().biloco_b200_norm_act_quant(
+                x.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
+                smooth.data_ptr() if smooth is not None else None,
+                out["X"].data_ptr() if (smooth is not None or norm_weight is not None) else None,
+                out["A"].data_ptr(), out["A_sf"].data_ptr(), out["gscale"].data_ptr(),
+                out["alpha"].data_ptr() if w_gscale is not None else None,
+                w_gscale.data_ptr() if w_gscale is not None else None, n_alpha, M, rows, K, rule_id,
+                torch.cuda.current_stream().cuda_stream)
     _lib.check(rc, f"act_quant (M={M}, K={K}, rule={rule})")
     return out

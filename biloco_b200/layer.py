@@ -120,6 +120,16 @@ class BiLoCoLinear(nn.Module):
         g = self._gemm_for(M, q["alpha"])
         return g(q["A"], q["A_sf"], q["X"]).view(-1, self.out_features)[:M]
 
+    def forward_quantized(self, q: dict, alpha: torch.Tensor):
+        """The fused linear on an activation that has been quantised already (fp4.quantize_activation with this layer's
+        rules and smoothing): q["A"], q["A_sf"], q["X"] for M <= 32 rows; alpha fp32 [1] = w_gscale * q["gscale"] on the
+        device. Lets several layers that read the same activation (q/k/v, gate/up) share one quantiser launch."""
+        M = q["X"].shape[0]
+        g = self._gemm_for(M, alpha)
+        if g.alpha.data_ptr() != alpha.data_ptr():       # (the launcher keeps the pointer it was built with)
+            g.alpha = alpha
+        return g(q["A"], q["A_sf"], q["X"]).view(-1, self.out_features)[:M]
+
     def forward(self, x):
         assert self.weight is None, "call quantize() first"
         shape = x.shape

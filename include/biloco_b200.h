@@ -97,6 +97,19 @@ int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_
                           void* A_codes, void* A_sf, float* a_gscale, float* alpha_out, const float* w_gscale,
                           int M, int A_rows, int K, int rule, biloco_stream_t stream);
 
+/* The same with the step in front of the linear folded in (the decode-step fusion around the path): if
+ * norm_weight_bf16 != NULL, every row is first RMS-normalised, x * rsqrt(mean(x^2) + eps) rounded to bf16, times the bf16
+ * weight, rounded to bf16 (then divided by smooth_bf16 if given), and that activation is written to Xn_bf16 [M,K]
+ * (required then; it is what the low-rank term and the quantisation consume). w_gscale / alpha_out are arrays of
+ * n_alpha (1..16) entries: one decode scale per linear that consumes this activation (q/k/v, gate/up), so the
+ * activation is quantised once for all of them.
+ * No counterpart in the reference (its layers call fake_quantize_fp4 per linear, biloco/layer.py:60, and the norm
+ * lives in the surrounding model). */
+int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_weight_bf16, float eps, const void* smooth_bf16,
+                               void* Xn_bf16, void* A_codes, void* A_sf, float* a_gscale, float* alpha_out,
+                               const float* w_gscale, int n_alpha, int M, int A_rows, int K, int rule,
+                               biloco_stream_t stream);
+
 /* Scratch bytes needed by biloco_b200_fused_linear for this problem on a device
  * with `num_sms` multiprocessors (0 = query the current device). The scratch must be zero-filled once
  * before the first call; it needs no clearing between calls (the reference's BiLoCoGemm owns z/flags/corr/cnt

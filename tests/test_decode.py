@@ -50,11 +50,13 @@ def test_decode_step_matches_fake_quant_layers_and_graph_replay():
     with torch.no_grad():
         try:
             BiLoCoLinear.forward = BiLoCoLinear.forward_fake_quant
+            model.fuse_norm_quant = False          # separate norm kernels, every linear through its own forward
             cache = model.new_cache(M, P)
             for t in range(P):
                 ref_logits = model.step(prompt[:, t], torch.tensor([t], device="cuda"), cache)
         finally:
             BiLoCoLinear.forward = fwd
+            model.fuse_norm_quant = True
             for h in hooks:
                 h.remove()
         assert torch.isfinite(ref_logits.float()).all() and len(seen) == P * len(layers)

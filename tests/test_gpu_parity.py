@@ -74,6 +74,36 @@ def test_act_quant_bit_exact(kernel, rule, M, K, rows, smooth):
         assert np.array_equal(out["X"].float().cpu().numpy(), xs)
 
 
+@pytest.mark.parametrize("M,K,smooth", [(1, 2560, False), (8, 5120, False), (32, 1024, True), (3, 256, False)])
+def test_norm_act_quant(kernel, M, K, smooth):
+    """RMSNorm folded into the quantiser launch: the normalised activation agrees with the torch composition to one bf16
+    unit in the last place (different summation order of the mean square), and codes, block scales, tensor scale and
+    the per-consumer decode scales are bit-exact for the activation the kernel itself produced."""
+    from biloco_b200 import fp4
+    g = torch.Generator(device="cuda").manual_seed(10 * M + K)
+    x = (torch.randn(M, K, device="cuda", generator=g) * 3).to(torch.bfloat16)
+    w = (torch.rand(K, device="cuda", generator=g) + 0.5).to(torch.bfloat16)
+    s = (torch.rand(K, device="cuda", generator=g) * 3 + 0.25).to(torch.bfloat16) if smooth else None
+    wg = torch.tensor([0.0123, 0.5, 2.0], device="cuda")
+    eps = 1e-6
+    out = fp4.quantize_activation(x, "mse", smooth=s, w_gscale=wg, rows=M, norm_weight=w, eps=eps)
+    xf = x.float()
+    ref = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(torch.bfloat16) * w
+    if smooth:
+        ref = ref / s
+    xn = out["X"].float()
+    ulp = torch.maximum(ref.float().abs(), torch.tensor(1e-30, device="cuda")) * 2.0 ** -7      # one bf16 ulp, at most
+    assert bool(((xn - ref.float()).abs() <= ulp * (2.0 if smooth else 1.0)).all())
+    assert float((xn != ref.float()).float().mean()) < 0.02                                      # and rarely different at all
+    codes, sf, gs = orc.nvfp4_quantize(xn.cpu().numpy(), "mse")
+    assert np.float32(out["gscale"].item()) == gs
+    assert np.array_equal(out["alpha"].cpu().numpy(), (wg.cpu().numpy() * gs).astype(np.float32))
+    assert np.array_equal(out["A"].cpu().numpy()[0][:M], codes)
+    want_sf = np.zeros(orc.nvfp4_sf_bytes(M, K), np.uint8)
+    want_sf[: orc.nvfp4_sf_bytes(M, K)] = orc.sf_swizzle(sf, K)
+    assert np.array_equal(out["A_sf"].view(torch.uint8).cpu().numpy(), want_sf)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 128, 256), (4, 256, 1024), (3, 136, 512)])
 def test_fp4_gemm_simt(kernel, lib, M, N, K):
     p = orc.random_problem(M, K, N, 8, scales="random", seed=7)
