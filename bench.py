@@ -209,6 +209,8 @@ def run_ours(args):
         _lib.load().biloco_b200_set_option(2, args.ring)
     if args.trigger >= 0:
         _lib.load().biloco_b200_set_option(3, args.trigger)
+    if args.lr_tc >= 0:
+        _lib.load().biloco_b200_set_option(4, args.lr_tc)
 
     K, N, r, M, L = args.K, args.N, args.r, args.M, args.layers
     layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank, mode=args.mode)
@@ -359,6 +361,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true", help="plain launches instead of programmatic dependent launches")
     ap.add_argument("--ring", type=int, default=0, help="pipeline stages in flight (0 = library default)")
     ap.add_argument("--trigger", type=int, default=-1, help="where a CTA lets the next launch start (-1 = library default)")
+    ap.add_argument("--lr-tc", type=int, default=-1, help="1/0: expansion on the tensor cores on/off (-1 = library default)")
     ap.add_argument("--mode", type=int, default=None, help="schedule of the fused kernel (default: the measured table)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")

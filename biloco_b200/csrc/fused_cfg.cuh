@@ -32,8 +32,9 @@ constexpr int TMEM_COLS = 256;
 constexpr int ACC_COL_STRIDE = 32;               // accumulator buffer b starts at column 32*b
 constexpr int SF_SETS = 4;                       // scale-factor column sets, used round-robin by consecutive units
 constexpr int SFA_COL = 64;                      // set q: 16 columns (4 MMAs x 4) at SFA_COL + 32*q
+constexpr int LR_D_COL = 192;                    // the tensor-core expansion's accumulators, 32 columns per segment parity
 constexpr int SFB_COL = 80;                      // set q: 16 columns at SFB_COL + 32*q
-static_assert(SFA_COL + 32 * SF_SETS <= TMEM_COLS, "scale-factor sets exceed the TMEM allocation");
+static_assert(SFA_COL + 32 * SF_SETS <= LR_D_COL && LR_D_COL + 64 <= TMEM_COLS, "scale-factor sets exceed the TMEM allocation");
 constexpr int CTRL_BYTES = 3072;
 constexpr int SMEM_BUDGET = 227 * 1024;
 constexpr uint64_t WAIT_BUDGET_NS = 200ull * 1000 * 1000;   // 200 ms per wait
@@ -45,8 +46,17 @@ constexpr uint64_t WAIT_BUDGET_NS = 200ull * 1000 * 1000;   // 200 ms per wait
 constexpr int XT_BYTES = 16384;
 constexpr int XK = XT_BYTES / 2;                 // k per pass of the z stage
 constexpr int VT_MIN_BYTES = 8192;
-constexpr int VT_MAX_BYTES = 65536;
+constexpr int VT_MAX_BYTES = 49152;
 constexpr int WORK_BYTES = XT_BYTES + VT_MIN_BYTES;       // 24 KB: the smallest work area
+// Tensor-core expansion (from LR_TC_MIN_ROWS rows): two 16 KB buffers for the +-1.0 bf16 image of 64 ranks of the tile's U signs
+// (128 columns x 128 bytes, 128-byte swizzle), per buffer the bf16 high and low parts of the matching z values
+// (MMA_N rows x 128 bytes each) and a 256-entry table byte -> eight bf16 signs.
+// Measured at K = N = 5120 (us per call, CUDA-core / tensor-core expansion, r = 512): M=4 16.4 / 17.9, M=8 21.6 / 21.3,
+// M=16 30.5 / 27.5, M=32 70.3 / 45.5; r = 1024, M=32: 126.5 / 80.2.
+constexpr int LR_TC_MIN_ROWS = 16;
+constexpr int LR_UA_BYTES = 16384;
+constexpr int LR_LUT_BYTES = 4096;
+__host__ __device__ constexpr int lr_bytes(int mma_n) { return 2 * LR_UA_BYTES + 4 * mma_n * 128 + LR_LUT_BYTES; }
 constexpr int ZR_MAX = 64;                       // ranks per chunk of the z stage (partial sums per warp in Ctrl)
 constexpr int ZS_FIRST = 4;                      // U words per segment fetched ahead of the dependency wait
 // z is staged for the expansion in chunks of zs_words(ROWS) rank words (32 ranks each): ROWS x (32*words + 4) floats
@@ -60,24 +70,24 @@ static_assert(8 * zs_stride(8) * 4 <= ZS_BYTES_SMALL && 4 * zs_stride(4) * 4 <= 
 constexpr int RED_OFF = ZS_BYTES_SMALL + 128;      // cluster mode (rows <= 8): partial sums of the peers start here,
 constexpr int RED_BYTES = WORK_BYTES - RED_OFF;    // after the z staging rows, [peer][row][128] floats
 
-// Rows <= 8 (MMA_N == 8): two CTAs fit on one SM (registers, shared memory and TMEM are all sized for it), so that
+// Launches of one or two rows: two CTAs fit on one SM (registers, shared memory and TMEM are all sized for it), so that
 // with programmatic dependent launch the next kernel of the stream is resident beside this one and has its first
 // weights in shared memory before this one has finished its dependent tail. More rows: one CTA per SM, deeper ring.
+__host__ __device__ constexpr int ctas_per_sm(int rows) { return rows <= 2 ? 2 : 1; }
 constexpr int CORESIDENT_SMEM = 113 * 1024;      // 2 x (113 KB + 1 KB reserved) = 228 KB, the SM's shared memory
 template <int MMA_N>
 struct Cfg {
     static constexpr int A_TILE_BYTES = MMA_N * KT_BYTES;
     static constexpr int STAGE_BYTES = W_TILE_BYTES + A_TILE_BYTES + 2 * SF_TILE_BYTES;
-    static constexpr int CTAS_PER_SM = MMA_N == 8 ? 2 : 1;
-    static constexpr int fixed_bytes(int vt_bytes) { return 1024 + CTRL_BYTES + XT_BYTES + vt_bytes; }
+    static constexpr int fixed_bytes(int vt_bytes) { return 1024 + CTRL_BYTES + XT_BYTES + vt_bytes; }      // (+ lr_bytes, see the launcher)
     static constexpr int stages_alone(int vt_bytes) { return (SMEM_BUDGET - fixed_bytes(vt_bytes)) / STAGE_BYTES; }
     static constexpr int stages_shared(int vt_bytes) { return (CORESIDENT_SMEM - fixed_bytes(vt_bytes)) / STAGE_BYTES; }
     static constexpr int smem_bytes(int ring, int vt_bytes) { return ring * STAGE_BYTES + fixed_bytes(vt_bytes); }
     static constexpr int STAGES = stages_alone(VT_MIN_BYTES);          // the deepest ring
     static_assert(STAGE_BYTES % 1024 == 0, "stage bases must stay 1024-byte aligned for the 128-byte swizzle");
     static_assert(STAGES >= 4 && STAGES <= 16, "stage count out of range");
-    static_assert(stages_alone(VT_MAX_BYTES) >= SF_SETS, "the ring must not be shorter than the scale-factor sets");
-    static_assert(stages_shared(VT_MIN_BYTES) >= SF_SETS || CTAS_PER_SM == 1, "the ring must not be shorter than the scale-factor sets");
+    static_assert(stages_alone(VT_MAX_BYTES + lr_bytes(MMA_N)) >= SF_SETS, "the ring must not be shorter than the scale-factor sets");
+    static_assert(stages_shared(VT_MIN_BYTES) >= SF_SETS || MMA_N != 8, "the ring must not be shorter than the scale-factor sets");
 };
 
 struct FusedParams {
@@ -104,6 +114,7 @@ struct FusedParams {
                               // dependency wait, 3 once its activation row has landed, 1 after its z stage, 2 after
                               // its first expansion (an exiting CTA counts as having done so)
     int vt_bytes;             // shared memory for the z stage's sign words (VT_MIN_BYTES .. VT_MAX_BYTES)
+    int lr_tc;                // expansion on the tensor cores (the launcher has added lr_bytes(MMA_N) behind the sign words)
     int nsl;                  // z stage: rank slices per activation row; work item (row m, slice s) = m*nsl + s goes to
                               // CTA (m*nsl + s) % G
     int cluster;              // > 1: a tile belongs to a cluster of this many CTAs (partial sums through DSMEM)
@@ -123,6 +134,8 @@ struct Ctrl {   // lives in shared memory after the stages
     float zall[8];                // z stage: per-warp partial sums of sum x
     uint64_t red_bar;             // cluster mode, finisher CTA: the other CTAs' partial sums are in this CTA's smem
     uint64_t x_bar;               // z stage: the activation row has landed (bulk copy)
+    uint64_t lr_free[2];          // tensor-core expansion: the MMAs that read operand buffer b have completed
+    uint64_t lr_done;             // tensor-core expansion: the segment's last MMA has completed
     uint64_t red_free;            // cluster mode, other CTAs: the finisher's z stage is over, its work area may be written
     uint32_t tmem_base;
     volatile int abort;

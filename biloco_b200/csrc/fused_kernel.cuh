@@ -20,7 +20,7 @@ __device__ __forceinline__ void tmem_ld_acc(uint32_t taddr, float* v) {
 }
 
 template <int MMA_N, int ROWS>
-__global__ void __launch_bounds__(NUM_THREADS, Cfg<MMA_N>::CTAS_PER_SM)
+__global__ void __launch_bounds__(NUM_THREADS, ctas_per_sm(ROWS))
 fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ FusedParams p) {
     static_assert(ROWS <= MMA_N, "the tensor-core tile must cover the rows");
@@ -71,6 +71,9 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         mbar_init(smem_u32(&ctrl->red_bar), p.cluster > 1 ? (uint32_t)(p.cluster - 1) : 1u);
         mbar_init(smem_u32(&ctrl->red_free), 1);
         mbar_init(smem_u32(&ctrl->x_bar), 1);
+        mbar_init(smem_u32(&ctrl->lr_free[0]), 1);
+        mbar_init(smem_u32(&ctrl->lr_free[1]), 1);
+        mbar_init(smem_u32(&ctrl->lr_done), 1);
         ctrl->abort = 0;
         fence_mbar_init();
         prefetch_tmap(&tmW);
@@ -217,6 +220,23 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         // ================= z stage, expansion, epilogue (128 threads) =================
         float* zs = reinterpret_cast<float*>(work);
         const bool owner_mode = (p.mode & 0xff) == 4;
+        // tensor-core expansion: operand buffers behind the sign words; table byte -> eight +-1.0 bf16 (bit set = +1)
+        uint8_t* lr = work + XT_BYTES + p.vt_bytes;
+        int gchunk = 0, lrseg = 0;
+        if constexpr (ROWS >= LR_TC_MIN_ROWS) {
+            if (p.lr_tc) {
+                uint4* lut = reinterpret_cast<uint4*>(lr + 2 * LR_UA_BYTES + 4 * MMA_N * 128);
+#pragma unroll
+                for (int e = tid; e < 256; e += EPI_THREADS) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        w[i] = (((e >> (2 * i)) & 1) ? 0x3F80u : 0xBF80u) | ((((e >> (2 * i + 1)) & 1) ? 0x3F80u : 0xBF80u) << 16);
+                    lut[e] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                // (made visible to the other epilogue threads by the barriers of the z stage)
+            }
+        }
 
         // U words of the first two segments' first ranks: requested before anything else, so that they do not queue
         // behind the weight stream later
@@ -273,7 +293,26 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 uint32_t uw_sel[ZS_FIRST];
 #pragma unroll
                 for (int w = 0; w < ZS_FIRST; ++w) uw_sel[w] = (seg & 1) ? uw_first[1][w] : uw_first[0][w];
-                if (!expand_z<ROWS>(corr, p, ctrl, p.zbuf, ucol, si.w0, si.w1, zs, tid, uw_sel, seg < 2, phase)) break;
+                bool on_tc = false;
+                if constexpr (ROWS >= LR_TC_MIN_ROWS) on_tc = p.lr_tc != 0;
+                if (on_tc) {
+                    if constexpr (ROWS >= LR_TC_MIN_ROWS) {
+                        const uint32_t d2 = tmem + LR_D_COL + 32u * (uint32_t)(lrseg & 1);
+                        if (!expand_z_tc<ROWS, MMA_N>(p, ctrl, lr, p.zbuf, ucol, si.w0, si.w1, tid, phase, d2, gchunk)) break;
+                        // the segment's sums: wait for its last MMA, read the accumulator (lane = this thread's column)
+                        if (!wait_bar(smem_u32(&ctrl->lr_done), lrseg & 1, ctrl, p.status, p.epoch, ST_ACC_FULL, warp)) break;
+                        tc_fence_after_sync();
+                        float c2[MMA_N];
+                        tmem_ld_acc<MMA_N>(d2 + ((uint32_t)(warp * 32) << 16), c2);
+                        tc_wait_ld();
+                        tc_fence_before_sync();
+#pragma unroll
+                        for (int m = 0; m < ROWS; ++m) corr[m] = c2[m];
+                        ++lrseg;
+                    }
+                } else if (!expand_z<ROWS>(corr, p, ctrl, p.zbuf, ucol, si.w0, si.w1, zs, tid, uw_sel, seg < 2, phase)) {
+                    break;
+                }
                 if (tid == 0 && p.stamps && seg == 0) p.stamps[(size_t)cta * STAMP_WORDS + 3] = globaltimer_ns();
             }
             if (p.trigger == 2 && tid == 0 && seg == 0) griddep_launch_dependents();

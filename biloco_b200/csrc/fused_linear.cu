@@ -121,6 +121,7 @@ static int g_use_pdl = 1;                        // launch with programmatic str
 static unsigned long long* g_stamps = nullptr;   // debug time-stamp buffer for subsequent launches (or null)
 static size_t g_stamps_bytes = 0;
 static size_t g_stamps_seq = 0;
+static int g_lr_tc = 1;                          // expansion on the tensor cores where the kernel supports it
 static int g_trigger = -1;                        // < 0: chosen per launch (see launch())
 
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
@@ -212,20 +213,24 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
         if (vt > VT_MAX_BYTES) vt = VT_MAX_BYTES;
     }
     p.vt_bytes = vt;
+    // expansion on the tensor cores from 16 rows up (below that the CUDA-core form is as fast); its operand buffers sit
+    // behind the sign words
+    p.lr_tc = (ROWS >= LR_TC_MIN_ROWS && p.R > 0 && g_lr_tc) ? 1 : 0;
+    const int extra = p.lr_tc ? lr_bytes(MMA_N) : 0;
     // where a CTA lets the next launch of the stream start (measured at K = N = 5120: once the activation row has
     // landed for the cluster schedule, straight after set-up otherwise)
     p.trigger = g_trigger >= 0 ? g_trigger : (p.cluster > 1 ? 3 : 0);
     // Ring depth decides how many CTAs share an SM: with the short ring the next launch of the stream moves in beside
     // this one (only useful when launches overlap, i.e. with programmatic dependent launch).
-    int ring = C::stages_alone(vt);
+    int ring = C::stages_alone(vt + extra);
     if (g_ring) ring = g_ring < ring ? g_ring : ring;
-    else if (C::CTAS_PER_SM == 2 && g_use_pdl && C::stages_shared(vt) >= SF_SETS) ring = C::stages_shared(vt);
+    else if (ctas_per_sm(ROWS) == 2 && g_use_pdl && C::stages_shared(vt + extra) >= SF_SETS) ring = C::stages_shared(vt + extra);
     if (ring < SF_SETS) ring = SF_SETS;
     p.ring = ring;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.G);
     cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = (size_t)C::smem_bytes(ring, vt);
+    cfg.dynamicSmemBytes = (size_t)C::smem_bytes(ring, vt + extra);
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -478,6 +483,7 @@ extern "C" int biloco_internal_use_pdl() { return g_use_pdl; }
 extern "C" int biloco_b200_set_option(int option, int value) {
     if (option == BILOCO_OPT_PDL) { g_use_pdl = value ? 1 : 0; return BILOCO_OK; }
     if (option == BILOCO_OPT_TRIGGER) { g_trigger = value; return BILOCO_OK; }
+    if (option == BILOCO_OPT_LR_TC) { g_lr_tc = value ? 1 : 0; return BILOCO_OK; }
     if (option == BILOCO_OPT_RING) { g_ring = value <= 0 ? 0 : value; return BILOCO_OK; }
     return BILOCO_ERR_MODE;
 }

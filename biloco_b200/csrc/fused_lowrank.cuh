@@ -342,4 +342,110 @@ __device__ __forceinline__ bool expand_z(float (&corr)[ROWS], const FusedParams&
     return good;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Expansion on the tensor cores (from LR_TC_MIN_ROWS activation rows): corr[n, m] = sum_i sign(U[i, n]) z[m, i] is a small GEMM with the tile's
+// 128 columns as MMA M, the activation rows as MMA N and the ranks as K. Per chunk of 64 ranks the epilogue threads
+//   * write the +-1.0 bf16 image of the chunk's U signs (thread = column; 8 table look-ups and 8 16-byte stores),
+//   * poll the chunk's z values (validity mark as in expand_z) and write them as TWO bf16 operands, high part and
+//     rounding remainder (z = hi + lo to 2^-17 relative), so that the products are exact and the sum is an fp32 sum,
+//   * and one thread issues 4 x 2 tcgen05.mma.kind::f16 (K = 16 each) into a TMEM accumulator of its own.
+// The sign image does not depend on z: it is written while z is still on its way. CUDA-core cost per column and 64
+// ranks: about 60 issue slots whatever the number of rows, against 64 * rows multiply-adds.
+// Operand buffers are double-buffered across chunks and segments (gchunk counts chunks since kernel start).
+template <int ROWS, int MMA_N>
+__device__ __forceinline__ bool expand_z_tc(const FusedParams& p, Ctrl* ctrl, uint8_t* lr, const float* zb, const int32_t* ucol, int w0, int w1,
+                                            int tid, uint32_t phase, uint32_t d_tmem, int& gchunk) {
+    constexpr int ZB = MMA_N * 128;                                   // bytes of one z operand (MMA_N rows x 64 bf16)
+    constexpr int NPIECE = (MMA_N * 8 + EPI_THREADS - 1) / EPI_THREADS;  // 16-byte pieces (8 ranks of one row) per thread
+    constexpr uint32_t idesc = make_idesc_bf16(TILE_N, MMA_N);
+    const uint4* lut = reinterpret_cast<const uint4*>(lr + 2 * LR_UA_BYTES + 4 * ZB);
+    const int nch = (w1 - w0 + 1) >> 1;
+    bool good = true;
+#pragma unroll 1
+    for (int ci = 0; ci < nch; ++ci, ++gchunk) {
+        const int c0 = w0 + 2 * ci;
+        const int buf = gchunk & 1;
+        const uint32_t uw0 = (uint32_t)ucol[c0];
+        const uint32_t uw1 = (c0 + 1 < w1) ? (uint32_t)ucol[c0 + 1] : 0u;          // (a missing word meets z = 0)
+        if (gchunk >= 2 && !wait_bar(smem_u32(&ctrl->lr_free[buf]), ((gchunk >> 1) - 1) & 1, ctrl, p.status, p.epoch, ST_ACC_EMPTY, 0))
+            good = false;
+        // sign image of this thread's column: 64 ranks = 128 bytes, 16-byte chunk c of row r at chunk c ^ (r & 7)
+        {
+            uint8_t* row = lr + buf * LR_UA_BYTES + (tid >> 3) * 1024 + (tid & 7) * 128;
+#pragma unroll
+            for (int pc = 0; pc < 8; ++pc) {
+                const uint32_t byte = ((pc < 4 ? uw0 : uw1) >> (8 * (pc & 3))) & 0xFFu;
+                *reinterpret_cast<uint4*>(row + ((pc ^ (tid & 7)) * 16)) = lut[byte];
+            }
+        }
+        // z pieces: (row m, ranks 8 pc .. 8 pc + 7 of the chunk), polled until every needed value carries this launch's mark
+        uint8_t* zh = lr + 2 * LR_UA_BYTES + buf * 2 * ZB;
+#pragma unroll
+        for (int q = 0; q < NPIECE; ++q) {
+            const int idx = tid + q * EPI_THREADS;
+            if (idx < MMA_N * 8) {
+                const int m = idx >> 3, pc = idx & 7;
+                const int e0 = 32 * c0 + 8 * pc;                              // first rank of the piece
+                uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
+                if (m < p.M && c0 + (pc >> 2) < w1 && e0 < p.R) {
+                    const float* src = zb + (size_t)m * p.Rpad + e0;
+                    uint4 a, b;
+                    uint64_t t0 = 0;
+#pragma unroll 1
+                    for (uint32_t it = 0;; ++it) {
+                        a = ld_volatile_v4(src);
+                        b = ld_volatile_v4(src + 4);
+                        uint32_t bad = 0;
+                        const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) bad |= (e0 + i < p.R) ? (v[i] ^ phase) : 0u;
+                        if (!(bad & 1u)) break;
+                        if ((it & 15u) == 15u) {
+                            if (ctrl->abort) { good = false; break; }
+                            const uint64_t now = globaltimer_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, p.status, p.epoch, ST_Z, 0); good = false; break; }
+                        }
+                    }
+                    const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+                    uint32_t h[4], l[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float z0 = (e0 + 2 * i < p.R) ? __uint_as_float(v[2 * i] & ~1u) : 0.f;
+                        float z1 = (e0 + 2 * i + 1 < p.R) ? __uint_as_float(v[2 * i + 1] & ~1u) : 0.f;
+                        const __nv_bfloat16 h0 = __float2bfloat16_rn(z0), h1 = __float2bfloat16_rn(z1);
+                        const __nv_bfloat16 l0 = __float2bfloat16_rn(z0 - __bfloat162float(h0));
+                        const __nv_bfloat16 l1 = __float2bfloat16_rn(z1 - __bfloat162float(h1));
+                        h[i] = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+                        l[i] = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+                    }
+                    hi = make_uint4(h[0], h[1], h[2], h[3]);
+                    lo = make_uint4(l[0], l[1], l[2], l[3]);
+                }
+                const int off = (m >> 3) * 1024 + (m & 7) * 128 + ((pc ^ (m & 7)) * 16);
+                *reinterpret_cast<uint4*>(zh + off) = hi;
+                *reinterpret_cast<uint4*>(zh + ZB + off) = lo;
+            }
+        }
+        fence_proxy_async();                                 // the operands were written with ordinary stores
+        named_bar_sync(1, EPI_THREADS);
+        if (ctrl->abort) { good = false; }
+        if (tid == 0) {
+            tc_fence_after_sync();
+            const uint64_t ad = make_smem_desc(smem_u32(lr + buf * LR_UA_BYTES), 1024, 2);
+            const uint64_t hd = make_smem_desc(smem_u32(zh), 1024, 2);
+            const uint64_t ld = make_smem_desc(smem_u32(zh + ZB), 1024, 2);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {                    // 16 ranks = 32 bytes along the swizzled row: +2 in the address field
+                tc_mma_bf16(d_tmem, ad + 2 * k, hd + 2 * k, idesc, (ci > 0 || k > 0) ? 1u : 0u);
+                tc_mma_bf16(d_tmem, ad + 2 * k, ld + 2 * k, idesc, 1u);
+            }
+            tc_commit(smem_u32(&ctrl->lr_free[buf]));
+            if (ci == nch - 1) tc_commit(smem_u32(&ctrl->lr_done));
+        }
+        if (!good) { ++gchunk; break; }
+    }
+    return good;
+}
+
 }  // namespace biloco

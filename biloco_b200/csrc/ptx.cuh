@@ -135,6 +135,15 @@ __device__ __forceinline__ void tc_mma_nvf4(uint32_t d_tmem, uint64_t a_desc, ui
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
         : "memory");
 }
+// D[tmem] (+)= A[smem] * B[smem]^T, bf16 operands, fp32 accumulation (kind::f16): the low-rank expansion.
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // mbarrier arrives once all tcgen05 operations issued so far by this thread have completed.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -189,6 +198,12 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 // [15] A major, [16] B major (0 = K), [17,23) N>>3, [23] scale format (0 = UE4M3), [24,29) M>>4.
 __host__ __device__ constexpr uint32_t make_idesc_nvf4(int mma_m, int mma_n) {
     return (1u << 7) | (1u << 10) | ((uint32_t)(mma_n >> 3) << 17) | (0u << 23) | ((uint32_t)(mma_m >> 4) << 24);
+}
+
+// Instruction descriptor of kind::f16 with bf16 operands and an fp32 accumulator: [4,6) D format (1 = f32), [7,10) A
+// format, [10,13) B format (1 = bf16), [15]/[16] A/B major (0 = K), [17,23) N>>3, [24,29) M>>4.
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int mma_m, int mma_n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(mma_n >> 3) << 17) | ((uint32_t)(mma_m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------------------------------------------------

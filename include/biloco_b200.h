@@ -212,6 +212,9 @@ int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t
  * -1 (default) chosen by the library, 0 after set-up, 4 after its dependency wait, 3 once its activation row has
  * landed, 1 after its z stage, 2 after its first expansion. Tuning aid. */
 #define BILOCO_OPT_TRIGGER 3
+/* 1 (default): from 16 activation rows up the expansion of z through the U signs runs on the tensor cores (bf16 sign
+ * image x z split into two bf16 parts, fp32 accumulation); 0: on the CUDA cores for every row count. */
+#define BILOCO_OPT_LR_TC 4
 int biloco_b200_set_option(int option, int value);
 
 /* Debug aid: while a device buffer is registered here, every fused launch of this process writes 16 uint64
