@@ -16,9 +16,8 @@ namespace biloco {
 // function: the work split, the coefficients, the sign words of the first chunk (cp.async, made visible with a
 // barrier). After the wait one thread requests the activation row with a single bulk copy and all threads wait on its
 // mbarrier; nothing else stands between the wait and the arithmetic.
-// Arithmetic: warp w takes the w-th eighth of the pass's 32-bit sign words, one word per lane; a lane unpacks the 32
-// activations of its word once and, for every rank, adds them under predicates taken from the sign bits (four
-// independent accumulators in flight). One shuffle reduction per run of up to six ranks (z_reduce_run), per-warp partial
+// Arithmetic: the eight warps share (run of ranks) x (block of 32 sign words) tasks, one word per lane; a lane unpacks
+// the activations of its word and, for every rank of the run, adds them under predicates taken from the sign bits. One shuffle reduction per run of up to six ranks (z_reduce_run), per-warp partial
 // sums in shared memory, one combine per chunk: z = S * (2 * sum_{sign=+1} x - sum x).
 // The CUDA-core code here is bound by instruction issue, not by latency (measured: the same cycles cold and warm,
 // alone or beside spinning warps), so what matters is the instruction count per element and an even spread over warps.
@@ -150,7 +149,7 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
 #pragma unroll 1
             for (int k0 = 0; k0 < p.K; k0 += XK) {
                 const int kc = (p.K - k0) < XK ? (p.K - k0) : XK;       // multiple of 256
-                const int words = kc >> 5, wpw = (words + Z_WARPS - 1) / Z_WARPS;     // at most 32 words per warp
+                const int words = kc >> 5;
                 if (waited) named_bar_sync(3, Z_THREADS);               // the previous pass has been consumed
                 z_issue_v(p, work, c0, nrc, k0, kc, zt);
                 cp_async_commit_wait_all();
@@ -177,12 +176,19 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
                 if (p.trigger == 3 && zt == 0) griddep_launch_dependents();
 
                 if (zt == 224 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 2] = globaltimer_ns();
-                const int w = zw * wpw + lane;
-                const bool active = lane < wpw && w < words;
-                const uint4* xs = reinterpret_cast<const uint4*>(work) + (active ? w : 0) * 4;     // 64 bytes = 32 bf16 of word w
+                // warp tasks = (run of up to ZRUN ranks) x (block of sign words), dealt round-robin to the eight warps: every
+                // task has all its lanes busy (up to the last, partial block) whatever the number of ranks
+                // (with one or two runs the words are dealt evenly to all eight warps instead: measured faster than full blocks)
+                const int nruns = (nrc + ZRUN - 1) / ZRUN;
+                const int bs = nruns <= 2 ? (words + Z_WARPS - 1) / Z_WARPS : 32;      // sign words per block (at most 32)
+                const int nwb = (words + bs - 1) / bs;
 #pragma unroll 1
-                for (int q0 = 0; q0 < nrc; q0 += ZRUN) {                // runs of up to six ranks
-                    const int nq = nrc - q0;
+                for (int task = zw; task < nruns * nwb; task += Z_WARPS) {
+                    const int run = task / nwb, wb = task - run * nwb;
+                    const int q0 = run * ZRUN, nq = nrc - q0;
+                    const int w = wb * bs + lane;
+                    const bool active = lane < bs && w < words;
+                    const uint4* xs = reinterpret_cast<const uint4*>(work) + (active ? w : 0) * 4;     // 64 bytes = 32 bf16 of word w
                     float sums[ZRUN];
 #pragma unroll
                     for (int q = 0; q < ZRUN; ++q) sums[q] = 0.f;
@@ -197,7 +203,7 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
                     const float tot = z_reduce_run(sums, lane);
                     const int rl = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
                     if ((lane & 3) == 0 && rl < ZRUN && q0 + rl < nrc) ctrl->zred[zw][q0 + rl] += tot;
-                    if (q0 == 0) {
+                    if (run == 0) {
 #pragma unroll
                         for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
                         if (lane == 0) ctrl->zall[zw] += plain;
