@@ -23,12 +23,12 @@ IMPLEMENTED_MODES = (2, 4, 5)
 
 # Fastest implemented mode per (M, rank) on B200 at K = N = 5120, from `bench.py --M .. --r .. --mode ..` (us per call,
 # 64 distinct layers per step, mode 2 / mode 5; M = 16, 32: mode 2 only, expansion on the tensor cores):
-#   r = 128 : M=1 10.7/9.2   M=2 11.6/9.5   M=4 12.8/12.3  M=8 14.4/14.4  M=16 16.9  M=32 22.8
-#   r = 256 : M=1 11.4/9.4   M=2 12.6/10.3  M=4 14.4/14.2  M=8 17.3/17.0  M=16 20.0  M=32 28.7
-#   r = 512 : M=1 12.4/10.6  M=2 15.2/12.7  M=4 17.0/16.4  M=8 22.2/21.7  M=16 27.5  M=32 45.6
-#   r = 1024: M=1 15.0/14.0  M=2 18.6/19.2  M=4 22.2/22.6  M=8 32.4/34.6  M=16 44.4  M=32 80.0
+#   r = 128 : M=1 11.1/9.2   M=2 11.6/9.7   M=4 12.9/12.4  M=8 14.7/14.6  M=16 16.5  M=32 21.4
+#   r = 256 : M=1 11.6/9.6   M=2 12.5/10.6  M=4 14.6/14.3  M=8 16.8/16.2  M=16 19.3  M=32 25.6
+#   r = 512 : M=1 12.6/10.7  M=2 15.1/13.0  M=4 16.6/15.6  M=8 21.5/20.2  M=16 25.1  M=32 39.4
+#   r = 1024: M=1 15.1/14.2  M=2 17.6/18.3  M=4 21.4/21.2  M=8 29.9/31.5  M=16 38.9  M=32 67.6
 # Mode 5 does not take M > 8; mode 4 loses everywhere. Ranks below 128 were not measured and follow r = 128.
-_MODE2_WINS = {(2, 1024), (4, 1024), (8, 1024)}
+_MODE2_WINS = {(2, 1024), (8, 1024)}
 DEFAULT_MODE = {M: {r: (2 if (M > 8 or (M, r) in _MODE2_WINS) else 5) for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
 
 def pack_signs(signs: torch.Tensor) -> torch.Tensor:
