@@ -52,7 +52,13 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     uint32_t seq = 0;         // (thread 0) launches completed on this scratch before this one
 
     // ---------------- set-up ----------------
-    if (tid == 0 && p.stamps) { p.stamps[(size_t)cta * STAMP_WORDS + 10] = globaltimer_ns(); p.stamps[(size_t)cta * STAMP_WORDS + 1] = clock64(); }
+    if (tid == 0 && p.stamps) {
+        uint32_t smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        p.stamps[(size_t)cta * STAMP_WORDS + 10] = globaltimer_ns();
+        p.stamps[(size_t)cta * STAMP_WORDS + 1] = clock64();
+        p.stamps[(size_t)cta * STAMP_WORDS + 7] = smid;
+    }
     if (tid == FIRST_SF_WARP * 32) {
 #pragma unroll 1
         for (int s = 0; s < ring; ++s) {

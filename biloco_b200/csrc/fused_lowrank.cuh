@@ -209,7 +209,6 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
                         if (lane == 0) ctrl->zall[zw] += plain;
                     }
                 }
-                if (zt == 224 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 7] = globaltimer_ns();
                 if (zt == 0 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 12] = globaltimer_ns();
             }
             named_bar_sync(3, Z_THREADS);
