@@ -218,7 +218,7 @@ def run_ours(args):
 
     def step_device():
         for ly in layers:
-            ly["out"] = ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], ly["x"])
+            ly["out"] = ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], ly["x"], A_rec=ly["q"].get("A_rec"))
 
     # ---- device-resident arm: one CUDA graph per step -------------------------------------------------
     side = torch.cuda.Stream()
@@ -283,7 +283,7 @@ def run_ours(args):
         x_dev.copy_(x_host, non_blocking=True)
         for i, ly in enumerate(layers):
             fp4.quantize_activation(x_dev[i], "mse", w_gscale=ly["w_gs"], rows=M, out=ly["q"])
-            ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], x_dev[i], out=y_dev[i])
+            ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], x_dev[i], out=y_dev[i], A_rec=ly["q"].get("A_rec"))
         y_host.copy_(y_dev, non_blocking=True)
 
     with torch.cuda.stream(side):

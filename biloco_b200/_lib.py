@@ -23,7 +23,9 @@ SIGNATURES = {
     "biloco_b200_binary_expand": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "biloco_b200_pack_u_col32": (_i, [_vp, _vp, _i, _i, _vp]),
     "biloco_b200_act_quant": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
-    "biloco_b200_norm_act_quant": (_i, [_vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "biloco_b200_norm_act_quant": (_i, [_vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "biloco_b200_act_rec_bytes": (_sz, [_i, _i]),
+    "biloco_b200_fused_linear_rec": (_i, [_vp] * 14 + [_sz] + [_i] * 7 + [_vp]),
     "biloco_b200_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "biloco_b200_scratch_head_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "biloco_b200_mode_supported": (_i, [_i, _i, _i, _i, _i, _i]),

@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
                                                               uint8_t* __restrict__ sf, float* __restrict__ a_gscale,
                                                               float* __restrict__ alpha_out, const float* __restrict__ w_gscale,
                                                               int M, int A_rows, int K, int rule, int given_scale, float target,
-                                                              int csize, const __nv_bfloat16* __restrict__ norm_w, float eps, int n_alpha) {
+                                                              int csize, const __nv_bfloat16* __restrict__ norm_w, float eps, int n_alpha,
+                                                              uint8_t* __restrict__ rec) {
     const int kblocks = K >> 4;
     __shared__ float red[Q_THREADS / 32];
     __shared__ float gs_sh;
@@ -192,6 +193,22 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
             const int row = M + i / kgroups, kg = i % kgroups;
             *reinterpret_cast<uint32_t*>(sf + ((size_t)(row >> 7) * kgroups + kg) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4) = 0u;
         }
+        // the per-k-tile record for the fused kernel, if asked for: [tile: mma_n rows x 128 B | four scale atoms]; rows M.. zero
+        if (rec) {
+            const int mma_n = M <= 8 ? 8 : (M <= 16 ? 16 : 32), nkt = K >> 8;
+            const int rec_bytes = mma_n * 128 + 2048;
+            const int tile_pad = (mma_n - M) * 8;                         // 16-byte chunks of the rows M .. mma_n-1 of one tile
+            for (int i = blockIdx.x * Q_THREADS + threadIdx.x; i < nkt * tile_pad; i += gridDim.x * Q_THREADS) {
+                const int kt = i / tile_pad, c = i - kt * tile_pad;
+                *reinterpret_cast<uint4*>(rec + (size_t)kt * rec_bytes + M * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            const int sf_pad = (128 - M) * 4;                             // 4-byte groups of the rows M .. 127 of one k-tile's atoms
+            for (int i = blockIdx.x * Q_THREADS + threadIdx.x; i < nkt * sf_pad; i += gridDim.x * Q_THREADS) {
+                const int kt = i / sf_pad, r = i - kt * sf_pad;
+                const int row = M + (r >> 2), a = r & 3;
+                *reinterpret_cast<uint32_t*>(rec + (size_t)kt * rec_bytes + mma_n * 128 + a * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4) = 0u;
+            }
+        }
         const int ncode = (A_rows - M) * (K >> 4);                       // 64-bit vectors of codes
         uint2* cz = reinterpret_cast<uint2*>(codes + (size_t)M * (K >> 1));
         for (int i = blockIdx.x * Q_THREADS + threadIdx.x; i < ncode; i += gridDim.x * Q_THREADS) cz[i] = make_uint2(0u, 0u);
@@ -243,14 +260,22 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
         if ((j & 7) == 0) *reinterpret_cast<uint32_t*>(codes + (size_t)row * (K >> 1) + kb * 8 + (j >> 3) * 4) = w;
         if (j == 0)
             sf[((size_t)(row >> 7) * (kblocks >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3)] = sfb;
+        if (rec) {      // the same codes and scale where the fused kernel's stage wants them (128-byte swizzle: chunk c of row r at c ^ (r & 7))
+            const int mma_n = M <= 8 ? 8 : (M <= 16 ? 16 : 32);
+            uint8_t* rk = rec + (size_t)(kb >> 4) * (mma_n * 128 + 2048);
+            const int b = (kb & 15) * 8 + (j >> 3) * 4;                   // byte of the word within the tile row
+            if ((j & 7) == 0) *reinterpret_cast<uint32_t*>(rk + row * 128 + (((b >> 4) ^ (row & 7)) << 4) + (b & 15)) = w;
+            if (j == 0) rk[mma_n * 128 + ((kb >> 2) & 3) * 512 + (row & 31) * 16 + ((row >> 5) & 3) * 4 + (kb & 3)] = sfb;
+        }
     }
 }
 
 }  // namespace
 
 static int launch_act_quant(const void* X_bf16, const void* norm_w, float eps, const void* smooth_bf16, void* Xs_bf16, void* A_codes,
-                            void* A_sf, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M, int A_rows,
-                            int K, int rule, biloco_stream_t stream) {
+                            void* A_sf, void* A_rec, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M,
+                            int A_rows, int K, int rule, biloco_stream_t stream) {
+    if (A_rec && (M > 32 || (K % 256) != 0 || ((uintptr_t)A_rec & 15))) return BILOCO_ERR_SHAPE;
     if (!X_bf16 || !A_codes || !A_sf || !a_gscale) return BILOCO_ERR_NULL;
     if (norm_w && !Xs_bf16) return BILOCO_ERR_NULL;
     if (n_alpha < 1 || n_alpha > 16) return BILOCO_ERR_SHAPE;
@@ -291,7 +316,7 @@ static int launch_act_quant(const void* X_bf16, const void* norm_w, float eps, c
     cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, act_quant_kernel, (const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16,
                            (__nv_bfloat16*)Xs_bf16, (uint8_t*)A_codes, (uint8_t*)A_sf, a_gscale, alpha_out, w_gscale, M, A_rows, K,
-                           rule, given_scale ? 1 : 0, target, csize, (const __nv_bfloat16*)norm_w, eps, n_alpha) != cudaSuccess)
+                           rule, given_scale ? 1 : 0, target, csize, (const __nv_bfloat16*)norm_w, eps, n_alpha, (uint8_t*)A_rec) != cudaSuccess)
         return BILOCO_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
@@ -299,14 +324,14 @@ static int launch_act_quant(const void* X_bf16, const void* norm_w, float eps, c
 extern "C" int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_bf16, void* A_codes, void* A_sf,
                                      float* a_gscale, float* alpha_out, const float* w_gscale, int M, int A_rows, int K,
                                      int rule, biloco_stream_t stream) {
-    return launch_act_quant(X_bf16, nullptr, 0.f, smooth_bf16, Xs_bf16, A_codes, A_sf, a_gscale, alpha_out, w_gscale, 1, M, A_rows, K,
-                            rule, stream);
+    return launch_act_quant(X_bf16, nullptr, 0.f, smooth_bf16, Xs_bf16, A_codes, A_sf, nullptr, a_gscale, alpha_out, w_gscale, 1, M, A_rows,
+                            K, rule, stream);
 }
 
 extern "C" int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_weight_bf16, float eps, const void* smooth_bf16,
-                                          void* Xn_bf16, void* A_codes, void* A_sf, float* a_gscale, float* alpha_out,
+                                          void* Xn_bf16, void* A_codes, void* A_sf, void* A_rec, float* a_gscale, float* alpha_out,
                                           const float* w_gscale, int n_alpha, int M, int A_rows, int K, int rule,
                                           biloco_stream_t stream) {
-    return launch_act_quant(X_bf16, norm_weight_bf16, eps, smooth_bf16, Xn_bf16, A_codes, A_sf, a_gscale, alpha_out, w_gscale, n_alpha,
-                            M, A_rows, K, rule, stream);
+    return launch_act_quant(X_bf16, norm_weight_bf16, eps, smooth_bf16, Xn_bf16, A_codes, A_sf, A_rec, a_gscale, alpha_out, w_gscale,
+                            n_alpha, M, A_rows, K, rule, stream);
 }

@@ -18,7 +18,7 @@ constexpr int SF_TILE_BYTES = 4 * 512;           // four 128x4 atoms
 constexpr int EPI_THREADS = 128;
 // Warp roles: 0-3 z stage / expansion / epilogue; 4-7 feeders: lane 0 of each requests the weight and activation
 // copies of every fourth unit, and the whole warp moves the scale factors of every unit from shared memory into its
-// 32-lane TMEM quadrant; 8-11 second half of the z stage; 12 MMA issue.
+// 32-lane TMEM quadrant; 8-11 second half of the z stage; 12 MMA issue; 13 refills.
 // Bulk copies issued by one thread complete one after the other (about 0.4 us each for anything up to 16 KB,
 // measured), copies issued by different warps overlap: several requesting warps are what lets one CTA pull its
 // share of the weight stream at HBM speed.
@@ -26,7 +26,8 @@ constexpr int PRODUCERS = 4;
 constexpr int FIRST_SF_WARP = 4;                 // 4 warps, one per 32-lane TMEM quadrant (warp id % 4)
 constexpr int FIRST_Z_WARP = 8;                  // 4 warps that only take part in the z stage
 constexpr int MMA_WARP = 12;
-constexpr int NUM_THREADS = (MMA_WARP + 1) * 32;
+constexpr int REFILL_WARP = 13;                 // re-requests stages as they come free (lanes 0..PRODUCERS-1)
+constexpr int NUM_THREADS = (REFILL_WARP + 1) * 32;
 static_assert(FIRST_SF_WARP % 4 == 0, "scale-factor warp q must own TMEM quadrant q");
 constexpr int TMEM_COLS = 256;
 constexpr int ACC_COL_STRIDE = 32;               // accumulator buffer b starts at column 32*b
@@ -94,6 +95,7 @@ struct FusedParams {
     const uint8_t* W_tiled;   // unit-contiguous weights (see biloco_b200_tile_weights) or null: row-major codes via TMA
     const uint8_t* W_sf;
     const uint8_t* A_sf;
+    const uint8_t* A_rec;     // per k-tile [activation tile as it sits in a stage | its four scale atoms] (one copy per unit), or null
     const float* alpha;
     const __nv_bfloat16* X;
     const uint8_t* Vp;
@@ -167,6 +169,21 @@ __device__ __noinline__ bool wait_bar(uint32_t bar, uint32_t parity, Ctrl* ctrl,
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 3u) == 3u) {          // (a try may have been parked for up to a millisecond)
+            if (ctrl->abort) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_BUDGET_NS) { fail(ctrl, status, epoch, code, role); return false; }
+        }
+    }
+}
+
+// Bounded mbarrier wait by polling (mbarrier.test_wait): for the lanes of the refill warp, which wait on different barriers.
+__device__ __noinline__ bool poll_bar(uint32_t bar, uint32_t parity, Ctrl* ctrl, int32_t* status, uint32_t epoch, int code, int role) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        if (mbar_test_wait(bar, parity)) return true;
+        __nanosleep(32);
+        if ((it & 63u) == 63u) {
             if (ctrl->abort) return false;
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;

@@ -97,6 +97,37 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
     if (p.trigger == 0) griddep_launch_dependents();   // the next kernel of the stream may start its set-up and weight prefetch
     if (tid == 0 && p.stamps) p.stamps[(size_t)cta * STAMP_WORDS + 0] = globaltimer_ns();
 
+    // copy requests of unit i (in processing order) into stage i % ring
+    const int nunits = u1 - u0;
+    const int head = SegWalk(u0, u1, p.nkt).head;     // units [head, u1) are processed first, then [u0, head)
+    const int nhead = u1 - head;
+    auto issue_w = [&](int i) {
+        const int u = i < nhead ? head + i : u0 + (i - nhead);
+        const uint32_t sbase = stage0 + (i % ring) * C::STAGE_BYTES;
+        const uint32_t bar = smem_u32(&ctrl->full[i % ring]);
+        mbar_arrive_expect_tx(bar, W_TILE_BYTES + C::A_TILE_BYTES + 2 * SF_TILE_BYTES);
+        if (p.W_tiled) {
+            // one contiguous 18 KB record per unit: pre-swizzled codes followed by the scale atoms
+            bulk_load(sbase, p.W_tiled + (size_t)u * (W_TILE_BYTES + SF_TILE_BYTES), W_TILE_BYTES + SF_TILE_BYTES, bar);
+        } else {
+            const int t = (int)((unsigned)u / (unsigned)p.nkt), kt = u - t * p.nkt;
+            tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
+            bulk_load(sbase + W_TILE_BYTES, p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
+        }
+    };
+    auto issue_a = [&](int i) {
+        const int u = i < nhead ? head + i : u0 + (i - nhead);
+        const int kt = (int)((unsigned)u % (unsigned)p.nkt);
+        const uint32_t sbase = stage0 + (i % ring) * C::STAGE_BYTES;
+        const uint32_t bar = smem_u32(&ctrl->full[i % ring]);
+        if (p.A_rec) {      // one copy: the tile (already swizzled) and its scale atoms, laid out by the activation quantiser
+            bulk_load(sbase + W_TILE_BYTES + SF_TILE_BYTES, p.A_rec + (size_t)kt * (C::A_TILE_BYTES + SF_TILE_BYTES),
+                      C::A_TILE_BYTES + SF_TILE_BYTES, bar);
+        } else {
+            tma_load_2d(sbase + W_TILE_BYTES + SF_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
+            bulk_load(sbase + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES, p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
+        }
+    };
     if (warp >= FIRST_Z_WARP && warp < MMA_WARP) {
         // ================= z warps: second half of the z stage =================
         if (p.R > 0) {
@@ -110,33 +141,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         // Lane 0 of feeder j requests the copies of units j, j+PRODUCERS, ... (in processing order). Weights do not
         // depend on the previous kernel of the stream: the first ring of weight records is requested at once, before
         // the dependency wait; activations are what that kernel produced and follow the wait. Later units are
-        // requested from inside the scale-factor loop, as their stages come free.
+        // requested by the refill warp, as their stages come free.
         const int mine = warp - FIRST_SF_WARP;
-        const int nunits = u1 - u0;
-        const int head = SegWalk(u0, u1, p.nkt).head;     // units [head, u1) are processed first, then [u0, head)
-        const int nhead = u1 - head;
-        auto issue_w = [&](int i) {
-            const int u = i < nhead ? head + i : u0 + (i - nhead);
-            const uint32_t sbase = stage0 + (i % ring) * C::STAGE_BYTES;
-            const uint32_t bar = smem_u32(&ctrl->full[i % ring]);
-            mbar_arrive_expect_tx(bar, W_TILE_BYTES + C::A_TILE_BYTES + 2 * SF_TILE_BYTES);
-            if (p.W_tiled) {
-                // one contiguous 18 KB record per unit: pre-swizzled codes followed by the scale atoms
-                bulk_load(sbase, p.W_tiled + (size_t)u * (W_TILE_BYTES + SF_TILE_BYTES), W_TILE_BYTES + SF_TILE_BYTES, bar);
-            } else {
-                const int t = (int)((unsigned)u / (unsigned)p.nkt), kt = u - t * p.nkt;
-                tma_load_2d(sbase, &tmW, kt * KT_BYTES, t * TILE_N, bar);
-                bulk_load(sbase + W_TILE_BYTES, p.W_sf + ((size_t)t * (p.K >> 6) + (size_t)kt * 4) * 512, SF_TILE_BYTES, bar);
-            }
-        };
-        auto issue_a = [&](int i) {
-            const int u = i < nhead ? head + i : u0 + (i - nhead);
-            const int kt = (int)((unsigned)u % (unsigned)p.nkt);
-            const uint32_t sbase = stage0 + (i % ring) * C::STAGE_BYTES;
-            const uint32_t bar = smem_u32(&ctrl->full[i % ring]);
-            tma_load_2d(sbase + W_TILE_BYTES + SF_TILE_BYTES, &tmA, kt * KT_BYTES, 0, bar);
-            bulk_load(sbase + W_TILE_BYTES + SF_TILE_BYTES + C::A_TILE_BYTES, p.A_sf + (size_t)kt * 4 * 512, SF_TILE_BYTES, bar);
-        };
         if (lane == 0) {
 #pragma unroll 1
             for (int i = mine; i < nunits && i < ring; i += PRODUCERS) issue_w(i);
@@ -152,6 +158,8 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         // eight of them per unit occupy the tensor pipe longer than the unit's four MMAs (measured); here warp q
         // writes quadrant q from registers instead: per unit 8 x 128-bit shared loads and 2 x tcgen05.st per thread.
         const uint32_t quad = (uint32_t)((warp & 3) * 32) << 16;
+        // (Leaving the TMEM stores of unit i in flight while waiting for unit i+1, and signalling unit i only then, was
+        // measured slower: 37.0 against 34.3 us on 8192 x 28672.)
 #pragma unroll 1
         for (int i = 0; i < nunits; ++i) {
             const int s = i % ring;
@@ -176,15 +184,22 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             tc_wait_st();
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&ctrl->sf_full[q]));
-            // refill: the stage of unit i-1 is the stage of unit j = i-1+ring; its feeder requests the copies as soon
-            // as the MMAs of unit i-1 have completed
-            const int j = i - 1 + ring;
-            bool fed = true;
-            if (i >= 1 && j < nunits && (j % PRODUCERS) == mine && lane == 0) {
-                fed = wait_bar(smem_u32(&ctrl->empty[j % ring]), ((j / ring) - 1) & 1, ctrl, p.status, p.epoch, ST_EMPTY, warp);
-                if (fed) { issue_w(j); issue_a(j); }
+        }
+    } else if (warp == REFILL_WARP) {
+        // ================= refills =================
+        // Lane j < PRODUCERS re-requests stage (i % ring) for units i = ring + j, ring + j + PRODUCERS, ... as soon as the
+        // MMAs of the unit that held the stage have completed. A warp of its own: a thread is held up while its copy
+        // request is accepted (about 0.4 us measured), which must not sit inside the scale-factor loop of the feeders
+        // (measured there: 0.9 us per unit and CTA, 3.0 TB/s on 8192 x 28672 instead of 4.6).
+        if (lane < PRODUCERS) {
+            griddep_wait();
+            fence_proxy_async_global();
+#pragma unroll 1
+            for (int i = ring + lane; i < nunits; i += PRODUCERS) {
+                if (!poll_bar(smem_u32(&ctrl->empty[i % ring]), ((i / ring) - 1) & 1, ctrl, p.status, p.epoch, ST_EMPTY, warp)) break;
+                issue_w(i);
+                issue_a(i);
             }
-            if (!__all_sync(0xffffffffu, fed)) break;
         }
     } else if (warp == MMA_WARP) {
         // ================= MMA issue =================

@@ -306,11 +306,12 @@ extern "C" int biloco_b200_tile_weights(const void* W_codes, const void* W_sf, v
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
-extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha, const void* A_codes,
-                                        const void* A_sf, const void* X_bf16, const void* V_packed, const int32_t* U_col32,
-                                        const void* S_bf16, const void* C_bf16, void* Y_bf16, void* scratch,
-                                        size_t scratch_bytes, int M, int A_rows, int N, int K, int R, int mode, int epoch,
-                                        biloco_stream_t stream) {
+static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha, const void* A_codes,
+                             const void* A_sf, const void* A_rec, const void* X_bf16, const void* V_packed, const int32_t* U_col32,
+                             const void* S_bf16, const void* C_bf16, void* Y_bf16, void* scratch,
+                             size_t scratch_bytes, int M, int A_rows, int N, int K, int R, int mode, int epoch,
+                             biloco_stream_t stream) {
+    if ((uintptr_t)A_rec & 15) return BILOCO_ERR_ALIGN;
     if ((!W_tiled && (!W_codes || !W_sf)) || !alpha || !A_codes || !A_sf || !Y_bf16 || !scratch) return BILOCO_ERR_NULL;
     if (R > 0 && (!X_bf16 || !V_packed || !U_col32 || !S_bf16)) return BILOCO_ERR_NULL;
     if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER && (mode & 0xff) != BILOCO_MODE_CLUSTER) return BILOCO_ERR_MODE;
@@ -337,6 +338,7 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
     p.W_tiled = (const uint8_t*)W_tiled;
     p.W_sf = (const uint8_t*)W_sf;
     p.A_sf = (const uint8_t*)A_sf;
+    p.A_rec = (const uint8_t*)A_rec;
     p.alpha = alpha;
     p.X = (const __nv_bfloat16*)X_bf16;
     p.Vp = (const uint8_t*)V_packed;
@@ -384,6 +386,31 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
 // ---------------------------------------------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_noalloc_scratch[BILOCO_NOALLOC_SCRATCH_BYTES];
 static void* g_noalloc_ptr[64] = {nullptr};                 // per device, filled by the first call on that device
+
+
+extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha, const void* A_codes,
+                                        const void* A_sf, const void* X_bf16, const void* V_packed, const int32_t* U_col32,
+                                        const void* S_bf16, const void* C_bf16, void* Y_bf16, void* scratch,
+                                        size_t scratch_bytes, int M, int A_rows, int N, int K, int R, int mode, int epoch,
+                                        biloco_stream_t stream) {
+    return fused_linear_impl(W_codes, W_sf, W_tiled, alpha, A_codes, A_sf, nullptr, X_bf16, V_packed, U_col32, S_bf16, C_bf16, Y_bf16,
+                             scratch, scratch_bytes, M, A_rows, N, K, R, mode, epoch, stream);
+}
+
+extern "C" int biloco_b200_fused_linear_rec(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                            const void* A_codes, const void* A_sf, const void* A_rec, const void* X_bf16,
+                                            const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16,
+                                            void* Y_bf16, void* scratch, size_t scratch_bytes, int M, int A_rows, int N, int K,
+                                            int R, int mode, int epoch, biloco_stream_t stream) {
+    return fused_linear_impl(W_codes, W_sf, W_tiled, alpha, A_codes, A_sf, A_rec, X_bf16, V_packed, U_col32, S_bf16, C_bf16, Y_bf16,
+                             scratch, scratch_bytes, M, A_rows, N, K, R, mode, epoch, stream);
+}
+
+extern "C" size_t biloco_b200_act_rec_bytes(int M, int K) {
+    if (M < 1 || M > 32 || K < KT || (K % KT)) return 0;
+    const int mma_n = M <= 8 ? 8 : (M <= 16 ? 16 : 32);
+    return (size_t)(K / KT) * (size_t)(mma_n * KT_BYTES + SF_TILE_BYTES);
+}
 
 extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
                                                 const void* A_codes, const void* A_sf, const void* X_bf16,
@@ -441,6 +468,7 @@ extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void*
     p.W_tiled = (const uint8_t*)W_tiled;
     p.W_sf = (const uint8_t*)W_sf;
     p.A_sf = (const uint8_t*)A_sf;
+    p.A_rec = nullptr;
     p.alpha = alpha;
     p.X = (const __nv_bfloat16*)X_bf16;
     p.Vp = (const uint8_t*)V_packed;

@@ -38,7 +38,10 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 // The wait carries a suspend-time hint: the hardware may park the thread until the phase completes or the time is up,
 // instead of returning at once. A waiting warp that spins takes issue slots from the warps that compute on the same
 // scheduler (measured: a 0.4 us CUDA-core stage took 1.5 us next to four spinning warps).
-constexpr uint32_t MBAR_SUSPEND_NS = 1000000u;
+#ifndef BILOCO_MBAR_SUSPEND_NS
+#define BILOCO_MBAR_SUSPEND_NS 1000000u
+#endif
+constexpr uint32_t MBAR_SUSPEND_NS = BILOCO_MBAR_SUSPEND_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -47,6 +50,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity), "r"(MBAR_SUSPEND_NS)
+        : "memory");
+    return ok != 0;
+}
+
+// The same test without a suspend-time hint, for lanes of ONE warp that wait on different barriers (a parked warp would
+// hold up its other lanes).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }

@@ -139,10 +139,18 @@ def activation_scale_from_amax(amax: torch.Tensor, rule: str = None) -> torch.Te
     return torch.where(amax > 0, amax / (6.0 * target), torch.ones_like(amax))
 
 
+def _rec_buffer(M: int, K: int, dev):
+    """Buffer for the per-k-tile activation record the fused kernel fetches with one copy per work unit (None when the
+    shape has none: more than 32 rows or K not a multiple of 256)."""
+    n = _lib.load().biloco_b200_act_rec_bytes(M, K) if (M <= 32 and K % 256 == 0) else 0
+    return torch.empty(n, device=dev, dtype=torch.uint8) if n else None
+
+
 def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor = None, w_gscale: torch.Tensor = None,
                         rows: int = None, out: dict = None, gscale: torch.Tensor = None, norm_weight: torch.Tensor = None,
                         eps: float = 1e-6):
-    """bf16 CUDA activation [M, K] -> dict(A [1, rows, K/2] uint8, A_sf float8 (atom layout), gscale fp32 [1],
+    """bf16 CUDA activation [M, K] -> dict(A [1, rows, K/2] uint8, A_sf float8 (atom layout), A_rec (the same codes and
+    scales as the fused kernel stages them, or None), gscale fp32 [1],
     alpha fp32 [1] (= w_gscale * gscale, when w_gscale is given), X bf16 [M, K] (x / smooth when smoothing)).
     ``gscale`` (fp32 [1]) supplies the tensor scale instead of deriving it from this tensor's own maximum.
     Runs the library's quantiser on the current stream; nothing returns to the host. Pass ``out`` (a dict from
@@ -160,7 +168,8 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
                    A_sf=torch.empty(nvfp4_sf_bytes(rows, K), device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn),
                    gscale=torch.empty(1, device=dev, dtype=torch.float32),
                    alpha=torch.empty(w_gscale.numel(), device=dev, dtype=torch.float32) if w_gscale is not None else None,
-                   X=torch.empty_like(x) if (smooth is not None or norm_weight is not None) else x)
+                   X=torch.empty_like(x) if (smooth is not None or norm_weight is not None) else x,
+                   A_rec=_rec_buffer(M, K, dev))
     elif smooth is None and norm_weight is None:
         out["X"] = x
     rule_id = _lib.RULES[rule]
@@ -168,8 +177,9 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
         out["gscale"].copy_(gscale.reshape(1))
         rule_id |= 0x100
     n_alpha = w_gscale.numel() if w_gscale is not None else 1
+    rec = out.get("A_rec")
     with torch.cuda.device(dev):
-        if norm_weight is None and n_alpha == 1:
+        if norm_weight is None and n_alpha == 1 and rec is None:
             rc = _lib.load().biloco_b200_act_quant(
                 x.data_ptr(), smooth.data_ptr() if smooth is not None else None,
                 out["X"].data_ptr() if smooth is not None else None, out["A"].data_ptr(), out["A_sf"].data_ptr(),
@@ -183,7 +193,7 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
                 x.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
                 smooth.data_ptr() if smooth is not None else None,
                 out["X"].data_ptr() if (smooth is not None or norm_weight is not None) else None,
-                out["A"].data_ptr(), out["A_sf"].data_ptr(), out["gscale"].data_ptr(),
+                out["A"].data_ptr(), out["A_sf"].data_ptr(), rec.data_ptr() if rec is not None else None, out["gscale"].data_ptr(),
                 out["alpha"].data_ptr() if w_gscale is not None else None,
                 w_gscale.data_ptr() if w_gscale is not None else None, n_alpha, M, rows, K, rule_id,
                 torch.cuda.current_stream().cuda_stream)

@@ -151,13 +151,15 @@ class BiLoCoGemm:
                        "read_status")
         return list(out)
 
-    def __call__(self, A_pad, A_sf, X_bf16, out=None):
-        """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten). ``out`` (not in the reference's signature):
-        a [rows, N] tensor to write into instead of a fresh one, e.g. a slice of a buffer that is read back in one copy."""
+    def __call__(self, A_pad, A_sf, X_bf16, out=None, A_rec=None):
+        """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten). Not in the reference's signature: ``out``,
+        a [rows, N] tensor to write into instead of a fresh one (e.g. a slice of a buffer that is read back in one copy),
+        and ``A_rec``, the activation quantiser's per-k-tile record (fp4.quantize_activation(...)["A_rec"]) with which the
+        kernel fetches the activation side of a work unit in one copy."""
         self.epoch += 1
-        if self.residual is not None or self.fp32_out or out is not None:   # not expressible in the operator schemas
+        if self.residual is not None or self.fp32_out or out is not None or A_rec is not None:   # not expressible in the operator schemas
             return _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32, self.z,
-                               self.M, self.epoch, self.mode, C=self.residual, out=out,
+                               self.M, self.epoch, self.mode, C=self.residual, out=out, A_rec=A_rec,
                                B_tiled=self.W_tiled if self.W_tiled.numel() else None, fp32_out=self.fp32_out)
         a = (A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32)
         if self.mode == 2:
@@ -182,10 +184,10 @@ class _FP4Only:
         self.epoch = 0
         self.residual = None
 
-    def __call__(self, A, A_sf, X_bf16=None):
+    def __call__(self, A, A_sf, X_bf16=None, out=None, A_rec=None):
         self.epoch += 1
         return _ops._fused(A, self.W_fp4, A_sf, self.W_sf, self.alpha, None, None, None, None, self.z, self.M, self.epoch,
-                           _lib.MODE_COUNTER, C=self.residual, B_tiled=self.W_tiled)
+                           _lib.MODE_COUNTER, C=self.residual, B_tiled=self.W_tiled, out=out, A_rec=A_rec)
 
 
 def reference(A_fp4, A_sf, W_fp4, W_sf, alpha, X_bf16, V_packed, U_packed, S):

@@ -118,7 +118,7 @@ class BiLoCoLinear(nn.Module):
                                     w_gscale=self.w_gscale, rows=M, out=self._acts.get(M))
         self._acts[M] = q
         g = self._gemm_for(M, q["alpha"])
-        return g(q["A"], q["A_sf"], q["X"]).view(-1, self.out_features)[:M]
+        return g(q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec")).view(-1, self.out_features)[:M]
 
     def forward_quantized(self, q: dict, alpha: torch.Tensor):
         """The fused linear on an activation that has been quantised already (fp4.quantize_activation with this layer's
@@ -128,7 +128,7 @@ class BiLoCoLinear(nn.Module):
         g = self._gemm_for(M, alpha)
         if g.alpha.data_ptr() != alpha.data_ptr():       # (the launcher keeps the pointer it was built with)
             g.alpha = alpha
-        return g(q["A"], q["A_sf"], q["X"]).view(-1, self.out_features)[:M]
+        return g(q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec")).view(-1, self.out_features)[:M]
 
     def forward(self, x):
         assert self.weight is None, "call quantize() first"

@@ -56,7 +56,8 @@ def _check_fp4_operands(A, B, A_sf, B_sf, alpha):
     return rows, N, K
 
 
-def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None, B_tiled=None, fp32_out=False):
+def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None, B_tiled=None, fp32_out=False,
+           A_rec=None):
     rows, N, K = _check_fp4_operands(A, B, A_sf, B_sf, alpha)
     _req(1 <= m_rows <= rows, "m_rows must be in [1, A.size(1)]")
     R = 0
@@ -78,10 +79,14 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
     if fp32_out:
         _req(D.dtype == torch.float32, "fp32 output buffer expected")
         mode |= 0x400
+    if A_rec is not None:
+        want = _lib.load().biloco_b200_act_rec_bytes(m_rows, K)
+        _req(A_rec.is_cuda and A_rec.is_contiguous() and A_rec.dtype == torch.uint8 and A_rec.numel() == want and want > 0,
+             f"activation record must be a contiguous uint8 CUDA tensor of {want} bytes")
     with torch.cuda.device(A.device):
-        rc = _lib.load().biloco_b200_fused_linear(
+        rc = _lib.load().biloco_b200_fused_linear_rec(
             B.data_ptr(), B_sf.data_ptr(), B_tiled.data_ptr() if B_tiled is not None else None, alpha.data_ptr(), A.data_ptr(), A_sf.data_ptr(),
-            X.data_ptr() if R else None, V.data_ptr() if R else None, U_col32.data_ptr() if R else None,
+            A_rec.data_ptr() if A_rec is not None else None, X.data_ptr() if R else None, V.data_ptr() if R else None, U_col32.data_ptr() if R else None,
             S.data_ptr() if R else None, C.data_ptr() if C is not None else None, D.data_ptr(),
             scratch.data_ptr(), scratch.numel() * scratch.element_size(),
             m_rows, rows, N, K, R, mode, epoch, _stream())

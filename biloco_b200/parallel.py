@@ -99,7 +99,7 @@ class ShardedBiLoCoLinear:
         q = fp4.quantize_activation(x, smooth=o["smooth_scale"], w_gscale=o["w_gscale"], rows=self.M, out=self._act, gscale=gscale)
         self._act = q
         self.alpha.copy_(q["alpha"])
-        y = self.gemm(q["A"], q["A_sf"], q["X"]).view(-1, self.N)[: self.M]
+        y = self.gemm(q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec")).view(-1, self.N)[: self.M]
         if self.kind == "row":
             y = y.contiguous()
             if dist.is_initialized() and dist.get_world_size(self.group) > 1:

@@ -106,9 +106,22 @@ int biloco_b200_act_quant(const void* X_bf16, const void* smooth_bf16, void* Xs_
  * No counterpart in the reference (its layers call fake_quantize_fp4 per linear, biloco/layer.py:60, and the norm
  * lives in the surrounding model). */
 int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_weight_bf16, float eps, const void* smooth_bf16,
-                               void* Xn_bf16, void* A_codes, void* A_sf, float* a_gscale, float* alpha_out,
+                               void* Xn_bf16, void* A_codes, void* A_sf, void* A_rec, float* a_gscale, float* alpha_out,
                                const float* w_gscale, int n_alpha, int M, int A_rows, int K, int rule,
                                biloco_stream_t stream);
+
+/* A_rec (optional, biloco_b200_act_rec_bytes(M, K) bytes, K % 256 == 0, M <= 32): the same codes and block scales once
+ * more, laid out per 256-wide k-tile exactly as the fused kernel keeps them in shared memory (the activation tile with
+ * the 128-byte swizzle applied, followed by its four scale atoms). biloco_b200_fused_linear_rec then fetches the
+ * activation side of a work unit with ONE bulk copy instead of a tiled TMA load plus a bulk copy: the copy engine of
+ * an SM takes requests one at a time, and three requests per unit held the stream at 3.7 TB/s on 8192 x 28672.
+ * Internal layout of this library (like the unit-contiguous weights); no counterpart in the reference. */
+size_t biloco_b200_act_rec_bytes(int M, int K);
+int biloco_b200_fused_linear_rec(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                 const void* A_codes, const void* A_sf, const void* A_rec, const void* X_bf16,
+                                 const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16,
+                                 void* Y_bf16, void* scratch, size_t scratch_bytes, int M, int A_rows, int N, int K,
+                                 int R, int mode, int epoch, biloco_stream_t stream);
 
 /* Scratch bytes needed by biloco_b200_fused_linear for this problem on a device
  * with `num_sms` multiprocessors (0 = query the current device). The scratch must be zero-filled once

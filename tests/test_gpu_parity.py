@@ -72,6 +72,22 @@ def test_act_quant_bit_exact(kernel, rule, M, K, rows, smooth):
     assert np.array_equal(sf_dev, want_sf)
     if smooth:
         assert np.array_equal(out["X"].float().cpu().numpy(), xs)
+    # the per-k-tile record holds the same codes (128-byte swizzle: 16-byte chunk c of row r at chunk c ^ (r & 7)) and the
+    # same scale atoms, zero beyond row M
+    rec = out["A_rec"].cpu().numpy()
+    mma_n = 8 if M <= 8 else (16 if M <= 16 else 32)
+    rb = mma_n * 128 + 2048
+    assert rec.size == (K // 256) * rb
+    sw = orc.sf_swizzle(sf, K)
+    for kt in range(K // 256):
+        tile = rec[kt * rb: kt * rb + mma_n * 128].reshape(mma_n, 8, 16)
+        for m in range(mma_n):
+            row = codes[m, kt * 128:(kt + 1) * 128].reshape(8, 16) if m < M else np.zeros((8, 16), np.uint8)
+            assert np.array_equal(tile[m][np.arange(8) ^ (m & 7)], row), (kt, m)
+        atoms = np.zeros(2048, np.uint8)
+        src = sw[kt * 2048:(kt + 1) * 2048] if M <= 128 else None
+        atoms[: src.size] = src
+        assert np.array_equal(rec[kt * rb + mma_n * 128: (kt + 1) * rb], atoms), kt
 
 
 @pytest.mark.parametrize("M,K,smooth", [(1, 2560, False), (8, 5120, False), (32, 1024, True), (3, 256, False)])
@@ -102,6 +118,22 @@ def test_norm_act_quant(kernel, M, K, smooth):
     want_sf = np.zeros(orc.nvfp4_sf_bytes(M, K), np.uint8)
     want_sf[: orc.nvfp4_sf_bytes(M, K)] = orc.sf_swizzle(sf, K)
     assert np.array_equal(out["A_sf"].view(torch.uint8).cpu().numpy(), want_sf)
+
+
+@pytest.mark.parametrize("M,K,N,R", [(1, 5120, 5120, 512), (8, 2560, 1024, 128), (32, 1024, 640, 64)])
+def test_fused_with_activation_record(kernel, M, K, N, R):
+    """The fused linear fed from the quantiser's per-k-tile record (one copy per work unit) gives bit-identical results to
+    the tiled-TMA path on the same quantised activation."""
+    from biloco_b200 import fp4
+    p = orc.random_problem(M, K, N, R, scales="random", seed=5 * M + R)
+    t = dev_problem(p)
+    q = fp4.quantize_activation(t["X"], "mse", w_gscale=torch.tensor([1e-3], device="cuda"), rows=M)
+    g = kernel.BiLoCoGemm(t["W"], t["W_sf"], q["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M)
+    y_tma = g(q["A"], q["A_sf"], q["X"]).view(-1, N)[:M].clone()
+    y_rec = g(q["A"], q["A_sf"], q["X"], A_rec=q["A_rec"]).view(-1, N)[:M].clone()
+    torch.cuda.synchronize()
+    assert g.status()[0] == 0
+    assert torch.isfinite(y_rec.float()).all() and torch.equal(y_tma.view(torch.int16), y_rec.view(torch.int16))
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 128, 256), (4, 256, 1024), (3, 136, 512)])
