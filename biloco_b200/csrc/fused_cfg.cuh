@@ -110,6 +110,12 @@ struct FusedParams {
     float* zbuf;
     float* partials;
     int M, N, K, R, Rw, Rpad;
+    // Column groups: several linears that read the same activation (q/k/v, gate/up) stacked along N in one launch. Group
+    // g owns the tiles [gtile[g-1], gtile[g]) (gtile[-1] = 0, unused entries INT_MAX), the ranks [g*Rg, (g+1)*Rg) of V, S
+    // and z, and the decode scale alpha[g]; a column's U words cover its own group's Rg ranks (Rw words). R is the total
+    // (what the z stage computes); a single linear is one group with Rg = R.
+    int ngroups, Rg;
+    int gtile[3];
     int ntile, nkt, G, max_slots;
     int ring;                 // pipeline stages (<= Cfg::STAGES); the shared-memory layout follows it
     int trigger;              // where the CTA lets the next kernel of the stream start: 0 after set-up, 4 after its own
@@ -124,6 +130,10 @@ struct FusedParams {
     int mode;
     unsigned long long* stamps;   // debug: STAMP_WORDS %globaltimer values per CTA, or null
 };
+
+__device__ __forceinline__ int tile_group(const FusedParams& p, int t) {
+    return (t >= p.gtile[0] ? 1 : 0) + (t >= p.gtile[1] ? 1 : 0) + (t >= p.gtile[2] ? 1 : 0);
+}
 
 struct Ctrl {   // lives in shared memory after the stages
     uint64_t full[16];

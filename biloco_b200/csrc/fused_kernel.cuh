@@ -294,7 +294,6 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         if (p.cluster > 1 && (cta % p.cluster) == p.cluster - 1 && tid < p.cluster - 1)
             mbar_arrive_remote_release(map_to_cta(smem_u32(&ctrl->red_free), (uint32_t)tid));
 
-        const float alpha = p.alpha[0];
         int seg = 0;
 #pragma unroll 1
         for (SegWalk sw(u0, u1, p.nkt); !sw.done(); sw.next(), ++seg) {
@@ -304,6 +303,9 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             const bool complete = si.complete;
             const int n = t * TILE_N + tid;
             const bool valid = n < p.N;
+            const int grp = tile_group(p, t);
+            const float alpha = p.alpha[grp];       // (requested here, needed after the expansion)
+            const float* zbg = p.zbuf + grp * p.Rg;
 
             float corr[ROWS];
 #pragma unroll
@@ -319,7 +321,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                 if (on_tc) {
                     if constexpr (ROWS >= LR_TC_MIN_ROWS) {
                         const uint32_t d2 = tmem + LR_D_COL + 32u * (uint32_t)(lrseg & 1);
-                        if (!expand_z_tc<ROWS, MMA_N>(p, ctrl, lr, p.zbuf, ucol, si.w0, si.w1, tid, phase, d2, gchunk)) break;
+                        if (!expand_z_tc<ROWS, MMA_N>(p, ctrl, lr, zbg, ucol, si.w0, si.w1, tid, phase, d2, gchunk)) break;
                         // the segment's sums: wait for its last MMA, read the accumulator (lane = this thread's column)
                         if (!wait_bar(smem_u32(&ctrl->lr_done), lrseg & 1, ctrl, p.status, p.epoch, ST_ACC_FULL, warp)) break;
                         tc_fence_after_sync();
@@ -331,7 +333,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                         for (int m = 0; m < ROWS; ++m) corr[m] = c2[m];
                         ++lrseg;
                     }
-                } else if (!expand_z<ROWS>(corr, p, ctrl, p.zbuf, ucol, si.w0, si.w1, zs, tid, uw_sel, seg < 2, phase)) {
+                } else if (!expand_z<ROWS>(corr, p, ctrl, zbg, ucol, si.w0, si.w1, zs, tid, uw_sel, seg < 2, phase)) {
                     break;
                 }
                 if (tid == 0 && p.stamps && seg == 0) p.stamps[(size_t)cta * STAMP_WORDS + 3] = globaltimer_ns();

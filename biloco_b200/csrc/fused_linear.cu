@@ -310,8 +310,23 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
                              const void* A_sf, const void* A_rec, const void* X_bf16, const void* V_packed, const int32_t* U_col32,
                              const void* S_bf16, const void* C_bf16, void* Y_bf16, void* scratch,
                              size_t scratch_bytes, int M, int A_rows, int N, int K, int R, int mode, int epoch,
-                             biloco_stream_t stream) {
+                             biloco_stream_t stream, int n_groups = 1, const int* group_rows = nullptr) {
     if ((uintptr_t)A_rec & 15) return BILOCO_ERR_ALIGN;
+    // column groups: R ranks per group, group g covers group_rows[g] output columns (whole 128-column tiles)
+    int gtile[3] = {0x7fffffff, 0x7fffffff, 0x7fffffff};
+    const int Rg = R;
+    if (n_groups != 1) {
+        if (n_groups < 1 || n_groups > 4 || !group_rows || R < 32 || (R % 32)) return BILOCO_ERR_SHAPE;
+        long long rows = 0;
+        for (int g = 0; g < n_groups; ++g) {
+            if (group_rows[g] < TILE_N || (group_rows[g] % TILE_N)) return BILOCO_ERR_SHAPE;
+            rows += group_rows[g];
+            if (g < n_groups - 1) gtile[g] = (int)(rows / TILE_N);
+        }
+        if (rows != N) return BILOCO_ERR_SHAPE;
+        if ((long long)R * n_groups > 0x7fffffff) return BILOCO_ERR_LIMIT;
+        R *= n_groups;
+    }
     if ((!W_tiled && (!W_codes || !W_sf)) || !alpha || !A_codes || !A_sf || !Y_bf16 || !scratch) return BILOCO_ERR_NULL;
     if (R > 0 && (!X_bf16 || !V_packed || !U_col32 || !S_bf16)) return BILOCO_ERR_NULL;
     if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER && (mode & 0xff) != BILOCO_MODE_CLUSTER) return BILOCO_ERR_MODE;
@@ -351,7 +366,9 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
     p.tile_cnt = (uint32_t*)(sc + L.off_tilecnt);
     p.zbuf = (float*)(sc + L.off_z);
     p.partials = (float*)(sc + L.off_part);
-    p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = L.Rw; p.Rpad = L.Rpad;
+    p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = (Rg + 31) / 32; p.Rpad = L.Rpad;
+    p.ngroups = n_groups; p.Rg = Rg;
+    for (int g = 0; g < 3; ++g) p.gtile[g] = gtile[g];
     p.ntile = L.ntile; p.nkt = L.nkt; p.G = L.G; p.max_slots = L.max_slots;
     p.epoch = (uint32_t)epoch;
     p.mode = mode;
@@ -404,6 +421,18 @@ extern "C" int biloco_b200_fused_linear_rec(const void* W_codes, const void* W_s
                                             int R, int mode, int epoch, biloco_stream_t stream) {
     return fused_linear_impl(W_codes, W_sf, W_tiled, alpha, A_codes, A_sf, A_rec, X_bf16, V_packed, U_col32, S_bf16, C_bf16, Y_bf16,
                              scratch, scratch_bytes, M, A_rows, N, K, R, mode, epoch, stream);
+}
+
+extern "C" int biloco_b200_fused_linear_grouped(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                                const void* A_codes, const void* A_sf, const void* A_rec, const void* X_bf16,
+                                                const void* V_packed, const int32_t* U_col32, const void* S_bf16,
+                                                const void* C_bf16, void* Y_bf16, void* scratch, size_t scratch_bytes, int M,
+                                                int A_rows, int N, int K, int R, int n_groups, const int* group_rows, int mode,
+                                                int epoch, biloco_stream_t stream) {
+    if (n_groups < 1 || !group_rows) return BILOCO_ERR_NULL;
+    if (n_groups == 1 && group_rows[0] != N) return BILOCO_ERR_SHAPE;
+    return fused_linear_impl(W_codes, W_sf, W_tiled, alpha, A_codes, A_sf, A_rec, X_bf16, V_packed, U_col32, S_bf16, C_bf16, Y_bf16,
+                             scratch, scratch_bytes, M, A_rows, N, K, R, mode, epoch, stream, n_groups, group_rows);
 }
 
 extern "C" size_t biloco_b200_act_rec_bytes(int M, int K) {
@@ -482,6 +511,8 @@ extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void*
     p.zbuf = (float*)(sc + L.off_z);
     p.partials = (float*)(sc + L.off_part);
     p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = L.Rw; p.Rpad = L.Rpad;
+    p.ngroups = 1; p.Rg = R;
+    for (int g = 0; g < 3; ++g) p.gtile[g] = 0x7fffffff;
     p.ntile = L.ntile; p.nkt = L.nkt; p.G = L.G; p.max_slots = L.max_slots;
     p.epoch = 1u;
     p.mode = mode;

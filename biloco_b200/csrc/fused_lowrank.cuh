@@ -242,7 +242,7 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
 // The consumers load the values they need straight away, 128 bits at a time, and reload until all four marks match:
 // one memory round trip after the last producer's store instead of three (counter, then poll, then data). The mark
 // costs one unit in the last place of an fp32 z value. Ranks >= R (padding of the last rank word) are never written
-// and read as zero; rows >= M of the staging area are left as they are (their sums are never stored). Values are staged zs_words(ROWS) rank words at a time in shared memory.
+// and read as zero (zb points at the first rank of the tile's column group, which has p.Rg ranks); rows >= M of the staging area are left as they are (their sums are never stored). Values are staged zs_words(ROWS) rank words at a time in shared memory.
 // uw_first holds this thread's first ZS_FIRST U words when they were fetched ahead of time (use_first).
 // Returns false when the poll ran out of time (status set, abort raised).
 template <int ROWS>
@@ -283,8 +283,8 @@ __device__ __forceinline__ bool expand_z(float (&corr)[ROWS], const FusedParams&
             for (int q = 0; q < NPT; ++q) {
                 if (goff[q] >= 0) {
                     const int e = 32 * c0 + (soff[q] % ZSTR);           // rank of v[q].x
-                    bad |= (e + 0 < p.R ? (v[q].x ^ phase) : 0u) | (e + 1 < p.R ? (v[q].y ^ phase) : 0u) |
-                           (e + 2 < p.R ? (v[q].z ^ phase) : 0u) | (e + 3 < p.R ? (v[q].w ^ phase) : 0u);
+                    bad |= (e + 0 < p.Rg ? (v[q].x ^ phase) : 0u) | (e + 1 < p.Rg ? (v[q].y ^ phase) : 0u) |
+                           (e + 2 < p.Rg ? (v[q].z ^ phase) : 0u) | (e + 3 < p.Rg ? (v[q].w ^ phase) : 0u);
                 }
             }
             if (!(bad & 1u)) break;
@@ -303,10 +303,10 @@ __device__ __forceinline__ bool expand_z(float (&corr)[ROWS], const FusedParams&
                 const int e = 32 * c0 + (soff[q] % ZSTR);
                 float4 zz;
                 // (the mark is cleared, so that the result does not depend on the launch count's parity)
-                zz.x = e + 0 < p.R ? __uint_as_float(v[q].x & ~1u) : 0.f;
-                zz.y = e + 1 < p.R ? __uint_as_float(v[q].y & ~1u) : 0.f;
-                zz.z = e + 2 < p.R ? __uint_as_float(v[q].z & ~1u) : 0.f;
-                zz.w = e + 3 < p.R ? __uint_as_float(v[q].w & ~1u) : 0.f;
+                zz.x = e + 0 < p.Rg ? __uint_as_float(v[q].x & ~1u) : 0.f;
+                zz.y = e + 1 < p.Rg ? __uint_as_float(v[q].y & ~1u) : 0.f;
+                zz.z = e + 2 < p.Rg ? __uint_as_float(v[q].z & ~1u) : 0.f;
+                zz.w = e + 3 < p.Rg ? __uint_as_float(v[q].w & ~1u) : 0.f;
                 *reinterpret_cast<float4*>(zs + soff[q]) = zz;
             }
         }
@@ -392,7 +392,7 @@ __device__ __forceinline__ bool expand_z_tc(const FusedParams& p, Ctrl* ctrl, ui
                 const int m = idx >> 3, pc = idx & 7;
                 const int e0 = 32 * c0 + 8 * pc;                              // first rank of the piece
                 uint4 hi = make_uint4(0u, 0u, 0u, 0u), lo = hi;
-                if (m < p.M && c0 + (pc >> 2) < w1 && e0 < p.R) {
+                if (m < p.M && c0 + (pc >> 2) < w1 && e0 < p.Rg) {
                     const float* src = zb + (size_t)m * p.Rpad + e0;
                     uint4 a, b;
                     uint64_t t0 = 0;
@@ -403,7 +403,7 @@ __device__ __forceinline__ bool expand_z_tc(const FusedParams& p, Ctrl* ctrl, ui
                         uint32_t bad = 0;
                         const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) bad |= (e0 + i < p.R) ? (v[i] ^ phase) : 0u;
+                        for (int i = 0; i < 8; ++i) bad |= (e0 + i < p.Rg) ? (v[i] ^ phase) : 0u;
                         if (!(bad & 1u)) break;
                         if ((it & 15u) == 15u) {
                             if (ctrl->abort) { good = false; break; }
@@ -416,8 +416,8 @@ __device__ __forceinline__ bool expand_z_tc(const FusedParams& p, Ctrl* ctrl, ui
                     uint32_t h[4], l[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        float z0 = (e0 + 2 * i < p.R) ? __uint_as_float(v[2 * i] & ~1u) : 0.f;
-                        float z1 = (e0 + 2 * i + 1 < p.R) ? __uint_as_float(v[2 * i + 1] & ~1u) : 0.f;
+                        float z0 = (e0 + 2 * i < p.Rg) ? __uint_as_float(v[2 * i] & ~1u) : 0.f;
+                        float z1 = (e0 + 2 * i + 1 < p.Rg) ? __uint_as_float(v[2 * i + 1] & ~1u) : 0.f;
                         const __nv_bfloat16 h0 = __float2bfloat16_rn(z0), h1 = __float2bfloat16_rn(z1);
                         const __nv_bfloat16 l0 = __float2bfloat16_rn(z0 - __bfloat162float(h0));
                         const __nv_bfloat16 l1 = __float2bfloat16_rn(z1 - __bfloat162float(h1));

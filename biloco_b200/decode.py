@@ -100,6 +100,7 @@ class Decoder(nn.Module):
         assert c.heads % tp == 0 and c.kv_heads % tp == 0 and c.intermediate % (256 * tp) == 0 and c.vocab % (8 * tp) == 0
         self.c, self.tp, self.group = c, tp, group
         self.fuse_norm_quant, self._shared = True, {}     # (see _normed_linears)
+        self.fuse_groups = True                           # q/k/v and gate/up as one stacked launch each
         lin_dev = "meta" if meta else device
         self.embed = nn.Embedding(c.vocab, c.hidden, device=device, dtype=dtype)
         self.blocks = nn.ModuleList(Block(c, lin_dev, dtype, tp) for _ in range(c.layers))
@@ -130,7 +131,8 @@ class Decoder(nn.Module):
     def _normed_linears(self, h, norm_w, layers, key):
         """[layer(rmsnorm(h) * norm_w) for layer in layers]. When the layers are unsmoothed kernel-backed BiLoCo layers
         the norm, the NVFP4 quantisation and one decode scale per layer come from ONE launch (the activation is the
-        same for all of them), followed by one fused linear per layer; otherwise the plain composition."""
+        same for all of them), followed by ONE stacked fused-linear launch for all of them (fuse_groups; needs equal
+        ranks and whole 128-column tiles) or one fused linear per layer; otherwise the plain composition."""
         from . import fp4
         M = h.shape[0]
         fusable = self.fuse_norm_quant and M <= 32 and all(isinstance(l, BiLoCoLinear) and l.weight is None and not l.smoothed
@@ -145,6 +147,15 @@ class Decoder(nn.Module):
         q = fp4.quantize_activation(h.contiguous(), fp4.CONFIG_X, w_gscale=st["w_gs"], rows=M, out=st["q"],
                                     norm_weight=norm_w, eps=self.c.eps)
         st["q"] = q
+        if self.fuse_groups and 2 <= len(layers) <= 4 and "grouped" not in st:
+            from .kernel import GroupedBiLoCoGemm
+            ok = all(l.rank == layers[0].rank and l.rank % 32 == 0 and l.out_features % 128 == 0 and l.bias is None for l in layers)
+            st["grouped"] = GroupedBiLoCoGemm([l._gemm_for(M, q["alpha"][i:i + 1]) for i, l in enumerate(layers)]) if ok else None
+            if ok:                      # the stacked launcher holds its own copies of the operands
+                for l in layers:
+                    l._gemms.pop(M, None)
+        if self.fuse_groups and st.get("grouped") is not None:
+            return st["grouped"](q["alpha"], q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec"))
         return [l.forward_quantized(q, q["alpha"][i:i + 1]) for i, l in enumerate(layers)]
 
     @staticmethod
@@ -263,6 +274,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a captured step")
     ap.add_argument("--no-fuse", action="store_true", help="separate RMSNorm kernels and one quantiser launch per linear")
+    ap.add_argument("--no-groups", action="store_true", help="one fused-linear launch per linear (q, k, v, gate, up separately)")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "decode needs a CUDA device (there is no CPU path)"
     c = PRESETS[args.model]
@@ -278,6 +290,7 @@ def main():
     torch.manual_seed(args.seed)
     model = Decoder(c, device=dev, meta=True, tp=world)
     model.fuse_norm_quant = not args.no_fuse
+    model.fuse_groups = not args.no_groups
     nlin = synthetic_quantize(model, args.rank, seed=args.seed + 1000 * rank)
     g = torch.Generator(device=dev).manual_seed(args.seed)           # (same prompt on every rank)
     prompt = torch.randint(0, c.vocab, (args.M, args.prompt), device=dev, generator=g)
@@ -301,7 +314,7 @@ def main():
     print(json.dumps({
         "metric": "decode tokens/s", "value": args.M * args.steps / sec, "unit": "tokens/s", "M": args.M, "n_gpus": world,
         "ms_per_step": sec / args.steps * 1e3, "model": args.model, "layers": c.layers, "linears": nlin, "rank": args.rank,
-        "prompt": args.prompt, "steps": args.steps, "fused_norm_quant": model.fuse_norm_quant, "data": "synthetic (random packed operands, random prompt)",
+        "prompt": args.prompt, "steps": args.steps, "fused_norm_quant": model.fuse_norm_quant, "stacked_qkv_gateup": model.fuse_groups and model.fuse_norm_quant, "data": "synthetic (random packed operands, random prompt)",
         "linear_bytes_per_step": nbytes, "linear_GBps": gbs, "hbm_peak_GBps": peak,
         "roofline_frac": (gbs / (peak * world)) if peak else None, "finite": bool(torch.isfinite(toks.float()).all())}))
     if world > 1:

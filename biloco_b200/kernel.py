@@ -169,6 +169,50 @@ class BiLoCoGemm:
         return ops.biloco_gemm_mode5(*a, self.z, self.W_tiled, self.none, self.M, self.epoch)
 
 
+class GroupedBiLoCoGemm:
+    """Several BiLoCoGemm problems that read the same activation (q/k/v, gate/up) as ONE launch: the weights stacked
+    along N, the low-rank factors side by side (every linear keeps its own R ranks and its own decode scale). Built from
+    the separate launchers, all for the same M, K and R and with N a multiple of 128; ``alpha`` at call time is the fp32
+    [n] vector of decode scales in the same order (fp4.quantize_activation with w_gscale of n entries writes it).
+    Returns the list of per-linear outputs, views [M, N_g] of one [M, sum N_g] result.
+    No counterpart in the reference (one launch per linear)."""
+
+    def __init__(self, gemms, mode: int = None):
+        g0 = gemms[0]
+        assert 2 <= len(gemms) <= 4 and all(isinstance(g, BiLoCoGemm) for g in gemms)
+        assert all(g.K == g0.K and g.R == g0.R and g.M == g0.M and g.N % 128 == 0 for g in gemms) and g0.R % 32 == 0
+        assert all(g.W_tiled.numel() for g in gemms) and all(g.residual is None and not g.fp32_out for g in gemms)
+        self.rows = [g.N for g in gemms]
+        self.N, self.K, self.R, self.M = sum(self.rows), g0.K, g0.R, g0.M
+        dev = g0.W_fp4.device
+        cat = torch.cat
+        self.W_fp4 = cat([g.W_fp4 for g in gemms], 0).contiguous()
+        # (block scales are stored per 128-row block and the re-laid weight per 128-row tile: stacking is concatenation)
+        self.W_sf = cat([g.W_sf.view(torch.uint8).reshape(-1) for g in gemms]).view(torch.float8_e4m3fn)
+        self.W_tiled = cat([g.W_tiled for g in gemms])
+        self.V = cat([g.V for g in gemms], 0).contiguous()
+        self.S = cat([g.S for g in gemms]).contiguous()
+        self.U_col32 = cat([g.U_col32 for g in gemms], 0).contiguous()
+        with torch.cuda.device(dev):
+            ok = supported_modes(self.M, self.N, self.K, self.R * len(gemms))
+            if mode is None:
+                mode = DEFAULT_MODE.get(self.M, {}).get(self.R)
+                mode = mode if mode in ok else (ok or [None])[0]
+            assert mode in ok, f"mode {mode} not available for the stacked problem"
+            self.mode = mode
+            nbytes = scratch_bytes(self.M, self.N, self.K, self.R * len(gemms))
+        self.z = torch.zeros(nbytes // 4, device=dev, dtype=torch.float32)
+        self.epoch = 0
+
+    status = BiLoCoGemm.status
+
+    def __call__(self, alpha, A_pad, A_sf, X_bf16, out=None, A_rec=None):
+        self.epoch += 1
+        D = _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, alpha, X_bf16, self.V, self.S, self.U_col32, self.z, self.M,
+                        self.epoch, self.mode, out=out, A_rec=A_rec, B_tiled=self.W_tiled, group_rows=self.rows)
+        return list(D.view(-1, self.N)[: self.M].split(self.rows, dim=1))
+
+
 class _FP4Only:
     """The NVFP4 GEMM alone (no low-rank term) with the launcher interface of BiLoCoGemm; used by BiLoCoLinear with
     method "fp4" (the NVFP4-only baseline of the reference, biloco/layer.py:4-5)."""

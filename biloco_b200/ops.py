@@ -40,14 +40,15 @@ def _req(cond, msg):
         raise RuntimeError(msg)
 
 
-def _check_fp4_operands(A, B, A_sf, B_sf, alpha):
+def _check_fp4_operands(A, B, A_sf, B_sf, alpha, n_alpha=1):
     # operand contract of csrc/element_traits.hpp:122-170 and csrc/biloco_gemm.cu:3092
     _req(A.dtype == torch.uint8 and B.dtype == torch.uint8, "A and B must be uint8")
     _req(A.dim() == 3 and A.size(0) == 1, "A must be [1, M, K/2]")
     _req(B.dim() == 2, "B must be [N, K/2]")
     _req(A.size(2) == B.size(1), f"inner dims mismatch: {A.size(2) * 2} vs {B.size(1) * 2}")
     _req(A_sf.dtype == torch.float8_e4m3fn and B_sf.dtype == torch.float8_e4m3fn, "block scales must be float8_e4m3fn")
-    _req(alpha.dtype == torch.float32 and alpha.numel() == 1, "alpha must be fp32 with one element")
+    _req(alpha.dtype == torch.float32 and alpha.numel() == n_alpha and alpha.is_contiguous(),
+         "alpha must be fp32 with one element" if n_alpha == 1 else f"alpha must be contiguous fp32 with {n_alpha} elements")
     _req(A.is_cuda and B.is_cuda and A_sf.is_cuda and B_sf.is_cuda and alpha.is_cuda, "all tensors must be CUDA")
     _req(A.is_contiguous() and B.is_contiguous() and A_sf.is_contiguous() and B_sf.is_contiguous(), "operands must be contiguous")
     rows, K, N = A.size(1), A.size(2) * 2, B.size(0)
@@ -57,10 +58,16 @@ def _check_fp4_operands(A, B, A_sf, B_sf, alpha):
 
 
 def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None, B_tiled=None, fp32_out=False,
-           A_rec=None):
-    rows, N, K = _check_fp4_operands(A, B, A_sf, B_sf, alpha)
+           A_rec=None, group_rows=None):
+    """One launch of the fused linear. group_rows (list of ints) makes it a stacked launch of several linears that read
+    the same activation: V and S hold the groups' ranks one after another, U_col32 each column's own group's words, alpha
+    one scale per group (see biloco_b200_fused_linear_grouped)."""
+    ng = len(group_rows) if group_rows is not None else 1
+    rows, N, K = _check_fp4_operands(A, B, A_sf, B_sf, alpha, ng)
     _req(1 <= m_rows <= rows, "m_rows must be in [1, A.size(1)]")
     R = 0
+    if group_rows is not None:
+        _req(V is not None and V.size(0) % ng == 0, "grouped launch needs the stacked low-rank factors")
     if V is not None:
         R = V.size(0)
         _req(X.dtype == torch.bfloat16 and X.is_contiguous() and X.dim() == 2 and X.size(0) == m_rows and X.size(1) == K,
@@ -69,7 +76,7 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
              "V_packed must be contiguous uint8 [R, K/8]")
         _req(S.dtype == torch.bfloat16 and S.is_contiguous() and S.dim() == 1 and S.size(0) == R, "S must be contiguous bf16 [R]")
         _req(U_col32.dtype == torch.int32 and U_col32.is_contiguous() and U_col32.dim() == 2 and U_col32.size(0) == N
-             and U_col32.size(1) == (R + 31) // 32, "U_col32 must be contiguous int32 [N, ceil(R/32)]")
+             and U_col32.size(1) == (R // ng + 31) // 32, "U_col32 must be contiguous int32 [N, ceil(R/32)]")
     _req(scratch.is_cuda and scratch.is_contiguous(), "scratch must be a contiguous CUDA tensor")
     if B_tiled is not None:
         want = _lib.load().biloco_b200_tiled_bytes(N, K)
@@ -83,13 +90,17 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
         want = _lib.load().biloco_b200_act_rec_bytes(m_rows, K)
         _req(A_rec.is_cuda and A_rec.is_contiguous() and A_rec.dtype == torch.uint8 and A_rec.numel() == want and want > 0,
              f"activation record must be a contiguous uint8 CUDA tensor of {want} bytes")
-    with torch.cuda.device(A.device):
-        rc = _lib.load().biloco_b200_fused_linear_rec(
-            B.data_ptr(), B_sf.data_ptr(), B_tiled.data_ptr() if B_tiled is not None else None, alpha.data_ptr(), A.data_ptr(), A_sf.data_ptr(),
+    ptrs = (B.data_ptr(), B_sf.data_ptr(), B_tiled.data_ptr() if B_tiled is not None else None, alpha.data_ptr(), A.data_ptr(), A_sf.data_ptr(),
             A_rec.data_ptr() if A_rec is not None else None, X.data_ptr() if R else None, V.data_ptr() if R else None, U_col32.data_ptr() if R else None,
             S.data_ptr() if R else None, C.data_ptr() if C is not None else None, D.data_ptr(),
-            scratch.data_ptr(), scratch.numel() * scratch.element_size(),
-            m_rows, rows, N, K, R, mode, epoch, _stream())
+            scratch.data_ptr(), scratch.numel() * scratch.element_size())
+    with torch.cuda.device(A.device):
+        if group_rows is None:
+            rc = _lib.load().biloco_b200_fused_linear_rec(*ptrs, m_rows, rows, N, K, R, mode, epoch, _stream())
+        else:
+            import ctypes
+            gr = (ctypes.c_int * ng)(*[int(g) for g in group_rows])
+            rc = _lib.load().biloco_b200_fused_linear_grouped(*ptrs, m_rows, rows, N, K, R // ng, ng, gr, mode, epoch, _stream())
     _lib.check(rc, f"biloco fused linear (mode {mode}, M={m_rows}, N={N}, K={K}, R={R})")
     return D
 

@@ -113,8 +113,8 @@ int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_weight_bf16,
 /* A_rec (optional, biloco_b200_act_rec_bytes(M, K) bytes, K % 256 == 0, M <= 32): the same codes and block scales once
  * more, laid out per 256-wide k-tile exactly as the fused kernel keeps them in shared memory (the activation tile with
  * the 128-byte swizzle applied, followed by its four scale atoms). biloco_b200_fused_linear_rec then fetches the
- * activation side of a work unit with ONE bulk copy instead of a tiled TMA load plus a bulk copy: the copy engine of
- * an SM takes requests one at a time, and three requests per unit held the stream at 3.7 TB/s on 8192 x 28672.
+ * activation side of a work unit with ONE bulk copy instead of a tiled TMA load plus a bulk copy (two requests per
+ * unit instead of three, no tensor map on the path; results are bit-identical, and the measured time is the same).
  * Internal layout of this library (like the unit-contiguous weights); no counterpart in the reference. */
 size_t biloco_b200_act_rec_bytes(int M, int K);
 int biloco_b200_fused_linear_rec(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
@@ -122,6 +122,23 @@ int biloco_b200_fused_linear_rec(const void* W_codes, const void* W_sf, const vo
                                  const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16,
                                  void* Y_bf16, void* scratch, size_t scratch_bytes, int M, int A_rows, int N, int K,
                                  int R, int mode, int epoch, biloco_stream_t stream);
+
+/* Several linears that read the same activation (q/k/v, gate/up) in ONE launch: n_groups (1..4) column groups stacked
+ * along N, group g covering group_rows[g] output columns (host array; every entry a multiple of 128, their sum = N).
+ * Every group has its own R ranks (R a multiple of 32): V_packed [n_groups*R, K/8] and S_bf16 [n_groups*R] are the
+ * groups' factors stacked in group order, U_col32 [N, R/32] holds for every column the sign words of its own group's
+ * ranks, alpha is an array of n_groups decode scales (what biloco_b200_norm_act_quant writes for n_alpha = n_groups).
+ * W_codes / W_sf / W_tiled are the groups' weights stacked along N (each group re-laid on its own or all at once: the
+ * same bytes), C_bf16 / Y_bf16 are [M, N]. The z stage computes all n_groups*R ranks once; a column tile expands its
+ * own group's. Scratch: biloco_b200_scratch_bytes(M, N, K, n_groups * R, num_sms). A_rec may be NULL.
+ * Column for column the result equals the separate launches' up to the fp32 summation order of the k split.
+ * No counterpart in the reference (one launch per linear, biloco/kernel.py:121-130). */
+int biloco_b200_fused_linear_grouped(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                     const void* A_codes, const void* A_sf, const void* A_rec, const void* X_bf16,
+                                     const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16,
+                                     void* Y_bf16, void* scratch, size_t scratch_bytes, int M, int A_rows, int N, int K,
+                                     int R, int n_groups, const int* group_rows, int mode, int epoch,
+                                     biloco_stream_t stream);
 
 /* Scratch bytes needed by biloco_b200_fused_linear for this problem on a device
  * with `num_sms` multiprocessors (0 = query the current device). The scratch must be zero-filled once

@@ -76,3 +76,6 @@ def test_decode_step_matches_fake_quant_layers_and_graph_replay():
     t_eager, _ = decode.greedy_decode(model, prompt, steps, use_graph=False)
     assert torch.equal(t_graph, t_eager)
     assert all(g_.status()[0] == 0 for m in layers.values() for g_ in m._gemms.values())
+    # q/k/v and gate/up ran as one stacked launch each
+    grouped = [st["grouped"] for st in model._shared.values() if st.get("grouped") is not None]
+    assert len(grouped) == 2 * c.layers and all(g_.status()[0] == 0 for g_ in grouped)

@@ -136,6 +136,54 @@ def test_fused_with_activation_record(kernel, M, K, N, R):
     assert torch.isfinite(y_rec.float()).all() and torch.equal(y_tma.view(torch.int16), y_rec.view(torch.int16))
 
 
+@pytest.mark.parametrize("M,K,R,rows", [(1, 2560, 128, (1024, 256, 256)), (8, 1024, 64, (384, 128)),
+                                        (32, 512, 32, (256, 256, 128, 128)), (16, 1024, 256, (512, 512)),
+                                        (2, 5120, 512, (5120, 1024, 1024))])
+def test_fused_grouped_launch(kernel, M, K, R, rows):
+    """Several linears on one activation as ONE launch (weights stacked along N, every linear with its own ranks and
+    decode scale): each linear's columns against the oracle's unfused and exact values for that linear, and against the
+    linear's own separate launch; consecutive launches bit-identical."""
+    probs = [orc.random_problem(M, K, n, R, scales="random", seed=31 * M + R + i) for i, n in enumerate(rows)]
+    for q in probs[1:]:                         # all linears read the first problem's activation
+        for k in ("X", "A", "A_pad", "A_sf"):
+            q[k] = probs[0][k]
+    ts = [dev_problem(q) for q in probs]
+    t0 = ts[0]
+    singles = [kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M) for t in ts]
+    alpha = torch.cat([t["alpha"] for t in ts]).contiguous()
+    refs = [oracle_outputs(q, M) for q in probs]
+    N = sum(rows)
+    for mode in kernel.supported_modes(M, N, K, R * len(rows)):
+        g = kernel.GroupedBiLoCoGemm(singles, mode=mode)
+        first = None
+        for it in range(3):
+            ys = [y.float().cpu().numpy() for y in g(alpha, t0["A_pad"], t0["A_sf"], t0["X"])]
+            for i, (y, (y_ref, y_exact)) in enumerate(zip(ys, refs)):
+                check_against_unfused(y, y_ref, f"grouped mode {mode} linear {i} launch {it}")
+                check_against_exact(y, y_exact, f"grouped mode {mode} linear {i} launch {it}")
+            if first is None:
+                first = ys
+            assert all(np.array_equal(a, b) for a, b in zip(ys, first)), f"grouped mode {mode}: launch {it} differs from launch 0"
+        assert g.status()[0] == 0, f"device-side wait ran out: {g.status()[:4]}"
+        for i, (sg, t) in enumerate(zip(singles, ts)):
+            y1 = sg(t0["A_pad"], t0["A_sf"], t0["X"]).view(-1, rows[i])[:M].float().cpu().numpy()
+            check_against_unfused(first[i], y1, f"grouped mode {mode} linear {i} vs its own launch")
+
+
+def test_grouped_launch_rejects_bad_groups(kernel):
+    from biloco_b200 import ops
+    p = orc.random_problem(1, 256, 256, 64, scales="random", seed=3)
+    t = dev_problem(p)
+    g = kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=1)
+    two = torch.cat([t["alpha"], t["alpha"]])
+    with pytest.raises(RuntimeError):          # groups must be whole 128-column tiles
+        ops._fused(t["A_pad"], t["W"], t["A_sf"], t["W_sf"], two, t["X"], t["V_packed"], t["S"],
+                   g.U_col32[:, :1].contiguous(), g.z, 1, 1, 2, group_rows=[192, 64])
+    with pytest.raises(RuntimeError):          # and add up to N
+        ops._fused(t["A_pad"], t["W"], t["A_sf"], t["W_sf"], two, t["X"], t["V_packed"], t["S"],
+                   g.U_col32[:, :1].contiguous(), g.z, 1, 1, 2, group_rows=[128, 256])
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 128, 256), (4, 256, 1024), (3, 136, 512)])
 def test_fp4_gemm_simt(kernel, lib, M, N, K):
     p = orc.random_problem(M, K, N, 8, scales="random", seed=7)
