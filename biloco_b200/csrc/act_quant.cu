@@ -65,7 +65,7 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
                                                               float* __restrict__ alpha_out, const float* __restrict__ w_gscale,
                                                               int M, int A_rows, int K, int rule, int given_scale, float target,
                                                               int csize, const __nv_bfloat16* __restrict__ norm_w, float eps, int n_alpha,
-                                                              uint8_t* __restrict__ rec) {
+                                                              uint8_t* __restrict__ rec, int swiglu) {
     const int kblocks = K >> 4;
     __shared__ float red[Q_THREADS / 32];
     __shared__ float gs_sh;
@@ -128,6 +128,45 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
         if (csize > 1) biloco::cluster_sync_all();
         else __syncthreads();
         X = Xs;                 // from here on: an already normalised and smoothed activation, nothing left to write back
+        smooth = nullptr;
+        Xs = nullptr;
+    }
+    // ---- optional gated activation in front: X is [M, 2K] = [gate | up] (the stacked output of a gate/up launch) and the
+    //      activation is bf16(bf16(silu(gate)) * up), silu(g) = g / (1 + exp(-g)) in fp32 (the roundings of the separate
+    //      silu and multiply kernels it replaces); then the smoothing division. Rows are shared as in the norm path ----
+    if (swiglu) {
+        const int kvec = K >> 3;
+        for (int row = csize > 1 ? (int)(blockIdx.x % (unsigned)csize) : 0; row < M; row += csize) {
+            const uint4* gr = reinterpret_cast<const uint4*>(X + (size_t)row * 2 * K);
+            const uint4* ur = gr + kvec;
+            uint4* xo = reinterpret_cast<uint4*>(Xs + (size_t)row * K);
+            for (int i = threadIdx.x; i < kvec; i += Q_THREADS) {
+                const uint4 a = gr[i], b = ur[i];
+                uint4 c = make_uint4(0u, 0u, 0u, 0u);
+                if (smooth) c = reinterpret_cast<const uint4*>(smooth)[i];
+                const uint32_t gw[4] = {a.x, a.y, a.z, a.w}, uw[4] = {b.x, b.y, b.z, b.w}, sw[4] = {c.x, c.y, c.z, c.w};
+                uint32_t o[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float gv[2] = {__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xFFFF0000u)};
+                    const float uv[2] = {__uint_as_float(uw[e] << 16), __uint_as_float(uw[e] & 0xFFFF0000u)};
+                    const float sv[2] = {__uint_as_float(sw[e] << 16), __uint_as_float(sw[e] & 0xFFFF0000u)};
+                    float v[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        v[h] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(gv[h], __fadd_rn(1.0f, expf(-gv[h])))));
+                        v[h] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v[h], uv[h])));
+                        if (smooth) v[h] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v[h], sv[h])));
+                    }
+                    o[e] = (__float_as_uint(v[0]) >> 16) | (__float_as_uint(v[1]) & 0xFFFF0000u);
+                }
+                xo[i] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
+        __threadfence();
+        if (csize > 1) biloco::cluster_sync_all();
+        else __syncthreads();
+        X = Xs;
         smooth = nullptr;
         Xs = nullptr;
     }
@@ -274,7 +313,8 @@ __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat1
 
 static int launch_act_quant(const void* X_bf16, const void* norm_w, float eps, const void* smooth_bf16, void* Xs_bf16, void* A_codes,
                             void* A_sf, void* A_rec, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M,
-                            int A_rows, int K, int rule, biloco_stream_t stream) {
+                            int A_rows, int K, int rule, biloco_stream_t stream, int swiglu = 0) {
+    if (swiglu && (!Xs_bf16 || norm_w)) return BILOCO_ERR_NULL;
     if (A_rec && (M > 32 || (K % 256) != 0 || ((uintptr_t)A_rec & 15))) return BILOCO_ERR_SHAPE;
     if (!X_bf16 || !A_codes || !A_sf || !a_gscale) return BILOCO_ERR_NULL;
     if (norm_w && !Xs_bf16) return BILOCO_ERR_NULL;
@@ -316,7 +356,7 @@ static int launch_act_quant(const void* X_bf16, const void* norm_w, float eps, c
     cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, act_quant_kernel, (const __nv_bfloat16*)X_bf16, (const __nv_bfloat16*)smooth_bf16,
                            (__nv_bfloat16*)Xs_bf16, (uint8_t*)A_codes, (uint8_t*)A_sf, a_gscale, alpha_out, w_gscale, M, A_rows, K,
-                           rule, given_scale ? 1 : 0, target, csize, (const __nv_bfloat16*)norm_w, eps, n_alpha, (uint8_t*)A_rec) != cudaSuccess)
+                           rule, given_scale ? 1 : 0, target, csize, (const __nv_bfloat16*)norm_w, eps, n_alpha, (uint8_t*)A_rec, swiglu) != cudaSuccess)
         return BILOCO_ERR_CUDA;
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
@@ -334,4 +374,11 @@ extern "C" int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_w
                                           biloco_stream_t stream) {
     return launch_act_quant(X_bf16, norm_weight_bf16, eps, smooth_bf16, Xn_bf16, A_codes, A_sf, A_rec, a_gscale, alpha_out, w_gscale,
                             n_alpha, M, A_rows, K, rule, stream);
+}
+
+extern "C" int biloco_b200_swiglu_act_quant(const void* GU_bf16, const void* smooth_bf16, void* Xa_bf16, void* A_codes, void* A_sf,
+                                            void* A_rec, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M,
+                                            int A_rows, int K, int rule, biloco_stream_t stream) {
+    return launch_act_quant(GU_bf16, nullptr, 0.f, smooth_bf16, Xa_bf16, A_codes, A_sf, A_rec, a_gscale, alpha_out, w_gscale, n_alpha, M,
+                            A_rows, K, rule, stream, 1);
 }

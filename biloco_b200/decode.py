@@ -101,6 +101,8 @@ class Decoder(nn.Module):
         self.c, self.tp, self.group = c, tp, group
         self.fuse_norm_quant, self._shared = True, {}     # (see _normed_linears)
         self.fuse_groups = True                           # q/k/v and gate/up as one stacked launch each
+        self.fuse_step = True                             # attention step as one launch; SwiGLU inside the down projection's
+                                                          # quantiser launch; residual adds inside the o / down launches
         lin_dev = "meta" if meta else device
         self.embed = nn.Embedding(c.vocab, c.hidden, device=device, dtype=dtype)
         self.blocks = nn.ModuleList(Block(c, lin_dev, dtype, tp) for _ in range(c.layers))
@@ -128,18 +130,20 @@ class Decoder(nn.Module):
         ang = torch.arange(max_len, device=device, dtype=torch.float32)[:, None] * inv[None, :]
         return dict(kv=kv, cos=ang.cos(), sin=ang.sin(), positions=torch.arange(max_len, device=device))
 
-    def _normed_linears(self, h, norm_w, layers, key):
+    def _normed_linears(self, h, norm_w, layers, key, stacked=False):
         """[layer(rmsnorm(h) * norm_w) for layer in layers]. When the layers are unsmoothed kernel-backed BiLoCo layers
         the norm, the NVFP4 quantisation and one decode scale per layer come from ONE launch (the activation is the
         same for all of them), followed by ONE stacked fused-linear launch for all of them (fuse_groups; needs equal
-        ranks and whole 128-column tiles) or one fused linear per layer; otherwise the plain composition."""
+        ranks and whole 128-column tiles) or one fused linear per layer; otherwise the plain composition.
+        stacked=True returns the outputs side by side as one [M, sum N] tensor instead of a list."""
         from . import fp4
         M = h.shape[0]
         fusable = self.fuse_norm_quant and M <= 32 and all(isinstance(l, BiLoCoLinear) and l.weight is None and not l.smoothed
                                                            and l.rank > 0 for l in layers)
         if not fusable:
             x = _rms(h, norm_w, self.c.eps)
-            return [l(x) for l in layers]
+            ys = [l(x) for l in layers]
+            return torch.cat(ys, dim=-1) if stacked else ys
         st = self._shared.get((key, M))
         if st is None:
             st = dict(w_gs=torch.cat([l.w_gscale.reshape(1) for l in layers]).contiguous(), q=None)
@@ -155,8 +159,26 @@ class Decoder(nn.Module):
                 for l in layers:
                     l._gemms.pop(M, None)
         if self.fuse_groups and st.get("grouped") is not None:
-            return st["grouped"](q["alpha"], q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec"))
-        return [l.forward_quantized(q, q["alpha"][i:i + 1]) for i, l in enumerate(layers)]
+            return st["grouped"](q["alpha"], q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec"), stacked=stacked)
+        ys = [l.forward_quantized(q, q["alpha"][i:i + 1]) for i, l in enumerate(layers)]
+        return torch.cat(ys, dim=-1) if stacked else ys
+
+    def _attention_step(self, qkv, b, cache, kc, vc, pos, heads, kv_heads):
+        """q/k norms, rotary embedding, cache update and attention over the cache for the current position in ONE launch of
+        the library (biloco_b200_decode_attention). qkv [M, (heads + 2 kv_heads) * head_dim] -> [M, heads * head_dim]."""
+        from . import _lib
+        c = self.c
+        M = qkv.shape[0]
+        out = torch.empty(M, heads * c.head_dim, device=qkv.device, dtype=torch.bfloat16)
+        qn = b.q_norm if c.qk_norm else None
+        kn = b.k_norm if c.qk_norm else None
+        with torch.cuda.device(qkv.device):
+            rc = _lib.load().biloco_b200_decode_attention(
+                qkv.data_ptr(), qn.data_ptr() if qn is not None else None, kn.data_ptr() if kn is not None else None, float(c.eps),
+                cache["cos"].data_ptr(), cache["sin"].data_ptr(), pos.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                M, heads, kv_heads, c.head_dim, kc.shape[2], torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "decode_attention")
+        return out
 
     @staticmethod
     def _rope(x, cos, sin):                  # x [M, H, D]; cos/sin [1, D/2]
@@ -173,18 +195,33 @@ class Decoder(nn.Module):
         cos = cache["cos"].index_select(0, pos)
         sin = cache["sin"].index_select(0, pos)
         mask = (cache["positions"] <= pos)[None, None, None, :]
+        kc0 = cache["kv"][0][0]
+        fuse = (self.fuse_step and h.is_cuda and M <= 32 and c.head_dim in (64, 128) and kc0.dtype == torch.bfloat16
+                and kc0.is_contiguous())
+
+        def kernel_layer(l):     # a quantised layer whose launches can take the residual / the gated activation
+            return fuse and isinstance(l, BiLoCoLinear) and l.weight is None and l.bias is None
         for li, (b, (kc, vc)) in enumerate(zip(self.blocks, cache["kv"])):
-            q, k, v = self._normed_linears(h, b.input_norm, [b.q_proj, b.k_proj, b.v_proj], (li, "qkv"))
-            q, k, v = q.view(M, heads, c.head_dim), k.view(M, kv_heads, c.head_dim), v.view(M, kv_heads, c.head_dim)
-            if c.qk_norm:
-                q, k = _rms(q, b.q_norm, c.eps), _rms(k, b.k_norm, c.eps)
-            q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
-            kc.index_copy_(2, pos, k.unsqueeze(2).to(kc.dtype))
-            vc.index_copy_(2, pos, v.unsqueeze(2).to(vc.dtype))
-            a = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, attn_mask=mask, enable_gqa=True)
-            h = h + b.o_proj(a.reshape(M, heads * c.head_dim))
-            gate, up = self._normed_linears(h, b.post_norm, [b.gate_proj, b.up_proj], (li, "mlp"))
-            h = h + b.down_proj(F.silu(gate) * up)
+            if fuse:
+                qkv = self._normed_linears(h, b.input_norm, [b.q_proj, b.k_proj, b.v_proj], (li, "qkv"), stacked=True)
+                a = self._attention_step(qkv.contiguous(), b, cache, kc, vc, pos, heads, kv_heads)
+            else:
+                q, k, v = self._normed_linears(h, b.input_norm, [b.q_proj, b.k_proj, b.v_proj], (li, "qkv"))
+                q, k, v = q.view(M, heads, c.head_dim), k.view(M, kv_heads, c.head_dim), v.view(M, kv_heads, c.head_dim)
+                if c.qk_norm:
+                    q, k = _rms(q, b.q_norm, c.eps), _rms(k, b.k_norm, c.eps)
+                q, k = self._rope(q, cos, sin), self._rope(k, cos, sin)
+                kc.index_copy_(2, pos, k.unsqueeze(2).to(kc.dtype))
+                vc.index_copy_(2, pos, v.unsqueeze(2).to(vc.dtype))
+                a = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, attn_mask=mask, enable_gqa=True)
+                a = a.reshape(M, heads * c.head_dim)
+            h = b.o_proj.forward_fused(a, residual=h) if kernel_layer(b.o_proj) else h + b.o_proj(a)
+            if kernel_layer(b.down_proj):
+                gu = self._normed_linears(h, b.post_norm, [b.gate_proj, b.up_proj], (li, "mlp"), stacked=True)
+                h = b.down_proj.forward_fused(gu.contiguous(), residual=h, swiglu=True)
+            else:
+                gate, up = self._normed_linears(h, b.post_norm, [b.gate_proj, b.up_proj], (li, "mlp"))
+                h = h + b.down_proj(F.silu(gate) * up)
         logits, = self._normed_linears(h, self.norm, [self.lm_head], (-1, "head"))
         if self.tp > 1:         # every rank gets the whole vocabulary (and takes the same argmax)
             parts = [torch.empty_like(logits) for _ in range(self.tp)]
@@ -274,6 +311,7 @@ def main():
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a captured step")
     ap.add_argument("--no-fuse", action="store_true", help="separate RMSNorm kernels and one quantiser launch per linear")
+    ap.add_argument("--no-step-fusion", action="store_true", help="attention step, SwiGLU and residual adds as separate torch kernels")
     ap.add_argument("--no-groups", action="store_true", help="one fused-linear launch per linear (q, k, v, gate, up separately)")
     args = ap.parse_args()
     assert torch.cuda.is_available(), "decode needs a CUDA device (there is no CPU path)"
@@ -291,6 +329,7 @@ def main():
     model = Decoder(c, device=dev, meta=True, tp=world)
     model.fuse_norm_quant = not args.no_fuse
     model.fuse_groups = not args.no_groups
+    model.fuse_step = not args.no_step_fusion
     nlin = synthetic_quantize(model, args.rank, seed=args.seed + 1000 * rank)
     g = torch.Generator(device=dev).manual_seed(args.seed)           # (same prompt on every rank)
     prompt = torch.randint(0, c.vocab, (args.M, args.prompt), device=dev, generator=g)
@@ -314,7 +353,7 @@ def main():
     print(json.dumps({
         "metric": "decode tokens/s", "value": args.M * args.steps / sec, "unit": "tokens/s", "M": args.M, "n_gpus": world,
         "ms_per_step": sec / args.steps * 1e3, "model": args.model, "layers": c.layers, "linears": nlin, "rank": args.rank,
-        "prompt": args.prompt, "steps": args.steps, "fused_norm_quant": model.fuse_norm_quant, "stacked_qkv_gateup": model.fuse_groups and model.fuse_norm_quant, "data": "synthetic (random packed operands, random prompt)",
+        "prompt": args.prompt, "steps": args.steps, "fused_norm_quant": model.fuse_norm_quant, "stacked_qkv_gateup": model.fuse_groups and model.fuse_norm_quant, "fused_step": model.fuse_step, "data": "synthetic (random packed operands, random prompt)",
         "linear_bytes_per_step": nbytes, "linear_GBps": gbs, "hbm_peak_GBps": peak,
         "roofline_frac": (gbs / (peak * world)) if peak else None, "finite": bool(torch.isfinite(toks.float()).all())}))
     if world > 1:

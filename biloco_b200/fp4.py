@@ -148,7 +148,7 @@ def _rec_buffer(M: int, K: int, dev):
 
 def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor = None, w_gscale: torch.Tensor = None,
                         rows: int = None, out: dict = None, gscale: torch.Tensor = None, norm_weight: torch.Tensor = None,
-                        eps: float = 1e-6):
+                        eps: float = 1e-6, swiglu: bool = False):
     """bf16 CUDA activation [M, K] -> dict(A [1, rows, K/2] uint8, A_sf float8 (atom layout), A_rec (the same codes and
     scales as the fused kernel stages them, or None), gscale fp32 [1],
     alpha fp32 [1] (= w_gscale * gscale, when w_gscale is given), X bf16 [M, K] (x / smooth when smoothing)).
@@ -157,10 +157,15 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
     an earlier call with the same shapes) to reuse its buffers, e.g. under CUDA-graph capture.
     ``norm_weight`` (bf16 [K]): RMS-normalise every row first (x * rsqrt(mean(x^2) + eps) -> bf16, * weight -> bf16) inside
     the same launch; X is then the normalised activation. ``w_gscale`` may hold n scales (fp32 [n]): alpha gets one entry
-    per linear that consumes this activation."""
+    per linear that consumes this activation.
+    ``swiglu``: x is [M, 2K] = [gate | up] and the activation quantised is silu(gate) * up (each rounded to bf16, as the
+    separate torch kernels would), computed inside the same launch; X is that activation."""
     rule = CONFIG_X if rule is None else rule
     assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
     M, K = x.shape
+    if swiglu:
+        assert norm_weight is None and gscale is None and K % 2 == 0
+        K //= 2
     rows = M if rows is None else rows
     dev = x.device
     if out is None:
@@ -168,9 +173,10 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
                    A_sf=torch.empty(nvfp4_sf_bytes(rows, K), device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn),
                    gscale=torch.empty(1, device=dev, dtype=torch.float32),
                    alpha=torch.empty(w_gscale.numel(), device=dev, dtype=torch.float32) if w_gscale is not None else None,
-                   X=torch.empty_like(x) if (smooth is not None or norm_weight is not None) else x,
+                   X=(torch.empty((M, K), device=dev, dtype=torch.bfloat16)
+                      if (smooth is not None or norm_weight is not None or swiglu) else x),
                    A_rec=_rec_buffer(M, K, dev))
-    elif smooth is None and norm_weight is None:
+    elif smooth is None and norm_weight is None and not swiglu:
         out["X"] = x
     rule_id = _lib.RULES[rule]
     if gscale is not None:          # tensor scale agreed elsewhere (tensor-parallel K-slices): do not recompute it
@@ -179,7 +185,14 @@ def quantize_activation(x: torch.Tensor, rule: str = None, smooth: torch.Tensor 
     n_alpha = w_gscale.numel() if w_gscale is not None else 1
     rec = out.get("A_rec")
     with torch.cuda.device(dev):
-        if norm_weight is None and n_alpha == 1 and rec is None:
+        if swiglu:
+            rc = _lib.load().biloco_b200_swiglu_act_quant(
+                x.data_ptr(), smooth.data_ptr() if smooth is not None else None, out["X"].data_ptr(), out["A"].data_ptr(),
+                out["A_sf"].data_ptr(), rec.data_ptr() if rec is not None else None, out["gscale"].data_ptr(),
+                out["alpha"].data_ptr() if w_gscale is not None else None,
+                w_gscale.data_ptr() if w_gscale is not None else None, n_alpha, M, rows, K, rule_id,
+                torch.cuda.current_stream().cuda_stream)
+        elif norm_weight is None and n_alpha == 1 and rec is None:
             rc = _lib.load().biloco_b200_act_quant(
                 x.data_ptr(), smooth.data_ptr() if smooth is not None else None,
                 out["X"].data_ptr() if smooth is not None else None, out["A"].data_ptr(), out["A_sf"].data_ptr(),

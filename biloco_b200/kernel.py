@@ -206,11 +206,13 @@ class GroupedBiLoCoGemm:
 
     status = BiLoCoGemm.status
 
-    def __call__(self, alpha, A_pad, A_sf, X_bf16, out=None, A_rec=None):
+    def __call__(self, alpha, A_pad, A_sf, X_bf16, out=None, A_rec=None, stacked=False):
+        """The per-linear outputs, or (stacked=True) the [M, sum N_g] tensor they are views of."""
         self.epoch += 1
         D = _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, alpha, X_bf16, self.V, self.S, self.U_col32, self.z, self.M,
                         self.epoch, self.mode, out=out, A_rec=A_rec, B_tiled=self.W_tiled, group_rows=self.rows)
-        return list(D.view(-1, self.N)[: self.M].split(self.rows, dim=1))
+        D = D.view(-1, self.N)[: self.M]
+        return D if stacked else list(D.split(self.rows, dim=1))
 
 
 class _FP4Only:

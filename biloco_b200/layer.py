@@ -112,13 +112,26 @@ class BiLoCoLinear(nn.Module):
             self._gemms[M] = g
         return g
 
-    def _rows(self, x2):
+    def _rows(self, x2, residual=None, swiglu=False):
         M = x2.shape[0]
         q = fp4.quantize_activation(x2, fp4.CONFIG_X, smooth=self.smooth_scale if self.smoothed else None,
-                                    w_gscale=self.w_gscale, rows=M, out=self._acts.get(M))
-        self._acts[M] = q
+                                    w_gscale=self.w_gscale, rows=M, out=self._acts.get((M, swiglu)), swiglu=swiglu)
+        self._acts[(M, swiglu)] = q
         g = self._gemm_for(M, q["alpha"])
+        if self.bias is None:          # (with a bias, residual holds the broadcast bias)
+            g.residual = residual
         return g(q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec")).view(-1, self.out_features)[:M]
+
+    def forward_fused(self, x, residual=None, swiglu=False):
+        """The kernel forward for at most 32 rows with the steps either side of the linear folded into its launches
+        (not in the reference's interface): ``swiglu`` — x is [M, 2 * in_features] = [gate | up] and the layer's input is
+        silu(gate) * up, formed inside the quantiser launch; ``residual`` (bf16 [M, out_features], layers without bias) is
+        added inside the fused kernel before its single rounding to bf16."""
+        assert self.weight is None and x.dim() == 2 and x.shape[0] <= MAX_ROWS and x.dtype == torch.bfloat16
+        assert x.shape[1] == self.in_features * (2 if swiglu else 1)
+        assert residual is None or (self.bias is None and residual.dtype == torch.bfloat16 and residual.is_contiguous()
+                                    and residual.shape == (x.shape[0], self.out_features))
+        return self._rows(x.contiguous(), residual=residual, swiglu=swiglu)
 
     def forward_quantized(self, q: dict, alpha: torch.Tensor):
         """The fused linear on an activation that has been quantised already (fp4.quantize_activation with this layer's

@@ -110,6 +110,14 @@ int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_weight_bf16,
                                const float* w_gscale, int n_alpha, int M, int A_rows, int K, int rule,
                                biloco_stream_t stream);
 
+/* The same with the gated activation of a SwiGLU block folded in: GU_bf16 is [M, 2K] = [gate | up] (the stacked output
+ * of a gate/up launch), the activation is bf16(bf16(silu(gate)) * up) with silu(g) = g / (1 + exp(-g)) in fp32 (the
+ * roundings of the separate silu and multiply it replaces), divided by smooth_bf16 if given; it is written to Xa_bf16
+ * [M, K] (required) and quantised. No counterpart in the reference (the surrounding model does this in torch). */
+int biloco_b200_swiglu_act_quant(const void* GU_bf16, const void* smooth_bf16, void* Xa_bf16, void* A_codes, void* A_sf,
+                                 void* A_rec, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M,
+                                 int A_rows, int K, int rule, biloco_stream_t stream);
+
 /* A_rec (optional, biloco_b200_act_rec_bytes(M, K) bytes, K % 256 == 0, M <= 32): the same codes and block scales once
  * more, laid out per 256-wide k-tile exactly as the fused kernel keeps them in shared memory (the activation tile with
  * the 128-byte swizzle applied, followed by its four scale atoms). biloco_b200_fused_linear_rec then fetches the
@@ -139,6 +147,18 @@ int biloco_b200_fused_linear_grouped(const void* W_codes, const void* W_sf, cons
                                      void* Y_bf16, void* scratch, size_t scratch_bytes, int M, int A_rows, int N, int K,
                                      int R, int n_groups, const int* group_rows, int mode, int epoch,
                                      biloco_stream_t stream);
+
+/* One decode step of attention between the stacked q/k/v launch and the output projection, as one launch: qkv_bf16
+ * [M, (H + 2*KVH) * D] (q heads, k heads, v heads; D = 64 or 128); optional per-head RMS norm of q and k (bf16 [D] weights,
+ * NULL = none); rotary embedding (halves convention) from cos_table / sin_table fp32 [max_len, D/2] at the position
+ * pos_dev[0] (int64 in device memory, so that a captured graph can be replayed while it advances); the new key and value
+ * are written to k_cache / v_cache bf16 [M, KVH, max_len, D] at that position; out_bf16 [M, H*D] = softmax(q k^T /
+ * sqrt(D)) v over positions 0 .. pos, fp32 arithmetic on bf16 inputs. Query head h reads KV head h / (H / KVH).
+ * No counterpart in the reference (the surrounding model does this with framework tensor operations). */
+int biloco_b200_decode_attention(const void* qkv_bf16, const void* q_norm_bf16, const void* k_norm_bf16, float eps,
+                                 const float* cos_table, const float* sin_table, const long long* pos_dev,
+                                 void* k_cache_bf16, void* v_cache_bf16, void* out_bf16, int M, int H, int KVH, int D,
+                                 int max_len, biloco_stream_t stream);
 
 /* Scratch bytes needed by biloco_b200_fused_linear for this problem on a device
  * with `num_sms` multiprocessors (0 = query the current device). The scratch must be zero-filled once

@@ -51,12 +51,14 @@ def test_decode_step_matches_fake_quant_layers_and_graph_replay():
         try:
             BiLoCoLinear.forward = BiLoCoLinear.forward_fake_quant
             model.fuse_norm_quant = False          # separate norm kernels, every linear through its own forward
+            model.fuse_step = False                # (and the attention step, SwiGLU and residual adds in torch)
             cache = model.new_cache(M, P)
             for t in range(P):
                 ref_logits = model.step(prompt[:, t], torch.tensor([t], device="cuda"), cache)
         finally:
             BiLoCoLinear.forward = fwd
             model.fuse_norm_quant = True
+            model.fuse_step = True
             for h in hooks:
                 h.remove()
         assert torch.isfinite(ref_logits.float()).all() and len(seen) == P * len(layers)
@@ -79,3 +81,73 @@ def test_decode_step_matches_fake_quant_layers_and_graph_replay():
     # q/k/v and gate/up ran as one stacked launch each
     grouped = [st["grouped"] for st in model._shared.values() if st.get("grouped") is not None]
     assert len(grouped) == 2 * c.layers and all(g_.status()[0] == 0 for g_ in grouped)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,H,KVH,D,qk_norm", [(1, 32, 8, 128, True), (3, 4, 2, 64, True), (8, 8, 8, 128, False), (2, 6, 2, 64, False)])
+def test_attention_step_kernel_matches_torch_composition(M, H, KVH, D, qk_norm):
+    """biloco_b200_decode_attention against the decoder's own torch composition (q/k RMS norm, rotary embedding, cache
+    update, masked attention) over several consecutive positions. Tolerances: the rotated key without a norm is
+    bit-exact (same fp32 operations); with the norm one bf16 ulp (the sum of squares is taken in another order); the
+    attention output 1e-2 of the row maximum (bf16 output, fp32 softmax on both sides)."""
+    torch.manual_seed(M * 100 + H)
+    c = decode.DecoderConfig(1, H * D, 256, H, KVH, D, 512, qk_norm=qk_norm)
+    model = decode.Decoder(c, device="cuda", meta=True)
+    b = model.blocks[0]
+    if qk_norm:
+        b.q_norm.data = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+        b.k_norm.data = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16)
+    L = 40
+    ca, cb = model.new_cache(M, L), model.new_cache(M, L)
+    for t in range(0, L, 3):          # (positions in between stay zero in both caches and take part in the softmax alike)
+        pos = torch.tensor([t], device="cuda")
+        qkv = torch.randn(M, (H + 2 * KVH) * D, device="cuda").to(torch.bfloat16)
+        out = model._attention_step(qkv, b, ca, ca["kv"][0][0], ca["kv"][0][1], pos, H, KVH)
+        q, k, v = qkv.split([H * D, KVH * D, KVH * D], dim=-1)
+        q, k, v = q.reshape(M, H, D), k.reshape(M, KVH, D), v.reshape(M, KVH, D)
+        if qk_norm:
+            q, k = decode._rms(q, b.q_norm, c.eps), decode._rms(k, b.k_norm, c.eps)
+        cos, sin = cb["cos"].index_select(0, pos), cb["sin"].index_select(0, pos)
+        q, k = model._rope(q, cos, sin), model._rope(k, cos, sin)
+        kc, vc = cb["kv"][0]
+        kc.index_copy_(2, pos, k.unsqueeze(2))
+        vc.index_copy_(2, pos, v.unsqueeze(2))
+        mask = (cb["positions"] <= pos)[None, None, None, :]
+        ref = torch.nn.functional.scaled_dot_product_attention(q.unsqueeze(2).float(), kc.float(), vc.float(), attn_mask=mask,
+                                                               enable_gqa=True).reshape(M, H * D)
+        ka, kb = ca["kv"][0][0][:, :, t].float(), kc[:, :, t].float()
+        if qk_norm:
+            assert torch.all((ka - kb).abs() <= 2.0 ** -7 * kb.abs() + 1e-30)
+        else:
+            assert torch.equal(ka, kb)
+        assert torch.equal(ca["kv"][0][1][:, :, t], vc[:, :, t])
+        err = (out.float() - ref).abs().max(dim=-1).values
+        assert torch.all(err <= 1e-2 * ref.abs().max(dim=-1).values), (t, err)
+        cb["kv"][0][0][:, :, t] = ca["kv"][0][0][:, :, t]     # keep the two caches identical for the next position
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,smooth", [(1, 9728, False), (8, 512, True), (32, 1024, False)])
+def test_swiglu_quantiser_and_fused_residual(M, K, smooth):
+    """The SwiGLU form of the quantiser writes exactly bf16(silu(gate)) * up as torch computes it and quantises it exactly as
+    the plain quantiser does; forward_fused(residual=...) adds the residual inside the launch."""
+    from biloco_b200 import fp4
+    torch.manual_seed(K + M)
+    gu = (2 * torch.randn(M, 2 * K, device="cuda")).to(torch.bfloat16)
+    sm = (0.5 + torch.rand(K, device="cuda")).to(torch.bfloat16) if smooth else None
+    wg = torch.tensor([1e-3], device="cuda")
+    a = fp4.quantize_activation(gu, "mse", smooth=sm, w_gscale=wg, rows=M, swiglu=True)
+    x = torch.nn.functional.silu(gu[:, :K]) * gu[:, K:]
+    bq = fp4.quantize_activation(x.contiguous(), "mse", smooth=sm, w_gscale=wg, rows=M)
+    assert torch.equal(a["X"].view(torch.int16), bq["X"].view(torch.int16))
+    for k in ("A", "A_sf", "gscale", "alpha", "A_rec"):
+        if a[k] is not None:
+            assert torch.equal(a[k].view(torch.uint8), bq[k].view(torch.uint8)), k
+    N = 256
+    layer = BiLoCoLinear.synthetic(K, N, 64, "cuda", seed=7)
+    res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    y0 = layer(x).float()
+    y1 = layer.forward_fused(gu, residual=res, swiglu=True).float()
+    want = y0 + res.float()
+    assert torch.all((y1 - want).abs() <= 2.0 ** -7 * want.abs().max())
+    assert torch.equal(layer(x).float(), y0)          # the residual does not stick to the launcher
