@@ -234,7 +234,15 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
-    if (g_use_pdl) {
+    // Every CTA of the grid must be resident at the same time (the z exchange). A cluster launch whose CTAs each take a
+    // whole SM and together nearly all SMs (48 clusters of 3 on 148 SMs, say) only fits when the clusters pack perfectly;
+    // started early, beside the last CTAs of a predecessor with another cluster shape, the first clusters were placed
+    // where the rest no longer fitted and the launch sat until its waits ran out (seen with q/k/v stacked at M = 8 behind
+    // a 7-CTA-cluster launch). Such launches start on an empty device: no programmatic early start for them.
+    int dev_sms = 0;
+    cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, dev);
+    const bool tight_clusters = p.cluster > 1 && ctas_per_sm(ROWS) == 1 && p.G * 20 > dev_sms * 17;
+    if (g_use_pdl && !tight_clusters) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;

@@ -151,3 +151,27 @@ def test_swiglu_quantiser_and_fused_residual(M, K, smooth):
     want = y0 + res.float()
     assert torch.all((y1 - want).abs() <= 2.0 ** -7 * want.abs().max())
     assert torch.equal(layer(x).float(), y0)          # the residual does not stick to the launcher
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M", [8, 32])
+def test_captured_step_chain_at_full_layer_shapes(M):
+    """A few Qwen3-4B-shaped layers (random packed operands) decoded through the captured step: every launch of the chain
+    quantiser -> stacked q/k/v -> attention -> quantiser -> o -> quantiser -> stacked gate/up -> quantiser -> down runs
+    back to back, each started early behind its predecessor where the launcher allows it. No device-side wait may run
+    out (launches whose CTAs must all be resident together, placed beside a predecessor of another cluster shape, once
+    did), and the captured step replays to the same tokens as eager launches."""
+    c = decode.DecoderConfig(**{**decode.PRESETS["qwen3-4b"].__dict__, "layers": 3, "vocab": 8192})
+    torch.manual_seed(0)
+    model = decode.Decoder(c, device="cuda", meta=True)
+    decode.synthetic_quantize(model, 512, seed=0)
+    prompt = torch.randint(0, c.vocab, (M, 3), device="cuda")
+    t_graph, sec = decode.greedy_decode(model, prompt, 4, use_graph=True)
+    t_eager, _ = decode.greedy_decode(model, prompt, 4, use_graph=False)
+    launchers = [g for m in model.modules() if isinstance(m, BiLoCoLinear) for g in m._gemms.values()]
+    launchers += [st["grouped"] for st in model._shared.values() if st.get("grouped") is not None]
+    assert len(launchers) >= 4 * c.layers + 1
+    bad = [(g.N, g.K, g.mode, g.status()[:4]) for g in launchers if g.status()[0] != 0]
+    assert not bad, f"device-side waits ran out: {bad}"
+    assert torch.equal(t_graph, t_eager)
+    assert sec / 4 < 0.05, f"{sec / 4 * 1e3:.1f} ms per step: a wait budget was spent somewhere"
