@@ -26,6 +26,7 @@ SIGNATURES = {
     "biloco_b200_norm_act_quant": (_i, [_vp, _vp, ctypes.c_float, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "biloco_b200_swiglu_act_quant": (_i, [_vp] * 9 + [_i] * 5 + [_vp]),
     "biloco_b200_decode_attention": (_i, [_vp, _vp, _vp, ctypes.c_float] + [_vp] * 6 + [_i] * 5 + [_vp]),
+    "biloco_b200_max_active_clusters": (_i, [_i, _i]),
     "biloco_b200_act_rec_bytes": (_sz, [_i, _i]),
     "biloco_b200_fused_linear_rec": (_i, [_vp] * 14 + [_sz] + [_i] * 7 + [_vp]),
     "biloco_b200_fused_linear_grouped": (_i, [_vp] * 14 + [_sz] + [_i] * 6 + [ctypes.POINTER(ctypes.c_int)] + [_i] * 2 + [_vp]),

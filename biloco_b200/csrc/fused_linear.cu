@@ -175,16 +175,72 @@ __global__ void tile_weights_kernel(const uint8_t* __restrict__ W, const uint8_t
 // (ntile * c <= SMs), at most 8, at most one per k-tile. 0 when the shape does not suit the mode: fewer than two
 // CTAs per tile, more than 8 rows (the peers' partial sums must fit the finisher's work area), or a grid that would
 // leave more than a third of the SMs idle.
-static int cluster_size_for(int M, int ntile, int nkt, int num_sms) {
+static int max_active_clusters(int rows, int cluster);
+
+// on_device: also ask the driver how many such clusters the current device holds at once (needs a CUDA context); the
+// host-only form (an SM count given by the caller) cannot know and assumes they all fit.
+static int cluster_size_for(int M, int ntile, int nkt, int num_sms, bool on_device) {
     if (M > 8) return 0;
     int c = num_sms / ntile;
     if (c > 8) c = 8;
     if (c > nkt) c = nkt;
     const int rows = M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : 8));
     while (c >= 2 && (c - 1) * rows * TILE_N * 4 > RED_BYTES) --c;     // the peers' partial sums must fit beside the staged z
+    if (on_device)
+        while (c >= 2 && max_active_clusters(rows, c) < ntile) --c;    // every cluster of the launch must be resident at once
     if (c < 2) return 0;
     if (ntile * c * 3 < num_sms * 2) return 0;
     return c;
+}
+
+// Clusters of `cluster` CTAs of the kernel for `rows` activation rows that the current device holds at the same time
+// (CTAs with the shared memory the launcher gives them: half an SM for rows <= 2, a whole SM above). Every CTA of a
+// launch must be resident at once (the z exchange), so a cluster schedule needs at least one cluster slot per tile;
+// the number depends on how the device's SMs are grouped, which only the driver knows. 0 when the query fails.
+template <int MMA_N, int ROWS>
+static int query_active_clusters(int cluster) {
+    if (cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET) != cudaSuccess)
+        return 0;
+    if (cluster > 8 && cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+        return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)cluster);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = ctas_per_sm(ROWS) == 2 ? (size_t)CORESIDENT_SMEM : (size_t)SMEM_BUDGET;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, fused_linear_kernel<MMA_N, ROWS>, &cfg) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n;
+}
+
+static int max_active_clusters(int rows, int cluster) {
+    static int cache[64][6][9];           // [device][row class][cluster size], 0 = not asked yet, -1 = query failed
+    int dev = 0;
+    if (cluster < 2 || cluster > 8 || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    const int rc = rows <= 1 ? 0 : (rows <= 2 ? 1 : (rows <= 4 ? 2 : (rows <= 8 ? 3 : (rows <= 16 ? 4 : 5))));
+    int& c = cache[dev][rc][cluster];
+    if (c == 0) {
+        int n = 0;
+        switch (rc) {
+            case 0: n = query_active_clusters<8, 1>(cluster); break;
+            case 1: n = query_active_clusters<8, 2>(cluster); break;
+            case 2: n = query_active_clusters<8, 4>(cluster); break;
+            case 3: n = query_active_clusters<8, 8>(cluster); break;
+            case 4: n = query_active_clusters<16, 16>(cluster); break;
+            default: n = query_active_clusters<32, 32>(cluster); break;
+        }
+        // The query credits one CTA per SM also for rows <= 2, whose CTAs are built so that two share an SM (launch
+        // bounds, 113 KB of shared memory; consecutive launches were observed side by side on the same SMs).
+        if (n > 0 && rc <= 1) n *= 2;
+        c = n > 0 ? n : -1;
+    }
+    return c > 0 ? c : 0;
 }
 
 static int rows_for(int M) { return M <= 1 ? 1 : (M <= 2 ? 2 : (M <= 4 ? 4 : (M <= 8 ? 8 : (M <= 16 ? 16 : 32)))); }
@@ -278,12 +334,18 @@ extern "C" size_t biloco_b200_scratch_head_bytes(int M, int N, int K, int R, int
     return L.off_z;
 }
 
+extern "C" int biloco_b200_max_active_clusters(int M, int cluster) {
+    if (M < 1 || M > 32) return 0;
+    return max_active_clusters(rows_for(M), cluster);
+}
+
 extern "C" int biloco_b200_mode_supported(int M, int N, int K, int R, int mode, int num_sms) {
+    const bool on_device = num_sms == 0;
     if (num_sms == 0) num_sms = device_sm_count();
     ScratchLayout L;
     if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
     if (mode == BILOCO_MODE_COUNTER || mode == BILOCO_MODE_OWNER) return 1;
-    if (mode == BILOCO_MODE_CLUSTER) return cluster_size_for(M, L.ntile, L.nkt, num_sms) >= 2 ? 1 : 0;
+    if (mode == BILOCO_MODE_CLUSTER) return cluster_size_for(M, L.ntile, L.nkt, num_sms, on_device) >= 2 ? 1 : 0;
     return 0;
 }
 
@@ -383,7 +445,7 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
     p.cluster = 0;
     p.ring = g_ring;
     if ((mode & 0xff) == BILOCO_MODE_CLUSTER) {
-        p.cluster = cluster_size_for(M, L.ntile, L.nkt, sms);
+        p.cluster = cluster_size_for(M, L.ntile, L.nkt, sms, true);
         if (p.cluster < 2) return BILOCO_ERR_SHAPE;
         p.G = L.ntile * p.cluster;
     }

@@ -148,6 +148,12 @@ int biloco_b200_fused_linear_grouped(const void* W_codes, const void* W_sf, cons
                                      int R, int n_groups, const int* group_rows, int mode, int epoch,
                                      biloco_stream_t stream);
 
+/* Clusters of `cluster` (2..8) CTAs of the fused kernel for M activation rows that the current device keeps resident at
+ * the same time (driver query; 0 if it fails). The cluster schedule needs one per 128-column tile, because every CTA of
+ * a launch must be resident at once; biloco_b200_mode_supported(..., num_sms = 0) and the launcher take it into account.
+ * No counterpart in the reference. */
+int biloco_b200_max_active_clusters(int M, int cluster);
+
 /* One decode step of attention between the stacked q/k/v launch and the output projection, as one launch: qkv_bf16
  * [M, (H + 2*KVH) * D] (q heads, k heads, v heads; D = 64 or 128); optional per-head RMS norm of q and k (bf16 [D] weights,
  * NULL = none); rotary embedding (halves convention) from cos_table / sin_table fp32 [max_len, D/2] at the position
