@@ -63,13 +63,22 @@ class RowParallel(nn.Module):
         super().__init__()
         self.shard, self.group, self._impl = shard, group, {}
 
-    def forward(self, x):
+    def _impl_for(self, M, local_scale):
         from .parallel import ShardedBiLoCoLinear
+        key = (M, local_scale)
+        if key not in self._impl:
+            self._impl[key] = ShardedBiLoCoLinear(self.shard.export_operands(), "row", M, group=self.group, presharded=True,
+                                                  local_scale=local_scale)
+        return self._impl[key]
+
+    def forward(self, x):
         x2 = x.reshape(-1, self.shard.in_features)
-        M = x2.shape[0]
-        if M not in self._impl:
-            self._impl[M] = ShardedBiLoCoLinear(self.shard.export_operands(), "row", M, group=self.group, presharded=True)
-        return self._impl[M](x2).reshape(*x.shape[:-1], self.shard.out_features)
+        return self._impl_for(x2.shape[0], False)(x2).reshape(*x.shape[:-1], self.shard.out_features)
+
+    def forward_fused(self, x, residual=None, swiglu=False):
+        """The decode-step form: every rank scales its own K-slice (no scale agreement), the residual travels inside rank
+        0's partial sum, silu(gate) * up is formed in the quantiser launch. x [M, K_local] (or [M, 2 K_local])."""
+        return self._impl_for(x.shape[0], True)(x, residual=residual, swiglu=swiglu)
 
 
 class Block(nn.Module):
@@ -200,7 +209,9 @@ class Decoder(nn.Module):
                 and kc0.is_contiguous())
 
         def kernel_layer(l):     # a quantised layer whose launches can take the residual / the gated activation
-            return fuse and isinstance(l, BiLoCoLinear) and l.weight is None and l.bias is None
+            if isinstance(l, RowParallel):
+                l = l.shard
+            return fuse and isinstance(l, BiLoCoLinear) and l.weight is None and l.bias is None and l.rank > 0
         for li, (b, (kc, vc)) in enumerate(zip(self.blocks, cache["kv"])):
             if fuse:
                 qkv = self._normed_linears(h, b.input_norm, [b.q_proj, b.k_proj, b.v_proj], (li, "qkv"), stacked=True)

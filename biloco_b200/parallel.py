@@ -10,7 +10,9 @@ The path shards without an exchange inside the kernel:
 
 The NVFP4 tensor scale of an activation is defined over the whole [tokens, K] tensor; ranks that hold K-slices agree on
 it with a one-float max all-reduce before quantising (`agree_on_activation_scale`), so the codes equal the single-GPU
-ones. The reference has no distributed code; this is the N/K sharding that BASELINE configs 3 and 4 ask for.
+ones. With ``local_scale=True`` every rank scales its own K-slice instead (its partial sum carries its own decode
+scale, so the sum is still the layer's output; the codes then differ from the single-GPU ones, within the same
+tolerance): one collective and half a dozen small kernels less per call, which is what a decode step wants. The reference has no distributed code; this is the N/K sharding that BASELINE configs 3 and 4 ask for.
 """
 import torch
 import torch.distributed as dist
@@ -73,11 +75,12 @@ class ShardedBiLoCoLinear:
     kind = "row":    forward(x_local [M, K/G]) -> y [M, N], all-reduced over the group.
     """
 
-    def __init__(self, ops: dict, kind: str, M: int, group=None, presharded: bool = False):
-        """ops: the operands of the whole layer (sharded here), or with presharded=True this rank's shard as it is."""
+    def __init__(self, ops: dict, kind: str, M: int, group=None, presharded: bool = False, local_scale: bool = False):
+        """ops: the operands of the whole layer (sharded here), or with presharded=True this rank's shard as it is.
+        local_scale (row shards): every rank quantises its K-slice with its own tensor scale (see the module text)."""
         from .kernel import BiLoCoGemm
         assert kind in ("column", "row")
-        self.kind, self.M, self.group = kind, M, group
+        self.kind, self.M, self.group, self.local_scale = kind, M, group, local_scale
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.ops = dict(ops) if presharded else (shard_column_parallel if kind == "column" else shard_row_parallel)(ops, world, rank)
@@ -89,16 +92,31 @@ class ShardedBiLoCoLinear:
         self.gemm.fp32_out = kind == "row"     # partial sums are reduced in fp32; one bf16 rounding after the all-reduce
         if o.get("bias") is not None:
             self.gemm.residual = o["bias"].to(torch.bfloat16).unsqueeze(0).expand(M, self.N).contiguous()
-        self._act = None
+        self._act = {}
+        self.smoothed = bool((o["smooth_scale"].float() != 1).any())     # (an all-ones vector: no division needed)
 
-    def forward(self, x):
+    def forward(self, x, residual=None, swiglu=False):
+        """residual (row shards, bf16 [M, N], no bias): added to the layer's output — inside rank 0's launch, so that
+        the all-reduce carries it. swiglu (local_scale only): x is [M, 2 K_local] = [gate | up] of this rank's columns
+        and the layer's input is silu(gate) * up, formed inside the quantiser launch."""
         from . import fp4
         o = self.ops
         x = x.to(torch.bfloat16).contiguous()
-        gscale = agree_on_activation_scale(x, o["smooth_scale"], group=self.group) if self.kind == "row" else None
-        q = fp4.quantize_activation(x, smooth=o["smooth_scale"], w_gscale=o["w_gscale"], rows=self.M, out=self._act, gscale=gscale)
-        self._act = q
-        self.alpha.copy_(q["alpha"])
+        assert not swiglu or self.local_scale
+        smooth = o["smooth_scale"] if self.smoothed else None
+        gscale = None
+        if self.kind == "row" and not self.local_scale:
+            gscale = agree_on_activation_scale(x, smooth, group=self.group)
+        q = fp4.quantize_activation(x, smooth=smooth, w_gscale=o["w_gscale"], rows=self.M, out=self._act.get(swiglu), gscale=gscale,
+                                    swiglu=swiglu)
+        self._act[swiglu] = q
+        self.gemm.alpha = q["alpha"]
+        if residual is not None:
+            assert self.kind == "row" and o.get("bias") is None
+            rank = dist.get_rank(self.group) if dist.is_initialized() else 0
+            self.gemm.residual = residual if rank == 0 else None
+        elif o.get("bias") is None:
+            self.gemm.residual = None
         y = self.gemm(q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec")).view(-1, self.N)[: self.M]
         if self.kind == "row":
             y = y.contiguous()

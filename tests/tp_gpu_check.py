@@ -58,6 +58,28 @@ def main():
     check_against_unfused(y_row.float().cpu().numpy(), y_full.float().cpu().numpy(), f"row-parallel, rank {rank}")
     assert row.gemm.status()[0] == 0 and col.gemm.status()[0] == 0
 
+    # decode-step form of the row shard: every rank scales its own K-slice (different FP4 codes than the single-GPU
+    # quantisation, so the yardstick is the unquantised-activation value: no further from it than the single-GPU
+    # kernel is), silu(gate) * up formed in the quantiser launch, the residual carried by rank 0's partial sum
+    gu = torch.randn(M, 2 * K, device=dev, generator=g).to(torch.bfloat16)
+    res = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+    xa = torch.nn.functional.silu(gu[:, :K]) * gu[:, K:]
+    xs = (xa / ops["smooth_scale"]).float()
+    w = fp4.dequantize_nvfp4(codes, sf, gs).float()
+    y_hp = xs @ w.T + ((xs @ V.T) * ops["S"].float()) @ U
+    qa = fp4.quantize_activation(xa.contiguous(), smooth=ops["smooth_scale"], w_gscale=gs, rows=M)
+    y_one = full(qa["A"], qa["A_sf"], qa["X"]).view(-1, N)[:M].float()
+    loc = parallel.ShardedBiLoCoLinear(ops, "row", M, local_scale=True)
+    for _ in range(2):
+        y_loc = loc(torch.cat([gu[:, klo:khi], gu[:, K + klo:K + khi]], dim=1).contiguous(), residual=res, swiglu=True)
+    torch.cuda.synchronize()
+    assert loc.gemm.status()[0] == 0
+    e_one = torch.linalg.norm(y_one - y_hp)
+    e_loc = torch.linalg.norm(y_loc.float() - res.float() - y_hp)
+    # (the residual is added before the single bf16 rounding of the sum: allow that rounding on top)
+    slack = 2.0 ** -8 * torch.linalg.norm(y_loc.float())
+    assert e_loc <= 1.25 * e_one + slack, (float(e_loc), float(e_one))
+
     # tensor-parallel decoder: q/k/v/gate/up/lm_head column shards, o/down row shards + all-reduce, captured decode step
     from biloco_b200 import decode
     model = decode.Decoder(decode.PRESETS["tiny-tp"], device=dev, meta=True, tp=world)
