@@ -36,7 +36,7 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of fused_linear_kernel<8> at M=1, K=N=5120, r=512,
 # from the ncu capture summarised in profiles/fused_linear_M1_K5120_N5120_r512.md (other shapes: null)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 15_530_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 15_543_000
 
 
 def algorithmic_bytes(K, N, r):
