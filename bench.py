@@ -342,9 +342,36 @@ def run_ours(args):
                                 "us_per_call": sec * 1e6,
                                 "sample": f"{n} calls of the CPU oracle's fake-quant forward of one layer "
                                           f"(M={M}, K={K}, N={N}, r={r}), median; BLAS threads = {torch.get_num_threads()}"}
+    if world == 1 and not args.no_decode and (M, K, N, r) == (1, 5120, 5120, 512):
+        try:
+            line["decode"] = decode_leg(torch)
+        except Exception as e:      # the linear's line stands on its own
+            line["decode"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def decode_leg(torch, prompt_len=16, steps=48):
+    """The other half of the metric, reported beside the linear's number: greedy decode of a Qwen3-4B-shaped decoder (36
+    layers, every linear a rank-512 layer with random packed operands, M = 1) through the captured step of
+    biloco_b200.decode; tokens/s and the fraction of the HBM peak the linears' bytes reach. Short prompt and run, so
+    that the default bench stays within minutes (a longer context adds attention time per step)."""
+    from biloco_b200 import decode
+    dev = torch.device("cuda", torch.cuda.current_device())
+    c = decode.PRESETS["qwen3-4b"]
+    torch.manual_seed(0)
+    model = decode.Decoder(c, device=dev, meta=True)
+    nlin = decode.synthetic_quantize(model, 512, seed=0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    prompt = torch.randint(0, c.vocab, (1, prompt_len), device=dev, generator=g)
+    toks, sec = decode.greedy_decode(model, prompt, steps, use_graph=True)
+    nbytes = decode.linear_bytes(model)
+    peak, _ = measured_hbm_peak()
+    return {"model": "Qwen3-4B-shaped (36 layers, hidden 2560, vocab 151936), random packed operands", "M": 1, "rank": 512,
+            "linears": nlin, "prompt": prompt_len, "steps": steps, "tokens_per_s": steps / sec, "ms_per_step": sec / steps * 1e3,
+            "linear_bytes_per_step": nbytes, "hbm_frac": nbytes * steps / sec / 1e9 / peak,
+            "finite": bool(torch.isfinite(toks.float()).all())}
 
 
 def main():
@@ -364,6 +391,7 @@ def main():
     ap.add_argument("--lr-tc", type=int, default=-1, help="1/0: expansion on the tensor cores on/off (-1 = library default)")
     ap.add_argument("--mode", type=int, default=None, help="schedule of the fused kernel (default: the measured table)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode leg (default workload, one GPU only)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")
     args = ap.parse_args()
     if args.impl == "reference":
