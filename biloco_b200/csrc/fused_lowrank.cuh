@@ -94,6 +94,49 @@ __device__ __forceinline__ void z_word_n(const uint4* xs, const uint32_t* vrow, 
     plain = ps;
 }
 
+// The same sums for a span of e consecutive activations starting at element e0 of the pass (e even, at most 32, e0 even):
+// with few ranks per CTA a lane takes K/256 elements instead of a whole sign word, so that all 256 lanes of the stage
+// have work (at K = 5120 a word per lane keeps 160 lanes busy with 32 elements each; a span per lane gives 256 lanes 20
+// each; at K = 2560, 80 lanes with 32 against 256 with 10). The span's sign bits come from one or two words of the rank's
+// row (funnel shift); the activations are read as 32-bit pairs.
+template <int NQ>
+__device__ __forceinline__ void z_span_n(const uint8_t* xrow, int e0, int e, const uint32_t* vq0, int words, int nq,
+                                         float (&sums)[ZRUN], float& plain) {
+    uint32_t vw[NQ];
+    float a0[NQ], a1[NQ];
+    const int wi = e0 >> 5, sh = e0 & 31;
+#pragma unroll
+    for (int q = 0; q < NQ; ++q) {
+        uint32_t lo = 0u, hi = 0u;
+        if (q < nq) {
+            lo = vq0[q * words + wi];
+            if (sh + e > 32) hi = vq0[q * words + wi + 1];     // (then wi + 1 < words: the span lies inside the pass)
+        }
+        vw[q] = __funnelshift_r(lo, hi, sh);
+        a0[q] = 0.f;
+        a1[q] = 0.f;
+    }
+    const uint32_t* xp = reinterpret_cast<const uint32_t*>(xrow + 2 * e0);
+    float ps = 0.f;
+    uint32_t m = 1u;
+#pragma unroll 1
+    for (int j = 0; j < e; j += 2) {
+        const uint32_t xw = xp[j >> 1];
+        const float x0 = __uint_as_float(xw << 16), x1 = __uint_as_float(xw & 0xFFFF0000u);
+        const uint32_t m2 = m << 1;
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            BILOCO_PADD(a0[q], vw[q], m, x0);
+            BILOCO_PADD(a1[q], vw[q], m2, x1);
+        }
+        ps += x0 + x1;
+        m <<= 2;
+    }
+#pragma unroll
+    for (int q = 0; q < ZRUN; ++q) sums[q] = q < NQ ? a0[q < NQ ? q : 0] + a1[q < NQ ? q : 0] : 0.f;
+    plain = ps;
+}
+
 // Sum of v[q] over the 32 lanes for up to eight ranks at once: a lane gives away half of its values at every step
 // (4 + 2 + 1 + 2 shuffles instead of 8 x 5). On return lane l holds the total of rank ((l >> 4) & 1) * 4 +
 // ((l >> 3) & 1) * 2 + ((l >> 2) & 1); ranks >= ZRUN are zero.
@@ -180,33 +223,58 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
                 // task has all its lanes busy (up to the last, partial block) whatever the number of ranks
                 // (with one or two runs the words are dealt evenly to all eight warps instead: measured faster than full blocks)
                 const int nruns = (nrc + ZRUN - 1) / ZRUN;
-                const int bs = nruns <= 2 ? (words + Z_WARPS - 1) / Z_WARPS : 32;      // sign words per block (at most 32)
-                const int nwb = (words + bs - 1) / bs;
+                const int e_lane = kc >> 8;                                            // elements per lane when all 256 lanes share the pass
+                if (nruns <= 2 && (e_lane & 1) == 0) {
+                    // few ranks: every lane takes a span of the pass (see z_span_n), all ranks of a run at once
+                    const int e0 = zw * (kc >> 3) + lane * e_lane;
 #pragma unroll 1
-                for (int task = zw; task < nruns * nwb; task += Z_WARPS) {
-                    const int run = task / nwb, wb = task - run * nwb;
-                    const int q0 = run * ZRUN, nq = nrc - q0;
-                    const int w = wb * bs + lane;
-                    const bool active = lane < bs && w < words;
-                    const uint4* xs = reinterpret_cast<const uint4*>(work) + (active ? w : 0) * 4;     // 64 bytes = 32 bf16 of word w
-                    float sums[ZRUN];
+                    for (int run = 0; run < nruns; ++run) {
+                        const int q0 = run * ZRUN, nq = nrc - q0;
+                        float sums[ZRUN];
+                        float plain = 0.f;
+                        const uint32_t* vq0 = vt + (size_t)q0 * words;
+                        if (nq <= 2) z_span_n<2>(work, e0, e_lane, vq0, words, nq, sums, plain);
+                        else if (nq <= 4) z_span_n<4>(work, e0, e_lane, vq0, words, nq, sums, plain);
+                        else if (nq == 5) z_span_n<5>(work, e0, e_lane, vq0, words, nq, sums, plain);
+                        else z_span_n<6>(work, e0, e_lane, vq0, words, nq, sums, plain);
+                        const float tot = z_reduce_run(sums, lane);
+                        const int rl = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                        if ((lane & 3) == 0 && rl < ZRUN && q0 + rl < nrc) ctrl->zred[zw][q0 + rl] += tot;
+                        if (run == 0) {
 #pragma unroll
-                    for (int q = 0; q < ZRUN; ++q) sums[q] = 0.f;
-                    float plain = 0.f;
-                    if (active) {
-                        const uint32_t* vrow = vt + (size_t)q0 * words + w;
-                        if (nq <= 2) z_word_n<2>(xs, vrow, words, nq, sums, plain);
-                        else if (nq <= 4) z_word_n<4>(xs, vrow, words, nq, sums, plain);
-                        else if (nq == 5) z_word_n<5>(xs, vrow, words, nq, sums, plain);
-                        else z_word_n<6>(xs, vrow, words, nq, sums, plain);
+                            for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
+                            if (lane == 0) ctrl->zall[zw] += plain;
+                        }
                     }
-                    const float tot = z_reduce_run(sums, lane);
-                    const int rl = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                    if ((lane & 3) == 0 && rl < ZRUN && q0 + rl < nrc) ctrl->zred[zw][q0 + rl] += tot;
-                    if (run == 0) {
+                } else {
+                    const int bs = nruns <= 2 ? (words + Z_WARPS - 1) / Z_WARPS : 32;      // sign words per block (at most 32)
+                    const int nwb = (words + bs - 1) / bs;
+#pragma unroll 1
+                    for (int task = zw; task < nruns * nwb; task += Z_WARPS) {
+                        const int run = task / nwb, wb = task - run * nwb;
+                        const int q0 = run * ZRUN, nq = nrc - q0;
+                        const int w = wb * bs + lane;
+                        const bool active = lane < bs && w < words;
+                        const uint4* xs = reinterpret_cast<const uint4*>(work) + (active ? w : 0) * 4;     // 64 bytes = 32 bf16 of word w
+                        float sums[ZRUN];
 #pragma unroll
-                        for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
-                        if (lane == 0) ctrl->zall[zw] += plain;
+                        for (int q = 0; q < ZRUN; ++q) sums[q] = 0.f;
+                        float plain = 0.f;
+                        if (active) {
+                            const uint32_t* vrow = vt + (size_t)q0 * words + w;
+                            if (nq <= 2) z_word_n<2>(xs, vrow, words, nq, sums, plain);
+                            else if (nq <= 4) z_word_n<4>(xs, vrow, words, nq, sums, plain);
+                            else if (nq == 5) z_word_n<5>(xs, vrow, words, nq, sums, plain);
+                            else z_word_n<6>(xs, vrow, words, nq, sums, plain);
+                        }
+                        const float tot = z_reduce_run(sums, lane);
+                        const int rl = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                        if ((lane & 3) == 0 && rl < ZRUN && q0 + rl < nrc) ctrl->zred[zw][q0 + rl] += tot;
+                        if (run == 0) {
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
+                            if (lane == 0) ctrl->zall[zw] += plain;
+                        }
                     }
                 }
                 if (zt == 0 && p.stamps && item == cta && c0 == it.ra && k0 == 0) p.stamps[(size_t)cta * STAMP_WORDS + 12] = globaltimer_ns();
