@@ -25,7 +25,7 @@ IMPLEMENTED_MODES = (2, 4, 5)
 # 64 distinct layers per step, mode 2 / mode 5; M = 16, 32: mode 2 only, expansion on the tensor cores):
 #   r = 128 : M=1 11.1/9.2   M=2 11.6/9.7   M=4 12.9/12.4  M=8 14.7/14.6  M=16 16.5  M=32 21.4
 #   r = 256 : M=1 11.6/9.6   M=2 12.5/10.6  M=4 14.6/14.3  M=8 16.8/16.2  M=16 19.3  M=32 25.6
-#   r = 512 : M=1 12.6/10.7  M=2 15.1/13.0  M=4 16.6/15.6  M=8 21.5/20.2  M=16 25.1  M=32 39.4
+#   r = 512 : M=1 12.6/10.1  M=2 15.1/12.6  M=4 16.6/15.7  M=8 21.5/20.2  M=16 24.7  M=32 38.3
 #   r = 1024: M=1 15.1/14.2  M=2 17.6/18.3  M=4 21.4/21.2  M=8 29.9/31.5  M=16 38.9  M=32 67.6
 # Mode 5 does not take M > 8; mode 4 loses everywhere. Ranks below 128 were not measured and follow r = 128.
 _MODE2_WINS = {(2, 1024), (8, 1024)}
