@@ -51,7 +51,9 @@ def extract_defs(path, names):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BILOCO_REFERENCE", "")
+    if not os.path.isdir(os.path.join(ref, "biloco")):
+        sys.exit("usage: make_golden.py <path of a checkout of the reference>   (or set BILOCO_REFERENCE)")
     peel = load_by_path("ref_peel", os.path.join(ref, "biloco", "peel.py"))
     kern = extract_defs(os.path.join(ref, "biloco", "kernel.py"),
                         {"pack_signs", "pack_u_col32", "nvfp4_sf_bytes", "modes_for", "DEFAULT_MODE", "RANKS"})
