@@ -17,7 +17,8 @@ namespace biloco {
 // barrier). After the wait one thread requests the activation row with a single bulk copy and all threads wait on its
 // mbarrier; nothing else stands between the wait and the arithmetic.
 // Arithmetic: the eight warps share (run of ranks) x (block of 32 sign words) tasks, one word per lane; a lane unpacks
-// the activations of its word and, for every rank of the run, adds them under predicates taken from the sign bits. One shuffle reduction per run of up to six ranks (z_reduce_run), per-warp partial
+// the activations of its word and, for every rank of the run, adds them under predicates taken from the sign bits. One
+// shuffle reduction per run of up to six ranks (z_reduce_run), per-warp partial
 // sums in shared memory, one combine per chunk: z = S * (2 * sum_{sign=+1} x - sum x).
 // The CUDA-core code here is bound by instruction issue, not by latency (measured: the same cycles cold and warm,
 // alone or beside spinning warps), so what matters is the instruction count per element and an even spread over warps.
@@ -310,7 +311,9 @@ __device__ __noinline__ uint32_t z_stage(const FusedParams& p, Ctrl* ctrl, uint8
 // The consumers load the values they need straight away, 128 bits at a time, and reload until all four marks match:
 // one memory round trip after the last producer's store instead of three (counter, then poll, then data). The mark
 // costs one unit in the last place of an fp32 z value. Ranks >= R (padding of the last rank word) are never written
-// and read as zero (zb points at the first rank of the tile's column group, which has p.Rg ranks); rows >= M of the staging area are left as they are (their sums are never stored). Values are staged zs_words(ROWS) rank words at a time in shared memory.
+// and read as zero (zb points at the first rank of the tile's column group, which has p.Rg ranks); rows >= M of the
+// staging area are left as they are (their sums are never stored). Values are staged zs_words(ROWS) rank words at a
+// time in shared memory.
 // uw_first holds this thread's first ZS_FIRST U words when they were fetched ahead of time (use_first).
 // Returns false when the poll ran out of time (status set, abort raised).
 template <int ROWS>

@@ -39,7 +39,7 @@ class BiLoCoLinear(nn.Module):
         self.register_buffer("w_gscale", torch.ones(1, device=dev, dtype=torch.float32))
         self.smoothed = False
         self._gemms = {}      # decode batch M -> BiLoCoGemm
-        self._acts = {}       # decode batch M -> reusable activation-quantiser outputs
+        self._acts = {}       # (decode batch M, SwiGLU input?) -> reusable activation-quantiser outputs
 
     @classmethod
     def synthetic(cls, in_features: int, out_features: int, rank: int, device, seed: int = 0):
