@@ -10,7 +10,8 @@ LIB_PATH = os.path.join(_HERE, "libbiloco_b200.so")
 
 OK = 0
 RULES = {"static_6": 0, "static_4": 1, "mse": 2}
-MODE_COUNTER, MODE_OWNER, MODE_CLUSTER = 2, 4, 5
+MODE_COUNTER, MODE_OWNER, MODE_CLUSTER, MODE_SLAB = 2, 4, 5, 7
+OPT_PDL, OPT_RING, OPT_TRIGGER, OPT_LR_TC, OPT_WAIT_BUDGET_US, OPT_SKIP_PUBLISH = 1, 2, 3, 4, 5, 6
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 
@@ -36,6 +37,9 @@ SIGNATURES = {
     "biloco_b200_schedule_info": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
     "biloco_b200_tiled_bytes": (_sz, [_i, _i]),
     "biloco_b200_tile_weights": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "biloco_b200_slab_bytes": (_sz, [_i, _i, _i]),
+    "biloco_b200_slab_info": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(ctypes.c_int)]),
+    "biloco_b200_tile_weights_slab": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "biloco_b200_fused_linear": (_i, [_vp] * 13 + [_sz] + [_i] * 7 + [_vp]),
     "biloco_b200_set_option": (_i, [_i, _i]),
     "biloco_b200_debug_stamps": (_i, [_vp, _sz]),

@@ -123,6 +123,10 @@ static size_t g_stamps_bytes = 0;
 static size_t g_stamps_seq = 0;
 static int g_lr_tc = 1;                          // expansion on the tensor cores where the kernel supports it
 static int g_trigger = -1;                        // < 0: chosen per launch (see launch())
+static unsigned long long g_wait_ns = WAIT_BUDGET_NS;   // budget of a device-side wait (row-slab schedule)
+static int g_inflight = 0;                        // row-slab schedule: weight records in flight while the ring fills (0: all)
+static int g_depmode = 0;                         // row-slab schedule: 1 = one warp executes the dependency wait for the CTA
+static int g_skip_publish = -1;                   // test aid: this CTA of a row-slab launch keeps its z values to itself
 
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 
@@ -318,6 +322,8 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
 
 }  // namespace biloco
 
+#include "slab_host.cuh"
+
 using namespace biloco;
 
 extern "C" size_t biloco_b200_scratch_bytes(int M, int N, int K, int R, int num_sms) {
@@ -331,7 +337,7 @@ extern "C" size_t biloco_b200_scratch_head_bytes(int M, int N, int K, int R, int
     if (num_sms == 0) num_sms = device_sm_count();
     ScratchLayout L;
     if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
-    return L.off_z;
+    return L.off_part;      // status words, counters and the z hand-off area (whose validity marks are relative to the counters)
 }
 
 extern "C" int biloco_b200_max_active_clusters(int M, int cluster) {
@@ -346,6 +352,10 @@ extern "C" int biloco_b200_mode_supported(int M, int N, int K, int R, int mode, 
     if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
     if (mode == BILOCO_MODE_COUNTER || mode == BILOCO_MODE_OWNER) return 1;
     if (mode == BILOCO_MODE_CLUSTER) return cluster_size_for(M, L.ntile, L.nkt, num_sms, on_device) >= 2 ? 1 : 0;
+    if (mode == BILOCO_MODE_SLAB) {
+        slab::Geo g;
+        return slab::slab_geometry(M, N, K, R, num_sms, g_use_pdl != 0, &g) ? 1 : 0;
+    }
     return 0;
 }
 
@@ -399,7 +409,9 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
     }
     if ((!W_tiled && (!W_codes || !W_sf)) || !alpha || !A_codes || !A_sf || !Y_bf16 || !scratch) return BILOCO_ERR_NULL;
     if (R > 0 && (!X_bf16 || !V_packed || !U_col32 || !S_bf16)) return BILOCO_ERR_NULL;
-    if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER && (mode & 0xff) != BILOCO_MODE_CLUSTER) return BILOCO_ERR_MODE;
+    if ((mode & 0xff) != BILOCO_MODE_COUNTER && (mode & 0xff) != BILOCO_MODE_OWNER && (mode & 0xff) != BILOCO_MODE_CLUSTER &&
+        (mode & 0xff) != BILOCO_MODE_SLAB)
+        return BILOCO_ERR_MODE;
     if (epoch < 1) return BILOCO_ERR_EPOCH;
     if (A_rows < M || A_rows > 128) return BILOCO_ERR_SHAPE;
     const int sms = device_sm_count();
@@ -410,6 +422,50 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
     if (((uintptr_t)W_codes & 15) || ((uintptr_t)A_codes & 15) || ((uintptr_t)W_sf & 15) || ((uintptr_t)A_sf & 15) ||
         ((uintptr_t)X_bf16 & 15) || ((uintptr_t)scratch & 255) || ((uintptr_t)U_col32 & 3))
         return BILOCO_ERR_ALIGN;
+
+    if ((mode & 0xff) == BILOCO_MODE_SLAB) {
+        // row slabs: W_tiled is the copy made by biloco_b200_tile_weights_slab (required), one column group
+        slab::Geo g;
+        if (n_groups != 1 || !slab::slab_geometry(M, N, K, R, sms, g_use_pdl != 0, &g)) return BILOCO_ERR_SHAPE;
+        if (!W_tiled) return BILOCO_ERR_NULL;
+        if ((uintptr_t)W_tiled & 15) return BILOCO_ERR_ALIGN;
+        uint8_t* sc = (uint8_t*)scratch;
+        slab::SlabParams q;
+        q.W_slab = (const uint8_t*)W_tiled;
+        q.A_codes = (const uint8_t*)A_codes;
+        q.A_sf = (const uint8_t*)A_sf;
+        q.alpha = alpha;
+        q.X = (const __nv_bfloat16*)X_bf16;
+        q.Vp = (const uint8_t*)V_packed;
+        q.Ucol = U_col32;
+        q.S = (const __nv_bfloat16*)S_bf16;
+        q.C = (const __nv_bfloat16*)C_bf16;
+        q.Y = Y_bf16;
+        q.status = (int32_t*)sc;
+        q.z_counter = (uint32_t*)(sc + L.off_zcnt);
+        q.zbuf = (float*)(sc + L.off_z);
+        q.M = M; q.N = N; q.K = K; q.R = R; q.Rw = L.Rw; q.Rpad = L.Rpad;
+        q.Rt = g.Rt; q.kg = g.kg; q.nkt = g.nkt; q.nsu = g.nsu; q.G = g.G;
+        q.nsl = g.nsl;
+        q.ring = g_ring > 0 && g_ring < g.ring ? g_ring : g.ring;
+        q.stage_bytes = g.stage_bytes;
+        // (a shorter ring keeps the offsets computed for the full one: the stages simply stay unused)
+        q.off_btile = g.off_btile; q.off_ctrl = g.off_ctrl; q.off_us = g.off_us; q.off_work = g.off_work; q.off_accp = g.off_accp; q.xs_off = g.xs_off; q.off_asf = g.off_asf;
+        q.depmode = g_depmode;
+        q.epoch = (uint32_t)epoch;
+        q.mode = mode;
+        q.wait_ns = g_wait_ns;
+        q.skip_publish_cta = g_skip_publish;
+        q.trigger = g_trigger >= 0 ? g_trigger : 0;
+        q.inflight = g_inflight;
+        q.stamps = nullptr;
+        if (g_stamps && g_stamps_bytes >= (size_t)g.G * slab::SLAB_STAMPS * 8) {
+            const size_t per = (size_t)g.G * slab::SLAB_STAMPS, slots = g_stamps_bytes / (per * 8);
+            q.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
+        }
+        return M <= 1 ? slab::slab_launch_rows<1>(q, g, g_use_pdl != 0, (cudaStream_t)stream)
+                      : slab::slab_launch_rows<2>(q, g, g_use_pdl != 0, (cudaStream_t)stream);
+    }
 
     CUtensorMap tmW, tmA;
     int rc = get_tensor_map(A_codes, A_rows, K / 2, L.mma_n, &tmA);
@@ -614,6 +670,13 @@ extern "C" int biloco_b200_set_option(int option, int value) {
     if (option == BILOCO_OPT_TRIGGER) { g_trigger = value; return BILOCO_OK; }
     if (option == BILOCO_OPT_LR_TC) { g_lr_tc = value ? 1 : 0; return BILOCO_OK; }
     if (option == BILOCO_OPT_RING) { g_ring = value <= 0 ? 0 : value; return BILOCO_OK; }
+    if (option == BILOCO_OPT_WAIT_BUDGET_US) {
+        g_wait_ns = value <= 0 ? WAIT_BUDGET_NS : (unsigned long long)value * 1000ull;
+        return BILOCO_OK;
+    }
+    if (option == BILOCO_OPT_SKIP_PUBLISH) { g_skip_publish = value; return BILOCO_OK; }
+    if (option == BILOCO_OPT_INFLIGHT) { g_inflight = value < 0 ? 0 : value; return BILOCO_OK; }
+    if (option == 8) { g_depmode = value ? 1 : 0; return BILOCO_OK; }      // (experiment)
     return BILOCO_ERR_MODE;
 }
 
@@ -622,6 +685,35 @@ extern "C" int biloco_b200_debug_stamps(void* device_buf, size_t bytes) {
     g_stamps_bytes = device_buf ? bytes : 0;
     g_stamps_seq = 0;
     return BILOCO_OK;
+}
+
+extern "C" size_t biloco_b200_slab_bytes(int N, int K, int num_sms) {
+    if (num_sms == 0) num_sms = device_sm_count();
+    slab::Geo g;
+    if (!slab::slab_layout(N, K, num_sms, &g)) return 0;
+    return (size_t)g.G * g.nkt * g.Rt * slab::UNIT_ROW_BYTES;
+}
+
+extern "C" int biloco_b200_slab_info(int M, int N, int K, int R, int num_sms, int* out8) {
+    if (!out8) return BILOCO_ERR_NULL;
+    if (num_sms == 0) num_sms = device_sm_count();
+    slab::Geo g;
+    if (!slab::slab_geometry(M, N, K, R, num_sms, g_use_pdl != 0, &g)) return BILOCO_ERR_SHAPE;
+    out8[0] = g.Rt; out8[1] = g.kg; out8[2] = g.nkt; out8[3] = g.nsu; out8[4] = g.G; out8[5] = g.ring; out8[6] = g.smem_bytes;
+    out8[7] = g.nr;
+    return BILOCO_OK;
+}
+
+extern "C" int biloco_b200_tile_weights_slab(const void* W_codes, const void* W_sf, void* W_slab, int N, int K, int num_sms,
+                                             biloco_stream_t stream) {
+    if (!W_codes || !W_sf || !W_slab) return BILOCO_ERR_NULL;
+    if (num_sms == 0) num_sms = device_sm_count();
+    slab::Geo g;
+    if (!slab::slab_layout(N, K, num_sms, &g)) return BILOCO_ERR_SHAPE;
+    if (((uintptr_t)W_slab & 15) || ((uintptr_t)W_codes & 15) || ((uintptr_t)W_sf & 15)) return BILOCO_ERR_ALIGN;
+    slab::tile_weights_slab_kernel<<<(unsigned)(g.G * g.nkt), 128, 0, (cudaStream_t)stream>>>(
+        (const uint8_t*)W_codes, (const uint8_t*)W_sf, (uint8_t*)W_slab, N, K, g.Rt, g.kg, g.nkt);
+    return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
 extern "C" int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t stream) {

@@ -1,0 +1,130 @@
+// Host side of the row-slab schedule (mode 7): geometry, the weight re-layout kernel and the launcher.
+// Included by fused_linear.cu (one translation unit: the launch options are shared).
+#pragma once
+#include "slab_kernel.cuh"
+
+namespace biloco {
+namespace slab {
+
+struct Geo {
+    int Rt, kg, nkt, nsu, G;        // rows per CTA, k-tiles per super-unit, k-tiles, super-units per CTA, CTAs
+    int nsl, nr;                    // z stage: rank slices per activation row, most ranks of a slice
+    int rows;                       // 1 or 2 (template parameter)
+    int stage_bytes, ring;
+    int off_btile, off_ctrl, off_us, off_work, off_accp, off_asf, xs_off, smem_bytes;
+};
+
+// Weight layout: depends on N, K and the SM count only (not on M), so one re-laid copy serves M = 1 and M = 2.
+static bool slab_layout(int N, int K, int num_sms, Geo* g) {
+    if (N < 8 || (N % 8) || K < 512 || (K % 512) || num_sms < 1) return false;      // (K / 256 must be even: a thread's span is pairs)
+    int rt = (N + num_sms - 1) / num_sms;
+    rt = (rt + 7) / 8 * 8;
+    if (rt > 128) return false;
+    g->Rt = rt;
+    g->G = (N + rt - 1) / rt;
+    g->nkt = K / KT;
+    int kg = 128 / rt;
+    if (kg > 4) kg = 4;
+    if (kg > g->nkt) kg = g->nkt;
+    g->kg = kg;
+    g->nsu = (g->nkt + kg - 1) / kg;
+    g->stage_bytes = (kg * rt * UNIT_ROW_BYTES + 1023) / 1024 * 1024;
+    return true;
+}
+
+static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coresident, Geo* g) {
+    if (M < 1 || M > 2 || R < 0) return false;
+    if (!slab_layout(N, K, num_sms, g)) return false;
+    g->rows = M;
+    g->nsl = g->G / M > 1 ? g->G / M : 1;
+    g->nr = R > 0 ? (R + g->nsl - 1) / g->nsl : 0;
+    if (g->nr > 2 * NRMAX) return false;
+    const int Rw = (R + 31) / 32, Rpad = Rw * 32;
+    const int vt = g->nr * (K / 8);
+    if (vt > VT_SLAB_MAX) return false;
+    // work area: during the z stage the sign words of the CTA's ranks and 2 KB per warp of staging for the activation
+    // row (rows of up to 8192 elements; longer rows are read span by span without staging); afterwards z and the
+    // expansion's partial sums
+    g->xs_off = (vt + 15) / 16 * 16;
+    const int zwork = R > 0 ? g->xs_off + LR_WARPS * 64 * 2 * XW_MAX : 0;
+    int work = g->rows * Rpad * 4 + g->rows * Rw * g->Rt * 4;
+    if (work < zwork) work = zwork;
+    const int btile = g->nsu * 1024, us = (Rw * g->Rt * 4 + 15) / 16 * 16, accp = (g->kg * g->rows * g->Rt * 4 + 15) / 16 * 16;
+    work = (work + 15) / 16 * 16;
+    const int asf = g->nkt * g->rows * 16;
+    const int fixed = btile + 1024 + us + work + accp + asf;
+    const int budget = (coresident ? CORESIDENT_SMEM : SMEM_BUDGET) - 1024;       // (alignment slack)
+    int ring = (budget - fixed) / g->stage_bytes;
+    if (ring > MAX_RING) ring = MAX_RING;
+    if (ring > g->nsu) ring = g->nsu;
+    if (ring < 1 || (ring < 2 && g->nsu >= 2)) return false;
+    g->ring = ring;
+    g->off_btile = ring * g->stage_bytes;
+    g->off_ctrl = g->off_btile + btile;
+    g->off_us = g->off_ctrl + 1024;
+    g->off_work = g->off_us + us;
+    g->off_accp = g->off_work + work;
+    g->off_asf = g->off_accp + accp;
+    int total = g->off_asf + asf;
+    // the tensor core reads 128 rows x 128 bytes from a stage's base whatever the super-unit's real height is
+    if (total < (ring - 1) * g->stage_bytes + 16384) total = (ring - 1) * g->stage_bytes + 16384;
+    g->smem_bytes = total + 1024;
+    return g->smem_bytes <= (coresident ? CORESIDENT_SMEM : SMEM_BUDGET);
+}
+
+// One block per (CTA slab c, k-tile kt): the unit's codes go to MMA row g Rt + r of its super-unit with the 128-byte
+// swizzle applied (16-byte chunk ch at chunk ch ^ (r & 7)), its block scales (four 32-bit words per row, one per 64-k
+// chunk) behind the codes of all units of the super-unit.
+__global__ void tile_weights_slab_kernel(const uint8_t* __restrict__ W, const uint8_t* __restrict__ W_sf, uint8_t* __restrict__ out,
+                                         int N, int K, int Rt, int kg, int nkt) {
+    const int c = blockIdx.x / nkt, kt = blockIdx.x - c * nkt;
+    const int j = kt / kg, g = kt - j * kg;
+    const int nu = (nkt - j * kg) < kg ? (nkt - j * kg) : kg;
+    uint8_t* su = out + ((size_t)c * nkt + (size_t)j * kg) * Rt * UNIT_ROW_BYTES;
+    for (int i = threadIdx.x; i < Rt * 8; i += blockDim.x) {
+        const int r = i >> 3, ch = i & 7;
+        const int n = c * Rt + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (n < N) v = *reinterpret_cast<const uint4*>(W + (size_t)n * (K >> 1) + kt * KT_BYTES + ch * 16);
+        *reinterpret_cast<uint4*>(su + (size_t)(g * Rt + r) * 128 + ((ch ^ (r & 7)) * 16)) = v;
+    }
+    for (int i = threadIdx.x; i < Rt * 4; i += blockDim.x) {
+        const int r = i >> 2, a = i & 3;
+        const int n = c * Rt + r;
+        uint32_t v = 0u;
+        if (n < N)
+            v = *reinterpret_cast<const uint32_t*>(W_sf + ((size_t)(n >> 7) * (K >> 6) + (size_t)kt * 4 + a) * 512 + (n & 31) * 16 + ((n >> 5) & 3) * 4);
+        *reinterpret_cast<uint32_t*>(su + (size_t)nu * Rt * 128 + (size_t)(g * Rt + r) * 16 + a * 4) = v;
+    }
+}
+
+template <int ROWS>
+static int slab_launch_rows(const SlabParams& p, const Geo& g, bool pdl, cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(slab_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET) != cudaSuccess)
+            return BILOCO_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)g.G);
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = (size_t)g.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, slab_kernel<ROWS>, p);
+    return e == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
+}
+
+}  // namespace slab
+}  // namespace biloco

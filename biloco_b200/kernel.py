@@ -19,7 +19,7 @@ ops = torch.ops.biloco
 RANKS = (16, 32, 64, 128, 256, 512, 1024)
 
 # Schedules implemented by the fused kernel (see include/biloco_b200.h, BILOCO_MODE_*).
-IMPLEMENTED_MODES = (2, 4, 5)
+IMPLEMENTED_MODES = (2, 4, 5, 7)
 
 # Fastest implemented mode per (M, rank) on B200 at K = N = 5120, from `bench.py --M .. --r .. --mode ..` (us per call,
 # 64 distinct layers per step, mode 2 / mode 5; M = 16, 32: mode 2 only, expansion on the tensor cores):
@@ -30,6 +30,16 @@ IMPLEMENTED_MODES = (2, 4, 5)
 # Mode 5 does not take M > 8; mode 4 loses everywhere. Ranks below 128 were not measured and follow r = 128.
 _MODE2_WINS = {(2, 1024), (8, 1024)}
 DEFAULT_MODE = {M: {r: (2 if (M > 8 or (M, r) in _MODE2_WINS) else 5) for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
+
+
+def default_mode(M: int, rank: int, ok):
+    """The schedule BiLoCoGemm picks among the modes `ok` that the shape takes: row slabs for one or two rows, else the
+    measured table's entry, else the first that is available."""
+    if M <= 2 and 7 in ok:
+        return 7
+    mode = DEFAULT_MODE.get(M, {}).get(rank)
+    return mode if mode in ok else (ok or [None])[0]
+
 
 def pack_signs(signs: torch.Tensor) -> torch.Tensor:
     """[..., n] +-1 -> uint8 [..., n/8]; bit i of byte j is set iff signs[..., 8j + i] >= 0
@@ -73,7 +83,7 @@ def modes_for(M: int, rank: int, K: int = 5120):
     host-side checks (K must be a multiple of 256, N of 8)."""
     if not (1 <= M <= 32) or rank < 1 or K % 256 != 0:
         return []
-    return [m for m in IMPLEMENTED_MODES if m != 5 or M <= 8]
+    return [m for m in IMPLEMENTED_MODES if (m != 5 or M <= 8) and (m != 7 or (M <= 2 and K % 512 == 0))]
 
 
 def supported_modes(M: int, N: int, K: int, rank: int, num_sms: int = 0):
@@ -117,8 +127,7 @@ class BiLoCoGemm:
         with torch.cuda.device(dev):
             ok = supported_modes(M, self.N, self.K, self.R)
         if mode is None:      # the table's choice if this shape takes it, else the first mode that does
-            mode = DEFAULT_MODE.get(M, {}).get(self.R)
-            mode = mode if mode in ok else (ok or [None])[0]
+            mode = default_mode(M, self.R, ok)
         self.mode = mode
         assert self.mode in ok, f"mode {self.mode} not available for M={M} N={self.N} K={self.K} R={self.R}"
         self.W_fp4, self.W_sf, self.alpha, self.V, self.S = W_fp4, W_sf, alpha, V_packed, S
@@ -126,7 +135,10 @@ class BiLoCoGemm:
         self.none = torch.zeros(0, device=dev, dtype=torch.int64)
         # unit-contiguous copy of the weight (the counterpart of the reference's V_perm / U_rw re-layouts): the
         # kernel then reads sequential 18 KB records instead of 128 strided 128-byte rows per tile
-        self.W_tiled = _ops.tile_weights(W_fp4, W_sf) if tile_weights else self.none
+        if self.mode == 7:    # the row-slab schedule streams its own re-laid copy (required)
+            self.W_tiled = _ops.tile_weights_slab(W_fp4, W_sf)
+        else:
+            self.W_tiled = _ops.tile_weights(W_fp4, W_sf) if tile_weights else self.none
         with torch.cuda.device(dev):
             nbytes = scratch_bytes(M, self.N, self.K, self.R)
             self._head = _lib.load().biloco_b200_scratch_head_bytes(M, self.N, self.K, self.R, 0) // 4
@@ -157,6 +169,10 @@ class BiLoCoGemm:
         and ``A_rec``, the activation quantiser's per-k-tile record (fp4.quantize_activation(...)["A_rec"]) with which the
         kernel fetches the activation side of a work unit in one copy."""
         self.epoch += 1
+        if self.mode == 7:        # no operator of the reference's schema set stands for this schedule
+            return _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32, self.z,
+                               self.M, self.epoch, self.mode, C=self.residual, out=out, B_tiled=self.W_tiled,
+                               fp32_out=self.fp32_out)
         if self.residual is not None or self.fp32_out or out is not None or A_rec is not None:   # not expressible in the operator schemas
             return _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32, self.z,
                                self.M, self.epoch, self.mode, C=self.residual, out=out, A_rec=A_rec,

@@ -79,7 +79,9 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
              and U_col32.size(1) == (R // ng + 31) // 32, "U_col32 must be contiguous int32 [N, ceil(R/32)]")
     _req(scratch.is_cuda and scratch.is_contiguous(), "scratch must be a contiguous CUDA tensor")
     if B_tiled is not None:
-        want = _lib.load().biloco_b200_tiled_bytes(N, K)
+        with torch.cuda.device(A.device):
+            want = (_lib.load().biloco_b200_slab_bytes(N, K, 0) if (mode & 0xff) == _lib.MODE_SLAB
+                    else _lib.load().biloco_b200_tiled_bytes(N, K))
         _req(B_tiled.is_cuda and B_tiled.is_contiguous() and B_tiled.dtype == torch.uint8 and B_tiled.numel() == want,
              f"tiled weight copy must be a contiguous uint8 CUDA tensor of {want} bytes")
     D = out if out is not None else torch.empty((1, rows, N), device=A.device, dtype=torch.float32 if fp32_out else torch.bfloat16)
@@ -114,6 +116,19 @@ def tile_weights(B, B_sf):
     out = torch.empty(nbytes, device=B.device, dtype=torch.uint8)
     with torch.cuda.device(B.device):
         _lib.check(lib.biloco_b200_tile_weights(B.data_ptr(), B_sf.data_ptr(), out.data_ptr(), N, K, _stream()), "tile_weights")
+    return out
+
+
+def tile_weights_slab(B, B_sf):
+    """Row-slab copy of the NVFP4 weight for the row-slab schedule (mode 7, one or two activation rows)."""
+    N, K = B.size(0), B.size(1) * 2
+    lib = _lib.load()
+    with torch.cuda.device(B.device):
+        nbytes = lib.biloco_b200_slab_bytes(N, K, 0)
+        _req(nbytes > 0, f"the row-slab schedule does not take a weight with N={N} K={K}")
+        out = torch.empty(nbytes, device=B.device, dtype=torch.uint8)
+        _lib.check(lib.biloco_b200_tile_weights_slab(B.data_ptr(), B_sf.data_ptr(), out.data_ptr(), N, K, 0, _stream()),
+                   "tile_weights_slab")
     return out
 
 

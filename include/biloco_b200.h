@@ -49,6 +49,12 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
 #define BILOCO_MODE_COUNTER 2
 #define BILOCO_MODE_OWNER 4
 #define BILOCO_MODE_CLUSTER 5
+/*   7: row slabs, for one or two activation rows: N is split only (CTA c owns the ceil8(N / SMs) weight rows c, all of K),
+ *      so no partial sum leaves a CTA; the tensor-core tile's 128 rows hold the same weight rows for up to four
+ *      consecutive k-tiles, matched by one activation-operand row per k-tile, and the diagonal blocks of the
+ *      accumulator are summed in the epilogue. Needs the copy made by biloco_b200_tile_weights_slab as W_tiled,
+ *      M <= 2, K % 512 == 0, N <= 128 * SMs, one column group. No counterpart in the reference. */
+#define BILOCO_MODE_SLAB 7
 
 /* OR-ed to the mode: Y is fp32 [M,N] instead of bf16 (the unrounded sum). For partial outputs that are reduced across
  * devices before the single bf16 rounding (row-parallel shards). No counterpart in the reference (single GPU). */
@@ -196,6 +202,18 @@ size_t biloco_b200_tiled_bytes(int N, int K);
  * biloco/kernel.py:98-102). K % 256 == 0; 16-byte aligned pointers. */
 int biloco_b200_tile_weights(const void* W_codes, const void* W_sf, void* W_tiled, int N, int K, biloco_stream_t stream);
 
+/* Row-slab copy of an [N, K] NVFP4 weight for BILOCO_MODE_SLAB: per CTA slab c (rows c Rt .., Rt = ceil8(N / num_sms))
+ * and per group of kg = min(128 / Rt, 4) consecutive k-tiles one contiguous record = the codes of the group's units
+ * with the shared-memory swizzle applied (row g Rt + r of the tensor-core tile), followed by their block scales
+ * (16 bytes per row and unit). The layout depends on N, K and the SM count only (num_sms = 0: the current device).
+ * biloco_b200_slab_bytes returns 0 for shapes the schedule does not take. biloco_b200_slab_info: out[0..7] = Rt, kg,
+ * k-tiles, records per CTA, CTAs, pipeline stages, shared memory per CTA, most ranks of a z slice (for tests and sizing).
+ * Replaces: the operand re-layouts BiLoCoGemm.__init__ performs in the reference (biloco/kernel.py:98-102). */
+size_t biloco_b200_slab_bytes(int N, int K, int num_sms);
+int biloco_b200_slab_info(int M, int N, int K, int R, int num_sms, int* out8);
+int biloco_b200_tile_weights_slab(const void* W_codes, const void* W_sf, void* W_slab, int N, int K, int num_sms,
+                                  biloco_stream_t stream);
+
 /* The fused decode linear, one launch:
  *     Y[m,n] = bf16( alpha[0] * sum_k A[m,k] W[n,k]  +  sum_i z[m,i] sign(U[i,n]) ),  z = S .* (X sign(V)^T)
  * W_codes u8 [N,K/2], W_sf E4M3 (atom layout, rows padded to 128), alpha fp32 [1] (device), A_codes u8
@@ -271,6 +289,16 @@ int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t
 /* 1 (default): from 16 activation rows up the expansion of z through the U signs runs on the tensor cores (bf16 sign
  * image x z split into two bf16 parts, fp32 accumulation); 0: on the CUDA cores for every row count. */
 #define BILOCO_OPT_LR_TC 4
+/* Budget of a device-side wait in microseconds (default 200 000; <= 0 restores the default). A wait that runs out
+ * records its code in the status words and the launch returns (row-slab schedule; the other schedules keep 200 ms).
+ * Counterpart in the reference: the bounded polls that record codes in Diag[4095] (csrc/biloco_gemm.cu:1149-1151). */
+#define BILOCO_OPT_WAIT_BUDGET_US 5
+/* Test aid for the failure path: CTA `value` of a row-slab launch computes its z values but does not publish them, so
+ * that every consumer's poll runs out of its budget (-1, the default: off). */
+#define BILOCO_OPT_SKIP_PUBLISH 6
+/* Row-slab schedule: weight records a CTA keeps in flight while it fills its ring ahead of the dependency wait
+ * (0, the default: chosen by the library). Tuning aid. */
+#define BILOCO_OPT_INFLIGHT 7
 int biloco_b200_set_option(int option, int value);
 
 /* Debug aid: while a device buffer is registered here, every fused launch of this process writes 16 uint64

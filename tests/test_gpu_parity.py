@@ -278,3 +278,42 @@ def test_fused_full_size_random_scales(kernel, M, r):
 @pytest.mark.parametrize("K,N", [(5120, 1024), (2560, 9728), (9728, 2560)])
 def test_fused_other_layer_shapes(kernel, K, N):
     _run_fused(kernel, orc.random_problem(2, K, N, 256, scales="random", seed=K + N), 2, N, launches=2)
+
+
+def _slab_layout_numpy(W, W_sf, N, K, Rt, kg):
+    """The row-slab weight copy stated in numpy: per CTA slab c and super-unit j (kg consecutive k-tiles) the codes of
+    MMA row g * Rt + r with the 128-byte swizzle (16-byte chunk ch at chunk ch ^ (r & 7)), then 16 scale bytes per row."""
+    nkt = K // 256
+    G = (N + Rt - 1) // Rt
+    out = np.zeros(G * nkt * Rt * 144, np.uint8)
+    sf_rows = orc.sf_unswizzle(W_sf, N, K)                               # [N, K/16]
+    for c in range(G):
+        for j in range((nkt + kg - 1) // kg):
+            nu = min(kg, nkt - j * kg)
+            base = (c * nkt + j * kg) * Rt * 144
+            for g in range(nu):
+                kt = j * kg + g
+                for r in range(Rt):
+                    n = c * Rt + r
+                    if n >= N:
+                        continue
+                    row = W[n, kt * 128:(kt + 1) * 128].reshape(8, 16)
+                    dst = out[base + (g * Rt + r) * 128: base + (g * Rt + r + 1) * 128].reshape(8, 16)
+                    dst[np.arange(8) ^ (r & 7)] = row
+                    o = base + nu * Rt * 128 + (g * Rt + r) * 16
+                    out[o:o + 16] = sf_rows[n, kt * 16:(kt + 1) * 16]
+    return out
+
+
+@pytest.mark.parametrize("N,K", [(128, 512), (384, 1024), (5120, 5120), (2560, 1536), (136, 512)])
+def test_slab_weight_layout(kernel, lib, N, K):
+    """biloco_b200_tile_weights_slab against the layout stated in numpy, byte for byte."""
+    import ctypes
+    from biloco_b200 import ops
+    p = orc.random_problem(1, K, N, 8, scales="random", seed=N + K)
+    t = dev_problem(p)
+    info = (ctypes.c_int * 8)()
+    assert lib.biloco_b200_slab_info(1, N, K, 8, 0, info) == 0
+    got = ops.tile_weights_slab(t["W"], t["W_sf"]).cpu().numpy()
+    want = _slab_layout_numpy(p["W"], p["W_sf"], N, K, info[0], info[1])
+    assert got.size == want.size and np.array_equal(got, want)
