@@ -125,7 +125,7 @@ static int g_lr_tc = 1;                          // expansion on the tensor core
 static int g_trigger = -1;                        // < 0: chosen per launch (see launch())
 static unsigned long long g_wait_ns = WAIT_BUDGET_NS;   // budget of a device-side wait (row-slab schedule)
 static int g_inflight = 0;                        // row-slab schedule: weight records in flight while the ring fills (0: all)
-static int g_depmode = 0;                         // row-slab schedule: 1 = one warp executes the dependency wait for the CTA
+static int g_dbg = 0;                             // row-slab schedule: timing experiments (see SlabParams::dbg)
 static int g_skip_publish = -1;                   // test aid: this CTA of a row-slab launch keeps its z values to itself
 
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
@@ -445,22 +445,25 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
         q.z_counter = (uint32_t*)(sc + L.off_zcnt);
         q.zbuf = (float*)(sc + L.off_z);
         q.M = M; q.N = N; q.K = K; q.R = R; q.Rw = L.Rw; q.Rpad = L.Rpad;
-        q.Rt = g.Rt; q.kg = g.kg; q.nkt = g.nkt; q.nsu = g.nsu; q.G = g.G;
+        q.Rt = g.Rt; q.kg = g.kg; q.nkt = g.nkt; q.nsu = g.nsu; q.G = g.grid; q.Grows = g.G;
         q.nsl = g.nsl;
         q.ring = g_ring > 0 && g_ring < g.ring ? g_ring : g.ring;
         q.stage_bytes = g.stage_bytes;
         // (a shorter ring keeps the offsets computed for the full one: the stages simply stay unused)
-        q.off_btile = g.off_btile; q.off_ctrl = g.off_ctrl; q.off_us = g.off_us; q.off_work = g.off_work; q.off_accp = g.off_accp; q.xs_off = g.xs_off; q.off_asf = g.off_asf;
-        q.depmode = g_depmode;
+        q.nbp = g.nbp; q.atile_bytes = g.atile_bytes;
+        q.off_ring = g.off_ring; q.off_ctrl = g.off_ctrl; q.off_us = g.off_us; q.off_work = g.off_work; q.off_accp = g.off_accp;
+        q.xs_off = g.xs_off; q.off_asf = g.off_asf;
         q.epoch = (uint32_t)epoch;
         q.mode = mode;
         q.wait_ns = g_wait_ns;
         q.skip_publish_cta = g_skip_publish;
-        q.trigger = g_trigger >= 0 ? g_trigger : 0;
+        q.trigger = g_trigger >= 0 ? g_trigger : 1;      // (measured: 8.3 us per call at K = N = 5120 against 8.4 with 0)
         q.inflight = g_inflight;
+        q.lut = g.lut;
+        q.dbg = g_dbg;
         q.stamps = nullptr;
-        if (g_stamps && g_stamps_bytes >= (size_t)g.G * slab::SLAB_STAMPS * 8) {
-            const size_t per = (size_t)g.G * slab::SLAB_STAMPS, slots = g_stamps_bytes / (per * 8);
+        if (g_stamps && g_stamps_bytes >= (size_t)g.grid * slab::SLAB_STAMPS * 8) {
+            const size_t per = (size_t)g.grid * slab::SLAB_STAMPS, slots = g_stamps_bytes / (per * 8);
             q.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
         }
         return M <= 1 ? slab::slab_launch_rows<1>(q, g, g_use_pdl != 0, (cudaStream_t)stream)
@@ -675,8 +678,8 @@ extern "C" int biloco_b200_set_option(int option, int value) {
         return BILOCO_OK;
     }
     if (option == BILOCO_OPT_SKIP_PUBLISH) { g_skip_publish = value; return BILOCO_OK; }
+    if (option == 9) { g_dbg = value; return BILOCO_OK; }      // (timing experiments; results are wrong while set)
     if (option == BILOCO_OPT_INFLIGHT) { g_inflight = value < 0 ? 0 : value; return BILOCO_OK; }
-    if (option == 8) { g_depmode = value ? 1 : 0; return BILOCO_OK; }      // (experiment)
     return BILOCO_ERR_MODE;
 }
 
@@ -699,7 +702,7 @@ extern "C" int biloco_b200_slab_info(int M, int N, int K, int R, int num_sms, in
     if (num_sms == 0) num_sms = device_sm_count();
     slab::Geo g;
     if (!slab::slab_geometry(M, N, K, R, num_sms, g_use_pdl != 0, &g)) return BILOCO_ERR_SHAPE;
-    out8[0] = g.Rt; out8[1] = g.kg; out8[2] = g.nkt; out8[3] = g.nsu; out8[4] = g.G; out8[5] = g.ring; out8[6] = g.smem_bytes;
+    out8[0] = g.Rt; out8[1] = g.kg; out8[2] = g.nkt; out8[3] = g.nsu; out8[4] = g.grid; out8[5] = g.ring; out8[6] = g.smem_bytes;
     out8[7] = g.nr;
     return BILOCO_OK;
 }

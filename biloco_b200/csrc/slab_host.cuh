@@ -7,11 +7,13 @@ namespace biloco {
 namespace slab {
 
 struct Geo {
-    int Rt, kg, nkt, nsu, G;        // rows per CTA, k-tiles per super-unit, k-tiles, super-units per CTA, CTAs
+    int Rt, kg, nkt, nsu, G;        // rows per CTA, k-tiles per super-unit, k-tiles, super-units per CTA, CTAs with rows
+    int grid;                       // CTAs launched: one per SM, the ones beyond G only take part in the z stage
+    int nbp;                        // MMA N: kg * Rt rounded up to a multiple of 16
     int nsl, nr;                    // z stage: rank slices per activation row, most ranks of a slice
     int rows;                       // 1 or 2 (template parameter)
-    int stage_bytes, ring;
-    int off_btile, off_ctrl, off_us, off_work, off_accp, off_asf, xs_off, smem_bytes;
+    int stage_bytes, ring, atile_bytes, lut;
+    int off_ring, off_ctrl, off_us, off_work, off_accp, off_asf, xs_off, smem_bytes;
 };
 
 // Weight layout: depends on N, K and the SM count only (not on M), so one re-laid copy serves M = 1 and M = 2.
@@ -23,12 +25,14 @@ static bool slab_layout(int N, int K, int num_sms, Geo* g) {
     g->Rt = rt;
     g->G = (N + rt - 1) / rt;
     g->nkt = K / KT;
-    int kg = 128 / rt;
-    if (kg > 4) kg = 4;
-    if (kg > g->nkt) kg = g->nkt;
-    g->kg = kg;
-    g->nsu = (g->nkt + kg - 1) / kg;
-    g->stage_bytes = (kg * rt * UNIT_ROW_BYTES + 1023) / 1024 * 1024;
+    // as many k-tiles per MMA as its 256 operand rows take (at most KG_MAX), then evened out over the super-units
+    int kmax = 256 / rt;
+    if (kmax > KG_MAX) kmax = KG_MAX;
+    if (kmax > g->nkt) kmax = g->nkt;
+    g->nsu = (g->nkt + kmax - 1) / kmax;
+    g->kg = (g->nkt + g->nsu - 1) / g->nsu;
+    g->nbp = (g->kg * rt + 15) / 16 * 16;
+    g->stage_bytes = (g->kg * rt * UNIT_ROW_BYTES + 1023) / 1024 * 1024;
     return true;
 }
 
@@ -36,38 +40,50 @@ static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coreside
     if (M < 1 || M > 2 || R < 0) return false;
     if (!slab_layout(N, K, num_sms, g)) return false;
     g->rows = M;
-    g->nsl = g->G / M > 1 ? g->G / M : 1;
+    // One CTA per SM, always: with exactly as many CTAs as SMs every SM hosts one CTA of this launch beside one of the
+    // next, and none hosts two of the same launch (which would take turns on the SM's tensor memory).
+    g->grid = (R > 0 && g->G < num_sms) ? num_sms : g->G;
+    g->nsl = g->grid / M > 1 ? g->grid / M : 1;
     g->nr = R > 0 ? (R + g->nsl - 1) / g->nsl : 0;
     if (g->nr > 2 * NRMAX) return false;
     const int Rw = (R + 31) / 32, Rpad = Rw * 32;
     const int vt = g->nr * (K / 8);
     if (vt > VT_SLAB_MAX) return false;
-    // work area: during the z stage the sign words of the CTA's ranks and 2 KB per warp of staging for the activation
-    // row (rows of up to 8192 elements; longer rows are read span by span without staging); afterwards z and the
-    // expansion's partial sums
+    // work area: during the z stage the sign words of the CTA's ranks and a staged copy of the activation row (rows of
+    // up to 8192 elements; longer rows are read span by span without staging); afterwards z and the expansion's
+    // partial sums
     g->xs_off = (vt + 15) / 16 * 16;
-    const int zwork = R > 0 ? g->xs_off + LR_WARPS * 64 * 2 * XW_MAX : 0;
+    const int zwork = R > 0 ? g->xs_off + (K / 256 <= 2 * XW_MAX ? 2 * K : 0) : 0;
     int work = g->rows * Rpad * 4 + g->rows * Rw * g->Rt * 4;
+    // expansion by table (16 sums per group of four ranks: 16 bytes per rank and row) where the table is small
+    g->lut = (R > 0 && g->rows * Rpad * 16 <= 8192) ? 1 : 0;
+    if (g->lut) work += g->rows * Rpad * 16;
     if (work < zwork) work = zwork;
-    const int btile = g->nsu * 1024, us = (Rw * g->Rt * 4 + 15) / 16 * 16, accp = (g->kg * g->rows * g->Rt * 4 + 15) / 16 * 16;
     work = (work + 15) / 16 * 16;
+    g->atile_bytes = (g->kg * g->rows + 7) / 8 * 1024;
+    const int atiles = g->nsu * g->atile_bytes;
+    const int us = (Rw * g->Rt * 4 + 15) / 16 * 16, accp = g->kg * g->rows * g->nbp * 4;
     const int asf = g->nkt * g->rows * 16;
-    const int fixed = btile + 1024 + us + work + accp + asf;
+    const int fixed = atiles + 1024 + us + work + accp + asf;
     const int budget = (coresident ? CORESIDENT_SMEM : SMEM_BUDGET) - 1024;       // (alignment slack)
     int ring = (budget - fixed) / g->stage_bytes;
     if (ring > MAX_RING) ring = MAX_RING;
     if (ring > g->nsu) ring = g->nsu;
     if (ring < 1 || (ring < 2 && g->nsu >= 2)) return false;
     g->ring = ring;
-    g->off_btile = ring * g->stage_bytes;
-    g->off_ctrl = g->off_btile + btile;
+    g->off_ring = atiles;
+    g->off_ctrl = g->off_ring + ring * g->stage_bytes;
     g->off_us = g->off_ctrl + 1024;
     g->off_work = g->off_us + us;
     g->off_accp = g->off_work + work;
     g->off_asf = g->off_accp + accp;
     int total = g->off_asf + asf;
-    // the tensor core reads 128 rows x 128 bytes from a stage's base whatever the super-unit's real height is
-    if (total < (ring - 1) * g->stage_bytes + 16384) total = (ring - 1) * g->stage_bytes + 16384;
+    // The tensor core reads 128 rows x 128 bytes from an activation tile's base and nbp rows x 128 bytes from a stage's
+    // base, whatever lies there: both windows must stay inside the allocation.
+    const int a_end = (g->nsu - 1) * g->atile_bytes + 16384;
+    const int w_end = g->off_ring + (ring - 1) * g->stage_bytes + g->nbp * 128;
+    if (total < a_end) total = a_end;
+    if (total < w_end) total = w_end;
     g->smem_bytes = total + 1024;
     return g->smem_bytes <= (coresident ? CORESIDENT_SMEM : SMEM_BUDGET);
 }
@@ -109,7 +125,7 @@ static int slab_launch_rows(const SlabParams& p, const Geo& g, bool pdl, cudaStr
         attr_set[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)g.G);
+    cfg.gridDim = dim3((unsigned)g.grid);
     cfg.blockDim = dim3(NT);
     cfg.dynamicSmemBytes = (size_t)g.smem_bytes;
     cfg.stream = stream;

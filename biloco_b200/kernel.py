@@ -197,7 +197,7 @@ class GroupedBiLoCoGemm:
         g0 = gemms[0]
         assert 2 <= len(gemms) <= 4 and all(isinstance(g, BiLoCoGemm) for g in gemms)
         assert all(g.K == g0.K and g.R == g0.R and g.M == g0.M and g.N % 128 == 0 for g in gemms) and g0.R % 32 == 0
-        assert all(g.W_tiled.numel() for g in gemms) and all(g.residual is None and not g.fp32_out for g in gemms)
+        assert all(g.residual is None and not g.fp32_out for g in gemms)
         self.rows = [g.N for g in gemms]
         self.N, self.K, self.R, self.M = sum(self.rows), g0.K, g0.R, g0.M
         dev = g0.W_fp4.device
@@ -205,15 +205,16 @@ class GroupedBiLoCoGemm:
         self.W_fp4 = cat([g.W_fp4 for g in gemms], 0).contiguous()
         # (block scales are stored per 128-row block and the re-laid weight per 128-row tile: stacking is concatenation)
         self.W_sf = cat([g.W_sf.view(torch.uint8).reshape(-1) for g in gemms]).view(torch.float8_e4m3fn)
-        self.W_tiled = cat([g.W_tiled for g in gemms])
+        # (the re-laid weight is stored per 128-row tile, so the stacked copy is the concatenation of the separate ones;
+        # launchers on the row-slab schedule hold another layout, so the stack is re-laid here)
+        self.W_tiled = _ops.tile_weights(self.W_fp4, self.W_sf)
         self.V = cat([g.V for g in gemms], 0).contiguous()
         self.S = cat([g.S for g in gemms]).contiguous()
         self.U_col32 = cat([g.U_col32 for g in gemms], 0).contiguous()
         with torch.cuda.device(dev):
-            ok = supported_modes(self.M, self.N, self.K, self.R * len(gemms))
+            ok = [m for m in supported_modes(self.M, self.N, self.K, self.R * len(gemms)) if m != 7]   # (row slabs: one group)
             if mode is None:
-                mode = DEFAULT_MODE.get(self.M, {}).get(self.R)
-                mode = mode if mode in ok else (ok or [None])[0]
+                mode = default_mode(self.M, self.R, ok)
             assert mode in ok, f"mode {mode} not available for the stacked problem"
             self.mode = mode
             nbytes = scratch_bytes(self.M, self.N, self.K, self.R * len(gemms))
