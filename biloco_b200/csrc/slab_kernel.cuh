@@ -86,7 +86,7 @@ struct SlabParams {
     int skip_publish_cta;     // test aid: this CTA does not publish its z values (-1: none)
     int trigger;              // where the CTA lets the next kernel of the stream start: 0 after set-up, 1 once its
                               // activations are in registers and its z slice is computed, 2 once it has seen all of z,
-                              // 3 after its store
+                              // 3 after its store, 4 once its last weight record has landed
     int dbg;                  // timing experiments (wrong results): 1 no MMAs are issued, 2 the z poll does not wait
     int lut;                  // expansion by look-up table (the launcher has added the table behind the partial sums)
     int inflight;             // weight records a CTA keeps in flight while it fills its ring (0: all at once)
@@ -496,11 +496,15 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 mbar_arrive(smem_u32(&ctrl->sf_full[j % NSETS]));
             }
             if (st == 0 && stamps) { stamps[11] = globaltimer_ns(); stamps[27] = (unsigned long long)clock64(); }
+            if (p.trigger == 4 && st == 0 && nsu <= ring) griddep_launch_dependents();
             // stages and sets that are filled again
 #pragma unroll 1
             for (int j = nfirst; j < nsu; ++j) {
                 const int set = j % NSETS;
                 bool ready = swait(smem_u32(&ctrl->full[j % ring]), (j / ring) & 1, ctrl, p, ST_FULL, warp);
+                // trigger 4: the next kernel of the stream moves in (and starts its weight burst) once this CTA's last
+                // weight record has landed, i.e. after the last global read on this launch's critical path
+                if (p.trigger == 4 && st == 0 && j == nsu - 1) griddep_launch_dependents();
                 if (ready && j >= NSETS) ready = swait(smem_u32(&ctrl->sf_empty[set]), ((j / NSETS) - 1) & 1, ctrl, p, ST_SF_EMPTY, warp);
                 if (!__all_sync(0xffffffffu, ready)) break;
                 tc_fence_after_sync();

@@ -317,3 +317,57 @@ def test_slab_weight_layout(kernel, lib, N, K):
     got = ops.tile_weights_slab(t["W"], t["W_sf"]).cpu().numpy()
     want = _slab_layout_numpy(p["W"], p["W_sf"], N, K, info[0], info[1])
     assert got.size == want.size and np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("r", [128, 256, 1024])
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32])
+def test_fused_config1_grid_random_scales(kernel, M, r):
+    """The batch / rank sweep of the mode table (K = N = 5120) with NON-zero block scales, so that the tensor-core product
+    and the low-rank term are both live at every point; every supported schedule, two launches each. (r = 512 is
+    covered by test_fused_full_size_random_scales and the other tests.)"""
+    _run_fused(kernel, orc.random_problem(M, 5120, 5120, r, scales="random", seed=77 * M + r), M, 5120, launches=2)
+
+
+def _column_subset(p, cols):
+    """The same problem restricted to the output columns `cols` (a multiple of 8 of them): y[:, n] depends on row n of W and
+    column n of U only, so the oracle can check a slice of a layer that is too large to dequantise whole."""
+    N = p["W"].shape[0]
+    K = p["W"].shape[1] * 2
+    q = dict(p)
+    q["W"] = p["W"][cols]
+    sf = orc.sf_unswizzle(p["W_sf"], N, K)[cols]
+    q["W_sf"] = orc.sf_swizzle(sf, K)
+    q["U"] = p["U"][:, cols]
+    q["U_packed"] = orc.pack_signs(q["U"])
+    return q
+
+
+@pytest.mark.parametrize("r", [512, 1024])
+@pytest.mark.parametrize("K,N", [(8192, 8192), (8192, 28672), (28672, 8192)])
+def test_fused_config3_large_shapes(kernel, K, N, r):
+    """Large-shape, large-batch linears (M = 32, r in {512, 1024}, non-zero scales), every supported schedule: the whole
+    output against the device's unfused composition (itself checked against the oracle at the smaller sizes), and three
+    256-column slices (first tile, a slice that straddles tiles in the middle, the last columns) against the CPU oracle's
+    unfused and exact values."""
+    M = 32
+    p = orc.random_problem(M, K, N, r, scales="random", seed=K // 64 + N // 128 + r)
+    t = dev_problem(p)
+    y_unf = kernel.reference(t["A"], t["A_sf"], t["W"], t["W_sf"], t["alpha"], t["X"], t["V_packed"], t["U_packed"], t["S"])
+    y_unf = y_unf.view(-1, N)[:M].float().cpu().numpy()
+    slices = [np.arange(0, 256), np.arange(N // 2 - 64, N // 2 + 192), np.arange(N - 256, N)]
+    refs = [oracle_outputs(_column_subset(p, c), M) for c in slices]
+    for c, (y_ref, _) in zip(slices, refs):
+        check_against_unfused(y_unf[:, c], y_ref, f"unfused device path, columns {c[0]}..")
+    for mode in kernel.supported_modes(M, N, K, r):
+        g = kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M, mode=mode)
+        y0 = None
+        for it in range(2):
+            y = g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].float().cpu().numpy()
+            check_against_unfused(y, y_unf, f"config 3 K={K} N={N} r={r} mode {mode} launch {it}")
+            for c, (y_ref, y_exact) in zip(slices, refs):
+                check_against_unfused(y[:, c], y_ref, f"config 3 K={K} N={N} r={r} mode {mode} columns {c[0]}..")
+                check_against_exact(y[:, c], y_exact, f"config 3 K={K} N={N} r={r} mode {mode} columns {c[0]}..")
+            y0 = y if y0 is None else y0
+            assert np.array_equal(y, y0)
+        assert g.status()[0] == 0, f"device-side wait ran out: {g.status()[:4]}"
+        del g
