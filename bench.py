@@ -17,9 +17,18 @@ default 64 layers that is 986 MB per step, far larger than L2, so every launch s
   cpu_baseline  the CPU oracle's fake-quant forward (biloco/layer.py:54-64 semantics) on the host cores,
                 bounded sample
 
+  tp_decode     (unless --no-decode) the sharded path: a Llama-3-70B-shaped decoder, every linear a rank-512 layer, q/k/v/
+                gate/up/lm_head column-parallel and o/down row-parallel over the N ranks with an NCCL all-reduce of the
+                fp32 partial sums inside the captured step (biloco_b200.decode); tokens/s, ms per step, all-reduces and
+                bytes per step. At N = 1 the same model on one GPU, so that the per-N lines give the parallel efficiency
+  comparator    (N = 1, default point, if oracle/_ref holds the reference's extension built for sm_100a) the reference's own
+                fused kernel on this GPU, in a process of its own: L2-warm as the reference measures and HBM-cold
+
 ``--impl reference`` times that CPU forward alone and prints the same line shape with "impl": "reference".
-Multi-GPU (torchrun, one rank per GPU): every rank runs its own set of layers (the path shards by layer / by
-output columns with no exchange), so scaling is weak and no collective sits on the data path.
+``--table`` prints the per-(M, rank) report of scripts/kernel_table.py instead (every schedule, L2-warm and HBM-cold, error
+over consecutive launches), as markdown.
+Multi-GPU (torchrun, one rank per GPU): `value` is measured on replicas (every rank its own layers: the single linear
+shards by layer / by output columns with no exchange, weak scaling); the tensor-parallel path is the tp_decode leg.
 """
 import argparse
 import json
@@ -34,9 +43,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of fused_linear_kernel<8> at M=1, K=N=5120, r=512,
-# from the ncu capture summarised in profiles/fused_linear_M1_K5120_N5120_r512.md (other shapes: null)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 15_543_000
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at M=1, K=N=5120, r=512 from one ncu capture per kernel
+# (summaries under profiles/; other shapes and kernels: null)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"slab_kernel": None, "fused_linear_kernel": 15_543_000}
 
 
 def algorithmic_bytes(K, N, r):
@@ -122,7 +131,7 @@ def make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed, mode=None, share_a
         else:
             q = fp4.quantize_activation(x, "mse", w_gscale=w_gs, rows=M)
         gemm = kernel.BiLoCoGemm(W, W_sf, q["alpha"], Vp, Up, S, M=M, mode=mode)
-        layers.append(dict(gemm=gemm, q=q, x=x, w_gs=w_gs))
+        layers.append(dict(gemm=gemm, q=q, x=x, w_gs=w_gs, ops=(W, W_sf, Vp, Up, S)))
     return layers
 
 
@@ -164,21 +173,25 @@ def run_reference(args):
     if rank != 0:
         return
     import torch
+    # every host core, whatever OMP_NUM_THREADS the launcher exported (torchrun sets it to 1)
+    torch.set_num_threads(os.cpu_count() or 1)
     K, N, r, M = args.K, args.N, args.r, args.M
-    sec, n = time_cpu_forward(M, K, N, r, calls=max(args.steps, 3), warm=max(args.warmup, 3), budget_s=120)
+    sec, n = time_cpu_forward(M, K, N, r, calls=max(min(args.steps, 200), 3), warm=max(args.warmup, 3), budget_s=120)
     gbs = algorithmic_bytes(K, N, r) / sec / 1e9
     cores = os.cpu_count()
     line = {
         "impl": "reference", "metric": "fused BiLoCo linear algorithmic HBM GB/s", "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": n, "warmup": max(args.warmup, 3), "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 (+ f32 sign accumulate)", "data": "synthetic",
-        "config": workload_config(args, layers=1),
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"{n} calls of the fake-quant forward of one layer (M={M}, K={K}, N={N}, r={r}), median; "
-                                   f"numpy/BLAS threads = {torch.get_num_threads()}"},
+        "config": workload_config(args, layers=args.layers),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{n} calls of the fake-quant forward of ONE of the step's {args.layers} layers (M={M}, K={K}, "
+                                   f"N={N}, r={r}), median; a step is {args.layers} such calls; torch threads = "
+                                   f"{torch.get_num_threads()} of {cores} host cores"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "us_per_call": sec * 1e6,
     }
+    line["ms_per_step"] = sec * 1e3 * args.layers
     print(json.dumps(line), flush=True)
 
 
@@ -218,7 +231,8 @@ def run_ours(args):
 
     def step_device():
         for ly in layers:
-            ly["out"] = ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], ly["x"], A_rec=ly["q"].get("A_rec"))
+            g = ly["gemm"]
+            ly["out"] = g(ly["q"]["A"], ly["q"]["A_sf"], ly["x"], A_rec=ly["q"].get("A_rec") if g.mode != 7 else None)
 
     # ---- device-resident arm: one CUDA graph per step -------------------------------------------------
     side = torch.cuda.Stream()
@@ -279,11 +293,20 @@ def run_ours(args):
     y_dev = torch.empty(L, M, N, device=dev, dtype=torch.bfloat16)
     y_host = torch.empty(L, M, N, dtype=torch.bfloat16).pin_memory()
 
+    # (the launchers of this arm are built for a stream in which a quantiser launch precedes every linear, as
+    # BiLoCoLinear.forward builds them; when that is the same schedule as the device arm's the launcher is shared)
+    for ly in layers:
+        g0 = ly["gemm"]
+        want = kernel.default_mode(M, r, kernel.supported_modes(M, N, K, r), back_to_back=False) if args.mode is None else args.mode
+        ly["gemm_e2e"] = g0 if g0.mode == want else kernel.BiLoCoGemm(ly["ops"][0], ly["ops"][1], ly["q"]["alpha"], *ly["ops"][2:],
+                                                                       M=M, mode=want)
+
     def step_e2e_body():
         x_dev.copy_(x_host, non_blocking=True)
         for i, ly in enumerate(layers):
             fp4.quantize_activation(x_dev[i], "mse", w_gscale=ly["w_gs"], rows=M, out=ly["q"])
-            ly["gemm"](ly["q"]["A"], ly["q"]["A_sf"], x_dev[i], out=y_dev[i], A_rec=ly["q"].get("A_rec"))
+            g = ly["gemm_e2e"]
+            g(ly["q"]["A"], ly["q"]["A_sf"], x_dev[i], out=y_dev[i], A_rec=ly["q"].get("A_rec") if g.mode != 7 else None)
         y_host.copy_(y_dev, non_blocking=True)
 
     with torch.cuda.stream(side):
@@ -315,12 +338,28 @@ def run_ours(args):
         e2e_s = float(t.item())
     e2e_value = world * L * bytes_call * e2e_steps / e2e_s / 1e9
 
+    # ---- tensor-parallel decode leg (every rank takes part) ---------------------------------------------
+    tp = None
+    default_point = (M, K, N, r) == (1, 5120, 5120, 512)
+    if not args.no_decode and default_point:
+        mode0, mode_e2e = layers[0]["gemm"].mode, layers[0]["gemm_e2e"].mode
+        del graph, graph_e2e
+        layers.clear()
+        torch.cuda.empty_cache()
+        try:
+            tp = tp_decode_leg(torch, dist, world, rank, dev, args)
+        except Exception as e:      # the linear's line stands on its own
+            tp = {"error": f"{type(e).__name__}: {e}"[:300]}
+    else:
+        mode0, mode_e2e = layers[0]["gemm"].mode, layers[0]["gemm_e2e"].mode
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
     peak, peak_kind = measured_hbm_peak()
+    kname = "slab_kernel" if mode0 == 7 else "fused_linear_kernel"
     achieved = bytes_call / (us_per_call * 1e-6) / 1e9
     line = {
         "metric": "fused BiLoCo linear algorithmic HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
@@ -333,8 +372,10 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": L * M * K * 2, "d2h_bytes_per_step": L * M * N * 2,
                 "steps": e2e_steps, "us_per_call": e2e_s / e2e_steps / L * 1e6},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (M, K, N, r) == (1, 5120, 5120, 512) else None, "peak_source": f"{peak_kind} (STREAM-style copy)",
-                     "kernel": "fused_linear_kernel", "algorithmic_bytes_per_launch": bytes_call},
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get(kname) if (M, K, N, r) == (1, 5120, 5120, 512) else None,
+                     "peak_source": f"{peak_kind} (STREAM-style copy)",
+                     "kernel": kname, "schedule": mode0, "algorithmic_bytes_per_launch": bytes_call},
+        "e2e_schedule": mode_e2e,
     }
     if world == 1 and not args.no_cpu:
         sec, n = time_cpu_forward(M, K, N, r, calls=200, warm=3, budget_s=args.cpu_budget)
@@ -342,14 +383,70 @@ def run_ours(args):
                                 "us_per_call": sec * 1e6,
                                 "sample": f"{n} calls of the CPU oracle's fake-quant forward of one layer "
                                           f"(M={M}, K={K}, N={N}, r={r}), median; BLAS threads = {torch.get_num_threads()}"}
-    if world == 1 and not args.no_decode and (M, K, N, r) == (1, 5120, 5120, 512):
+    if tp is not None:
+        line["tp_decode"] = tp
+    if world == 1 and not args.no_decode and default_point:
         try:
             line["decode"] = decode_leg(torch)
         except Exception as e:      # the linear's line stands on its own
             line["decode"] = {"error": f"{type(e).__name__}: {e}"[:300]}
+    if world == 1 and not args.no_comparator and default_point:
+        line["comparator"] = comparator_leg()
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
+
+
+def comparator_leg():
+    """The reference's own extension (built for sm_100a into oracle/_ref by oracle/build_ref_kernel.py) at the headline
+    point, in a process of its own; absent library: says so."""
+    so = os.path.join(ROOT, "oracle", "_ref", "biloco_ref_C.so")
+    if not os.path.exists(so):
+        return {"unavailable": "oracle/_ref/biloco_ref_C.so is not built (python -m oracle.build_ref_kernel)"}
+    try:
+        out = subprocess.run([sys.executable, "-m", "oracle.ref_kernel", "--Ms", "1"], cwd=ROOT, capture_output=True, text=True,
+                             timeout=300)
+        row = json.loads(out.stdout.strip().splitlines()[-1])["rows"]["1"]
+        return {"what": "reference extension csrc/biloco_gemm.cu on this GPU, K=N=5120, r=512, M=1; us per launch",
+                "fp4_only_pad_us_l2_warm": row["pad_us"], "fp4_only_pad_us_hbm_cold": row.get("pad_cold_us"),
+                "fused_mode4_us_l2_warm": row["mode4_us"], "fused_mode4_us_hbm_cold": row.get("mode4_cold_us"),
+                "fused_mode4_err_over_max": row["mode4_err_over_max"],
+                "fused_mode2": "wrong result at M=1 on this device (max error = max |y_ref|), not timed"
+                               if row["mode2_err_over_max"] > 0.01 else row["mode2_us"],
+                "not_run": "fp4_gemm / fp4_gemm_residual (cluster multicast loads) and mode 5 (unbounded waits): closed on this pool"}
+    except Exception as e:
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+
+def tp_decode_leg(torch, dist, world, rank, dev, args):
+    """The N/K-sharded path: greedy decode of a Llama-3-70B-shaped decoder (80 layers, hidden 8192, intermediate 28672, 64
+    query / 8 KV heads, vocabulary 128256; every linear a rank-512 layer with random packed operands) through the captured
+    step of biloco_b200.decode: q/k/v, gate/up and lm_head column-parallel, o and down row-parallel with one NCCL
+    all-reduce of the fp32 partial sums each inside the step. One rank per GPU; at world size 1 the whole model on one."""
+    from biloco_b200 import decode
+    c = decode.PRESETS["llama3-70b"]
+    if args.tp_layers:
+        c = decode.DecoderConfig(**{**c.__dict__, "layers": args.tp_layers})
+    torch.manual_seed(0)
+    model = decode.Decoder(c, device=dev, meta=True, tp=world)
+    nlin = decode.synthetic_quantize(model, 512, seed=1000 * rank)
+    g = torch.Generator(device=dev).manual_seed(0)
+    prompt = torch.randint(0, c.vocab, (args.tp_M, args.tp_prompt), device=dev, generator=g)
+    toks, sec = decode.greedy_decode(model, prompt, args.tp_steps, use_graph=True)
+    nbytes = decode.linear_bytes(model) * world
+    if dist is not None:
+        t = torch.tensor([sec], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+    peak, _ = measured_hbm_peak()
+    n_ar = 2 * c.layers if world > 1 else 0
+    return {"model": f"Llama-3-70B-shaped ({c.layers} layers, hidden 8192, intermediate 28672, vocab 128256), random packed operands",
+            "parallelism": f"tp{world}: q/k/v/gate/up/lm_head column shards, o/down row shards", "M": args.tp_M, "rank": 512,
+            "linears_per_rank": nlin, "prompt": args.tp_prompt, "steps": args.tp_steps,
+            "tokens_per_s": args.tp_M * args.tp_steps / sec, "ms_per_step": sec / args.tp_steps * 1e3,
+            "all_reduces_per_step": n_ar, "all_reduce_bytes_each": args.tp_M * c.hidden * 4 if world > 1 else 0,
+            "linear_bytes_per_step": nbytes, "hbm_frac_of_n_gpus": nbytes * args.tp_steps / sec / 1e9 / (peak * world),
+            "finite": bool(torch.isfinite(toks.float()).all())}
 
 
 def decode_leg(torch, prompt_len=16, steps=48):
@@ -374,6 +471,74 @@ def decode_leg(torch, prompt_len=16, steps=48):
             "finite": bool(torch.isfinite(toks.float()).all())}
 
 
+def run_table(args):
+    """The report of scripts/kernel_table.py:44-77 for this library on this GPU, as markdown: per (M, rank) at K = N = 5120
+    every schedule the shape takes, timed L2-warm (the reference's protocol: a graph of 64 launches on the same operands,
+    median of 30 replays) and HBM-cold (a graph over `--table-layers` distinct layers, > L2), with the largest error
+    over `--stress` consecutive launches against the unfused device path (non-zero block scales: both terms live)."""
+    import torch
+    from biloco_b200 import fp4, kernel
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    K, N, L = args.K, args.N, args.table_layers
+    Ms = [int(x) for x in args.table_Ms.split(",")]
+    ranks = [int(x) for x in args.table_ranks.split(",")]
+    modes = (2, 4, 5, 7)
+    print(f"# Kernel table, {torch.cuda.get_device_name()}, K={K} N={N}: us per launch, L2-warm / HBM-cold ({L} distinct layers); "
+          f"error = max|y - y_unfused| / max|y_unfused| over {args.stress} launches\n")
+    print("| M | r | " + " | ".join(f"mode {m}" for m in modes) + " | best cold | GB/s | of peak | max err |")
+    print("|---|---|" + "---|" * (len(modes) + 4))
+    peak, _ = measured_hbm_peak()
+    for M in Ms:
+        for r in ranks:
+            layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=17 * M + r, mode=2)
+            ly0 = layers[0]
+            W, W_sf, Vp, Up, S = ly0["ops"]
+            y_ref = kernel.reference(ly0["q"]["A"], ly0["q"]["A_sf"], W, W_sf, ly0["q"]["alpha"], ly0["x"], Vp, Up, S)
+            y_ref = y_ref.view(-1, N)[:M].float()
+            cells, best, worst = [], None, 0.0
+            for mode in modes:
+                if mode not in kernel.supported_modes(M, N, K, r):
+                    cells.append("-")
+                    continue
+                gs = [kernel.BiLoCoGemm(*ly["ops"][:2], ly["q"]["alpha"], *ly["ops"][2:], M=M, mode=mode) for ly in layers]
+                err = 0.0
+                for _ in range(args.stress):
+                    y = gs[0](ly0["q"]["A"], ly0["q"]["A_sf"], ly0["x"]).view(-1, N)[:M].float()
+                    err = max(err, float((y - y_ref).abs().max() / y_ref.abs().max()))
+                assert gs[0].status()[0] == 0
+                warm = kernel.time_graph(lambda: gs[0](ly0["q"]["A"], ly0["q"]["A_sf"], ly0["x"]))
+                cold = kernel.time_graph(lambda: [g(ly["q"]["A"], ly["q"]["A_sf"], ly["x"]) for g, ly in zip(gs, layers)], batch=1) / L
+                cells.append(f"{warm:.2f} / {cold:.2f}")
+                worst = max(worst, err)
+                if best is None or cold < best[1]:
+                    best = (mode, cold)
+                del gs
+            gbs = algorithmic_bytes(K, N, r) / (best[1] * 1e-6) / 1e9
+            print(f"| {M} | {r} | " + " | ".join(cells) + f" | {best[1]:.2f} (mode {best[0]}) | {gbs:.0f} | {gbs / peak:.3f} | {worst:.1e} |",
+                  flush=True)
+            del layers
+            torch.cuda.empty_cache()
+    so = os.path.join(ROOT, "oracle", "_ref", "biloco_ref_C.so")
+    if os.path.exists(so) and (K, N) == (5120, 5120):
+        out = subprocess.run([sys.executable, "-m", "oracle.ref_kernel", "--Ms", "1,2,4,8", "--cold-layers", str(L)], cwd=ROOT,
+                             capture_output=True, text=True, timeout=900)
+        try:
+            rows = json.loads(out.stdout.strip().splitlines()[-1])["rows"]
+            print("\n# The reference's own extension (csrc/biloco_gemm.cu built for sm_100a) on the same GPU, r = 512: us per launch, "
+                  "L2-warm / HBM-cold; fp4_gemm, fp4_gemm_residual and mode 5 are not run (closed on this pool)\n")
+            print("| M | pad (FP4 only) | s128 (FP4 only) | mode 2 | mode 4 | mode 4 max err |")
+            print("|---|---|---|---|---|---|")
+            for M, row in rows.items():
+                f = lambda k: f"{row[k]:.2f}" if k in row else "-"
+                m2 = "wrong result" if row["mode2_err_over_max"] > 0.01 else f"{f('mode2_us')} / {f('mode2_cold_us')}"
+                print(f"| {M} | {f('pad_us')} / {f('pad_cold_us')} | {f('s128_us')} / - | {m2} | {f('mode4_us')} / {f('mode4_cold_us')} | "
+                      f"{row['mode4_err_over_max']:.1e} |")
+        except Exception as e:
+            print(f"\n(reference extension: no result: {type(e).__name__}: {e}; stderr tail: {out.stderr[-300:]})")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -393,8 +558,20 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode leg (default workload, one GPU only)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")
+    ap.add_argument("--no-comparator", action="store_true", help="skip the reference extension's leg (one GPU, default workload)")
+    ap.add_argument("--tp-layers", type=int, default=0, help="tp_decode leg: decoder layers (0 = all 80)")
+    ap.add_argument("--tp-M", type=int, default=1, help="tp_decode leg: sequences decoded together")
+    ap.add_argument("--tp-prompt", type=int, default=512)
+    ap.add_argument("--tp-steps", type=int, default=128)
+    ap.add_argument("--table", action="store_true", help="print the per-(M, rank) kernel table as markdown instead")
+    ap.add_argument("--table-Ms", default="1,2,4,8,16,32")
+    ap.add_argument("--table-ranks", default="128,256,512,1024")
+    ap.add_argument("--table-layers", type=int, default=24, help="distinct layers of the HBM-cold graph (24 x 15 MB > L2)")
+    ap.add_argument("--stress", type=int, default=50, help="--table: launches checked against the unfused path per schedule")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.table:
+        run_table(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

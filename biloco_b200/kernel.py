@@ -32,13 +32,17 @@ _MODE2_WINS = {(2, 1024), (8, 1024)}
 DEFAULT_MODE = {M: {r: (2 if (M > 8 or (M, r) in _MODE2_WINS) else 5) for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
 
 
-def default_mode(M: int, rank: int, ok):
-    """The schedule BiLoCoGemm picks among the modes `ok` that the shape takes: row slabs for one or two rows, else the
-    measured table's entry, else the first that is available."""
-    if M <= 2 and 7 in ok:
+def default_mode(M: int, rank: int, ok, back_to_back: bool = True):
+    """The schedule BiLoCoGemm picks among the modes `ok` that the shape takes. Row slabs (mode 7) for one or two rows when
+    the launches of a stream follow one another directly (the reference's measurement protocol, a chain of linears): a
+    row-slab CTA takes the SM's whole tensor memory and relies on meeting exactly one CTA of the next launch on its SM.
+    With other kernels in between (an activation quantiser per linear, the decode step) two CTAs of one launch can land
+    on one SM and take turns (measured: 20.6 us per layer against 16.4 with the cluster schedule), so
+    back_to_back=False keeps to the measured table of the other schedules; then the first that is available."""
+    if M <= 2 and 7 in ok and back_to_back:
         return 7
     mode = DEFAULT_MODE.get(M, {}).get(rank)
-    return mode if mode in ok else (ok or [None])[0]
+    return mode if mode in ok else ([m for m in ok if m != 7] or [None])[0]
 
 
 def pack_signs(signs: torch.Tensor) -> torch.Tensor:
@@ -120,14 +124,15 @@ class BiLoCoGemm:
     as the reference requires, stays valid).
     """
 
-    def __init__(self, W_fp4, W_sf, alpha, V_packed, U_packed, S, M: int, mode: int = None, tile_weights: bool = True):
+    def __init__(self, W_fp4, W_sf, alpha, V_packed, U_packed, S, M: int, mode: int = None, tile_weights: bool = True,
+                 back_to_back: bool = True):
         self.N, self.K = W_fp4.shape[0], W_fp4.shape[1] * 2
         self.R, self.M = V_packed.shape[0], M
         dev = W_fp4.device
         with torch.cuda.device(dev):
             ok = supported_modes(M, self.N, self.K, self.R)
         if mode is None:      # the table's choice if this shape takes it, else the first mode that does
-            mode = default_mode(M, self.R, ok)
+            mode = default_mode(M, self.R, ok, back_to_back)
         self.mode = mode
         assert self.mode in ok, f"mode {self.mode} not available for M={M} N={self.N} K={self.K} R={self.R}"
         self.W_fp4, self.W_sf, self.alpha, self.V, self.S = W_fp4, W_sf, alpha, V_packed, S
@@ -214,7 +219,7 @@ class GroupedBiLoCoGemm:
         with torch.cuda.device(dev):
             ok = [m for m in supported_modes(self.M, self.N, self.K, self.R * len(gemms)) if m != 7]   # (row slabs: one group)
             if mode is None:
-                mode = default_mode(self.M, self.R, ok)
+                mode = default_mode(self.M, self.R, ok, back_to_back=False)
             assert mode in ok, f"mode {mode} not available for the stacked problem"
             self.mode = mode
             nbytes = scratch_bytes(self.M, self.N, self.K, self.R * len(gemms))

@@ -104,7 +104,8 @@ class BiLoCoLinear(nn.Module):
         g = self._gemms.get(M)
         if g is None:
             if self.rank > 0:
-                g = BiLoCoGemm(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), alpha, self.V_packed, self.U_packed, self.S, M=M)
+                g = BiLoCoGemm(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), alpha, self.V_packed, self.U_packed, self.S, M=M,
+                               back_to_back=False)      # (a quantiser launch sits between the linears)
             else:
                 g = _FP4Only(self.W_codes, self.W_sf.view(torch.float8_e4m3fn), alpha, M=M)
             if self.bias is not None:     # added inside the kernel, before its single bf16 rounding

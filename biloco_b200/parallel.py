@@ -88,7 +88,8 @@ class ShardedBiLoCoLinear:
         self.N, self.K = o["W_codes"].shape[0], o["W_codes"].shape[1] * 2
         dev = o["W_codes"].device
         self.alpha = torch.zeros(1, device=dev, dtype=torch.float32)
-        self.gemm = BiLoCoGemm(o["W_codes"], o["W_sf"].view(torch.float8_e4m3fn), self.alpha, o["V_packed"], o["U_packed"], o["S"], M=M)
+        self.gemm = BiLoCoGemm(o["W_codes"], o["W_sf"].view(torch.float8_e4m3fn), self.alpha, o["V_packed"], o["U_packed"], o["S"], M=M,
+                               back_to_back=False)
         self.gemm.fp32_out = kind == "row"     # partial sums are reduced in fp32; one bf16 rounding after the all-reduce
         if o.get("bias") is not None:
             self.gemm.residual = o["bias"].to(torch.bfloat16).unsqueeze(0).expand(M, self.N).contiguous()
