@@ -45,7 +45,7 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch at M=1, K=N=5120, r=512 from one ncu capture per kernel
 # (summaries under profiles/; other shapes and kernels: null)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {"slab_kernel": None, "fused_linear_kernel": 15_543_000}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"slab_kernel": 15_511_000, "fused_linear_kernel": 15_543_000}
 
 
 def algorithmic_bytes(K, N, r):

@@ -11,12 +11,13 @@
 //  * Work unit = (128-row tile t, 256-wide k-tile kt): 16 KB of E2M1 codes + 2 KB of E4M3 scales. The
 //    T = ntile * nkt units are split evenly over all CTAs (one per SM) as contiguous ranges in (t, kt)
 //    order ("stream-K", schedule.h), so every SM streams the same number of weight bytes whatever N is.
-//  * Warp roles (192 threads): warps 0-3 = z stage, U expansion and epilogue (thread = TMEM lane = weight row);
-//    warp 4 = TMA producer; warp 5 = TMEM allocation + MMA issue.
-//  * Per stage: W codes by a 2-D TMA tile (128 rows x 128 B, 128-byte swizzle), activation codes by a 2-D TMA
-//    tile (MMA_N rows x 128 B), both scale tiles by untiled bulk copies (the 128x4 atom layout is already what
-//    tcgen05.cp 32x128b.warpx4 wants: 4 atoms of 512 B per k-tile). Four tcgen05.mma kind::mxf4nvf4
-//    (K = 64 each) per stage.
+//  * Warp roles (448 threads): warps 0-3 = z stage, U expansion and epilogue (thread = TMEM lane = weight row);
+//    warps 4-7 = feeders (first copy requests; scale factors from shared memory into TMEM with tcgen05.st, one
+//    32-lane quadrant each); warps 8-11 = second half of the z stage; warp 12 = TMEM allocation + MMA issue;
+//    warp 13 = refills (re-requests stages as they come free).
+//  * Per stage: one contiguous 18 KB record (codes already swizzled + the four 512 B scale atoms) by a bulk copy, or
+//    from row-major weights a 2-D TMA tile (128 rows x 128 B, 128-byte swizzle) + a bulk copy of the atoms; the
+//    activation tile likewise. Four tcgen05.mma kind::mxf4nvf4 (K = 64 each) per stage.
 //  * A tile whose k-range is shared by several CTAs is finished by the CTA that holds its last k-tile: the
 //    others store fp32 partials (alpha*acc + their slice of the low-rank term) to scratch and bump the tile's
 //    counter; the finisher adds them in slot order (deterministic), rounds and stores.
@@ -127,6 +128,25 @@ static unsigned long long g_wait_ns = WAIT_BUDGET_NS;   // budget of a device-si
 static int g_inflight = 0;                        // row-slab schedule: weight records in flight while the ring fills (0: all)
 static int g_dbg = 0;                             // row-slab schedule: timing experiments (see SlabParams::dbg)
 static int g_skip_publish = -1;                   // test aid: this CTA of a row-slab launch keeps its z values to itself
+
+// Streams on which an operand re-layout (tile_weights, tile_weights_slab, pack_u_col32) was the last thing this library
+// enqueued. The fused kernels read their static operands BEFORE griddepcontrol.wait when they are launched with
+// programmatic stream serialization (that is the point: the weight prefetch overlaps the previous kernel), so a fused
+// launch that directly follows the kernel which WRITES such an operand must not start early: the first fused launch on
+// such a stream goes out as a plain launch.
+static std::mutex g_fresh_mu;
+static std::unordered_map<cudaStream_t, int> g_fresh_streams;
+extern "C" void biloco_internal_mark_relayout(cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_fresh_mu);
+    g_fresh_streams[stream] = 1;
+}
+static bool consume_relayout_mark(cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_fresh_mu);
+    auto it = g_fresh_streams.find(stream);
+    if (it == g_fresh_streams.end()) return false;
+    g_fresh_streams.erase(it);
+    return true;
+}
 
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 
@@ -239,9 +259,17 @@ static int max_active_clusters(int rows, int cluster) {
             case 4: n = query_active_clusters<16, 16>(cluster); break;
             default: n = query_active_clusters<32, 32>(cluster); break;
         }
-        // The query credits one CTA per SM also for rows <= 2, whose CTAs are built so that two share an SM (launch
-        // bounds, 113 KB of shared memory; consecutive launches were observed side by side on the same SMs).
-        if (n > 0 && rc <= 1) n *= 2;
+        // The cluster query credits one CTA per SM also for rows <= 2, whose CTAs are built so that two share an SM
+        // (launch bounds, 113 KB of shared memory). Twice the count is relied on only if the occupancy query for a
+        // single CTA of that size confirms that two are resident per SM.
+        if (n > 0 && rc <= 1) {
+            int per_sm = 0;
+            const cudaError_t e = rc == 0
+                ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_linear_kernel<8, 1>, NUM_THREADS, (size_t)CORESIDENT_SMEM)
+                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_linear_kernel<8, 2>, NUM_THREADS, (size_t)CORESIDENT_SMEM);
+            if (e == cudaSuccess && per_sm >= 2) n *= 2;
+            else cudaGetLastError();
+        }
         c = n > 0 ? n : -1;
     }
     return c > 0 ? c : 0;
@@ -302,7 +330,8 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
     int dev_sms = 0;
     cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, dev);
     const bool tight_clusters = p.cluster > 1 && ctas_per_sm(ROWS) == 1 && p.G * 20 > dev_sms * 17;
-    if (g_use_pdl && !tight_clusters) {
+    const bool after_relayout = consume_relayout_mark(stream);
+    if (g_use_pdl && !tight_clusters && !after_relayout) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
@@ -383,6 +412,7 @@ extern "C" int biloco_b200_tile_weights(const void* W_codes, const void* W_sf, v
     if (units > 0x7fffffffll) return BILOCO_ERR_LIMIT;
     tile_weights_kernel<<<(unsigned)units, 256, 0, (cudaStream_t)stream>>>((const uint8_t*)W_codes, (const uint8_t*)W_sf,
                                                                             (uint8_t*)W_tiled, N, K, nkt);
+    biloco_internal_mark_relayout((cudaStream_t)stream);
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
@@ -466,8 +496,9 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
             const size_t per = (size_t)g.grid * slab::SLAB_STAMPS, slots = g_stamps_bytes / (per * 8);
             q.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
         }
-        return M <= 1 ? slab::slab_launch_rows<1>(q, g, g_use_pdl != 0, (cudaStream_t)stream)
-                      : slab::slab_launch_rows<2>(q, g, g_use_pdl != 0, (cudaStream_t)stream);
+        const bool pdl = g_use_pdl != 0 && !consume_relayout_mark((cudaStream_t)stream);
+        return M <= 1 ? slab::slab_launch_rows<1>(q, g, pdl, (cudaStream_t)stream)
+                      : slab::slab_launch_rows<2>(q, g, pdl, (cudaStream_t)stream);
     }
 
     CUtensorMap tmW, tmA;
@@ -716,6 +747,7 @@ extern "C" int biloco_b200_tile_weights_slab(const void* W_codes, const void* W_
     if (((uintptr_t)W_slab & 15) || ((uintptr_t)W_codes & 15) || ((uintptr_t)W_sf & 15)) return BILOCO_ERR_ALIGN;
     slab::tile_weights_slab_kernel<<<(unsigned)(g.G * g.nkt), 128, 0, (cudaStream_t)stream>>>(
         (const uint8_t*)W_codes, (const uint8_t*)W_sf, (uint8_t*)W_slab, N, K, g.Rt, g.kg, g.nkt);
+    biloco_internal_mark_relayout((cudaStream_t)stream);
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 

@@ -145,6 +145,8 @@ extern "C" int biloco_b200_binary_expand(const float* z, const void* U_packed, v
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
+extern "C" void biloco_internal_mark_relayout(cudaStream_t stream);      // (fused_linear.cu: the next fused launch on this stream starts plain)
+
 extern "C" int biloco_b200_pack_u_col32(const void* U_packed, int32_t* U_col32, int N, int R, biloco_stream_t stream) {
     if (!U_packed || !U_col32) return BILOCO_ERR_NULL;
     if (R < 1 || N < 8 || (N % 8) != 0) return BILOCO_ERR_SHAPE;
@@ -152,5 +154,6 @@ extern "C" int biloco_b200_pack_u_col32(const void* U_packed, int32_t* U_col32, 
     const long long total = (long long)N * words;
     pack_u_col32_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const uint8_t*)U_packed, U_col32,
                                                                                            N, R, words);
+    biloco_internal_mark_relayout((cudaStream_t)stream);
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }

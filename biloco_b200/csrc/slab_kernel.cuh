@@ -193,8 +193,10 @@ __device__ __forceinline__ float reduce8(const float (&v)[NRMAX], int lane) {
 // One segment of a thread's activation span against NQ ranks: sums[q] += sum of the segment's activations whose sign bit
 // in rank (r0 + q)'s row is set; plain += sum of all of them. xw holds the segment's n2 bf16 pairs; the segment starts
 // at element idx of the row (bit sh of sign word wi).
+// (Not inlined: it serves rows longer than 8192 elements only, and code that is never run should not sit between the
+// lines that are: the kernel's instructions are fetched once per launch and instruction fetch shows in its stall profile.)
 template <int NQ>
-__device__ __forceinline__ void zspan(const uint32_t (&xw)[XW_MAX], int n2, const uint32_t* vt, int words, int wi, int sh,
+__device__ __noinline__ void zspan(const uint32_t (&xw)[XW_MAX], int n2, const uint32_t* vt, int words, int wi, int sh,
                                       int r0, int nr, float (&sums)[NRMAX], float& plain) {
     // With eight ranks the eight sums are chains enough to cover the add latency; with four, each rank gets two.
     constexpr bool TWO = NQ <= 4;
@@ -267,6 +269,34 @@ __device__ __forceinline__ void zspan_rolled(const uint32_t* xs, int n2, const u
 #pragma unroll
     for (int q = 0; q < NQ; ++q) sums[q] += a1[q];
     plain += ps;
+}
+
+// Expansion without the table (ranks or rows for which the table would not fit): per item (rank word, column) 32 adds
+// under predicates taken from the word's bits. Not inlined (see zspan).
+template <int ROWS>
+__device__ __noinline__ void expand_padd(const float* zs, float* corrp, const uint32_t* us, int nit, int Rt, int Rw, int Rpad, int lt) {
+#pragma unroll 1
+    for (int id = lt; id < nit; id += LR_THREADS) {
+        const int w = id / Rt, col = id - w * Rt;
+        float c0[ROWS], c1[ROWS];
+#pragma unroll
+        for (int m = 0; m < ROWS; ++m) { c0[m] = 0.f; c1[m] = 0.f; }
+        uint32_t ub = us[id];
+#pragma unroll 1
+        for (int b = 0; b < 32; b += 4) {
+#pragma unroll
+            for (int m = 0; m < ROWS; ++m) {
+                const float4 zz = *reinterpret_cast<const float4*>(zs + m * Rpad + 32 * w + b);
+                BILOCO_SPADD(c0[m], ub, 1u, zz.x);
+                BILOCO_SPADD(c1[m], ub, 2u, zz.y);
+                BILOCO_SPADD(c0[m], ub, 4u, zz.z);
+                BILOCO_SPADD(c1[m], ub, 8u, zz.w);
+            }
+            ub >>= 4;
+        }
+#pragma unroll
+        for (int m = 0; m < ROWS; ++m) corrp[(m * Rw + w) * Rt + col] = c0[m] + c1[m];
+    }
 }
 
 template <int ROWS>
@@ -744,29 +774,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                     }
                 }
             } else {
-#pragma unroll 1
-                for (int id = lt; id < nit; id += LR_THREADS) {
-                    const int w = id / Rt, col = id - w * Rt;
-                    const uint32_t uw = us[id];
-                    float c0[ROWS], c1[ROWS];
-#pragma unroll
-                    for (int m = 0; m < ROWS; ++m) { c0[m] = 0.f; c1[m] = 0.f; }
-                    uint32_t ub = uw;
-#pragma unroll 1
-                    for (int b = 0; b < 32; b += 4) {
-#pragma unroll
-                        for (int m = 0; m < ROWS; ++m) {
-                            const float4 zz = *reinterpret_cast<const float4*>(zs + m * p.Rpad + 32 * w + b);
-                            BILOCO_SPADD(c0[m], ub, 1u, zz.x);
-                            BILOCO_SPADD(c1[m], ub, 2u, zz.y);
-                            BILOCO_SPADD(c0[m], ub, 4u, zz.z);
-                            BILOCO_SPADD(c1[m], ub, 8u, zz.w);
-                        }
-                        ub >>= 4;
-                    }
-#pragma unroll
-                    for (int m = 0; m < ROWS; ++m) corrp[(m * p.Rw + w) * Rt + col] = c0[m] + c1[m];
-                }
+                expand_padd<ROWS>(zs, corrp, us, nit, Rt, p.Rw, p.Rpad, lt);
             }
             if (lt == 0 && stamps) { stamps[6] = globaltimer_ns(); stamps[22] = (unsigned long long)clock64(); }
         }

@@ -3,9 +3,10 @@
 The decoder is an ordinary ``nn.Module`` built from ``nn.Linear`` layers (q/k/v/o, gate/up/down, lm_head), so the
 model-level entry points apply to it unchanged (``biloco_b200.model.quantize_model`` / ``replace_linears``); for
 throughput measurements ``synthetic_quantize`` swaps in layers with random packed operands instead of decomposing
-random weights. Everything between the linears (embedding, RMSNorm, rotary embedding, attention over a static KV
-cache, argmax) is plain torch. One decode step is captured in a CUDA graph and replayed for the prompt and the
-generated tokens with no host interaction in between.
+random weights. Between the linears the step uses the library's fused launches where the layers allow it (RMSNorm or
+SwiGLU inside the quantiser launch, q/k/v and gate/up as one stacked launch each, the attention step as one launch,
+residual adds inside the o / down launches); embedding, final argmax and the fall-back paths are plain torch. One decode
+step is captured in a CUDA graph and replayed for the prompt and the generated tokens with no host interaction in between.
 
     python -m biloco_b200.decode --model qwen3-4b --M 1 --prompt 128 --steps 256
     torchrun --nproc-per-node 8 -m biloco_b200.decode --model llama3-70b --M 1 --prompt 512 --steps 128     # tensor parallel
@@ -46,7 +47,8 @@ PRESETS = {
     "qwen3-4b": DecoderConfig(36, 2560, 9728, 32, 8, 128, 151936, qk_norm=True),
     "llama3-70b": DecoderConfig(80, 8192, 28672, 64, 8, 128, 128256, rope_theta=5e5, eps=1e-5),
     "tiny": DecoderConfig(2, 256, 512, 4, 2, 64, 512, qk_norm=True),
-    "tiny-tp": DecoderConfig(2, 256, 1024, 8, 2, 64, 512, qk_norm=True),      # splits over 2 ranks (K shards of 256)
+    # splits over 2 or 4 ranks: column shards of at least 128 rows (whole block-scale atoms), K shards of at least 256
+    "tiny-tp": DecoderConfig(2, 256, 1024, 8, 8, 128, 512, qk_norm=True),
 }
 
 
@@ -254,6 +256,27 @@ def synthetic_quantize(model: Decoder, rank: int, seed: int = 0):
                 setattr(parent, name, layer)
                 n += 1
     return n
+
+
+def shard_decoder(full: Decoder, world: int, rank: int, group=None) -> Decoder:
+    """The tensor-parallel decoder of `rank` cut out of a single-GPU decoder whose linears are quantised layers: q/k/v,
+    gate/up and lm_head keep their rank's output columns (whole heads), o and down their rank's input columns; embedding
+    and norm weights are shared. For checking the tensor-parallel step against the single-GPU one on the same operands."""
+    from .parallel import shard_column_parallel, shard_row_parallel
+    dev = full.embed.weight.device
+    tp = Decoder(full.c, device=dev, meta=True, tp=world, group=group)
+    tp.fuse_norm_quant, tp.fuse_groups, tp.fuse_step = full.fuse_norm_quant, full.fuse_groups, full.fuse_step
+    tp.embed, tp.norm = full.embed, full.norm
+    for bt, bf in zip(tp.blocks, full.blocks):
+        for n in ("input_norm", "post_norm", "q_norm", "k_norm"):
+            if hasattr(bf, n):
+                setattr(bt, n, getattr(bf, n))
+        for n in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"):
+            setattr(bt, n, BiLoCoLinear.from_operands(shard_column_parallel(getattr(bf, n).export_operands(), world, rank)))
+        for n in ("o_proj", "down_proj"):
+            setattr(bt, n, RowParallel(BiLoCoLinear.from_operands(shard_row_parallel(getattr(bf, n).export_operands(), world, rank)), group))
+    tp.lm_head = BiLoCoLinear.from_operands(shard_column_parallel(full.lm_head.export_operands(), world, rank))
+    return tp
 
 
 def linear_bytes(model: nn.Module):

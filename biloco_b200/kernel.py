@@ -268,7 +268,9 @@ def reference(A_fp4, A_sf, W_fp4, W_sf, alpha, X_bf16, V_packed, U_packed, S):
 
 def time_graph(fn, pre=None, iters: int = 30, batch: int = 64):
     """Median time per launch (us) of fn, replaying a CUDA graph of pre() followed by `batch` launches
-    (the reference's timing protocol, biloco/kernel.py:145-168: same operands every launch, so L2-warm)."""
+    (the reference's timing protocol, biloco/kernel.py:145-168: same operands every launch, so L2-warm).
+    This function follows the reference's step by step on purpose (warm-up, capture, 5 untimed replays, `iters` timed
+    replays, median): numbers are only comparable with the reference's tables if the protocol is the same."""
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(s):

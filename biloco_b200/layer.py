@@ -37,7 +37,7 @@ class BiLoCoLinear(nn.Module):
         self.register_buffer("W_codes", torch.zeros(N, K // 2, device=dev, dtype=torch.uint8))
         self.register_buffer("W_sf", torch.zeros(fp4.nvfp4_sf_bytes(N, K), device=dev, dtype=torch.uint8))
         self.register_buffer("w_gscale", torch.ones(1, device=dev, dtype=torch.float32))
-        self.smoothed = False
+        self._smoothed = None        # (decided from smooth_scale on first use, see `smoothed`)
         self._gemms = {}      # decode batch M -> BiLoCoGemm
         self._acts = {}       # (decode batch M, SwiGLU input?) -> reusable activation-quantiser outputs
 
@@ -60,7 +60,25 @@ class BiLoCoLinear(nn.Module):
         sf = (torch.rand(fp4.nvfp4_sf_bytes(N, K), device=device, generator=g) * 1.75 + 0.25).to(torch.float8_e4m3fn)
         self.register_buffer("W_sf", sf.view(torch.uint8))
         self.register_buffer("w_gscale", torch.full((1,), 1e-3, device=device, dtype=torch.float32))
-        self.smoothed = False
+        self._smoothed = False
+        self._gemms, self._acts = {}, {}
+        return self
+
+    @classmethod
+    def from_operands(cls, ops: dict):
+        """A quantised layer around given packed operands (the dict of export_operands, e.g. one rank's shard of a layer
+        made by biloco_b200.parallel.shard_column_parallel / shard_row_parallel)."""
+        self = cls.__new__(cls)
+        nn.Module.__init__(self)
+        N, K = ops["W_codes"].shape[0], ops["W_codes"].shape[1] * 2
+        self.in_features, self.out_features, self.method, self.smooth_factor = K, N, "biloco", 0.5
+        self.rank = ops["V_packed"].shape[0]
+        self.weight = None
+        self.bias = None if ops.get("bias") is None else nn.Parameter(ops["bias"].to(torch.bfloat16), requires_grad=False)
+        for name in ("smooth_scale", "V_packed", "U_packed", "S", "W_codes", "w_gscale"):
+            self.register_buffer(name, ops[name].contiguous())
+        self.register_buffer("W_sf", ops["W_sf"].view(torch.uint8).contiguous())
+        self._smoothed = None
         self._gemms, self._acts = {}, {}
         return self
 
@@ -76,7 +94,7 @@ class BiLoCoLinear(nn.Module):
             w_col_max = W.abs().max(dim=0).values.clamp(min=1e-6)
             s = (a ** self.smooth_factor) / (w_col_max ** (1 - self.smooth_factor))
             self.smooth_scale.copy_(s.to(torch.bfloat16))
-            self.smoothed = True
+            self._smoothed = True
             W = W * s
         if self.rank > 0:
             U, V, alpha, R = decompose(W, r=self.rank, T=T)
@@ -91,6 +109,23 @@ class BiLoCoLinear(nn.Module):
         self.w_gscale.copy_(gs)
         self.weight = None
         self._gemms.clear()
+
+    @property
+    def smoothed(self) -> bool:
+        """Whether the activation has to be divided by smooth_scale (any entry different from 1). Derived from the buffer
+        itself, once, so that a layer restored with load_state_dict or filled by copying buffers behaves like the one
+        that was saved."""
+        if self._smoothed is None:
+            self._smoothed = bool((self.smooth_scale.float() != 1).any())
+        return self._smoothed
+
+    @smoothed.setter
+    def smoothed(self, value):
+        self._smoothed = None if value is None else bool(value)
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        super()._load_from_state_dict(*args, **kwargs)
+        self._smoothed = None
 
     def export_operands(self):
         """What the fused kernel consumes, as a dict of tensors (the packed counterpart of the reference's state dict)."""
@@ -113,10 +148,10 @@ class BiLoCoLinear(nn.Module):
             self._gemms[M] = g
         return g
 
-    def _rows(self, x2, residual=None, swiglu=False):
+    def _rows(self, x2, residual=None, swiglu=False, gscale=None):
         M = x2.shape[0]
         q = fp4.quantize_activation(x2, fp4.CONFIG_X, smooth=self.smooth_scale if self.smoothed else None,
-                                    w_gscale=self.w_gscale, rows=M, out=self._acts.get((M, swiglu)), swiglu=swiglu)
+                                    w_gscale=self.w_gscale, rows=M, out=self._acts.get((M, swiglu)), swiglu=swiglu, gscale=gscale)
         self._acts[(M, swiglu)] = q
         g = self._gemm_for(M, q["alpha"])
         if self.bias is None:          # (with a bias, residual holds the broadcast bias)
@@ -150,8 +185,13 @@ class BiLoCoLinear(nn.Module):
         x2 = x.to(torch.bfloat16).reshape(-1, self.in_features).contiguous()
         if x2.shape[0] <= MAX_ROWS:
             y = self._rows(x2)
-        else:   # longer inputs (prefill) go through in blocks of 32 rows; each block gets its own tensor scale
-            y = torch.cat([self._rows(x2[i:i + MAX_ROWS].contiguous()).clone() for i in range(0, x2.shape[0], MAX_ROWS)], dim=0)
+        else:
+            # longer inputs (prefill, evaluation) go through in blocks of 32 rows that all use ONE tensor scale, taken over
+            # the whole smoothed activation as the reference quantises it (biloco/fp4.py:3-4, biloco/layer.py:60)
+            xs = (x2 / self.smooth_scale) if self.smoothed else x2
+            gscale = fp4.activation_scale_from_amax(xs.float().abs().max().reshape(1), fp4.CONFIG_X)
+            y = torch.cat([self._rows(x2[i:i + MAX_ROWS].contiguous(), gscale=gscale).clone()
+                           for i in range(0, x2.shape[0], MAX_ROWS)], dim=0)
         return y.reshape(*shape[:-1], self.out_features).to(torch.bfloat16)
 
     # ------------------------------------------------------------------------------------------------------

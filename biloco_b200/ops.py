@@ -132,26 +132,30 @@ def tile_weights_slab(B, B_sf):
     return out
 
 
-def _tiled_or_none(t):
+def _tiled_or_none(t, N, K):
     # The schemas have no argument for the re-laid-out weight. BiLoCoGemm passes it in the slot of one of the
-    # reference's own internal-layout tensors (V_perm / Diag / Corr); an empty tensor there means "row-major only".
-    return t if (t is not None and t.numel() > 0 and t.dtype == torch.uint8) else None
+    # reference's own internal-layout tensors (V_perm / Diag / Corr). Whatever else a caller written against the
+    # reference puts there (its pack_v_perm bytes, a Diag buffer) is accepted and ignored: only a uint8 tensor of exactly
+    # biloco_b200_tiled_bytes(N, K) bytes is taken for the tiled weight.
+    if t is None or t.numel() == 0 or t.dtype != torch.uint8 or not t.is_cuda:
+        return None
+    return t if t.numel() == _lib.load().biloco_b200_tiled_bytes(N, K) else None
 
 
 def biloco_gemm_mode2(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Z_scratch, Flags, Diag, V_perm, U_rw,
                       m_rows, epoch):
     return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Z_scratch, m_rows, epoch, _lib.MODE_COUNTER,
-                  B_tiled=_tiled_or_none(V_perm))
+                  B_tiled=_tiled_or_none(V_perm, B.size(0), B.size(1) * 2))
 
 
 def biloco_gemm_mode4(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Ztag, Diag, m_rows, epoch):
     return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Ztag, m_rows, epoch, _lib.MODE_OWNER,
-                  B_tiled=_tiled_or_none(Diag))
+                  B_tiled=_tiled_or_none(Diag, B.size(0), B.size(1) * 2))
 
 
 def biloco_gemm_mode5(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, Corr, Cnt, m_rows, epoch):
     return _fused(A, B, A_sf, B_sf, alpha, X_bf16, V_packed, S, U_col32, Zbuf, m_rows, epoch, _lib.MODE_CLUSTER,
-                  B_tiled=_tiled_or_none(Corr))
+                  B_tiled=_tiled_or_none(Corr, B.size(0), B.size(1) * 2))
 
 
 # ---- FP4-only GEMMs (the reference's unfused path and its baselines) ---------------------------------------

@@ -45,7 +45,9 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
  *   5: a tile belongs to a thread-block cluster of c CTAs (c = SMs / tiles, at most 8) that split its k-tiles; the
  *      partial sums go to the finishing CTA through distributed shared memory instead of global memory (M <= 8 and
  *      a tile count that lets tiles * c fill at least two thirds of the SMs; other shapes are refused)
- * In all of them z is computed by all CTAs at entry (rank-sliced) and handed over through an arrival counter. */
+ * In all of them z is computed by all CTAs at entry (rank-sliced) and handed over without a counter: every published z
+ * value carries a validity mark in its lowest mantissa bit that flips with each launch completed on the scratch, and the
+ * consumers poll the values themselves. */
 #define BILOCO_MODE_COUNTER 2
 #define BILOCO_MODE_OWNER 4
 #define BILOCO_MODE_CLUSTER 5
@@ -222,8 +224,9 @@ int biloco_b200_tile_weights_slab(const void* W_codes, const void* W_sf, void* W
  * W_tiled (may be NULL): the copy made by biloco_b200_tile_weights; when given it is streamed instead of
  * W_codes / W_sf (which may then be NULL).
  * R == 0 skips the low-rank term (X, V, U, S may then be NULL). C_bf16 (may be NULL): bf16 [M,N] added
- * before the final rounding. `epoch` (>= 1) is the caller's launch count on this scratch (recorded in the status
- * words when a wait gives up, and selecting one of two z buffers).
+* before the final rounding. `epoch` (>= 1) is the caller's launch count on this scratch; it is recorded in the status
+ * words when a wait gives up and has no other effect (the validity mark of the z values follows a launch count that the
+ * kernels keep in the scratch itself, so a captured CUDA graph can be replayed).
  * Shapes: 1 <= M <= 32, K % 256 == 0, N % 8 == 0. 16-byte alignment for W_codes, A_codes, W_sf, A_sf, X.
  * Device-side waits are bounded; a wait that ran out leaves a non-zero code in the first int32 of scratch
  * (read it with biloco_b200_read_status) and the call's output is undefined.
@@ -245,15 +248,19 @@ int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, const void* 
  * plan at start-up, plugins loaded into a process whose memory budget is fully handed out. biloco_b200_fused_linear
  * asks such a caller for a scratch buffer it cannot provide. This variant takes none: its scratch is an array built
  * into the library (BILOCO_NOALLOC_SCRATCH_BYTES of device memory on every GPU that loads the library, held until the
- * process exits). It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are still
+ * process exits; with the CUDA runtime's lazy module loading the driver sets the array aside when the library's code is
+ * first loaded on a device, which on a GPU whose memory is fully committed can make that first call fail with
+ * BILOCO_ERR_CUDA). It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs are still
  * the caller's. Same arithmetic and same results as biloco_b200_fused_linear (arguments as there, minus scratch and
- * epoch).
+ * epoch), with two restrictions: `mode` is BILOCO_MODE_COUNTER or BILOCO_MODE_OWNER (optionally OR-ed with
+ * BILOCO_OUT_FP32); BILOCO_MODE_CLUSTER and BILOCO_MODE_SLAB return BILOCO_ERR_MODE here.
  *   - Limit: problems whose biloco_b200_scratch_bytes(M, N, K, R, 0) exceeds BILOCO_NOALLOC_SCRATCH_BYTES are rejected
  *     with BILOCO_ERR_LIMIT (nothing is enqueued). K = N = 5120 needs 0.8 MB (M <= 8) to 2.8 MB (M = 32).
  *   - The first call on a device looks up the array's device address (a set-up step of a few microseconds): make
  *     that first call outside any stream capture.
  *   - All calls on a device share the one array. It keeps what the previous call left; each call clears, on `stream`,
- *     the words that have to start at zero. Two calls that overlap on the GPU (different streams without ordering)
+ *     the words that have to start at zero (a cudaMemsetAsync of up to about 0.3 MB in front of the kernel, which also
+ *     means that this launch does not start early under the previous kernel of the stream). Two calls that overlap on the GPU (different streams without ordering)
  *     race on it: keep calls to this entry point ordered.
  * No counterpart in the reference (its scratch tensors are allocated by BiLoCoGemm through PyTorch). */
 #define BILOCO_NOALLOC_SCRATCH_BYTES (4 * 1024 * 1024)
@@ -276,6 +283,12 @@ int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t
  * serialization, so that its set-up and its weight prefetch overlap the tail of the previous kernel of the stream
  * (the kernel itself waits for that kernel before it reads activations or touches scratch). 0 = plain launches.
  * The reference launches with a "pdl" flag as well (csrc/biloco_gemm.cu:3421-3429). */
+/* Contract that comes with it: the fused kernels read their STATIC operands (W_codes / W_sf / W_tiled, V_packed, U_col32,
+ * S) before that wait, so these must be complete before the kernel that precedes the fused launch on the stream begins.
+ * The library's own re-layout calls (biloco_b200_tile_weights, biloco_b200_tile_weights_slab, biloco_b200_pack_u_col32)
+ * are covered: the first fused launch that follows one of them on the same stream is issued as a plain launch. A caller
+ * that writes these operands with a kernel of its own directly in front of a fused launch sets BILOCO_OPT_PDL to 0 for
+ * that launch (or puts any other kernel in between). Activations, alpha, C and the scratch are read after the wait. */
 #define BILOCO_OPT_PDL 1
 /* Pipeline stages the fused kernel keeps in flight. 0 (default): chosen by the library - for M <= 8 with dependent
  * launch on, a ring of 4 stages so that two consecutive launches are resident on an SM at the same time (the second

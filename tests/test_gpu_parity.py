@@ -371,3 +371,59 @@ def test_fused_config3_large_shapes(kernel, K, N, r):
             assert np.array_equal(y, y0)
         assert g.status()[0] == 0, f"device-side wait ran out: {g.status()[:4]}"
         del g
+
+
+@pytest.mark.parametrize("mode", [2, 5, 7])
+def test_fused_directly_after_relayout(kernel, lib, mode):
+    """Re-layout kernels (tile_weights / tile_weights_slab / pack_u_col32) followed by the fused launch with NOTHING in
+    between on the stream: the fused kernels read static operands ahead of their dependency wait when launched with
+    programmatic stream serialization, so the library issues the first launch after a re-layout as a plain one. Called
+    through the C ABI, repeatedly, on fresh buffers each time."""
+    from biloco_b200 import _lib
+    M, K, N, R = 1, 5120, 5120, 512
+    p = orc.random_problem(M, K, N, R, scales="random", seed=41)
+    t = dev_problem(p)
+    y_ref, _ = oracle_outputs(p, M)
+    stream = torch.cuda.current_stream().cuda_stream
+    slab = mode == 7
+    nbytes = lib.biloco_b200_slab_bytes(N, K, 0) if slab else lib.biloco_b200_tiled_bytes(N, K)
+    scratch = torch.zeros(lib.biloco_b200_scratch_bytes(M, N, K, R, 0) // 4, device="cuda", dtype=torch.float32)
+    for it in range(4):
+        tiled = torch.full((nbytes,), 0x77, device="cuda", dtype=torch.uint8)          # stale bytes a too-early read would see
+        ucol = torch.full((N, R // 32), -1, device="cuda", dtype=torch.int32)
+        y = torch.zeros(128, N, device="cuda", dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        if slab:
+            rc = lib.biloco_b200_tile_weights_slab(t["W"].data_ptr(), t["W_sf"].data_ptr(), tiled.data_ptr(), N, K, 0, stream)
+        else:
+            rc = lib.biloco_b200_tile_weights(t["W"].data_ptr(), t["W_sf"].data_ptr(), tiled.data_ptr(), N, K, stream)
+        assert rc == 0
+        assert lib.biloco_b200_pack_u_col32(t["U_packed"].data_ptr(), ucol.data_ptr(), N, R, stream) == 0
+        rc = lib.biloco_b200_fused_linear(t["W"].data_ptr(), t["W_sf"].data_ptr(), tiled.data_ptr(), t["alpha"].data_ptr(),
+                                          t["A_pad"].data_ptr(), t["A_sf"].data_ptr(), t["X"].data_ptr(), t["V_packed"].data_ptr(),
+                                          ucol.data_ptr(), t["S"].data_ptr(), None, y.data_ptr(), scratch.data_ptr(),
+                                          scratch.numel() * 4, M, 128, N, K, R, mode, it + 1, stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        check_against_unfused(y[:M].float().cpu().numpy(), y_ref, f"mode {mode}, call {it} directly after the re-layout")
+
+
+def test_reference_layout_arguments_are_ignored(kernel):
+    """A caller written against the reference passes ITS internal-layout tensors (pack_v_perm bytes as V_perm, a Diag
+    buffer, Corr / Cnt scratch) to the mode operators; they are accepted and ignored, and the result is the same as
+    with empty tensors in those slots."""
+    M, K, N, R = 2, 5120, 1024, 64
+    p = orc.random_problem(M, K, N, R, scales="random", seed=9)
+    t = dev_problem(p)
+    y_ref, _ = oracle_outputs(p, M)
+    ucol = kernel.pack_u_col32(t["U_packed"], N, R)
+    a = (t["A_pad"], t["W"], t["A_sf"], t["W_sf"], t["alpha"], t["X"], t["V_packed"], t["S"], ucol)
+    z = torch.zeros(kernel.scratch_bytes(M, N, K, R) // 4, device="cuda")
+    v_perm = torch.randint(0, 256, (R * 2 * 128 * 4,), device="cuda", dtype=torch.uint8)       # the reference's pack_v_perm size
+    flags = torch.zeros(4096, device="cuda", dtype=torch.int32)
+    diag = torch.zeros(4096, device="cuda", dtype=torch.int32)
+    u_rw = ucol.t().contiguous()
+    y2 = kernel.ops.biloco_gemm_mode2(*a, z, flags, diag, v_perm, u_rw, M, 1).view(-1, N)[:M].float().cpu().numpy()
+    check_against_unfused(y2, y_ref, "mode 2 with the reference's V_perm / U_rw / Flags / Diag")
+    y4 = kernel.ops.biloco_gemm_mode4(*a, z, diag.view(torch.uint8), M, 2).view(-1, N)[:M].float().cpu().numpy()
+    check_against_unfused(y4, y_ref, "mode 4 with a Diag buffer")

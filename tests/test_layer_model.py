@@ -147,3 +147,34 @@ def test_config0_layer(M):
     # the low-rank term matters: dropping it changes the output by much more than the tolerance
     z = kernel.ops.binary_z_reference(x, bl.V_packed, bl.S)
     assert float(z.abs().max()) > 0
+
+
+@pytest.mark.gpu
+def test_long_input_shares_one_tensor_scale_and_smoothed_follows_the_buffers():
+    """More than 32 rows go through the kernel in blocks of 32 that all use ONE NVFP4 tensor scale, taken over the whole
+    smoothed activation as the reference does (biloco/fp4.py:3-4): with one block 50x larger than the rest, per-block
+    scales would quantise the small rows far more finely than the fake-quant forward does. And a layer whose buffers
+    are filled by load_state_dict divides by its smoothing vector like the layer that was saved."""
+    torch.manual_seed(3)
+    bl = BiLoCoLinear.synthetic(1024, 512, 64, "cuda", seed=5)
+    smooth = (torch.rand(1024, device="cuda") * 2 + 0.5).to(torch.bfloat16)
+    bl.smooth_scale.copy_(smooth)
+    bl.smoothed = None                                   # (re-derive from the buffer just written)
+    assert bl.smoothed
+    x = torch.randn(70, 1024, device="cuda")
+    x[:32] *= 50.0                                       # the first block dominates the maximum
+    x = x.to(torch.bfloat16)
+    y = bl(x).float()
+    y_fq = bl.forward_fake_quant(x).float()
+    err = float(torch.linalg.norm(y - y_fq) / torch.linalg.norm(y_fq))
+    assert err <= 1e-2, err
+    # rows of the small blocks: same quantisation grid as the reference's (coarse: set by the large rows)
+    small = float(torch.linalg.norm(y[32:] - y_fq[32:]) / torch.linalg.norm(y_fq[32:]))
+    assert small <= 3e-2, small
+    # a fresh layer that receives the buffers through load_state_dict
+    other = BiLoCoLinear.synthetic(1024, 512, 64, "cuda", seed=99)
+    assert not other.smoothed
+    other.load_state_dict(bl.state_dict())
+    assert other.smoothed
+    y2 = other(x[:8].contiguous()).float()
+    assert torch.equal(y2, bl(x[:8].contiguous()).float())
