@@ -199,7 +199,8 @@ def workload_config(args, layers):
     return {"workload": f"configs[1] point M={args.M}, r={args.r}: fused BiLoCo linear K={args.K} N={args.N}, "
                         f"{layers} distinct layers per step",
             "M": args.M, "K": args.K, "N": args.N, "r": args.r, "layers_per_step": layers,
-            "l2_policy": "inputs larger than L2 (each step streams layers x weights from HBM)",
+            "l2_policy": "inputs larger than L2 (each step streams layers x weights from HBM; the device arm's launches read one "
+                         "shared activation row, like a decoder's hidden state)",
             "algorithmic_bytes_per_call": algorithmic_bytes(args.K, args.N, args.r)}
 
 
@@ -226,7 +227,9 @@ def run_ours(args):
         _lib.load().biloco_b200_set_option(4, args.lr_tc)
 
     K, N, r, M, L = args.K, args.N, args.r, args.M, args.layers
-    layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank, mode=args.mode)
+    # One activation buffer for all layers of the device arm, as the hidden state of a decoder is (written by the previous
+    # kernel, so L2-resident when the linear reads it); the weights and factors are distinct per layer and come from HBM.
+    layers = make_layers(torch, kernel, fp4, dev, L, M, K, N, r, seed=1234 + rank, mode=args.mode, share_act=not args.own_activations)
     bytes_call = algorithmic_bytes(K, N, r)
 
     def step_device():
@@ -558,6 +561,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode leg (default workload, one GPU only)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")
+    ap.add_argument("--own-activations", action="store_true",
+                    help="device arm: every layer reads its own activation buffers (they then come from HBM too)")
     ap.add_argument("--no-comparator", action="store_true", help="skip the reference extension's leg (one GPU, default workload)")
     ap.add_argument("--tp-layers", type=int, default=0, help="tp_decode leg: decoder layers (0 = all 80)")
     ap.add_argument("--tp-M", type=int, default=1, help="tp_decode leg: sequences decoded together")

@@ -126,6 +126,7 @@ static int g_lr_tc = 1;                          // expansion on the tensor core
 static int g_trigger = -1;                        // < 0: chosen per launch (see launch())
 static unsigned long long g_wait_ns = WAIT_BUDGET_NS;   // budget of a device-side wait (row-slab schedule)
 static int g_inflight = 0;                        // row-slab schedule: weight records in flight while the ring fills (0: all)
+static bool slab_coresident() { return g_use_pdl != 0; }      // (two launches side by side on an SM: half of its shared memory each)
 static int g_dbg = 0;                             // row-slab schedule: timing experiments (see SlabParams::dbg)
 static int g_skip_publish = -1;                   // test aid: this CTA of a row-slab launch keeps its z values to itself
 
@@ -383,7 +384,7 @@ extern "C" int biloco_b200_mode_supported(int M, int N, int K, int R, int mode, 
     if (mode == BILOCO_MODE_CLUSTER) return cluster_size_for(M, L.ntile, L.nkt, num_sms, on_device) >= 2 ? 1 : 0;
     if (mode == BILOCO_MODE_SLAB) {
         slab::Geo g;
-        return slab::slab_geometry(M, N, K, R, num_sms, g_use_pdl != 0, &g) ? 1 : 0;
+        return slab::slab_geometry(M, N, K, R, num_sms, slab_coresident(), &g) ? 1 : 0;
     }
     return 0;
 }
@@ -456,7 +457,7 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
     if ((mode & 0xff) == BILOCO_MODE_SLAB) {
         // row slabs: W_tiled is the copy made by biloco_b200_tile_weights_slab (required), one column group
         slab::Geo g;
-        if (n_groups != 1 || !slab::slab_geometry(M, N, K, R, sms, g_use_pdl != 0, &g)) return BILOCO_ERR_SHAPE;
+        if (n_groups != 1 || !slab::slab_geometry(M, N, K, R, sms, slab_coresident(), &g)) return BILOCO_ERR_SHAPE;
         if (!W_tiled) return BILOCO_ERR_NULL;
         if ((uintptr_t)W_tiled & 15) return BILOCO_ERR_ALIGN;
         uint8_t* sc = (uint8_t*)scratch;
@@ -732,7 +733,7 @@ extern "C" int biloco_b200_slab_info(int M, int N, int K, int R, int num_sms, in
     if (!out8) return BILOCO_ERR_NULL;
     if (num_sms == 0) num_sms = device_sm_count();
     slab::Geo g;
-    if (!slab::slab_geometry(M, N, K, R, num_sms, g_use_pdl != 0, &g)) return BILOCO_ERR_SHAPE;
+    if (!slab::slab_geometry(M, N, K, R, num_sms, slab_coresident(), &g)) return BILOCO_ERR_SHAPE;
     out8[0] = g.Rt; out8[1] = g.kg; out8[2] = g.nkt; out8[3] = g.nsu; out8[4] = g.grid; out8[5] = g.ring; out8[6] = g.smem_bytes;
     out8[7] = g.nr;
     return BILOCO_OK;

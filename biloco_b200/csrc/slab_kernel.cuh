@@ -51,7 +51,7 @@ constexpr int NRMAX = 8;                 // ranks per pass of the z stage
 constexpr int XW_MAX = 16;               // 32-bit activation words (pairs of bf16) a thread holds per 32-element segment
 constexpr int UNIT_ROW_BYTES = 144;      // 128 bytes of codes + 16 bytes of block scales per weight row and k-tile
 constexpr int VT_SLAB_MAX = 16384;       // shared memory for the sign words of a CTA's ranks
-constexpr int SLAB_STAMPS = 32;              // debug: 16 %globaltimer stamps per CTA followed by the same 16 as clock64
+constexpr int SLAB_STAMPS = 48;              // debug: 16 %globaltimer stamps per CTA, the same 16 as clock64, 16 more clock64 stamps of the GEMM side
 
 struct SlabParams {
     const uint8_t* W_slab;
@@ -350,6 +350,37 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         bulk_load(base + p.off_ring + slot * p.stage_bytes, wbase + (size_t)j * su_stride, bytes, bar);
     };
 
+    // Read-out of the accumulator's useful lanes (operand rows 0 .. kg M - 1 = TMEM lanes 0..15) to shared memory, as they
+    // are; the diagonal blocks are picked when the outputs are summed. Only warps whose index is a multiple of four may
+    // read those lanes: the two low-rank warps 0 and 8, the first GEMM-side warp and the MMA warp take every fourth
+    // 32-column chunk each (one warp alone spends 0.15 us per chunk on the TMEM round trip).
+    auto read_out = [&](int share) {
+        tc_fence_after_sync();
+        const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
+        const bool active = lane < kg * ROWS;
+#pragma unroll 1
+        for (int c0 = 32 * share; c0 < p.nbp; c0 += 128) {
+            float d[32];
+            tmem_ld_x16(tmem + (uint32_t)c0, d);
+            tmem_ld_x16(tmem + (uint32_t)c0 + 16, d + 16);
+            tc_wait_ld();
+            if (active) {
+                float4* dst = reinterpret_cast<float4*>(accp + lane * p.nbp + c0);      // (nbp and c0 are multiples of 16)
+                const int nv = (p.nbp - c0) < 32 ? (p.nbp - c0) >> 2 : 8;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i < nv) dst[i] = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
+            }
+        }
+        tc_fence_before_sync();
+    };
+    // (the two helper warps arrive on barrier 4 without waiting; the 256 low-rank threads wait there for all 320)
+    auto helper_read_out = [&](int share) {
+        swait(smem_u32(&ctrl->acc_full), 0, ctrl, p, ST_ACC_FULL, warp);      // (on failure: status set, arrive all the same)
+        read_out(share);
+        asm volatile("bar.arrive 4, 320;" ::: "memory");
+    };
+
     const bool has_rows = cta < p.Grows;
     if (!has_rows && (warp >= FIRST_SF_WARP && warp < FIRST_Z_WARP || warp >= MMA_WARP)) {
         // a CTA without weight rows: only its low-rank threads work (z slice), the others go straight to the exit
@@ -386,12 +417,13 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
         const uint32_t idesc = make_idesc_nvf4(128, p.nbp);
         bool ok = swait(smem_u32(&ctrl->b_ready), 0, ctrl, p, ST_FULL, warp);
-        if (lane == 0 && stamps) stamps[15] = globaltimer_ns();
+        if (lane == 0 && stamps) { stamps[15] = globaltimer_ns(); stamps[35] = (unsigned long long)clock64(); }
 #pragma unroll 1
         for (int j = 0; ok && j < nsu; ++j) {
             const int slot = j % ring, set = j % NSETS;
             if (!swait(smem_u32(&ctrl->full[slot]), (j / ring) & 1, ctrl, p, ST_FULL, warp)) break;
             if (!swait(smem_u32(&ctrl->sf_full[set]), (j / NSETS) & 1, ctrl, p, ST_SF_FULL, warp)) break;
+            if (lane == 0 && stamps && j < 4) stamps[36 + j] = (unsigned long long)clock64();
             tc_fence_after_sync();
             if (lane == 0) {
                 const uint64_t adesc = make_smem_desc(base + j * p.atile_bytes, 1024, 2);                        // activation rows
@@ -408,6 +440,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             __syncwarp();
         }
         if (lane == 0 && stamps) { stamps[12] = globaltimer_ns(); stamps[28] = (unsigned long long)clock64(); }
+        helper_read_out(3);
     } else if (warp >= FIRST_SF_WARP && warp < FIRST_Z_WARP) {
         // ================= GEMM side: weight copies, scale factors -> TMEM, activation codes -> shared memory =================
         const int st = tid - FIRST_SF_WARP * 32;                    // 0..127
@@ -515,8 +548,10 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 const int a = i & 3, m = (i >> 2) % ROWS, kt = (i >> 2) / ROWS;
                 asf_w[i] = m < p.M ? ld_cg_u32(p.A_sf + ((size_t)(m >> 7) * (p.K >> 6) + (size_t)kt * 4 + a) * 512 + (m & 31) * 16 + ((m >> 5) & 3) * 4) : 0u;
             }
+            if (st == 0 && stamps) stamps[32] = (unsigned long long)clock64();
             fence_proxy_async();                      // the activation tiles were written with ordinary stores
             mbar_arrive(smem_u32(&ctrl->b_ready));
+            if (st == 0 && stamps) stamps[33] = (unsigned long long)clock64();
             named_bar_sync(2, 128);                   // the scales are in shared memory
 #pragma unroll 1
             for (int j = 0; j < nfirst; ++j) {        // (set by set: the first MMAs start while the later sets are written)
@@ -524,6 +559,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 tc_wait_st();
                 tc_fence_before_sync();
                 mbar_arrive(smem_u32(&ctrl->sf_full[j % NSETS]));
+                if (st == 0 && stamps && j == 0) stamps[34] = (unsigned long long)clock64();
             }
             if (st == 0 && stamps) { stamps[11] = globaltimer_ns(); stamps[27] = (unsigned long long)clock64(); }
             if (p.trigger == 4 && st == 0 && nsu <= ring) griddep_launch_dependents();
@@ -545,6 +581,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 mbar_arrive(smem_u32(&ctrl->sf_full[set]));
             }
         }
+        if (warp == FIRST_SF_WARP) helper_read_out(2);
     } else {
         // ================= low-rank side (256 threads), read-out and store =================
         const int lt = warp < 4 ? tid : tid - (FIRST_Z_WARP - 4) * 32;      // 0..255
@@ -794,34 +831,17 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             }
         }
 
-        // ---- accumulators: D[g' M + m, g Rt + r]; operand rows 0 .. kg M - 1 are TMEM lanes 0..15, which the two low-rank
-        // warps 0 and 8 may read. They copy those lanes as they are to shared memory, half of the columns each; the
-        // diagonal blocks g = g' are picked when the outputs are summed. ----
+        // ---- accumulators: D[g' M + m, g Rt + r]; the diagonal blocks g = g' are picked when the outputs are summed ----
         if (has_rows && (warp == 0 || warp == FIRST_Z_WARP)) {
             if (!swait(smem_u32(&ctrl->acc_full), 0, ctrl, p, ST_ACC_FULL, warp)) good = false;
-            tc_fence_after_sync();
             if (lt == 0 && stamps) { stamps[7] = globaltimer_ns(); stamps[23] = (unsigned long long)clock64(); }
-            const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
-            const bool active = lane < kg * ROWS;
-            const int half = (p.nbp + 63) / 64 * 32;                        // columns of the first warp (a multiple of 32)
-            const int c_lo = warp == 0 ? 0 : half, c_hi = warp == 0 ? (half < p.nbp ? half : p.nbp) : p.nbp;
-#pragma unroll 1
-            for (int c0 = c_lo; c0 < c_hi; c0 += 32) {
-                float d[32];
-                tmem_ld_x16(tmem + (uint32_t)c0, d);
-                tmem_ld_x16(tmem + (uint32_t)c0 + 16, d + 16);
-                tc_wait_ld();
-                if (active) {
-                    float4* dst = reinterpret_cast<float4*>(accp + lane * p.nbp + c0);      // (nbp and c0 are multiples of 16)
-                    const int nv = (p.nbp - c0) < 32 ? (p.nbp - c0) >> 2 : 8;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        if (i < nv) dst[i] = make_float4(d[4 * i], d[4 * i + 1], d[4 * i + 2], d[4 * i + 3]);
-                }
-            }
-            tc_fence_before_sync();
+            if (warp == FIRST_Z_WARP && lane == 0 && stamps) stamps[42] = (unsigned long long)clock64();   // (warp 8 gets here earlier)
+            read_out(warp == 0 ? 0 : 1);
+            if (lt == 0 && stamps) stamps[43] = (unsigned long long)clock64();
         }
-        named_bar_sync(3, LR_THREADS);
+        if (has_rows) asm volatile("bar.sync 4, 320;" ::: "memory");      // (with the two helper warps' arrivals)
+        else named_bar_sync(3, LR_THREADS);
+        if (lt == 0 && stamps) stamps[44] = (unsigned long long)clock64();
         if (lt < ROWS * Rt) {
             const int m = lt / Rt, r = lt - m * Rt;
             const int n = cta * Rt + r;

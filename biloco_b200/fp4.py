@@ -64,8 +64,15 @@ def _e2m1_values(codes: torch.Tensor) -> torch.Tensor:
     return lut[codes.long()]
 
 
+def _div(a: torch.Tensor, scalar: float) -> torch.Tensor:
+    """a / scalar, correctly rounded on every device: a CUDA tensor divided by a Python number is multiplied by the
+    number's reciprocal instead (one ulp off for divisors such as 6 and 1536, enough to move a block scale that sits on an
+    E4M3 rounding boundary to its neighbour); tensor / tensor on the same device is a true division."""
+    return a / torch.full_like(a, scalar)
+
+
 def _quant_with_div(xb, t, div, gs):
-    sf = (t / div).clamp(0.0, 448.0).to(torch.float8_e4m3fn)
+    sf = _div(t, div).clamp(0.0, 448.0).to(torch.float8_e4m3fn)
     d = sf.to(torch.float32) * gs
     live = d > 0
     q = xb / torch.where(live, d, torch.ones_like(d)).unsqueeze(-1)
@@ -84,7 +91,7 @@ def quantize_nvfp4(x: torch.Tensor, rule: str = None, global_scale=None):
     target = 448.0 if rule == "static_6" else 256.0
     if global_scale is None:
         amax = x.abs().max() if x.numel() else torch.zeros((), device=x.device)
-        gs = torch.where(amax > 0, amax / (6.0 * target), torch.ones_like(amax)).to(torch.float32)
+        gs = torch.where(amax > 0, _div(amax, 6.0 * target), torch.ones_like(amax)).to(torch.float32)
     else:
         gs = torch.as_tensor(global_scale, dtype=torch.float32, device=x.device).reshape(())
     xb = x.view(rows, K // 16, 16)
@@ -136,7 +143,7 @@ def activation_scale_from_amax(amax: torch.Tensor, rule: str = None) -> torch.Te
     rule = CONFIG_X if rule is None else rule
     target = 448.0 if rule == "static_6" else 256.0
     amax = amax.to(torch.float32).reshape(1)
-    return torch.where(amax > 0, amax / (6.0 * target), torch.ones_like(amax))
+    return torch.where(amax > 0, _div(amax, 6.0 * target), torch.ones_like(amax))
 
 
 def _rec_buffer(M: int, K: int, dev):

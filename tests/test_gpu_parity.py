@@ -90,6 +90,30 @@ def test_act_quant_bit_exact(kernel, rule, M, K, rows, smooth):
         assert np.array_equal(rec[kt * rb + mma_n * 128: (kt + 1) * rb], atoms), kt
 
 
+@pytest.mark.parametrize("rule", ["static_6", "static_4", "mse"])
+def test_torch_quantiser_on_device_bit_exact_with_oracle(kernel, rule):
+    """The torch quantiser (weights, and the fake-quant forward the layer tests compare with) run ON THE GPU gives the
+    oracle's codes and scales bit for bit, also on inputs whose block scales sit on E4M3 rounding boundaries: a CUDA tensor
+    divided by a Python number is multiplied by the reciprocal, one ulp off for 6 and 1536, which moved such a scale to its
+    neighbour. Built from few distinct bf16 magnitudes so that max|block| / (6 gs) is a short binary fraction often."""
+    from biloco_b200 import fp4
+    rng = np.random.default_rng(5)
+    K = 512
+    vals = np.array([0.25, 0.375, 0.5, 0.75, 1.0, 1.25, 1.5, 1.75, 2.0, 2.5, 3.0, 3.5, 4.0, 5.0, 6.0, 7.0], np.float32)
+    for trial in range(40):
+        x = vals[rng.integers(0, 16, (6, K))] * np.where(rng.random((6, K)) < 0.5, -1.0, 1.0).astype(np.float32)
+        x *= np.float32(2.0) ** rng.integers(-3, 3, (6, K // 16)).repeat(16, axis=1)
+        x[0, 0] = np.float32([3.5, 7.0, 5.0, 3.0][trial % 4]) * 4          # the tensor maximum (6 x 256 does not divide it)
+        x = orc.bf16_round(x)
+        p, sf, gs = orc.nvfp4_quantize(x, rule)
+        tp, tsf, tgs = fp4.quantize_nvfp4(torch.from_numpy(x).cuda(), rule)
+        assert np.float32(tgs.item()) == gs
+        assert np.array_equal(fp4.unswizzle_scales(tsf, 6, K).view(torch.uint8).cpu().numpy(), np.asarray(sf).view(np.uint8)), trial
+        assert np.array_equal(tp.cpu().numpy(), p), trial
+        q = fp4.quantize_activation(torch.from_numpy(x).cuda().to(torch.bfloat16), rule)
+        assert np.array_equal(q["A"].cpu().numpy()[0], p) and np.float32(q["gscale"].item()) == gs, trial
+
+
 @pytest.mark.parametrize("M,K,smooth", [(1, 2560, False), (8, 5120, False), (32, 1024, True), (3, 256, False)])
 def test_norm_act_quant(kernel, M, K, smooth):
     """RMSNorm folded into the quantiser launch: the normalised activation agrees with the torch composition to one bf16
