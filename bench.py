@@ -304,11 +304,21 @@ def run_ours(args):
         ly["gemm_e2e"] = g0 if g0.mode == want else kernel.BiLoCoGemm(ly["ops"][0], ly["ops"][1], ly["q"]["alpha"], *ly["ops"][2:],
                                                                        M=M, mode=want)
 
+    # Where the row-slab launcher takes the raw activation (M <= 2), the step is ONE launch per layer: the kernel
+    # quantises the activation itself (--e2e-two-launches keeps the quantiser launch in front of every linear).
+    one_launch = (not args.e2e_two_launches) and all(ly["gemm"].mode == 7 and ly["gemm"].raw_supported() for ly in layers)
+    if one_launch:
+        for ly in layers:
+            ly["gemm_e2e"] = ly["gemm"]
+
     def step_e2e_body():
         x_dev.copy_(x_host, non_blocking=True)
         for i, ly in enumerate(layers):
-            fp4.quantize_activation(x_dev[i], "mse", w_gscale=ly["w_gs"], rows=M, out=ly["q"])
             g = ly["gemm_e2e"]
+            if one_launch:
+                g.raw(x_dev[i], ly["w_gs"], "mse", out=y_dev[i])
+                continue
+            fp4.quantize_activation(x_dev[i], "mse", w_gscale=ly["w_gs"], rows=M, out=ly["q"])
             g(ly["q"]["A"], ly["q"]["A_sf"], x_dev[i], out=y_dev[i], A_rec=ly["q"].get("A_rec") if g.mode != 7 else None)
         y_host.copy_(y_dev, non_blocking=True)
 
@@ -379,6 +389,7 @@ def run_ours(args):
                      "peak_source": f"{peak_kind} (STREAM-style copy)",
                      "kernel": kname, "schedule": mode0, "algorithmic_bytes_per_launch": bytes_call},
         "e2e_schedule": mode_e2e,
+        "e2e_launches_per_layer": 1 if one_launch else 2,
     }
     if world == 1 and not args.no_cpu:
         sec, n = time_cpu_forward(M, K, N, r, calls=200, warm=3, budget_s=args.cpu_budget)
@@ -561,6 +572,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode leg (default workload, one GPU only)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")
+    ap.add_argument("--e2e-two-launches", action="store_true",
+                    help="end-to-end arm: quantiser launch + fused launch per layer instead of the one-launch raw-activation form")
     ap.add_argument("--own-activations", action="store_true",
                     help="device arm: every layer reads its own activation buffers (they then come from HBM too)")
     ap.add_argument("--no-comparator", action="store_true", help="skip the reference extension's leg (one GPU, default workload)")

@@ -21,6 +21,7 @@
 
 #include "../../include/biloco_b200.h"
 #include "ptx.cuh"
+#include "quant_math.cuh"
 
 extern "C" int biloco_internal_use_pdl();
 
@@ -30,34 +31,11 @@ namespace {
 constexpr int Q_THREADS = 256;
 constexpr int Q_MAX_CLUSTER = 8;
 
-__device__ __forceinline__ uint32_t e2m1_rn(float q) {
-    const float a = fabsf(q);
-    uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
-    return c | ((__float_as_uint(q) >> 31) << 3);
-}
-__device__ __forceinline__ float e2m1_value(uint32_t code) {
-    const uint32_t m = code & 7u;
-    // 0, .5, 1, 1.5, 2, 3, 4, 6
-    const float mag = m < 4u ? 0.5f * (float)m : (m == 4u ? 2.0f : (m == 5u ? 3.0f : (m == 6u ? 4.0f : 6.0f)));
-    return (code & 8u) ? -mag : mag;
-}
-__device__ __forceinline__ float e4m3_to_float(uint8_t b) {
-    const __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
-    return __half2float(__half(h));
-}
-__device__ __forceinline__ uint8_t float_to_e4m3_sat(float v) {
-    return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
-}
-
-// bf16 pair -> two floats, optionally divided by the smoothing pair and rounded back to bf16
-__device__ __forceinline__ void unpack_smoothed(uint32_t w, uint32_t sm, bool smooth, float& lo, float& hi) {
-    lo = __uint_as_float(w << 16);
-    hi = __uint_as_float(w & 0xFFFF0000u);
-    if (smooth) {
-        lo = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(lo, __uint_as_float(sm << 16))));
-        hi = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(hi, __uint_as_float(sm & 0xFFFF0000u))));
-    }
-}
+using biloco::qm::e2m1_rn;
+using biloco::qm::e2m1_value;
+using biloco::qm::e4m3_to_float;
+using biloco::qm::float_to_e4m3_sat;
+using biloco::qm::unpack_smoothed;
 
 __global__ void __launch_bounds__(Q_THREADS) act_quant_kernel(const __nv_bfloat16* X, const __nv_bfloat16* smooth,
                                                               __nv_bfloat16* Xs, uint8_t* __restrict__ codes,

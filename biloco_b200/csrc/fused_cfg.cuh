@@ -156,7 +156,7 @@ static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
 
 enum : int {   // status codes of waits that ran out
     ST_EMPTY = 101, ST_FULL = 102, ST_ACC_EMPTY = 103, ST_ACC_FULL = 104, ST_Z = 105, ST_TILE = 106, ST_SF_FULL = 107,
-    ST_SF_EMPTY = 108, ST_CLUSTER = 109,
+    ST_SF_EMPTY = 108, ST_CLUSTER = 109, ST_ACT = 110,
 };
 
 // The wait helpers are deliberately not inlined: the kernel's machine code is executed once, cold, per CTA, and

@@ -152,7 +152,7 @@ static bool consume_relayout_mark(cudaStream_t stream) {
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 
 struct ScratchLayout {
-    size_t off_zcnt, off_tilecnt, off_z, off_part, total;
+    size_t off_zcnt, off_tilecnt, off_z, off_arec, off_part, total;
     int ntile, nkt, G, max_slots, Rw, Rpad, mma_n;
 };
 
@@ -171,6 +171,8 @@ static bool make_layout(int M, int N, int K, int R, int num_sms, ScratchLayout* 
     L->off_zcnt = off; off += 64;
     L->off_tilecnt = off; off += ((size_t)L->ntile * 4 + 127) / 128 * 128;
     L->off_z = off; off += (size_t)2 * 32 * L->Rpad * sizeof(float);
+    // raw-activation form of the row-slab schedule: one 16-byte record per 16-element block of the activation (M <= 2)
+    L->off_arec = off; off += (M <= 2 && K % 512 == 0) ? (size_t)M * K : 0;
     L->off_part = off; off += (size_t)L->ntile * L->max_slots * L->mma_n * TILE_N * sizeof(float);
     L->total = (off + 255) / 256 * 256;
     return true;
@@ -417,6 +419,72 @@ extern "C" int biloco_b200_tile_weights(const void* W_codes, const void* W_sf, v
     return cudaGetLastError() == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
+// Raw-activation arguments of the row-slab schedule (the kernel quantises the activation itself).
+struct SlabAct {
+    const void* Xraw; const void* norm_w; const void* smooth; const float* w_gscale; float* act_out; float eps; int rule; int swiglu;
+};
+
+static int slab_launch(const void* W_slab, const float* alpha, const void* A_codes, const void* A_sf, const void* X_bf16,
+                       const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16, void* Y, void* scratch,
+                       const ScratchLayout& L, int M, int N, int K, int R, int mode, int epoch, int sms, const SlabAct* act,
+                       cudaStream_t stream) {
+    slab::Geo g;
+    if (!slab::slab_geometry(M, N, K, R, sms, slab_coresident(), &g, act != nullptr)) return BILOCO_ERR_SHAPE;
+    if (!W_slab) return BILOCO_ERR_NULL;
+    if ((uintptr_t)W_slab & 15) return BILOCO_ERR_ALIGN;
+    uint8_t* sc = (uint8_t*)scratch;
+    slab::SlabParams q;
+    q.W_slab = (const uint8_t*)W_slab;
+    q.A_codes = (const uint8_t*)A_codes;
+    q.A_sf = (const uint8_t*)A_sf;
+    q.alpha = alpha;
+    q.X = (const __nv_bfloat16*)X_bf16;
+    q.Vp = (const uint8_t*)V_packed;
+    q.Ucol = U_col32;
+    q.S = (const __nv_bfloat16*)S_bf16;
+    q.C = (const __nv_bfloat16*)C_bf16;
+    q.Y = Y;
+    q.status = (int32_t*)sc;
+    q.z_counter = (uint32_t*)(sc + L.off_zcnt);
+    q.zbuf = (float*)(sc + L.off_z);
+    q.M = M; q.N = N; q.K = K; q.R = R; q.Rw = L.Rw; q.Rpad = L.Rpad;
+    q.Rt = g.Rt; q.kg = g.kg; q.nkt = g.nkt; q.nsu = g.nsu; q.G = g.grid; q.Grows = g.G;
+    q.nsl = g.nsl;
+    q.ring = g_ring > 0 && g_ring < g.ring ? g_ring : g.ring;
+    q.stage_bytes = g.stage_bytes;
+    // (a shorter ring keeps the offsets computed for the full one: the stages simply stay unused)
+    q.nbp = g.nbp; q.atile_bytes = g.atile_bytes;
+    q.off_ring = g.off_ring; q.off_ctrl = g.off_ctrl; q.off_us = g.off_us; q.off_work = g.off_work; q.off_accp = g.off_accp;
+    q.xs_off = g.xs_off; q.off_asf = g.off_asf;
+    q.epoch = (uint32_t)epoch;
+    q.mode = mode;
+    q.wait_ns = g_wait_ns;
+    q.skip_publish_cta = g_skip_publish;
+    q.trigger = g_trigger >= 0 ? g_trigger : 1;      // (measured: 8.3 us per call at K = N = 5120 against 8.4 with 0)
+    q.inflight = g_inflight;
+    q.lut = g.lut;
+    q.dbg = g_dbg;
+    q.stamps = nullptr;
+    q.act_rec = (unsigned long long*)(sc + L.off_arec);
+    q.Xraw = nullptr; q.norm_w = nullptr; q.smooth = nullptr; q.w_gscale = nullptr; q.act_out = nullptr;
+    q.eps = 0.f; q.act_rule = 0; q.act_swiglu = 0;
+    if (act) {
+        q.Xraw = (const __nv_bfloat16*)act->Xraw;
+        q.norm_w = (const __nv_bfloat16*)act->norm_w;
+        q.smooth = (const __nv_bfloat16*)act->smooth;
+        q.w_gscale = act->w_gscale;
+        q.act_out = act->act_out;
+        q.eps = act->eps; q.act_rule = act->rule; q.act_swiglu = act->swiglu;
+    }
+    if (g_stamps && g_stamps_bytes >= (size_t)g.grid * slab::SLAB_STAMPS * 8) {
+        const size_t per = (size_t)g.grid * slab::SLAB_STAMPS, slots = g_stamps_bytes / (per * 8);
+        q.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
+    }
+    const bool pdl = g_use_pdl != 0 && !consume_relayout_mark(stream);
+    if (act) return M <= 1 ? slab::slab_launch_rows<1, true>(q, g, pdl, stream) : slab::slab_launch_rows<2, true>(q, g, pdl, stream);
+    return M <= 1 ? slab::slab_launch_rows<1, false>(q, g, pdl, stream) : slab::slab_launch_rows<2, false>(q, g, pdl, stream);
+}
+
 static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha, const void* A_codes,
                              const void* A_sf, const void* A_rec, const void* X_bf16, const void* V_packed, const int32_t* U_col32,
                              const void* S_bf16, const void* C_bf16, void* Y_bf16, void* scratch,
@@ -456,50 +524,9 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
 
     if ((mode & 0xff) == BILOCO_MODE_SLAB) {
         // row slabs: W_tiled is the copy made by biloco_b200_tile_weights_slab (required), one column group
-        slab::Geo g;
-        if (n_groups != 1 || !slab::slab_geometry(M, N, K, R, sms, slab_coresident(), &g)) return BILOCO_ERR_SHAPE;
-        if (!W_tiled) return BILOCO_ERR_NULL;
-        if ((uintptr_t)W_tiled & 15) return BILOCO_ERR_ALIGN;
-        uint8_t* sc = (uint8_t*)scratch;
-        slab::SlabParams q;
-        q.W_slab = (const uint8_t*)W_tiled;
-        q.A_codes = (const uint8_t*)A_codes;
-        q.A_sf = (const uint8_t*)A_sf;
-        q.alpha = alpha;
-        q.X = (const __nv_bfloat16*)X_bf16;
-        q.Vp = (const uint8_t*)V_packed;
-        q.Ucol = U_col32;
-        q.S = (const __nv_bfloat16*)S_bf16;
-        q.C = (const __nv_bfloat16*)C_bf16;
-        q.Y = Y_bf16;
-        q.status = (int32_t*)sc;
-        q.z_counter = (uint32_t*)(sc + L.off_zcnt);
-        q.zbuf = (float*)(sc + L.off_z);
-        q.M = M; q.N = N; q.K = K; q.R = R; q.Rw = L.Rw; q.Rpad = L.Rpad;
-        q.Rt = g.Rt; q.kg = g.kg; q.nkt = g.nkt; q.nsu = g.nsu; q.G = g.grid; q.Grows = g.G;
-        q.nsl = g.nsl;
-        q.ring = g_ring > 0 && g_ring < g.ring ? g_ring : g.ring;
-        q.stage_bytes = g.stage_bytes;
-        // (a shorter ring keeps the offsets computed for the full one: the stages simply stay unused)
-        q.nbp = g.nbp; q.atile_bytes = g.atile_bytes;
-        q.off_ring = g.off_ring; q.off_ctrl = g.off_ctrl; q.off_us = g.off_us; q.off_work = g.off_work; q.off_accp = g.off_accp;
-        q.xs_off = g.xs_off; q.off_asf = g.off_asf;
-        q.epoch = (uint32_t)epoch;
-        q.mode = mode;
-        q.wait_ns = g_wait_ns;
-        q.skip_publish_cta = g_skip_publish;
-        q.trigger = g_trigger >= 0 ? g_trigger : 1;      // (measured: 8.3 us per call at K = N = 5120 against 8.4 with 0)
-        q.inflight = g_inflight;
-        q.lut = g.lut;
-        q.dbg = g_dbg;
-        q.stamps = nullptr;
-        if (g_stamps && g_stamps_bytes >= (size_t)g.grid * slab::SLAB_STAMPS * 8) {
-            const size_t per = (size_t)g.grid * slab::SLAB_STAMPS, slots = g_stamps_bytes / (per * 8);
-            q.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
-        }
-        const bool pdl = g_use_pdl != 0 && !consume_relayout_mark((cudaStream_t)stream);
-        return M <= 1 ? slab::slab_launch_rows<1>(q, g, pdl, (cudaStream_t)stream)
-                      : slab::slab_launch_rows<2>(q, g, pdl, (cudaStream_t)stream);
+        if (n_groups != 1) return BILOCO_ERR_SHAPE;
+        return slab_launch(W_tiled, alpha, A_codes, A_sf, X_bf16, V_packed, U_col32, S_bf16, C_bf16, Y_bf16, scratch, L, M, N, K, R,
+                           mode, epoch, sms, nullptr, (cudaStream_t)stream);
     }
 
     CUtensorMap tmW, tmA;
@@ -573,6 +600,40 @@ extern "C" int biloco_b200_fused_linear(const void* W_codes, const void* W_sf, c
                                         biloco_stream_t stream) {
     return fused_linear_impl(W_codes, W_sf, W_tiled, alpha, A_codes, A_sf, nullptr, X_bf16, V_packed, U_col32, S_bf16, C_bf16, Y_bf16,
                              scratch, scratch_bytes, M, A_rows, N, K, R, mode, epoch, stream);
+}
+
+extern "C" int biloco_b200_fused_linear_act_supported(int M, int N, int K, int R, int num_sms) {
+    if (num_sms <= 0) num_sms = device_sm_count();
+    if (num_sms < 1 || M < 1 || M > 2) return 0;
+    ScratchLayout L;
+    if (!make_layout(M, N, K, R, num_sms, &L)) return 0;
+    slab::Geo g;
+    return slab::slab_geometry(M, N, K, R, num_sms, slab_coresident(), &g, true) ? 1 : 0;
+}
+
+extern "C" int biloco_b200_fused_linear_act(const void* W_slab, const float* w_gscale, const void* X_raw_bf16, const void* norm_weight_bf16,
+                                            float eps, const void* smooth_bf16, int swiglu, int rule, const void* V_packed,
+                                            const int32_t* U_col32, const void* S_bf16, const void* C_bf16, void* Y, float* act_out,
+                                            void* scratch, size_t scratch_bytes, int M, int N, int K, int R, int flags, int epoch,
+                                            biloco_stream_t stream) {
+    if (!W_slab || !w_gscale || !X_raw_bf16 || !Y || !scratch) return BILOCO_ERR_NULL;
+    if (R > 0 && (!V_packed || !U_col32 || !S_bf16)) return BILOCO_ERR_NULL;
+    if (rule != BILOCO_RULE_STATIC_6 && rule != BILOCO_RULE_STATIC_4 && rule != BILOCO_RULE_MSE) return BILOCO_ERR_MODE;
+    if (swiglu && norm_weight_bf16) return BILOCO_ERR_MODE;
+    if (flags & ~0x400) return BILOCO_ERR_MODE;
+    if (epoch < 1) return BILOCO_ERR_EPOCH;
+    if (M < 1 || M > 2) return BILOCO_ERR_SHAPE;
+    const int sms = device_sm_count();
+    if (sms < 1) return BILOCO_ERR_CUDA;
+    ScratchLayout L;
+    if (!make_layout(M, N, K, R, sms, &L)) return BILOCO_ERR_SHAPE;
+    if (scratch_bytes < L.total) return BILOCO_ERR_SCRATCH;
+    if (((uintptr_t)X_raw_bf16 & 15) || ((uintptr_t)norm_weight_bf16 & 15) || ((uintptr_t)smooth_bf16 & 15) ||
+        ((uintptr_t)scratch & 255) || ((uintptr_t)U_col32 & 3) || ((uintptr_t)w_gscale & 3) || ((uintptr_t)act_out & 3))
+        return BILOCO_ERR_ALIGN;
+    SlabAct act = {X_raw_bf16, norm_weight_bf16, smooth_bf16, w_gscale, act_out, eps, rule, swiglu ? 1 : 0};
+    return slab_launch(W_slab, nullptr, nullptr, nullptr, nullptr, V_packed, U_col32, S_bf16, C_bf16, Y, scratch, L, M, N, K, R,
+                       BILOCO_MODE_SLAB | (flags & 0x400), epoch, sms, &act, (cudaStream_t)stream);
 }
 
 extern "C" int biloco_b200_fused_linear_rec(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,

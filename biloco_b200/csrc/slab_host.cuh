@@ -36,7 +36,7 @@ static bool slab_layout(int N, int K, int num_sms, Geo* g) {
     return true;
 }
 
-static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coresident, Geo* g) {
+static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coresident, Geo* g, bool raw = false) {
     if (M < 1 || M > 2 || R < 0) return false;
     if (!slab_layout(N, K, num_sms, g)) return false;
     g->rows = M;
@@ -53,7 +53,8 @@ static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coreside
     // up to 8192 elements; longer rows are read span by span without staging); afterwards z and the expansion's
     // partial sums
     g->xs_off = (vt + 15) / 16 * 16;
-    const int zwork = R > 0 ? g->xs_off + (K / 256 <= 2 * XW_MAX ? 2 * K : 0) : 0;
+    // (raw-activation form: all M rows of the activation are formed and staged there, whatever K and R are)
+    const int zwork = raw ? g->xs_off + M * 2 * K : (R > 0 ? g->xs_off + (K / 256 <= 2 * XW_MAX ? 2 * K : 0) : 0);
     int work = g->rows * Rpad * 4 + g->rows * Rw * g->Rt * 4;
     // expansion by table (16 sums per group of four ranks: 16 bytes per rank and row) where the table is small
     g->lut = (R > 0 && g->rows * Rpad * 16 <= 8192) ? 1 : 0;
@@ -114,13 +115,13 @@ __global__ void tile_weights_slab_kernel(const uint8_t* __restrict__ W, const ui
     }
 }
 
-template <int ROWS>
+template <int ROWS, bool RAW>
 static int slab_launch_rows(const SlabParams& p, const Geo& g, bool pdl, cudaStream_t stream) {
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(slab_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET) != cudaSuccess)
+        if (cudaFuncSetAttribute(slab_kernel<ROWS, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET) != cudaSuccess)
             return BILOCO_ERR_CUDA;
         attr_set[dev] = true;
     }
@@ -138,7 +139,7 @@ static int slab_launch_rows(const SlabParams& p, const Geo& g, bool pdl, cudaStr
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, slab_kernel<ROWS>, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, slab_kernel<ROWS, RAW>, p);
     return e == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 

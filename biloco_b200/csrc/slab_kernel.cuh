@@ -33,6 +33,7 @@
 // -> shared memory, first weight copies; 8-11 low-rank side; 12 TMEM allocation + MMA issue; 13 later weight copies.
 #pragma once
 #include "fused_cfg.cuh"
+#include "quant_math.cuh"
 
 namespace biloco {
 namespace slab {
@@ -91,6 +92,24 @@ struct SlabParams {
     int lut;                  // expansion by look-up table (the launcher has added the table behind the partial sums)
     int inflight;             // weight records a CTA keeps in flight while it fills its ring (0: all at once)
     unsigned long long* stamps;
+    // Raw-activation form (Xraw != nullptr): the kernel quantises the activation itself instead of reading A_codes /
+    // A_sf / alpha / X. Every CTA forms the whole (normalised, smoothed) activation in shared memory and takes its
+    // maximum (cheap, and the z stage runs from the staged copy); the quantisation proper is SHARED: CTA c quantises
+    // the blocks [c nblk / G, (c + 1) nblk / G) and publishes each as two 64-bit words in act_rec
+    //     word 0 = codes of elements 0..11 (48 bits) | mark << 48,  word 1 = codes of elements 12..15 | scale << 16 | mark << 48
+    // (mark = low 16 bits of this launch's number on the scratch + 1: every word is its own flag, as the z values are),
+    // and every CTA with weight rows gathers all records into its operand tiles. (A thread that quantises a whole
+    // 16-element block alone runs a dependent chain of about 1500 instructions, 10 us; every CTA quantising the whole
+    // row with a lane per element would still cost about 3 us of issue slots per CTA.)
+    const __nv_bfloat16* Xraw;       // bf16 [M, K]; [M, 2K] = [gate | up] with act_swiglu
+    const __nv_bfloat16* norm_w;     // RMS-norm weight [K] or nullptr
+    const __nv_bfloat16* smooth;     // smoothing vector [K] or nullptr
+    const float* w_gscale;           // the weights' tensor scale [1] (static)
+    unsigned long long* act_rec;     // scratch: one 16-byte record per 16-element block of the activation (see below)
+    float* act_out;                  // optional [2]: tensor scale of the activation, alpha = w_gscale * scale (CTA 0 writes)
+    float eps;
+    int act_rule;                    // 0 static_6, 1 static_4, 2 mse
+    int act_swiglu;
 };
 
 struct SCtrl {
@@ -106,6 +125,10 @@ struct SCtrl {
     uint32_t tmem_base;
     uint32_t seq;             // launches completed on this scratch before this one (read once per CTA)
     volatile int abort;
+    float nred[LR_WARPS];     // raw-activation form: sums of squares / maxima of the low-rank warps
+    float amaxw[LR_WARPS];
+    float gs, alpha_s;        // the activation's tensor scale and alpha = wgs * gs
+    float wgs;                // the weights' tensor scale (read before the dependency wait)
 };
 static_assert(sizeof(SCtrl) <= 1024, "slab control block too large");
 
@@ -299,7 +322,36 @@ __device__ __noinline__ void expand_padd(const float* zs, float* corrp, const ui
     }
 }
 
-template <int ROWS>
+// Raw-activation form: this CTA's share of the activation's 16-element blocks, [cta nblk / G, (cta + 1) nblk / G), quantised
+// by `nth` threads (whole warps; t = the thread's index among them) with a lane per element, each block published as two
+// 64-bit words that carry `mark` in their top 16 bits (layout: see SlabParams).
+__device__ __noinline__ void quantise_share(int t, int nth, int lane, int cta, const SlabParams& p, const uint8_t* xsb, float gs, uint32_t seq) {
+    const int kblocks = p.K >> 4, nblk = p.M * kblocks;
+    const int b0 = (int)((unsigned)cta * (unsigned)nblk / (unsigned)p.G), b1 = (int)((unsigned)(cta + 1) * (unsigned)nblk / (unsigned)p.G);
+    const int nl = ((b1 - b0) * 16 + 31) & ~31;      // (nblk <= 2048 and G <= 65535: the products fit 32 bits)
+    const unsigned long long mark = (unsigned long long)((seq + 1u) & 0xFFFFu) << 48;
+#pragma unroll 1
+    for (int li = t; li < nl; li += nth) {
+        const int b = b0 + (li >> 4), j = li & 15;
+        float x = 0.f;
+        if (b < b1) {
+            const int row = b / kblocks, kb = b - row * kblocks;
+            x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(xsb + (size_t)row * 2 * p.K)[kb * 16 + j]);
+        }
+        uint2 codes;
+        uint8_t sfb;
+        qm::quant_lane16(x, lane, gs, p.act_rule, codes, sfb);
+        if (j == 0 && b < b1) {
+            const unsigned long long w0 = (unsigned long long)codes.x | ((unsigned long long)(codes.y & 0xFFFFu) << 32) | mark;
+            const unsigned long long w1 = (unsigned long long)(codes.y >> 16) | ((unsigned long long)sfb << 16) | mark;
+            asm volatile("st.global.v2.u64 [%0], {%1, %2};" ::"l"(p.act_rec + 2 * (size_t)b), "l"(w0), "l"(w1) : "memory");
+        }
+    }
+}
+
+// RAW: the raw-activation form (its prologue is compiled into an instantiation of its own, so that the plain form keeps its
+// registers and its instruction footprint)
+template <int ROWS, bool RAW>
 __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ SlabParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -498,7 +550,67 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         if (st == 0 && stamps) { stamps[13] = globaltimer_ns(); stamps[29] = (unsigned long long)clock64(); }
         griddep_wait();
         if (st == 0 && stamps) { stamps[14] = globaltimer_ns(); stamps[30] = (unsigned long long)clock64(); }
-        if (ok) {
+        constexpr bool raw = RAW;
+        // (the named barriers of these four warps are passed by all 128 threads whatever `ok` says: a warp whose wait ran
+        // out must not leave the others at a barrier that has no time limit)
+        if (raw) {
+            asm volatile("bar.sync 5, 384;" ::: "memory");      // the low-rank threads have staged the activation and set the scale
+            quantise_share(st, 128, lane, cta, p, work + p.xs_off, ctrl->gs, ctrl->seq);
+            if (st == 0 && stamps) stamps[47] = (unsigned long long)clock64();
+        }
+        if (ok && raw) {
+            // raw-activation form: gather the published records of all blocks (whoever quantised them) into the operand
+            // tiles: 8 bytes of codes = half a 16-byte chunk of row n = (kt % kg) * M + m of tile kt / kg (128-byte swizzle),
+            // the scale byte where sfa_move expects it
+            const unsigned long long mark = (unsigned long long)((ctrl->seq + 1u) & 0xFFFFu);
+            const int kblocks = p.K >> 4, nblk = p.M * kblocks;
+            uint8_t* asf_b = sm + p.off_asf;
+            // (a thread's records, at most GMAX at a time, are requested together: one round trip per attempt, not one per record)
+            constexpr int GMAX = 4;
+#pragma unroll 1
+            for (int b00 = st; b00 < nblk && ok; b00 += 128 * GMAX) {
+                unsigned long long w0[GMAX], w1[GMAX];
+                uint64_t t0 = 0;
+#pragma unroll 1
+                for (uint32_t it = 0;; ++it) {
+                    bool all = true;
+#pragma unroll
+                    for (int u = 0; u < GMAX; ++u) {
+                        const int b = b00 + 128 * u;
+                        if (b < nblk)
+                            asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0[u]), "=l"(w1[u]) : "l"(p.act_rec + 2 * (size_t)b) : "memory");
+                    }
+#pragma unroll
+                    for (int u = 0; u < GMAX; ++u)
+                        if (b00 + 128 * u < nblk) all = all && (w0[u] >> 48) == mark && (w1[u] >> 48) == mark;
+                    if (all) break;
+                    if ((it & 15u) == 15u) {
+                        if (ctrl->abort) { ok = false; break; }
+                        const uint64_t now = globaltimer_ns();
+                        if (t0 == 0) t0 = now;
+                        else if (now - t0 > p.wait_ns) { sfail(ctrl, p.status, p.epoch, ST_ACT, warp); ok = false; break; }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < GMAX; ++u) {
+                    const int b = b00 + 128 * u;
+                    if (b < nblk) {
+                        const int row = b / kblocks, kb = b - row * kblocks;
+                        const int kt = kb >> 4, j = kt / kg, g = kt - j * kg, n = g * ROWS + row;
+                        const int byte = (kb & 15) * 8, c = byte >> 4;
+                        const uint2 codes = make_uint2((uint32_t)w0[u], (uint32_t)((w0[u] >> 32) & 0xFFFFull) | ((uint32_t)(w1[u] & 0xFFFFull) << 16));
+                        *reinterpret_cast<uint2*>(atile + j * p.atile_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) * 16) + (byte & 8)) = codes;
+                        asf_b[((kt * ROWS + row) * 4 + ((kb >> 2) & 3)) * 4 + (kb & 3)] = (uint8_t)(w1[u] >> 16);
+                    }
+                }
+            }
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && raw) {
+            if (st == 0 && stamps) stamps[32] = (unsigned long long)clock64();
+            fence_proxy_async();                      // the activation tiles were written with ordinary stores
+            mbar_arrive(smem_u32(&ctrl->b_ready));
+        } else if (ok) {
             // Every global read of this side is issued before any of them is waited for (one memory round trip in all).
             // Block scales: the four bytes of (k-tile kt, 64-k chunk a, row m) sit in atom 4 kt + a of the 128x4 layout.
             uint32_t* asf_w = reinterpret_cast<uint32_t*>(sm + p.off_asf);
@@ -551,8 +663,10 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             if (st == 0 && stamps) stamps[32] = (unsigned long long)clock64();
             fence_proxy_async();                      // the activation tiles were written with ordinary stores
             mbar_arrive(smem_u32(&ctrl->b_ready));
+        }
+        named_bar_sync(2, 128);                       // the scales are in shared memory
+        if (ok) {
             if (st == 0 && stamps) stamps[33] = (unsigned long long)clock64();
-            named_bar_sync(2, 128);                   // the scales are in shared memory
 #pragma unroll 1
             for (int j = 0; j < nfirst; ++j) {        // (set by set: the first MMAs start while the later sets are written)
                 sfa_move(j, tmem);
@@ -618,6 +732,8 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             }
             cp_async_wait_all();
         }
+        constexpr bool raw = RAW;
+        if (raw && lt == 0) ctrl->wgs = p.w_gscale[0];                       // (static, like the weights)
         float s_coef[2] = {0.f, 0.f};                                        // (nr <= 2 * NRMAX: two passes at most)
         if (lt < NRMAX) {
             if (lt < nr) s_coef[0] = __bfloat162float(p.S[ra + lt]);
@@ -631,7 +747,147 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         // 128-byte line are served one after another by its L2 slice (measured: the launch count read by all threads
         // and the activation row read in 4-byte pieces cost 1.5 - 6 us; one reader and coalesced 16-byte loads, 0.5).
         float alpha_r = 0.f;
-        if (lt < ROWS * Rt) alpha_r = __uint_as_float(ld_cg_u32(p.alpha));
+        if (!raw && lt < ROWS * Rt) alpha_r = __uint_as_float(ld_cg_u32(p.alpha));
+        if (raw) {
+            // ---- raw-activation form, first half (these 256 threads): the activation as the linear sees it -- RMS-normalised
+            //      (x * rsqrt(mean(x^2) + eps) -> bf16, * weight -> bf16), or silu(gate) * up (each rounded to bf16), then divided
+            //      by the smoothing vector -> bf16 -- written to the staging rows in shared memory, and its maximum. Thread lt
+            //      takes the 16-byte vectors lt, lt + 256, ... of a row; the sum of squares runs in the order the stand-alone
+            //      quantiser uses (per thread in index order, shuffle tree, warps in index order), so both give the same bits. ----
+            uint8_t* xsb = work + p.xs_off;
+            const int kvec = p.K >> 3;
+            float amax = 0.f;
+            if (lt == LR_THREADS - 1) {      // the launch number of this scratch (one reader per CTA: a hot line)
+                const uint4 c0 = ld_volatile_v4(p.z_counter + 8), c1 = ld_volatile_v4(p.z_counter + 12);
+                ctrl->seq = (((c0.x + c0.y) + (c0.z + c0.w)) + ((c1.x + c1.y) + (c1.z + c1.w))) >> 20;
+            }
+#pragma unroll 1
+            for (int row = 0; row < p.M; ++row) {
+                uint4* dst = reinterpret_cast<uint4*>(xsb + (size_t)row * 2 * p.K);
+                const uint4* sv = reinterpret_cast<const uint4*>(p.smooth);
+                if (p.norm_w) {
+                    const uint4* xr = reinterpret_cast<const uint4*>(p.Xraw + (size_t)row * p.K);
+                    float ss = 0.f;
+#pragma unroll 1
+                    for (int i = lt; i < kvec; i += LR_THREADS) {
+                        const uint4 a = ld_cg_v4(xr + i);
+                        dst[i] = a;
+                        const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
+                            ss = fmaf(lo, lo, ss);
+                            ss = fmaf(hi, hi, ss);
+                        }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (row > 0) named_bar_sync(3, LR_THREADS);              // (nred is reused from the previous row)
+                    if (lane == 0) ctrl->nred[lw] = ss;
+                    named_bar_sync(3, LR_THREADS);
+                    float tot = 0.f;
+#pragma unroll
+                    for (int i = 0; i < LR_WARPS; ++i) tot += ctrl->nred[i];
+                    const float inv = rsqrtf(tot / (float)p.K + p.eps);
+                    const uint4* gw4 = reinterpret_cast<const uint4*>(p.norm_w);
+#pragma unroll 1
+                    for (int i = lt; i < kvec; i += LR_THREADS) {
+                        const uint4 a = dst[i], g = gw4[i];
+                        uint4 c = make_uint4(0u, 0u, 0u, 0u);
+                        if (sv) c = sv[i];
+                        const uint32_t w[4] = {a.x, a.y, a.z, a.w}, gw[4] = {g.x, g.y, g.z, g.w}, sw[4] = {c.x, c.y, c.z, c.w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float v[2] = {__uint_as_float(w[e] << 16), __uint_as_float(w[e] & 0xFFFF0000u)};
+                            const float gv[2] = {__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xFFFF0000u)};
+                            const float sf2[2] = {__uint_as_float(sw[e] << 16), __uint_as_float(sw[e] & 0xFFFF0000u)};
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                v[h] = __bfloat162float(__float2bfloat16_rn(v[h] * inv));
+                                v[h] = __bfloat162float(__float2bfloat16_rn(v[h] * gv[h]));
+                                if (sv) v[h] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v[h], sf2[h])));
+                                amax = fmaxf(amax, fabsf(v[h]));
+                            }
+                            o[e] = (__float_as_uint(v[0]) >> 16) | (__float_as_uint(v[1]) & 0xFFFF0000u);
+                        }
+                        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                } else if (p.act_swiglu) {
+                    const uint4* gr = reinterpret_cast<const uint4*>(p.Xraw + (size_t)row * 2 * p.K);
+                    const uint4* ur = gr + kvec;
+#pragma unroll 1
+                    for (int i = lt; i < kvec; i += LR_THREADS) {
+                        const uint4 a = ld_cg_v4(gr + i), b = ld_cg_v4(ur + i);
+                        uint4 c = make_uint4(0u, 0u, 0u, 0u);
+                        if (sv) c = sv[i];
+                        const uint32_t gw[4] = {a.x, a.y, a.z, a.w}, uw[4] = {b.x, b.y, b.z, b.w}, sw[4] = {c.x, c.y, c.z, c.w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float gv[2] = {__uint_as_float(gw[e] << 16), __uint_as_float(gw[e] & 0xFFFF0000u)};
+                            const float uv[2] = {__uint_as_float(uw[e] << 16), __uint_as_float(uw[e] & 0xFFFF0000u)};
+                            const float sf2[2] = {__uint_as_float(sw[e] << 16), __uint_as_float(sw[e] & 0xFFFF0000u)};
+                            float v[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                v[h] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(gv[h], __fadd_rn(1.0f, expf(-gv[h])))));
+                                v[h] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(v[h], uv[h])));
+                                if (sv) v[h] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(v[h], sf2[h])));
+                                amax = fmaxf(amax, fabsf(v[h]));
+                            }
+                            o[e] = (__float_as_uint(v[0]) >> 16) | (__float_as_uint(v[1]) & 0xFFFF0000u);
+                        }
+                        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                } else {
+                    const uint4* xr = reinterpret_cast<const uint4*>(p.Xraw + (size_t)row * p.K);
+#pragma unroll 1
+                    for (int i = lt; i < kvec; i += LR_THREADS) {
+                        const uint4 a = ld_cg_v4(xr + i);
+                        uint4 c = make_uint4(0u, 0u, 0u, 0u);
+                        if (sv) c = sv[i];
+                        const uint32_t w[4] = {a.x, a.y, a.z, a.w}, sw[4] = {c.x, c.y, c.z, c.w};
+                        uint32_t o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float lo, hi;
+                            qm::unpack_smoothed(w[e], sw[e], sv != nullptr, lo, hi);
+                            amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
+                            o[e] = (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xFFFF0000u);
+                        }
+                        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+            if (lt == 0 && stamps) stamps[40] = (unsigned long long)clock64();
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (lane == 0) ctrl->amaxw[lw] = amax;
+            named_bar_sync(3, LR_THREADS);
+            if (lt == 0) {
+                float v = 0.f;
+#pragma unroll
+                for (int i = 0; i < LR_WARPS; ++i) v = fmaxf(v, ctrl->amaxw[i]);
+                const float target = p.act_rule == 0 ? 448.0f : 256.0f;
+                const float gs = v > 0.f ? __fdiv_rn(v, 6.0f * target) : 1.0f;
+                ctrl->gs = gs;
+                ctrl->alpha_s = __fmul_rn(ctrl->wgs, gs);
+                if (cta == 0 && p.act_out) { p.act_out[0] = gs; p.act_out[1] = ctrl->alpha_s; }
+            }
+            // the staged rows, the scale and the launch number are complete; the four GEMM-side warps (idle until the
+            // records arrive) quantise this CTA's share, in a CTA without weight rows these threads do it themselves
+            if (has_rows) {
+                asm volatile("bar.sync 5, 384;" ::: "memory");
+            } else {
+                named_bar_sync(3, LR_THREADS);
+                quantise_share(lt, LR_THREADS, lane, cta, p, xsb, ctrl->gs, ctrl->seq);
+            }
+            if (lt == 0 && stamps) stamps[41] = (unsigned long long)clock64();
+            if (lt == 0 && stamps) stamps[46] = (unsigned long long)clock64();
+            if (lt < ROWS * Rt) alpha_r = ctrl->alpha_s;
+            if (lt == 0 && stamps) stamps[45] = (unsigned long long)clock64();
+        }
         bool good = true;
         uint32_t phase = 0u;
 
@@ -641,7 +897,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             const uint32_t* xrow = reinterpret_cast<const uint32_t*>(p.X + (size_t)zm * p.K) + ((lt * e) >> 1);
             const bool single = e <= 2 * XW_MAX;                              // the whole span fits the registers: loaded once
             uint32_t xw[XW_MAX];
-            if (single && nr > 0) {
+            if (single && nr > 0 && !raw) {
                 // The warp's 32 spans are 64 e contiguous bytes of the row: fetched as 16-byte pieces (whole lines, every
                 // line once per CTA), starting at a line that depends on the CTA so that the CTAs do not all ask the same
                 // L2 slice at the same moment, staged in this warp's own piece of shared memory, read back span by span.
@@ -673,8 +929,9 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 }
                 __syncwarp();
             }
-            const uint32_t* mine = reinterpret_cast<const uint32_t*>(work + p.xs_off + lw * (64 * e)) + ((lane * e) >> 1);
-            if (lt == 0 && !(single && nr > 0)) {
+            // (raw-activation form: the staged rows are whole rows in order, row zm is this CTA's)
+            const uint32_t* mine = reinterpret_cast<const uint32_t*>(work + p.xs_off + (raw ? (size_t)zm * 2 * p.K : (size_t)0) + lw * (64 * e)) + ((lane * e) >> 1);
+            if (lt == 0 && !raw && !(single && nr > 0)) {
                 const uint4 c0 = ld_volatile_v4(p.z_counter + 8), c1 = ld_volatile_v4(p.z_counter + 12);
                 ctrl->seq = (((c0.x + c0.y) + (c0.z + c0.w)) + ((c1.x + c1.y) + (c1.z + c1.w))) >> 20;
             }
@@ -691,7 +948,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                     const int n2 = ((e - s0) < 2 * XW_MAX ? (e - s0) : 2 * XW_MAX) >> 1;      // pairs in this segment
                     if (!single) {
 #pragma unroll
-                        for (int i = 0; i < XW_MAX; ++i) xw[i] = i < n2 ? ld_cg_u32(xrow + (s0 >> 1) + i) : 0u;
+                        for (int i = 0; i < XW_MAX; ++i) xw[i] = i < n2 ? (raw ? mine[(s0 >> 1) + i] : ld_cg_u32(xrow + (s0 >> 1) + i)) : 0u;
                     }
                     const int idx = lt * e + s0, wi = idx >> 5, sh = idx & 31;
                     if (single) {
@@ -869,7 +1126,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
     }
     if (tid == 0) {
         // this CTA's share of 2^20: the sum over the CTAs of a launch is exactly 2^20 whatever the grid size
-        if (p.R > 0) {
+        if (p.R > 0 || RAW) {
             const uint32_t share = (uint32_t)((((unsigned long long)(cta + 1)) << 20) / (unsigned)p.G) -
                                    (uint32_t)((((unsigned long long)cta) << 20) / (unsigned)p.G);
             red_add_u32(p.z_counter + 8 + (cta & 7), share);

@@ -168,6 +168,24 @@ class BiLoCoGemm:
                        "read_status")
         return list(out)
 
+    def raw_supported(self) -> bool:
+        """True when raw() can run this problem (row-slab schedule with room for the staged activation)."""
+        if self.mode != 7:
+            return False
+        with torch.cuda.device(self.z.device):
+            return bool(_lib.load().biloco_b200_fused_linear_act_supported(self.M, self.N, self.K, self.R, 0))
+
+    def raw(self, x, w_gscale, rule="mse", norm_weight=None, eps=1e-6, smooth=None, swiglu=False, out=None, act_out=None):
+        """One launch from the RAW bf16 activation (row-slab schedule only): RMS norm or silu(gate) * up, smoothing, NVFP4
+        quantisation with `rule` and the linear; x [M, K] ([M, 2K] with swiglu), w_gscale fp32 [1] = the weights' tensor
+        scale. Same bits as fp4.quantize_activation followed by __call__. Returns [M, N]. No counterpart in the reference
+        (biloco/layer.py:55-63 runs smoothing, fake quantisation and the matmuls as separate kernels)."""
+        assert self.mode == 7, "the raw-activation form exists for the row-slab schedule (mode 7)"
+        self.epoch += 1
+        return _ops.fused_linear_act(x, self.W_tiled, self.N, w_gscale, self.V, self.S, self.U_col32, self.z, self.epoch, rule,
+                                     norm_weight=norm_weight, eps=eps, smooth=smooth, swiglu=swiglu, C=self.residual, out=out,
+                                     fp32_out=self.fp32_out, act_out=act_out)
+
     def __call__(self, A_pad, A_sf, X_bf16, out=None, A_rec=None):
         """Returns bf16 [1, rows, N]; rows >= M are padding (left unwritten). Not in the reference's signature: ``out``,
         a [rows, N] tensor to write into instead of a fresh one (e.g. a slice of a buffer that is read back in one copy),

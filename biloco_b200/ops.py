@@ -107,6 +107,44 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
     return D
 
 
+def fused_linear_act(x, B_slab, N, w_gscale, V, S, U_col32, scratch, epoch, rule, norm_weight=None, eps=1e-6, smooth=None,
+                     swiglu=False, C=None, out=None, fp32_out=False, act_out=None):
+    """One launch of the fused linear on a RAW bf16 activation (biloco_b200_fused_linear_act): RMS norm or silu(gate) * up,
+    smoothing, NVFP4 quantisation and the linear itself. x bf16 [M, K] ([M, 2K] with swiglu), M <= 2; B_slab the row-slab
+    copy of the weight; w_gscale fp32 [1]. Returns bf16 (or fp32) [M, N]."""
+    _req(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous(), "x must be contiguous bf16 [M, K] on a CUDA device")
+    M = x.size(0)
+    K = x.size(1) // 2 if swiglu else x.size(1)
+    _req(1 <= M <= 2, "the raw-activation form takes one or two rows")
+    _req(w_gscale.dtype == torch.float32 and w_gscale.numel() == 1, "w_gscale must be fp32 [1]")
+    for t, what in ((norm_weight, "norm_weight"), (smooth, "smooth")):
+        _req(t is None or (t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() == K), f"{what} must be contiguous bf16 [K]")
+    R = 0
+    if V is not None:
+        R = V.size(0)
+        _req(V.dtype == torch.uint8 and V.is_contiguous() and V.dim() == 2 and V.size(1) == K // 8, "V_packed must be contiguous uint8 [R, K/8]")
+        _req(S.dtype == torch.bfloat16 and S.is_contiguous() and S.numel() == R, "S must be contiguous bf16 [R]")
+        _req(U_col32.dtype == torch.int32 and U_col32.is_contiguous() and tuple(U_col32.shape) == (N, (R + 31) // 32),
+             "U_col32 must be contiguous int32 [N, ceil(R/32)]")
+    lib = _lib.load()
+    with torch.cuda.device(x.device):
+        want = lib.biloco_b200_slab_bytes(N, K, 0)
+    _req(want > 0 and B_slab.is_cuda and B_slab.dtype == torch.uint8 and B_slab.is_contiguous() and B_slab.numel() == want,
+         f"row-slab weight copy must be a contiguous uint8 CUDA tensor of {want} bytes")
+    _req(C is None or (C.dtype == torch.bfloat16 and C.is_contiguous() and tuple(C.shape) == (M, N)), "C must be contiguous bf16 [M, N]")
+    D = out if out is not None else torch.empty((M, N), device=x.device, dtype=torch.float32 if fp32_out else torch.bfloat16)
+    _req(D.is_contiguous() and D.dtype == (torch.float32 if fp32_out else torch.bfloat16) and D.numel() >= M * N, "output buffer")
+    with torch.cuda.device(x.device):
+        rc = lib.biloco_b200_fused_linear_act(
+            B_slab.data_ptr(), w_gscale.data_ptr(), x.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None,
+            float(eps), smooth.data_ptr() if smooth is not None else None, 1 if swiglu else 0, _lib.RULES[rule],
+            V.data_ptr() if R else None, U_col32.data_ptr() if R else None, S.data_ptr() if R else None,
+            C.data_ptr() if C is not None else None, D.data_ptr(), act_out.data_ptr() if act_out is not None else None,
+            scratch.data_ptr(), scratch.numel() * scratch.element_size(), M, N, K, R, 0x400 if fp32_out else 0, epoch, _stream())
+    _lib.check(rc, f"biloco fused linear on a raw activation (M={M}, N={N}, K={K}, R={R})")
+    return D
+
+
 def tile_weights(B, B_sf):
     """Unit-contiguous copy of the NVFP4 weight (codes [N, K/2] + block scales) that the fused kernel streams fastest."""
     N, K = B.size(0), B.size(1) * 2

@@ -126,6 +126,31 @@ int biloco_b200_swiglu_act_quant(const void* GU_bf16, const void* smooth_bf16, v
                                  void* A_rec, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M,
                                  int A_rows, int K, int rule, biloco_stream_t stream);
 
+/* The fused decode linear on a RAW activation, one launch (row-slab schedule, M <= 2): the kernel forms the activation
+ * the linear sees, quantises it to NVFP4 itself and multiplies -- no quantiser launch in front and no A_codes / A_sf /
+ * alpha / X buffers in between. Per row of X_raw (bf16 [M,K]; [M,2K] = [gate | up] with swiglu != 0):
+ *     x = X_raw                                                      (norm_weight == NULL, swiglu == 0)
+ *     x = bf16(bf16(X_raw * rsqrt(mean(X_raw^2) + eps)) * norm_weight)          (norm_weight: bf16 [K])
+ *     x = bf16(bf16(silu(gate)) * up)                                           (swiglu; not together with norm_weight)
+ *     x = bf16(x / smooth)                                                      (smooth: bf16 [K], may be NULL)
+ * then the tensor scale, block scales and codes of biloco_b200_act_quant for `rule` (BILOCO_RULE_STATIC_6 / _STATIC_4 /
+ * _MSE, bit for bit the same as that launch gives), alpha = w_gscale[0] * tensor scale, and
+ *     Y[m,n] = bf16( alpha * sum_k A[m,k] W[n,k]  +  sum_i z[m,i] sign(U[i,n])  (+ C[m,n]) ),  z = S .* (x sign(V)^T).
+ * W_slab: the copy made by biloco_b200_tile_weights_slab; w_gscale: fp32 [1] on the device (the weights' tensor scale,
+ * static like the weights: it is read before the previous kernel of the stream has finished). act_out (may be NULL):
+ * fp32 [2] on the device, receives the activation's tensor scale and alpha. flags: BILOCO_OUT_FP32 (Y is fp32) or 0.
+ * scratch: as for biloco_b200_fused_linear (biloco_b200_scratch_bytes for the same M, N, K, R), same bounded waits and
+ * status words. Shapes: those biloco_b200_slab_info accepts with enough shared memory left for M rows of K bf16.
+ * Replaces: the reference layer's activation path in front of its linear -- division by smooth_scale, fake_quantize_fp4
+ * (biloco/layer.py:55,60; biloco/fp4.py:30-35) -- together with torch.ops.biloco.biloco_gemm_mode2/4/5
+ * (csrc/bindings.cpp:37-43); the reference runs them as separate kernels. */
+int biloco_b200_fused_linear_act_supported(int M, int N, int K, int R, int num_sms);      /* 1 / 0; num_sms = 0: current device */
+int biloco_b200_fused_linear_act(const void* W_slab, const float* w_gscale, const void* X_raw_bf16,
+                                 const void* norm_weight_bf16, float eps, const void* smooth_bf16, int swiglu, int rule,
+                                 const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16,
+                                 void* Y, float* act_out, void* scratch, size_t scratch_bytes, int M, int N, int K, int R,
+                                 int flags, int epoch, biloco_stream_t stream);
+
 /* A_rec (optional, biloco_b200_act_rec_bytes(M, K) bytes, K % 256 == 0, M <= 32): the same codes and block scales once
  * more, laid out per 256-wide k-tile exactly as the fused kernel keeps them in shared memory (the activation tile with
  * the 128-byte swizzle applied, followed by its four scale atoms). biloco_b200_fused_linear_rec then fetches the

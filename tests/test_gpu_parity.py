@@ -451,3 +451,48 @@ def test_reference_layout_arguments_are_ignored(kernel):
     check_against_unfused(y2, y_ref, "mode 2 with the reference's V_perm / U_rw / Flags / Diag")
     y4 = kernel.ops.biloco_gemm_mode4(*a, z, diag.view(torch.uint8), M, 2).view(-1, N)[:M].float().cpu().numpy()
     check_against_unfused(y4, y_ref, "mode 4 with a Diag buffer")
+
+
+@pytest.mark.parametrize("M,K,N,R", [(1, 5120, 5120, 512), (2, 5120, 5120, 512), (1, 1024, 2560, 128), (2, 2560, 1024, 40),
+                                      (1, 9728, 2560, 256), (1, 512, 640, 0), (1, 8192, 1024, 512)])
+@pytest.mark.parametrize("pre", ["plain", "smooth", "norm", "norm+smooth", "swiglu", "swiglu+smooth"])
+def test_fused_raw_activation_matches_two_launches(kernel, M, K, N, R, pre):
+    """biloco_b200_fused_linear_act (RMS norm / SwiGLU, smoothing, NVFP4 quantisation and the linear in ONE launch, the
+    activation quantised by every CTA for itself) against the quantiser launch followed by the fused launch on the same
+    schedule: the same bits, call after call, for every scale rule; and the two-launch result is the one the other tests
+    pin to the oracle. Activations with outlier channels and an all-zero block."""
+    from biloco_b200 import fp4
+    if not kernel.supported_modes(M, N, K, R).count(7):
+        pytest.skip("shape not on the row-slab schedule")
+    g = torch.Generator(device="cuda").manual_seed(1000 * M + K + R)
+    W = (torch.randn(N, K, device="cuda", generator=g) * 0.02)
+    codes, sf, wgs = fp4.quantize_nvfp4(W, "mse")
+    if R > 0:
+        V = torch.where(torch.randn(R, K, device="cuda", generator=g) >= 0, 1.0, -1.0)
+        U = torch.where(torch.randn(R, N, device="cuda", generator=g) >= 0, 1.0, -1.0)
+        Vp, Up = kernel.pack_signs(V), kernel.pack_signs(U)
+        S = (torch.randn(R, device="cuda", generator=g) * 0.01).to(torch.bfloat16)
+    swiglu = pre.startswith("swiglu")
+    x = torch.randn(M, 2 * K if swiglu else K, device="cuda", generator=g)
+    x[:, torch.randperm(x.shape[1], device="cuda", generator=g)[: max(1, K // 100)]] *= 20
+    x[0, 32:48] = 0.0
+    x = x.to(torch.bfloat16).contiguous()
+    smooth = (torch.rand(K, device="cuda", generator=g) * 3 + 0.25).to(torch.bfloat16) if "smooth" in pre else None
+    norm_w = (torch.rand(K, device="cuda", generator=g) + 0.5).to(torch.bfloat16) if pre.startswith("norm") else None
+    res = torch.randn(M, N, device="cuda", generator=g).to(torch.bfloat16)
+    for rule in ("mse", "static_6", "static_4"):
+        q = fp4.quantize_activation(x, rule, smooth=smooth, w_gscale=wgs, rows=M, norm_weight=norm_w, eps=1e-5, swiglu=swiglu)
+        if R > 0:
+            two = kernel.BiLoCoGemm(codes, sf, q["alpha"], Vp, Up, S, M=M, mode=7)
+            one = kernel.BiLoCoGemm(codes, sf, q["alpha"], Vp, Up, S, M=M, mode=7)
+        else:
+            pytest.skip("FP4-only launcher has no row-slab form")
+        two.residual = one.residual = res
+        act = torch.zeros(2, device="cuda")
+        for call in range(3):
+            y2 = two(q["A"], q["A_sf"], q["X"]).view(-1, N)[:M].clone()
+            y1 = one.raw(x, wgs, rule, norm_weight=norm_w, eps=1e-5, smooth=smooth, swiglu=swiglu, act_out=act).clone()
+            torch.cuda.synchronize()
+            assert one.status()[0] == 0 and two.status()[0] == 0
+            assert torch.equal(act[:1], q["gscale"]) and torch.equal(act[1:], q["alpha"]), (rule, call)
+            assert torch.equal(y1.view(torch.int16), y2.view(torch.int16)), (rule, call, float((y1.float() - y2.float()).abs().max()))
