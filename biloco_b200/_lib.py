@@ -29,6 +29,8 @@ SIGNATURES = {
     "biloco_b200_decode_attention": (_i, [_vp, _vp, _vp, ctypes.c_float] + [_vp] * 6 + [_i] * 5 + [_vp]),
     "biloco_b200_max_active_clusters": (_i, [_i, _i]),
     "biloco_b200_act_rec_bytes": (_sz, [_i, _i]),
+    "biloco_b200_peel_scratch_bytes": (_sz, [_i, _i, _i]),
+    "biloco_b200_binary_peel": (_i, [_vp] * 6 + [_sz] + [_i] * 4 + [_vp]),
     "biloco_b200_fused_linear_act_supported": (_i, [_i] * 5),
     "biloco_b200_fused_linear_act": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _i, _i] + [_vp] * 7 + [_sz] + [_i] * 6 + [_vp]),
     "biloco_b200_fused_linear_rec": (_i, [_vp] * 14 + [_sz] + [_i] * 7 + [_vp]),

@@ -15,6 +15,7 @@ extern "C" const char* biloco_b200_error_string(int code) {
         case BILOCO_ERR_MODE: return "unknown mode or quantisation rule";
         case BILOCO_ERR_EPOCH: return "epoch must be >= 1";
         case BILOCO_ERR_LIMIT: return "size beyond the stated maximum";
+        case BILOCO_ERR_WAIT: return "a bounded wait on the device ran out";
         default: return "unknown error code";
     }
 }

@@ -1,11 +1,14 @@
 """Binary low-rank decomposition  W ~ U diag(alpha) V^T + R  with U, V in {+-1}.
 
-Host-side (PyTorch) operand generator for the fused kernel: greedy rank-one sign peeling followed by a joint
-least-squares refit of the coefficients. Same algorithm, seeding and operation order as the reference's
-``biloco/peel.py`` (binary_peel :14-42, refit_alphas :45-58, decompose :61-66), so that with the same seed and
-device the factors coincide; tests/golden pins this on CPU.
+Operand generator for the fused kernel: greedy rank-one sign peeling followed by a joint least-squares refit of the
+coefficients. Same algorithm and seeding as the reference's ``biloco/peel.py`` (binary_peel :14-42, refit_alphas
+:45-58, decompose :61-66). On a CUDA device the peeling runs in the library's own kernels (one pass over the residual
+per alternation, the previous atom's rank-one update folded into the next atom's first pass: csrc/peel.cu); on the
+CPU it is the plain torch restatement, which tests/golden pins to the reference's output.
 """
 import torch
+
+from . import _lib
 
 _seed = 42
 
@@ -22,6 +25,32 @@ def _sgn(t: torch.Tensor) -> torch.Tensor:
     return s
 
 
+def use_kernel(m: int, n: int) -> bool:
+    """True when the library's peeling kernels take an m x n matrix (n a multiple of 4, at most 14336; wider matrices take the torch path)."""
+    return bool(_lib.load().biloco_b200_peel_scratch_bytes(m, n, 148))
+
+
+def _peel_on_device(W, r, T, gen):
+    """binary_peel through biloco_b200_binary_peel. The start vectors are drawn one atom at a time from the generator, as
+    the reference draws them (biloco/peel.py:31), before the kernels run."""
+    m, n = W.shape
+    dev = W.device
+    lib = _lib.load()
+    v0 = torch.empty((r, n), device=dev, dtype=torch.float32)
+    for i in range(r):
+        v0[i] = torch.randn(n, generator=gen, device=dev, dtype=torch.float32)
+    R = W.contiguous().clone()
+    U = torch.empty((m, r), device=dev, dtype=torch.float32)
+    V = torch.empty((n, r), device=dev, dtype=torch.float32)
+    S = torch.empty(r, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        nbytes = lib.biloco_b200_peel_scratch_bytes(m, n, 0)
+        scratch = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+        _lib.check(lib.biloco_b200_binary_peel(R.data_ptr(), v0.data_ptr(), U.data_ptr(), V.data_ptr(), S.data_ptr(), scratch.data_ptr(),
+                                               nbytes, m, n, r, T, torch.cuda.current_stream().cuda_stream), f"binary_peel (m={m}, n={n}, r={r})")
+    return U, V, S, R
+
+
 @torch.no_grad()
 def binary_peel(W: torch.Tensor, r: int, T: int = 5, generator: torch.Generator = None):
     """Peel r sign atoms off W. Atom i: random signs v; T rounds of u = sgn(R v), v = sgn(R^T u);
@@ -29,6 +58,8 @@ def binary_peel(W: torch.Tensor, r: int, T: int = 5, generator: torch.Generator 
     m, n = W.shape
     dev, dt = W.device, W.dtype
     gen = generator if generator is not None else torch.Generator(device=dev).manual_seed(_seed)
+    if W.is_cuda and dt == torch.float32 and use_kernel(m, n):
+        return _peel_on_device(W, r, T, gen)
     U = torch.empty((m, r), device=dev, dtype=dt)
     V = torch.empty((n, r), device=dev, dtype=dt)
     alphas = torch.empty(r, device=dev, dtype=dt)

@@ -30,6 +30,7 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
 #define BILOCO_ERR_MODE -6           /* unknown schedule (mode) or quantisation rule */
 #define BILOCO_ERR_EPOCH -7          /* epoch must be >= 1 */
 #define BILOCO_ERR_LIMIT -8          /* size beyond a stated maximum */
+#define BILOCO_ERR_WAIT -9           /* a bounded wait on the device ran out (host-synchronous routines only) */
 
 /* NVFP4 block-scale selection rules of the activation quantiser (biloco/fp4.py:12-18). */
 #define BILOCO_RULE_STATIC_6 0
@@ -125,6 +126,19 @@ int biloco_b200_norm_act_quant(const void* X_bf16, const void* norm_weight_bf16,
 int biloco_b200_swiglu_act_quant(const void* GU_bf16, const void* smooth_bf16, void* Xa_bf16, void* A_codes, void* A_sf,
                                  void* A_rec, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M,
                                  int A_rows, int K, int rule, biloco_stream_t stream);
+
+/* Greedy sign peeling on the GPU:  W ~ sum_i S[i] u_i v_i^T + R  with u_i, v_i in {+-1}  (the decomposition that yields
+ * the packed low-rank operands). R: fp32 [m][n] on the device, holds W on entry and the residual on return (updated in
+ * place). v_init: fp32 [r][n], the random start vector of every atom (only its signs are used; sgn(0) = +1). Atom i:
+ * v = sgn(v_init[i]); T times  u = sgn(R v), v = sgn(R^T u);  S[i] = u^T R v / (m n);  R <- R - S[i] u v^T.
+ * Outputs: U fp32 [m][r], V fp32 [n][r] (+-1), S fp32 [r]. scratch: biloco_b200_peel_scratch_bytes(m, n, 0) bytes, 16-byte
+ * aligned (0 = shape not taken: n % 4 != 0 or n > 14336). The call returns when the work is done (it synchronises the
+ * stream: an offline step, not for graph capture); BILOCO_ERR_WAIT if a bounded device-side wait for a row copy ran out. Sums are fp32 in a fixed order (deterministic); one pass over the
+ * residual performs a whole alternation and carries the previous atom's update (see csrc/peel.cu).
+ * Replaces: binary_peel (biloco/peel.py:14-42), which issues 2 T + 2 library products and an outer-product update per atom. */
+size_t biloco_b200_peel_scratch_bytes(int m, int n, int num_sms);
+int biloco_b200_binary_peel(float* R, const float* v_init, float* U, float* V, float* S, void* scratch, size_t scratch_bytes,
+                            int m, int n, int r, int T, biloco_stream_t stream);
 
 /* The fused decode linear on a RAW activation, one launch (row-slab schedule, M <= 2): the kernel forms the activation
  * the linear sees, quantises it to NVFP4 itself and multiplies -- no quantiser launch in front and no A_codes / A_sf /
