@@ -29,6 +29,12 @@ SIGNATURES = {
     "biloco_b200_decode_attention": (_i, [_vp, _vp, _vp, ctypes.c_float] + [_vp] * 6 + [_i] * 5 + [_vp]),
     "biloco_b200_max_active_clusters": (_i, [_i, _i]),
     "biloco_b200_act_rec_bytes": (_sz, [_i, _i]),
+    "biloco_b200_peer_buffer_bytes": (_sz, [_i, _i]),
+    "biloco_b200_peer_buffer_create": (_i, [_sz, ctypes.POINTER(ctypes.c_void_p), _vp]),
+    "biloco_b200_peer_buffer_open": (_i, [_vp, ctypes.POINTER(ctypes.c_void_p)]),
+    "biloco_b200_peer_buffer_close": (_i, [_vp]),
+    "biloco_b200_peer_buffer_destroy": (_i, [_vp]),
+    "biloco_b200_peer_allreduce": (_i, [_vp] * 5 + [_i] * 5 + [_vp]),
     "biloco_b200_peel_scratch_bytes": (_sz, [_i, _i, _i]),
     "biloco_b200_binary_peel": (_i, [_vp] * 6 + [_sz] + [_i] * 4 + [_vp]),
     "biloco_b200_fused_linear_act_supported": (_i, [_i] * 5),

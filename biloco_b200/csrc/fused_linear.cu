@@ -135,6 +135,7 @@ static int g_skip_publish = -1;                   // test aid: this CTA of a row
 // programmatic stream serialization (that is the point: the weight prefetch overlaps the previous kernel), so a fused
 // launch that directly follows the kernel which WRITES such an operand must not start early: the first fused launch on
 // such a stream goes out as a plain launch.
+extern "C" unsigned long long biloco_internal_wait_ns() { return g_wait_ns; }
 static std::mutex g_fresh_mu;
 static std::unordered_map<cudaStream_t, int> g_fresh_streams;
 extern "C" void biloco_internal_mark_relayout(cudaStream_t stream) {

@@ -66,9 +66,11 @@ __device__ __forceinline__ bool peel_wait(uint32_t bar, uint32_t parity, int* er
 
 // One pass over the residual (see the file header). grid = G CTAs, CTA c owns rows [c m / G, (c + 1) m / G). Rows travel
 // between global and shared memory as bulk copies (one per row, two stages in flight); the warps only touch shared memory.
+template <int RB>
 __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
     extern __shared__ __align__(128) uint8_t smraw[];
-    const int n = a.n, nv = n >> 2, rb = a.rb;
+    const int n = a.n, nv = n >> 2;
+    constexpr int rb = RB;
     float* stage0 = reinterpret_cast<float*>(smraw);                    // [2][rb][n]
     uint8_t* vs = smraw + (size_t)2 * rb * n * 4;                       // [n] sign bytes of v (0x80 = negative)
     uint8_t* vp = vs + n;                                               // [n] sign bytes of v_prev
@@ -89,18 +91,22 @@ __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
         bad = 0;
     }
     __syncthreads();
-    auto issue = [&](int k) {      // thread 0: the rows of chunk k into stage k % 2
+    constexpr int wpr = PW / RB;                   // warps per row
+    const int myrow = warp / wpr, myseg = warp - myrow * wpr;
+    const int v0i = (int)((long long)myseg * nv / wpr), v1i = (int)((long long)(myseg + 1) * nv / wpr);
+    // Chunk k into stage k % 2: lane 0 of EVERY warp copies the piece of a row that its warp will read (a thread's bulk
+    // copies are served one after another, copies of different threads overlap); thread 0 announces the byte count.
+    auto issue = [&](int k) {
         const int st = k & 1, rbeg = r0 + k * rb;
         const int nr = (r1 - rbeg) < rb ? (r1 - rbeg) : rb;
         const uint32_t bar = biloco::smem_u32(&full[st]);
-        biloco::mbar_arrive_expect_tx(bar, row_bytes * (uint32_t)nr);
-        for (int q = 0; q < nr; ++q)
-            biloco::bulk_load(biloco::smem_u32(stage0 + ((size_t)st * rb + q) * n), a.R + (size_t)(rbeg + q) * n, row_bytes, bar);
+        if (tid == 0) biloco::mbar_arrive_expect_tx(bar, row_bytes * (uint32_t)nr);
+        if (lane == 0 && myrow < nr && v1i > v0i)
+            biloco::bulk_load(biloco::smem_u32(stage0 + ((size_t)st * rb + myrow) * n + 4 * (size_t)v0i),
+                              a.R + (size_t)(rbeg + myrow) * n + 4 * (size_t)v0i, (uint32_t)(v1i - v0i) * 16u, bar);
     };
-    if (tid == 0) {
-        if (nch > 0) issue(0);
-        if (nch > 1) issue(1);
-    }
+    if (nch > 0) issue(0);
+    if (nch > 1) issue(1);
     for (int i = tid; i < n; i += PT) {
         vs[i] = (uint8_t)((__float_as_uint(a.v[i]) >> 24) & 0x80u);
         if (a.deflate) vp[i] = (uint8_t)((__float_as_uint(a.v_prev[i]) >> 24) & 0x80u);
@@ -110,9 +116,6 @@ __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
 #pragma unroll
     for (int k = 0; k < MAXC; ++k) col[k] = 0.f;
     float asum = 0.f;
-    const int wpr = PW / rb;                       // warps per row
-    const int myrow = warp / wpr, myseg = warp - myrow * wpr;
-    const int v0i = (int)((long long)myseg * nv / wpr), v1i = (int)((long long)(myseg + 1) * nv / wpr);
     __syncthreads();
     for (int k = 0; k < nch; ++k) {
         const int st = k & 1, rbeg = r0 + k * rb;
@@ -123,7 +126,7 @@ __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
         if (bad) break;
         float* rows = stage0 + (size_t)st * rb * n;
         // ---- the warp's segment of its row: the previous atom's update (in shared memory), the partial dot product ----
-        float d = 0.f;
+        float d = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;      // (four chains: x, y, z, w lanes of the vectors; combined below in a fixed order)
         if (myrow < nr) {
             float4* s4 = reinterpret_cast<float4*>(rows + (size_t)myrow * n);
             const float au = a.deflate ? aus[myrow] : 0.f;
@@ -137,10 +140,11 @@ __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
                     x.z = __fsub_rn(x.z, flipb(au, (pv >> 16) & 0xffu)); x.w = __fsub_rn(x.w, flipb(au, pv >> 24));
                     s4[i] = x;
                 }
-                d = __fadd_rn(d, flipb(x.x, sv & 0xffu)); d = __fadd_rn(d, flipb(x.y, (sv >> 8) & 0xffu));
-                d = __fadd_rn(d, flipb(x.z, (sv >> 16) & 0xffu)); d = __fadd_rn(d, flipb(x.w, sv >> 24));
+                d = __fadd_rn(d, flipb(x.x, sv & 0xffu)); d1 = __fadd_rn(d1, flipb(x.y, (sv >> 8) & 0xffu));
+                d2 = __fadd_rn(d2, flipb(x.z, (sv >> 16) & 0xffu)); d3 = __fadd_rn(d3, flipb(x.w, sv >> 24));
             }
         }
+        d = __fadd_rn(__fadd_rn(d, d1), __fadd_rn(d2, d3));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) d = __fadd_rn(d, __shfl_xor_sync(0xffffffffu, d, o));
         if (lane == 0) dseg[warp] = d;
@@ -169,12 +173,18 @@ __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
                 for (int q = 0; q < nr; ++q) asum = __fadd_rn(asum, dseg[q * wpr]);
         } else {
             // column sums of the stage, rows in order
+            float usr[RB];
+#pragma unroll
+            for (int q = 0; q < RB; ++q) usr[q] = us[q];
 #pragma unroll
             for (int kk = 0; kk < MAXC; ++kk) {
+                if (kk * PT >= n) break;                       // (uniform: the columns beyond n belong to nobody)
                 const int cc = tid + kk * PT;
                 if (cc < n) {
                     float t = col[kk];
-                    for (int q = 0; q < nr; ++q) t = __fadd_rn(t, flip(rows[(size_t)q * n + cc], us[q]));
+#pragma unroll
+                    for (int q = 0; q < RB; ++q)
+                        if (q < nr) t = __fadd_rn(t, flip(rows[(size_t)q * n + cc], usr[q]));
                     col[kk] = t;
                 }
             }
@@ -182,7 +192,7 @@ __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
         // the stage is free once everybody has read it (and the copies out of it have read it): refill it
         if (a.deflate && tid == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         __syncthreads();
-        if (tid == 0 && k + 2 < nch) issue(k + 2);
+        if (k + 2 < nch) issue(k + 2);
     }
     if (a.deflate && tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     if (bad) {      // copies may still be in flight towards the stages: let them land before the shared memory is released
@@ -201,24 +211,37 @@ __global__ void __launch_bounds__(PT, 1) peel_pass_kernel(PeelArgs a) {
     }
 }
 
-// v[c] = sgn(sum over the CTAs, in order, of their column sums); optionally stored as column `atom` of V [n][r] too.
-__global__ void peel_colsign_kernel(const float* __restrict__ colpart, float* __restrict__ v, float* __restrict__ Vout, int n, int G,
-                                    int r, int atom) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= n) return;
+// v[c] = sgn(sum over the CTAs of their column sums); optionally stored as column `atom` of V [n][r] too. A block takes 32
+// columns; its eight warps each add an eighth of the CTAs' values (in CTA order, sixteen loads in flight), and the eight
+// sums are added in warp order: a fixed order, with an eighth of the serial latency.
+__global__ void __launch_bounds__(256) peel_colsign_kernel(const float* __restrict__ colpart, float* __restrict__ v, float* __restrict__ Vout,
+                                                           int n, int G, int r, int atom) {
+    __shared__ float part[8][32];
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + lane;
+    const int g0 = (int)((long long)w * G / 8), g1 = (int)((long long)(w + 1) * G / 8);
     float t = 0.f;
-    int g = 0;
-    for (; g + 16 <= G; g += 16) {        // (sixteen loads in flight, added in CTA order)
-        float x[16];
+    if (c < n) {
+        int g = g0;
+        for (; g + 16 <= g1; g += 16) {
+            float x[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = __ldcg(colpart + (size_t)(g + i) * n + c);
+            for (int i = 0; i < 16; ++i) x[i] = __ldcg(colpart + (size_t)(g + i) * n + c);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) t = __fadd_rn(t, x[i]);
+            for (int i = 0; i < 16; ++i) t = __fadd_rn(t, x[i]);
+        }
+        for (; g < g1; ++g) t = __fadd_rn(t, __ldcg(colpart + (size_t)g * n + c));
     }
-    for (; g < G; ++g) t = __fadd_rn(t, __ldcg(colpart + (size_t)g * n + c));
-    const float s = sgn1(t);
-    v[c] = s;
-    if (Vout) Vout[(size_t)c * r + atom] = s;
+    part[w][lane] = t;
+    __syncthreads();
+    if (w == 0 && c < n) {
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tot = __fadd_rn(tot, part[i][lane]);
+        const float s = sgn1(tot);
+        v[c] = s;
+        if (Vout) Vout[(size_t)c * r + atom] = s;
+    }
 }
 
 // alpha = (sum of the CTAs' partial sums, in order) / (m n); also S[atom], and u as column `atom` of U [m][r].
@@ -246,6 +269,16 @@ static int peel_rows_per_stage(int n) {
     for (int t = 1; t <= PW; t *= 2)
         if (2ll * t * n * 4 <= room) rb = t;
     return rb;
+}
+
+static void launch_pass(const PeelArgs& a, int G, size_t smem, cudaStream_t stream) {
+    switch (a.rb) {
+        case 1: peel_pass_kernel<1><<<G, PT, smem, stream>>>(a); break;
+        case 2: peel_pass_kernel<2><<<G, PT, smem, stream>>>(a); break;
+        case 4: peel_pass_kernel<4><<<G, PT, smem, stream>>>(a); break;
+        case 8: peel_pass_kernel<8><<<G, PT, smem, stream>>>(a); break;
+        default: peel_pass_kernel<16><<<G, PT, smem, stream>>>(a); break;
+    }
 }
 
 }  // namespace
@@ -280,7 +313,11 @@ extern "C" int biloco_b200_binary_peel(float* R, const float* v_init, float* U, 
     const size_t smem = (size_t)2 * rb * n * sizeof(float) + 2 * (size_t)n;
     static bool attr_set[64] = {false};
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(peel_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PEEL_SMEM + 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(peel_pass_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, PEEL_SMEM + 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(peel_pass_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, PEEL_SMEM + 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(peel_pass_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, PEEL_SMEM + 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(peel_pass_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, PEEL_SMEM + 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(peel_pass_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, PEEL_SMEM + 1024) != cudaSuccess)
             return BILOCO_ERR_CUDA;
         attr_set[dev] = true;
     }
@@ -300,7 +337,7 @@ extern "C" int biloco_b200_binary_peel(float* R, const float* v_init, float* U, 
     a.err = (int*)(alpha + 1);
     cudaMemsetAsync(alpha, 0, 16, stream);
     a.alpha_prev = alpha;
-    const int cb = 64, cg = (n + cb - 1) / cb;      // (small blocks: the few thousand columns spread over many SMs)
+    const int cb = 256, cg = (n + cb - 1) / cb;
     for (int atom = 0; atom < r; ++atom) {
         // (the atom's vectors alternate between the two buffers, so that the previous atom's stay readable for the update)
         float* u = (atom & 1) ? u_prev : u_cur;
@@ -312,11 +349,11 @@ extern "C" int biloco_b200_binary_peel(float* R, const float* v_init, float* U, 
             a.v = v; a.u = u; a.u_prev = up; a.v_prev = vpv;
             a.deflate = (t == 0 && atom > 0) ? 1 : 0;
             a.dots_only = 0;
-            peel_pass_kernel<<<G, PT, smem, stream>>>(a);
-            peel_colsign_kernel<<<cg, cb, 0, stream>>>(colpart, v, t == T - 1 ? V : nullptr, n, G, r, atom);
+            launch_pass(a, G, smem, stream);
+            peel_colsign_kernel<<<(n + 31) / 32, 256, 0, stream>>>(colpart, v, t == T - 1 ? V : nullptr, n, G, r, atom);
         }
         a.v = v; a.u = u; a.deflate = 0; a.dots_only = 1;
-        peel_pass_kernel<<<G, PT, smem, stream>>>(a);
+        launch_pass(a, G, smem, stream);
         peel_alpha_kernel<<<(m + 255) / 256 < 64 ? (m + 255) / 256 : 64, 256, 0, stream>>>(apart, G, (float)m * (float)n, alpha, S, u, U, m, r,
                                                                                              atom);
     }
@@ -328,7 +365,7 @@ extern "C" int biloco_b200_binary_peel(float* R, const float* v_init, float* U, 
         a.v_prev = (atom & 1) ? v_cur : v_prev;
         a.v = a.v_prev;
         a.deflate = 1; a.dots_only = 0;
-        peel_pass_kernel<<<G, PT, smem, stream>>>(a);
+        launch_pass(a, G, smem, stream);
     }
     if (cudaGetLastError() != cudaSuccess) return BILOCO_ERR_CUDA;
     // the decomposition is an offline step: wait for it and report a wait that ran out on the device

@@ -68,12 +68,105 @@ def agree_on_activation_scale(x_local: torch.Tensor, smooth_local: torch.Tensor 
     return fp4.activation_scale_from_amax(amax, rule)
 
 
+class PeerAllReduce:
+    """All-reduce of fp32 partial outputs over peer memory in ONE launch per rank (biloco_b200_peer_allreduce: NVLink
+    stores into the peers' receive buffers, value and call number in one 8-byte word, sums in rank order, so every rank
+    gets the same bits). One object per process group, shared by all its row-parallel layers: the group's calls must be
+    issued in the same order on every rank, which a tensor-parallel model does. Replaces ncclAllReduce + the cast to bf16
+    where the message is a decode step's [M, N] (latency-bound). No counterpart in the reference."""
+
+    _by_group = {}
+
+    @classmethod
+    def for_group(cls, group, device, count):
+        """The group's object, (re)created collectively when `count` elements do not fit its slots."""
+        key = id(group) if group is not None else 0
+        obj = cls._by_group.get(key)
+        if obj is None or obj.slot_elems < count:
+            if obj is not None:
+                obj.close()
+            obj = cls(group, device, max(count, 32 * 8192))
+            cls._by_group[key] = obj
+        return obj
+
+    def __init__(self, group, device, slot_elems):
+        import ctypes
+        from . import _lib
+        lib = _lib.load()
+        self.group, self.device, self.slot_elems = group, torch.device(device), int(slot_elems)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        with torch.cuda.device(self.device):
+            nbytes = lib.biloco_b200_peer_buffer_bytes(self.world, self.slot_elems)
+            assert nbytes > 0, "peer all-reduce: group too large"
+            ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+            _lib.check(lib.biloco_b200_peer_buffer_create(nbytes, ctypes.byref(ptr), handle), "peer_buffer_create")
+            self.local = ptr.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self.ptrs, self._opened = [], []
+            for p in range(self.world):
+                if p == self.rank:
+                    self.ptrs.append(self.local)
+                    continue
+                q = ctypes.c_void_p()
+                h = (ctypes.c_ubyte * 64).from_buffer_copy(handles[p])
+                _lib.check(lib.biloco_b200_peer_buffer_open(h, ctypes.byref(q)), f"peer_buffer_open (rank {p})")
+                self.ptrs.append(q.value)
+                self._opened.append(q.value)
+            self.table = torch.tensor(self.ptrs, dtype=torch.int64, device=self.device)
+            self.status = torch.zeros(16, dtype=torch.int32, device=self.device)
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)          # every rank has mapped every buffer before anybody stores into one
+
+    def __call__(self, partial, residual=None, out=None, fp32_out=False):
+        """partial fp32 (contiguous, <= slot_elems elements) -> the sum over the ranks (+ residual bf16), bf16 or fp32, same shape."""
+        from . import _lib
+        assert partial.is_cuda and partial.dtype == torch.float32 and partial.is_contiguous() and partial.numel() <= self.slot_elems
+        assert residual is None or (residual.dtype == torch.bfloat16 and residual.is_contiguous() and residual.numel() == partial.numel())
+        if out is None:
+            out = torch.empty(partial.shape, device=partial.device, dtype=torch.float32 if fp32_out else torch.bfloat16)
+        with torch.cuda.device(self.device):
+            rc = _lib.load().biloco_b200_peer_allreduce(
+                partial.data_ptr(), residual.data_ptr() if residual is not None else None, out.data_ptr(), self.table.data_ptr(),
+                self.status.data_ptr(), self.world, self.rank, partial.numel(), self.slot_elems, 0x400 if fp32_out else 0,
+                torch.cuda.current_stream().cuda_stream)
+        _lib.check(rc, "peer_allreduce")
+        return out
+
+    def failed(self) -> bool:
+        """True when a poll of an earlier call ran out of its time budget (synchronises)."""
+        return bool(self.status[0].item())
+
+    def close(self):
+        """Collective: unmap the peers' buffers, then free the local one."""
+        from . import _lib
+        lib = _lib.load()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for q in self._opened:
+                lib.biloco_b200_peer_buffer_close(q)
+            self._opened = []
+            dist.barrier(group=self.group)
+            if self.local:
+                lib.biloco_b200_peer_buffer_destroy(self.local)
+                self.local = None
+
+    @classmethod
+    def close_all(cls):
+        for obj in list(cls._by_group.values()):
+            obj.close()
+        cls._by_group.clear()
+
+
 class ShardedBiLoCoLinear:
     """One rank's shard of a quantised layer, run through the fused kernel.
 
     kind = "column": forward(x [M, K]) -> y [M, N/G] (local columns).
     kind = "row":    forward(x_local [M, K/G]) -> y [M, N], all-reduced over the group.
     """
+
+    peer_allreduce = True      # row shards on CUDA under NCCL: the library's own one-launch all-reduce instead of ncclAllReduce + cast
 
     def __init__(self, ops: dict, kind: str, M: int, group=None, presharded: bool = False, local_scale: bool = False):
         """ops: the operands of the whole layer (sharded here), or with presharded=True this rank's shard as it is.
@@ -122,6 +215,8 @@ class ShardedBiLoCoLinear:
         if self.kind == "row":
             y = y.contiguous()
             if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+                if self.peer_allreduce and y.is_cuda and dist.get_backend(self.group) == "nccl":
+                    return PeerAllReduce.for_group(self.group, y.device, y.numel())(y)      # fp32 partials in, bf16 sum out
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)      # fp32 [M, N] over NVLink
             y = y.to(torch.bfloat16)
         return y

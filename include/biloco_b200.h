@@ -127,6 +127,28 @@ int biloco_b200_swiglu_act_quant(const void* GU_bf16, const void* smooth_bf16, v
                                  void* A_rec, float* a_gscale, float* alpha_out, const float* w_gscale, int n_alpha, int M,
                                  int A_rows, int K, int rule, biloco_stream_t stream);
 
+/* All-reduce of the K-sharded linears' fp32 partial outputs over peer memory, ONE launch per rank (one process per GPU;
+ * plain NVLink stores and loads, no library collective). Every rank creates a receive buffer of
+ * biloco_b200_peer_buffer_bytes(world, slot_elems) bytes (biloco_b200_peer_buffer_create: device memory, zeroed, plus
+ * its 64-byte inter-process handle), sends the handle to its peers by whatever means the host has (the Python side uses
+ * torch.distributed.all_gather_object) and maps theirs (biloco_b200_peer_buffer_open). recv_ptrs_dev: device array of
+ * `world` pointers, entry p = rank p's buffer as mapped in this process (entry `rank`: the local one). A call:
+ *     out[i] = round( sum over ranks p = 0 .. world-1, in that order, of partial_p[i]  (+ residual[i]) ),  i < count
+ * The calls of a group are numbered by a counter the kernel keeps in `status` (so a captured CUDA graph can be
+ * replayed); the ranks must issue the group's calls in the same order. Rank r stores {value, call number} words into its
+ * slot of every peer's buffer and polls its own buffer for the peers' words: one traversal of the link; every rank forms
+ * the same sum bit for bit. count <= slot_elems.
+ * out: bf16 (or fp32 with BILOCO_OUT_FP32 in flags); residual_bf16 may be NULL. status: int32 [16] on the device, zeroed
+ * once before the first call and then left alone (word 8 is the call counter); word 0 becomes 1 when a poll ran out of
+ * its time budget (BILOCO_OPT_WAIT_BUDGET_US; the call's output is then undefined). No counterpart in the reference. */
+size_t biloco_b200_peer_buffer_bytes(int world, int slot_elems);
+int biloco_b200_peer_buffer_create(size_t bytes, void** ptr, void* handle64);
+int biloco_b200_peer_buffer_open(const void* handle64, void** ptr);
+int biloco_b200_peer_buffer_close(void* ptr);
+int biloco_b200_peer_buffer_destroy(void* ptr);
+int biloco_b200_peer_allreduce(const float* partial, const void* residual_bf16, void* out, void* const* recv_ptrs_dev, int* status,
+                               int world, int rank, int count, int slot_elems, int flags, biloco_stream_t stream);
+
 /* Greedy sign peeling on the GPU:  W ~ sum_i S[i] u_i v_i^T + R  with u_i, v_i in {+-1}  (the decomposition that yields
  * the packed low-rank operands). R: fp32 [m][n] on the device, holds W on entry and the residual on return (updated in
  * place). v_init: fp32 [r][n], the random start vector of every atom (only its signs are used; sgn(0) = +1). Atom i:

@@ -56,3 +56,35 @@ def test_z_poll_runs_out_and_scratch_recovers():
     assert torch.equal(again.view(torch.int16), clean.view(torch.int16)), "the call after reset() differs from a clean one"
     again = run()
     assert torch.equal(again.view(torch.int16), clean.view(torch.int16))
+
+
+def test_peer_allreduce_wait_runs_out_and_reports(lib):
+    """The peer all-reduce polls its own receive buffer for the peers' words with a time budget. Here a 'group' of two
+    with nobody behind rank 1 (its buffer is a second local allocation that nothing reads or writes back): the poll runs
+    out, the kernel records it and returns, the context stays usable, and a later launch on the same GPU is unaffected."""
+    import ctypes
+    world, slot = 2, 1024
+    nbytes = lib.biloco_b200_peer_buffer_bytes(world, slot)
+    bufs = []
+    for _ in range(2):
+        p, h = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        assert lib.biloco_b200_peer_buffer_create(nbytes, ctypes.byref(p), h) == 0
+        bufs.append(p.value)
+    table = torch.tensor(bufs, dtype=torch.int64, device="cuda")
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    part = torch.ones(512, device="cuda")
+    out = torch.zeros(512, device="cuda", dtype=torch.bfloat16)
+    assert lib.biloco_b200_set_option(5, 2000) == 0              # BILOCO_OPT_WAIT_BUDGET_US
+    try:
+        rc = lib.biloco_b200_peer_allreduce(part.data_ptr(), None, out.data_ptr(), table.data_ptr(), status.data_ptr(), world, 0, 512, slot, 0,
+                                            torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+    finally:
+        lib.biloco_b200_set_option(5, 0)
+    st = status.cpu().tolist()
+    assert st[0] == 1 and st[2] == 1 and st[3] == 0, st            # gave up, in call 1, on rank 0
+    assert (st[8] >> 20) == 1                                       # the call counter advanced all the same
+    assert float((torch.ones(8, device="cuda") * 2).sum()) == 16.0   # the context still works
+    for b in bufs:
+        assert lib.biloco_b200_peer_buffer_destroy(b) == 0

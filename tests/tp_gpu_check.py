@@ -112,6 +112,63 @@ def main():
     ref = out.clone()
     dist.broadcast(ref, src=0)
     assert torch.equal(ref, out), "ranks disagree on the generated tokens"
+    # the library's one-launch all-reduce over peer memory: the same bits on every rank, equal to the sum of the gathered
+    # partials in rank order; call after call (both sets of slots, the device-side call counter), eagerly and as replays of
+    # a captured graph; and the row-parallel layer gives the same output through it as through NCCL (two ranks: a + b)
+    red = parallel.PeerAllReduce.for_group(None, dev, 32 * 8192)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    for count, fp32_out in ((8192, False), (5, False), (32 * 8192, True), (8 * 2048, False)):
+        for call in range(3):
+            part = torch.randn(count, device=dev, generator=g)
+            resid = torch.randn(count, device=dev, generator=g).to(torch.bfloat16) if call == 1 else None
+            if resid is not None:
+                dist.broadcast(resid, src=0)
+            got = red(part, residual=resid, fp32_out=fp32_out)
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            want = torch.zeros_like(part)
+            for q in parts:
+                want = want + q
+            if resid is not None:
+                want = want + resid.float()
+            want = want if fp32_out else want.to(torch.bfloat16)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), (count, call, float((got.float() - want.float()).abs().max()))
+    part = torch.randn(4096, device=dev, generator=g)
+    outg = torch.empty(4096, device=dev, dtype=torch.bfloat16)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        red(part, out=outg)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            red(part, out=outg)
+            red(outg.float(), out=outg)
+    torch.cuda.current_stream().wait_stream(side)
+    parts = [torch.empty_like(part) for _ in range(world)]
+    dist.all_gather(parts, part)
+    s1 = torch.zeros_like(part)
+    for q in parts:
+        s1 = s1 + q
+    s1 = s1.to(torch.bfloat16).float()
+    want = torch.zeros_like(part)
+    for _ in range(world):
+        want = want + s1
+    want = want.to(torch.bfloat16)
+    for _ in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(outg, want), "captured peer all-reduce differs on replay"
+    assert not red.failed()
+    if world == 2:
+        parallel.ShardedBiLoCoLinear.peer_allreduce = False
+        y_nccl = row(x[:, klo:khi].contiguous()).clone()
+        parallel.ShardedBiLoCoLinear.peer_allreduce = True
+        y_peer = row(x[:, klo:khi].contiguous()).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(y_nccl.view(torch.int16), y_peer.view(torch.int16)), "peer all-reduce and NCCL disagree"
+    parallel.PeerAllReduce.close_all()
     dist.barrier()
     if rank == 0:
         print(f"tensor-parallel check ok on {world} GPUs (decoder logits vs single GPU: worst relative error {float(same):.3g})", flush=True)
