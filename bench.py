@@ -435,8 +435,8 @@ def comparator_leg():
 def tp_decode_leg(torch, dist, world, rank, dev, args):
     """The N/K-sharded path: greedy decode of a Llama-3-70B-shaped decoder (80 layers, hidden 8192, intermediate 28672, 64
     query / 8 KV heads, vocabulary 128256; every linear a rank-512 layer with random packed operands) through the captured
-    step of biloco_b200.decode: q/k/v, gate/up and lm_head column-parallel, o and down row-parallel with one NCCL
-    all-reduce of the fp32 partial sums each inside the step. One rank per GPU; at world size 1 the whole model on one."""
+    step of biloco_b200.decode: q/k/v, gate/up and lm_head column-parallel, o and down row-parallel with one all-reduce of
+    the fp32 partial sums each inside the step (the library's one-launch all-reduce over peer memory; --tp-nccl: NCCL). One rank per GPU; at world size 1 the whole model on one."""
     from biloco_b200 import decode
     c = decode.PRESETS["llama3-70b"]
     if args.tp_layers:
@@ -446,7 +446,22 @@ def tp_decode_leg(torch, dist, world, rank, dev, args):
     nlin = decode.synthetic_quantize(model, 512, seed=1000 * rank)
     g = torch.Generator(device=dev).manual_seed(0)
     prompt = torch.randint(0, c.vocab, (args.tp_M, args.tp_prompt), device=dev, generator=g)
+    from biloco_b200 import parallel
+    ar = "none"
+    if world > 1:
+        # two eager steps first: if a poll of the library's peer-memory all-reduce ran out of its budget on any rank, the
+        # timed run uses NCCL instead (and says so)
+        parallel.ShardedBiLoCoLinear.peer_allreduce = not args.tp_nccl
+        decode.greedy_decode(model, prompt[:, :2], 1, use_graph=False)
+        bad = torch.tensor([1.0 if any(o.failed() for o in parallel.PeerAllReduce._by_group.values()) else 0.0], device=dev)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if bad.item() > 0:
+            parallel.ShardedBiLoCoLinear.peer_allreduce = False
+        ar = ("one launch over peer memory (biloco_b200_peer_allreduce)" if parallel.ShardedBiLoCoLinear.peer_allreduce
+              else ("ncclAllReduce + cast" + ("" if args.tp_nccl else " (the peer-memory all-reduce reported a failed wait)")))
     toks, sec = decode.greedy_decode(model, prompt, args.tp_steps, use_graph=True)
+    if world > 1:
+        parallel.PeerAllReduce.close_all()
     nbytes = decode.linear_bytes(model) * world
     if dist is not None:
         t = torch.tensor([sec], device=dev)
@@ -458,7 +473,7 @@ def tp_decode_leg(torch, dist, world, rank, dev, args):
             "parallelism": f"tp{world}: q/k/v/gate/up/lm_head column shards, o/down row shards", "M": args.tp_M, "rank": 512,
             "linears_per_rank": nlin, "prompt": args.tp_prompt, "steps": args.tp_steps,
             "tokens_per_s": args.tp_M * args.tp_steps / sec, "ms_per_step": sec / args.tp_steps * 1e3,
-            "all_reduces_per_step": n_ar, "all_reduce_bytes_each": args.tp_M * c.hidden * 4 if world > 1 else 0,
+            "all_reduce": ar, "all_reduces_per_step": n_ar, "all_reduce_bytes_each": args.tp_M * c.hidden * 4 if world > 1 else 0,
             "linear_bytes_per_step": nbytes, "hbm_frac_of_n_gpus": nbytes * args.tp_steps / sec / 1e9 / (peak * world),
             "finite": bool(torch.isfinite(toks.float()).all())}
 
@@ -572,6 +587,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the whole-model decode leg (default workload, one GPU only)")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of CPU work for the baseline sample")
+    ap.add_argument("--tp-nccl", action="store_true", help="tensor-parallel decode leg: NCCL all-reduce instead of the library's own")
     ap.add_argument("--e2e-two-launches", action="store_true",
                     help="end-to-end arm: quantiser launch + fused launch per layer instead of the one-launch raw-activation form")
     ap.add_argument("--own-activations", action="store_true",

@@ -344,6 +344,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (0 = the preset's)")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-graph", action="store_true", help="eager launches instead of a captured step")
+    ap.add_argument("--autotune", action="store_true", help="pick every linear's schedule by measuring it once per shape on this GPU")
     ap.add_argument("--no-fuse", action="store_true", help="separate RMSNorm kernels and one quantiser launch per linear")
     ap.add_argument("--no-step-fusion", action="store_true", help="attention step, SwiGLU and residual adds as separate torch kernels")
     ap.add_argument("--no-groups", action="store_true", help="one fused-linear launch per linear (q, k, v, gate, up separately)")
@@ -361,6 +362,9 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(args.seed)
     model = Decoder(c, device=dev, meta=True, tp=world)
+    if args.autotune:
+        from . import kernel
+        kernel.AUTOTUNE = True
     model.fuse_norm_quant = not args.no_fuse
     model.fuse_groups = not args.no_groups
     model.fuse_step = not args.no_step_fusion

@@ -45,6 +45,58 @@ def default_mode(M: int, rank: int, ok, back_to_back: bool = True):
     return mode if mode in ok else ([m for m in ok if m != 7] or [None])[0]
 
 
+_TUNED = {}          # (device index, M, N, K, R, back_to_back) -> mode, filled by tuned_mode()
+AUTOTUNE = False     # BiLoCoGemm(mode=None): measure the schedules once per shape instead of reading the 5120 x 5120 table
+
+
+@torch.no_grad()
+def tuned_mode(M: int, N: int, K: int, R: int, back_to_back: bool = True, device=None, verbose: bool = False):
+    """The fastest schedule for this shape ON THIS GPU, measured once per process and cached: every schedule the shape
+    takes runs a captured graph over enough distinct random weight copies to exceed L2 (HBM-cold, at most 16 copies), the
+    median of 12 replays decides. With back_to_back=False a quantiser launch sits in front of every linear, as in a layer's
+    forward, and the row-slab schedule is left out (see default_mode). The table DEFAULT_MODE holds what this returns at
+    K = N = 5120; other shapes (8192 x 8192, 28672-wide MLPs, shards) do not always agree with it."""
+    from . import fp4
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (dev.index, M, N, K, R, back_to_back)
+    if key in _TUNED:
+        return _TUNED[key]
+    with torch.cuda.device(dev):
+        ok = [m for m in supported_modes(M, N, K, R) if back_to_back or m != 7]
+        if len(ok) <= 1:
+            _TUNED[key] = ok[0] if ok else None
+            return _TUNED[key]
+        wbytes = N * K // 2
+        copies = max(2, min(16, -(-140_000_000 // wbytes)))
+        g = torch.Generator(device=dev).manual_seed(1)
+        x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        wgs = torch.full((1,), 1e-3, device=dev)
+        q = fp4.quantize_activation(x, "mse", w_gscale=wgs, rows=M)
+        V = torch.randint(0, 256, (R, K // 8), device=dev, dtype=torch.uint8, generator=g)
+        U = torch.randint(0, 256, (R, N // 8), device=dev, dtype=torch.uint8, generator=g)
+        S = (torch.randn(R, device=dev, generator=g) * 0.01).to(torch.bfloat16)
+        Ws = [torch.randint(0, 256, (N, K // 2), device=dev, dtype=torch.uint8, generator=g) for _ in range(copies)]
+        sf = torch.full((nvfp4_sf_bytes(N, K),), 0x38, device=dev, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        best, best_us, seen = None, None, {}
+        for m in ok:
+            gemms = [BiLoCoGemm(W, sf, q["alpha"], V, U, S, M=M, mode=m) for W in Ws]
+
+            def run():
+                for gm in gemms:
+                    if not back_to_back:
+                        fp4.quantize_activation(x, "mse", w_gscale=wgs, rows=M, out=q)
+                    gm(q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec") if m != 7 else None)
+            us = time_graph(run, None, iters=12, batch=1) / copies
+            seen[m] = us
+            if all(gm.status()[0] == 0 for gm in gemms) and (best_us is None or us < best_us):
+                best, best_us = m, us
+            del gemms
+        if verbose:
+            print(f"tuned_mode M={M} N={N} K={K} R={R} back_to_back={back_to_back}: " + ", ".join(f"mode {m}: {u:.1f} us" for m, u in seen.items()) + f" -> {best}")
+    _TUNED[key] = best
+    return best
+
+
 def pack_signs(signs: torch.Tensor) -> torch.Tensor:
     """[..., n] +-1 -> uint8 [..., n/8]; bit i of byte j is set iff signs[..., 8j + i] >= 0
     (same bit order and zero-is-plus rule as biloco/kernel.py:29-34)."""
@@ -131,6 +183,8 @@ class BiLoCoGemm:
         dev = W_fp4.device
         with torch.cuda.device(dev):
             ok = supported_modes(M, self.N, self.K, self.R)
+        if mode is None and AUTOTUNE and len(ok) > 1:      # measured once per shape on this GPU
+            mode = tuned_mode(M, self.N, self.K, self.R, back_to_back, device=dev)
         if mode is None:      # the table's choice if this shape takes it, else the first mode that does
             mode = default_mode(M, self.R, ok, back_to_back)
         self.mode = mode

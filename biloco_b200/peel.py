@@ -95,3 +95,45 @@ def decompose(W: torch.Tensor, r: int, T: int = 5):
     U, V, S, _ = binary_peel(W, r=r, T=T)
     S, R = refit_alphas(W, U, V, S)
     return U, V, S, R
+
+
+def main():
+    """python -m biloco_b200.peel [--m 5120 --n 5120 --r 64 --T 5]: decompose a random matrix on the GPU and report the
+    time per atom of the peeling kernels, the residual norm, and the same for the torch-operations path (--torch)."""
+    global use_kernel
+    import argparse
+    import json
+    import time
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--m", type=int, default=5120)
+    ap.add_argument("--n", type=int, default=5120)
+    ap.add_argument("--r", type=int, default=64)
+    ap.add_argument("--T", type=int, default=5)
+    ap.add_argument("--torch", action="store_true", help="also time the torch-operations path on the same GPU")
+    a = ap.parse_args()
+    assert torch.cuda.is_available(), "needs a CUDA device"
+    torch.manual_seed(0)
+    W = torch.randn(a.m, a.n, device="cuda") * 0.02
+    out = {"m": a.m, "n": a.n, "r": a.r, "T": a.T, "kernel_path": use_kernel(a.m, a.n)}
+    binary_peel(W, min(a.r, 2), a.T)
+    torch.cuda.synchronize()
+    t = time.perf_counter()
+    U, V, S, R = binary_peel(W, a.r, a.T)
+    torch.cuda.synchronize()
+    out["ms_per_atom"] = (time.perf_counter() - t) * 1e3 / a.r
+    out["residual_over_W"] = float(R.norm() / W.norm())
+    if a.torch:
+        keep, use_kernel = use_kernel, (lambda m, n: False)
+        binary_peel(W, 2, a.T)
+        torch.cuda.synchronize()
+        t = time.perf_counter()
+        _, _, _, R2 = binary_peel(W, a.r, a.T)
+        torch.cuda.synchronize()
+        out["torch_ms_per_atom"] = (time.perf_counter() - t) * 1e3 / a.r
+        out["torch_residual_over_W"] = float(R2.norm() / W.norm())
+        use_kernel = keep
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()

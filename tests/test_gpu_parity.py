@@ -496,3 +496,15 @@ def test_fused_raw_activation_matches_two_launches(kernel, M, K, N, R, pre):
             assert one.status()[0] == 0 and two.status()[0] == 0
             assert torch.equal(act[:1], q["gscale"]) and torch.equal(act[1:], q["alpha"]), (rule, call)
             assert torch.equal(y1.view(torch.int16), y2.view(torch.int16)), (rule, call, float((y1.float() - y2.float()).abs().max()))
+
+
+def test_tuned_mode_measures_and_caches(kernel):
+    """kernel.tuned_mode picks a schedule the shape takes by timing them on this GPU, once per shape; with a quantiser launch
+    between the linears (back_to_back=False) the row-slab schedule is not a candidate."""
+    M, N, K, R = 1, 1024, 2048, 64
+    ok = kernel.supported_modes(M, N, K, R)
+    m1 = kernel.tuned_mode(M, N, K, R, back_to_back=True)
+    assert m1 in ok
+    assert kernel.tuned_mode(M, N, K, R, back_to_back=True) == m1 and (0, M, N, K, R, True) in kernel._TUNED
+    m2 = kernel.tuned_mode(M, N, K, R, back_to_back=False)
+    assert m2 in ok and m2 != 7
