@@ -12,6 +12,7 @@ OK = 0
 RULES = {"static_6": 0, "static_4": 1, "mse": 2}
 MODE_COUNTER, MODE_OWNER, MODE_CLUSTER, MODE_SLAB = 2, 4, 5, 7
 OPT_PDL, OPT_RING, OPT_TRIGGER, OPT_LR_TC, OPT_WAIT_BUDGET_US, OPT_SKIP_PUBLISH = 1, 2, 3, 4, 5, 6
+OPT_ZTC = 8
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 

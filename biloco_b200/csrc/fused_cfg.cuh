@@ -109,6 +109,8 @@ struct FusedParams {
     uint32_t* tile_cnt;
     float* zbuf;
     float* partials;
+    uint32_t* ztc_cnt;        // tensor-core z launch (ztc_kernel.cuh): arrival counters per rank block; nullptr = not available
+    size_t part_bytes;        // bytes of `partials` (the z launch keeps its partial sums there until the fused launch starts)
     int M, N, K, R, Rw, Rpad;
     // Column groups: several linears that read the same activation (q/k/v, gate/up) stacked along N in one launch. Group
     // g owns the tiles [gtile[g-1], gtile[g]) (gtile[-1] = 0, unused entries INT_MAX), the ranks [g*Rg, (g+1)*Rg) of V, S

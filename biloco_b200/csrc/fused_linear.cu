@@ -46,6 +46,7 @@
 
 #include "../../include/biloco_b200.h"
 #include "fused_kernel.cuh"
+#include "ztc_kernel.cuh"
 
 namespace biloco {
 
@@ -123,6 +124,7 @@ static unsigned long long* g_stamps = nullptr;   // debug time-stamp buffer for 
 static size_t g_stamps_bytes = 0;
 static size_t g_stamps_seq = 0;
 static int g_lr_tc = 1;                          // expansion on the tensor cores where the kernel supports it
+static int g_ztc = -1;                           // z stage as a tensor-core launch of its own: -1 from ZTC_MIN_ROWS rows, 0 never, n > 0 from n rows
 static int g_trigger = -1;                        // < 0: chosen per launch (see launch())
 static unsigned long long g_wait_ns = WAIT_BUDGET_NS;   // budget of a device-side wait (row-slab schedule)
 static int g_inflight = 0;                        // row-slab schedule: weight records in flight while the ring fills (0: all)
@@ -153,7 +155,7 @@ static bool consume_relayout_mark(cudaStream_t stream) {
 static int mma_n_for(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 
 struct ScratchLayout {
-    size_t off_zcnt, off_tilecnt, off_z, off_arec, off_part, total;
+    size_t off_zcnt, off_tilecnt, off_z, off_arec, off_ztc, off_part, part_bytes, total;
     int ntile, nkt, G, max_slots, Rw, Rpad, mma_n;
 };
 
@@ -174,7 +176,20 @@ static bool make_layout(int M, int N, int K, int R, int num_sms, ScratchLayout* 
     L->off_z = off; off += (size_t)2 * 32 * L->Rpad * sizeof(float);
     // raw-activation form of the row-slab schedule: one 16-byte record per 16-element block of the activation (M <= 2)
     L->off_arec = off; off += (M <= 2 && K % 512 == 0) ? (size_t)M * K : 0;
-    L->off_part = off; off += (size_t)L->ntile * L->max_slots * L->mma_n * TILE_N * sizeof(float);
+    L->off_ztc = off; off = (off + 64 + 255) / 256 * 256;      // arrival counters of the tensor-core z launch (16 rank blocks)
+    {
+        // split-K partial sums of the fused kernel; the tensor-core z launch parks its own partial sums there first
+        size_t part = (size_t)L->ntile * L->max_slots * L->mma_n * TILE_N * sizeof(float);
+        const int nrb = (R + 127) / 128;
+        if (M >= ztc::ZTC_MIN_ROWS && nrb >= 1 && nrb <= 16 && nrb <= num_sms) {      // (fewer rows: the z launch is optional and used only if it fits)
+            int nks = num_sms / nrb;
+            if (nks > K / 64) nks = K / 64;
+            const size_t zp = (size_t)nrb * nks * L->mma_n * 128 * sizeof(float);
+            if (zp > part) part = zp;
+        }
+        L->off_part = off; off += part;
+        L->part_bytes = part;
+    }
     L->total = (off + 255) / 256 * 256;
     return true;
 }
@@ -305,6 +320,22 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
         if (vt > VT_MAX_BYTES) vt = VT_MAX_BYTES;
     }
     p.vt_bytes = vt;
+    // z on the tensor cores as a launch of its own in front of this one (ztc_kernel.cuh): the fused kernel then has no z items
+    int dev_sms = 0;
+    cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, dev);
+    const int ztc_from = g_ztc < 0 ? ztc::ZTC_MIN_ROWS : g_ztc;
+    bool use_ztc = ztc_from > 0 && p.M >= ztc_from && p.R > 0 && p.ztc_cnt != nullptr && dev_sms > 0;
+    int z_nrb = 0, z_nks = 0;
+    if (use_ztc) {
+        z_nrb = (p.R + 127) / 128;
+        if (z_nrb > 16 || z_nrb > dev_sms) use_ztc = false;
+        else {
+            z_nks = dev_sms / z_nrb;
+            if (z_nks > p.K / 64) z_nks = p.K / 64;
+            if ((size_t)z_nrb * z_nks * MMA_N * 128 * sizeof(float) > p.part_bytes) use_ztc = false;
+        }
+    }
+    if (use_ztc) p.nsl = 0;
     // expansion on the tensor cores from 16 rows up (below that the CUDA-core form is as fast); its operand buffers sit
     // behind the sign words
     p.lr_tc = (ROWS >= LR_TC_MIN_ROWS && p.R > 0 && g_lr_tc) ? 1 : 0;
@@ -331,10 +362,36 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
     // started early, beside the last CTAs of a predecessor with another cluster shape, the first clusters were placed
     // where the rest no longer fitted and the launch sat until its waits ran out (seen with q/k/v stacked at M = 8 behind
     // a 7-CTA-cluster launch). Such launches start on an empty device: no programmatic early start for them.
-    int dev_sms = 0;
-    cudaDeviceGetAttribute(&dev_sms, cudaDevAttrMultiProcessorCount, dev);
     const bool tight_clusters = p.cluster > 1 && ctas_per_sm(ROWS) == 1 && p.G * 20 > dev_sms * 17;
-    const bool after_relayout = consume_relayout_mark(stream);
+    bool after_relayout = consume_relayout_mark(stream);
+    if (use_ztc) {
+        ztc::ZtcParams z;
+        z.Vp = p.Vp; z.X = p.X; z.S = p.S; z.zbuf = p.zbuf; z.part = p.partials; z.cnt = p.ztc_cnt; z.z_counter = p.z_counter;
+        z.status = p.status; z.wait_ns = WAIT_BUDGET_NS; z.M = p.M; z.K = p.K; z.R = p.R; z.Rpad = p.Rpad; z.nrb = z_nrb; z.nks = z_nks;
+        z.epoch = p.epoch;
+        cudaLaunchConfig_t zc = {};
+        zc.gridDim = dim3((unsigned)(z_nrb * z_nks));
+        zc.blockDim = dim3(ztc::ZT);
+        zc.dynamicSmemBytes = (size_t)(1024 + ztc::NBUF * (ztc::A_BYTES + MMA_N * 128) + 4096);
+        static bool zattr[64] = {false};
+        if (dev >= 0 && dev < 64 && !zattr[dev]) {
+            if (cudaFuncSetAttribute(ztc::ztc_kernel<MMA_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024) != cudaSuccess)
+                return BILOCO_ERR_CUDA;
+            zattr[dev] = true;
+        }
+        zc.stream = stream;
+        cudaLaunchAttribute za[1];
+        int nz = 0;
+        if (g_use_pdl && !after_relayout) {
+            za[nz].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            za[nz].val.programmaticStreamSerializationAllowed = 1;
+            ++nz;
+        }
+        zc.attrs = za;
+        zc.numAttrs = nz;
+        if (cudaLaunchKernelEx(&zc, ztc::ztc_kernel<MMA_N>, z) != cudaSuccess) return BILOCO_ERR_CUDA;
+        after_relayout = false;      // (the z launch stands between the re-layout and this one)
+    }
     if (g_use_pdl && !tight_clusters && !after_relayout) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
@@ -555,6 +612,8 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
     p.tile_cnt = (uint32_t*)(sc + L.off_tilecnt);
     p.zbuf = (float*)(sc + L.off_z);
     p.partials = (float*)(sc + L.off_part);
+    p.ztc_cnt = (uint32_t*)(sc + L.off_ztc);
+    p.part_bytes = L.part_bytes;
     p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = (Rg + 31) / 32; p.Rpad = L.Rpad;
     p.ngroups = n_groups; p.Rg = Rg;
     for (int g = 0; g < 3; ++g) p.gtile[g] = gtile[g];
@@ -733,6 +792,8 @@ extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void*
     p.tile_cnt = (uint32_t*)(sc + L.off_tilecnt);
     p.zbuf = (float*)(sc + L.off_z);
     p.partials = (float*)(sc + L.off_part);
+    p.ztc_cnt = (uint32_t*)(sc + L.off_ztc);
+    p.part_bytes = L.part_bytes;
     p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = L.Rw; p.Rpad = L.Rpad;
     p.ngroups = 1; p.Rg = R;
     for (int g = 0; g < 3; ++g) p.gtile[g] = 0x7fffffff;
@@ -766,6 +827,7 @@ extern "C" int biloco_b200_set_option(int option, int value) {
     if (option == BILOCO_OPT_PDL) { g_use_pdl = value ? 1 : 0; return BILOCO_OK; }
     if (option == BILOCO_OPT_TRIGGER) { g_trigger = value; return BILOCO_OK; }
     if (option == BILOCO_OPT_LR_TC) { g_lr_tc = value ? 1 : 0; return BILOCO_OK; }
+    if (option == BILOCO_OPT_ZTC) { g_ztc = value; return BILOCO_OK; }
     if (option == BILOCO_OPT_RING) { g_ring = value <= 0 ? 0 : value; return BILOCO_OK; }
     if (option == BILOCO_OPT_WAIT_BUDGET_US) {
         g_wait_ns = value <= 0 ? WAIT_BUDGET_NS : (unsigned long long)value * 1000ull;

@@ -373,6 +373,9 @@ int biloco_b200_read_status(const void* scratch, int32_t* out16, biloco_stream_t
 /* Row-slab schedule: weight records a CTA keeps in flight while it fills its ring ahead of the dependency wait
  * (0, the default: chosen by the library). Tuning aid. */
 #define BILOCO_OPT_INFLIGHT 7
+/* z stage as a tensor-core launch of its own in front of the fused launch (schedules 2 / 4 / 5): -1 (default) from 16
+ * activation rows, 0 never, n > 0 from n rows. */
+#define BILOCO_OPT_ZTC 8
 int biloco_b200_set_option(int option, int value);
 
 /* Debug aid: while a device buffer is registered here, every fused launch of this process writes 16 uint64

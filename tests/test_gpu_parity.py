@@ -508,3 +508,35 @@ def test_tuned_mode_measures_and_caches(kernel):
     assert kernel.tuned_mode(M, N, K, R, back_to_back=True) == m1 and (0, M, N, K, R, True) in kernel._TUNED
     m2 = kernel.tuned_mode(M, N, K, R, back_to_back=False)
     assert m2 in ok and m2 != 7
+
+
+@pytest.mark.parametrize("M,K,N,R,mode", [(32, 5120, 5120, 512, 2), (16, 5120, 5120, 512, 2), (32, 1024, 1024, 128, 2), (32, 2560, 1024, 200, 2),
+                                          (24, 256, 640, 72, 2), (32, 5120, 2560, 1024, 2), (8, 5120, 5120, 512, 5), (4, 2048, 1024, 64, 2),
+                                          (17, 8192, 1024, 512, 2)])
+def test_fused_with_tensor_core_z_launch(kernel, lib, M, K, N, R, mode):
+    """The z stage as a tensor-core launch of its own in front of the fused launch (default from 16 rows; forced here for
+    the smaller batches): against the oracle's unfused value with non-zero block scales, bit-identical call after call and
+    within an ulp-level distance of the in-kernel CUDA-core z stage (same sums, other order of additions). Ranks that are
+    not a multiple of 128, a K of four chunks, eight rank blocks."""
+    from biloco_b200 import _lib
+    if mode not in kernel.supported_modes(M, N, K, R):
+        pytest.skip("schedule not available for this shape")
+    p = orc.random_problem(M, K, N, R, scales="random", seed=300 + M + R)
+    t = dev_problem(p)
+    y_ref, _ = oracle_outputs(p, M)
+    outs = {}
+    try:
+        for ztc in (1, 0):
+            assert lib.biloco_b200_set_option(_lib.OPT_ZTC, ztc) == 0
+            g = kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M, mode=mode)
+            ys = []
+            for _ in range(4):
+                ys.append(g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].clone())
+            torch.cuda.synchronize()
+            assert g.status()[0] == 0, g.status()[:4]
+            assert all(torch.equal(ys[0].view(torch.int16), y.view(torch.int16)) for y in ys[1:])
+            check_against_unfused(ys[0].float().cpu().numpy(), y_ref, f"ztc={ztc}")
+            outs[ztc] = ys[0].float()
+    finally:
+        lib.biloco_b200_set_option(_lib.OPT_ZTC, -1)
+    assert float((outs[1] - outs[0]).abs().max()) <= 2.0 ** -7 * float(outs[0].abs().max())      # (bf16 outputs: at most an ulp apart)
