@@ -41,6 +41,7 @@ SIGNATURES = {
     "biloco_b200_fused_linear_act_supported": (_i, [_i] * 5),
     "biloco_b200_fused_linear_act": (_i, [_vp, _vp, _vp, _vp, ctypes.c_float, _vp, _i, _i] + [_vp] * 7 + [_sz] + [_i] * 6 + [_vp]),
     "biloco_b200_fused_linear_rec": (_i, [_vp] * 14 + [_sz] + [_i] * 7 + [_vp]),
+    "biloco_b200_fused_linear_push": (_i, [_vp] * 14 + [_sz] + [_i] * 7 + [_vp, _vp, _i, _i, _i, _vp]),
     "biloco_b200_fused_linear_grouped": (_i, [_vp] * 14 + [_sz] + [_i] * 6 + [ctypes.POINTER(ctypes.c_int)] + [_i] * 2 + [_vp]),
     "biloco_b200_scratch_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "biloco_b200_scratch_head_bytes": (_sz, [_i, _i, _i, _i, _i]),

@@ -111,6 +111,12 @@ struct FusedParams {
     float* partials;
     uint32_t* ztc_cnt;        // tensor-core z launch (ztc_kernel.cuh): arrival counters per rank block; nullptr = not available
     size_t part_bytes;        // bytes of `partials` (the z launch keeps its partial sums there until the fused launch starts)
+    // Row-parallel use (peer_reduce.cu): the thread that stores an fp32 output also stores {value, call number} into this
+    // rank's slot of every peer's receive buffer, so the all-reduce's transfer starts with the tile's epilogue instead of
+    // with a later launch. ar_world <= 1: off.
+    uint2* const* ar_recv;    // [ar_world] device table: rank q's receive buffer as mapped here
+    const uint32_t* ar_counter;   // the group's call counter (bits 20..: completed calls), advanced by the gather launch
+    int ar_world, ar_rank, ar_slot;
     int M, N, K, R, Rw, Rpad;
     // Column groups: several linears that read the same activation (q/k/v, gate/up) stacked along N in one launch. Group
     // g owns the tiles [gtile[g-1], gtile[g]) (gtile[-1] = 0, unused entries INT_MAX), the ranks [g*Rg, (g+1)*Rg) of V, S
@@ -153,6 +159,7 @@ struct Ctrl {   // lives in shared memory after the stages
     uint64_t red_free;            // cluster mode, other CTAs: the finisher's z stage is over, its work area may be written
     uint32_t tmem_base;
     volatile int abort;
+    uint32_t ar_seq;          // number of the all-reduce call this launch's outputs belong to
 };
 static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
 

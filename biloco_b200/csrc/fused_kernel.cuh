@@ -19,6 +19,18 @@ __device__ __forceinline__ void tmem_ld_acc(uint32_t taddr, float* v) {
     }
 }
 
+// Row-parallel use: this rank's fp32 output element `idx`, with the number of the all-reduce call it belongs to, into this
+// rank's slot of every peer's receive buffer (one aligned 8-byte store each: value and flag travel together; the gather
+// launch of peer_reduce.cu polls for them).
+__device__ __forceinline__ void ar_push(const FusedParams& p, uint32_t seq, int idx, float v) {
+    const size_t off = (size_t)(seq & 1u) * p.ar_world * p.ar_slot + (size_t)p.ar_rank * p.ar_slot + idx;
+    const uint32_t bits = __float_as_uint(v);
+    for (int q = 0; q < p.ar_world; ++q) {
+        if (q == p.ar_rank) continue;
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p.ar_recv[q] + off), "r"(bits), "r"(seq) : "memory");
+    }
+}
+
 template <int MMA_N, int ROWS>
 __global__ void __launch_bounds__(NUM_THREADS, ctas_per_sm(ROWS))
 fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
@@ -289,6 +301,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         if (p.trigger == 1 && tid == 0) griddep_launch_dependents();
         griddep_wait();            // (again, for the R == 0 path; a second wait returns at once)
+        if (p.ar_world > 1 && tid == 0) ctrl->ar_seq = (ld_volatile_u32(p.ar_counter) >> 20) + 1u;      // (read by the storing threads behind a barrier)
         // Cluster mode: the other CTAs of the cluster deposit their partial sums in this (the finishing) CTA's work
         // area, which its z stage has been using until now: tell them it is free.
         if (p.cluster > 1 && (cta % p.cluster) == p.cluster - 1 && tid < p.cluster - 1)
@@ -380,8 +393,10 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                             if (m < p.M) {
                                 float o = v[m];
                                 if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
-                                if (p.mode & 0x400) reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
-                                else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
+                                if (p.mode & 0x400) {
+                                    reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
+                                    if (p.ar_world > 1) ar_push(p, ctrl->ar_seq, m * p.N + n, o);
+                                } else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
                             }
                         }
                     }
@@ -415,8 +430,10 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                         if (m < p.M) {
                             float o = v[m];
                             if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
-                            if (p.mode & 0x400) reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
-                                else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
+                            if (p.mode & 0x400) {
+                                reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
+                                if (p.ar_world > 1) ar_push(p, ctrl->ar_seq, m * p.N + n, o);
+                            } else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
                         }
                     }
                 }

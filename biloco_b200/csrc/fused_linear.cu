@@ -543,11 +543,16 @@ static int slab_launch(const void* W_slab, const float* alpha, const void* A_cod
     return M <= 1 ? slab::slab_launch_rows<1, false>(q, g, pdl, stream) : slab::slab_launch_rows<2, false>(q, g, pdl, stream);
 }
 
+// Row-parallel use: where the epilogue pushes its fp32 outputs (peer_reduce.cu's receive buffers).
+struct ArPush {
+    void* const* recv_ptrs_dev; const int* status; int world, rank, slot_elems;
+};
+
 static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha, const void* A_codes,
                              const void* A_sf, const void* A_rec, const void* X_bf16, const void* V_packed, const int32_t* U_col32,
                              const void* S_bf16, const void* C_bf16, void* Y_bf16, void* scratch,
                              size_t scratch_bytes, int M, int A_rows, int N, int K, int R, int mode, int epoch,
-                             biloco_stream_t stream, int n_groups = 1, const int* group_rows = nullptr) {
+                             biloco_stream_t stream, int n_groups = 1, const int* group_rows = nullptr, const ArPush* ar = nullptr) {
     if ((uintptr_t)A_rec & 15) return BILOCO_ERR_ALIGN;
     // column groups: R ranks per group, group g covers group_rows[g] output columns (whole 128-column tiles)
     int gtile[3] = {0x7fffffff, 0x7fffffff, 0x7fffffff};
@@ -614,6 +619,16 @@ static int fused_linear_impl(const void* W_codes, const void* W_sf, const void* 
     p.partials = (float*)(sc + L.off_part);
     p.ztc_cnt = (uint32_t*)(sc + L.off_ztc);
     p.part_bytes = L.part_bytes;
+    p.ar_recv = nullptr; p.ar_counter = nullptr; p.ar_world = 0; p.ar_rank = 0; p.ar_slot = 0;
+    if (ar) {
+        if (!(mode & 0x400) || (mode & 0xff) == BILOCO_MODE_SLAB) return BILOCO_ERR_MODE;      // fp32 partial sums of the tile kernels only
+        if (!ar->recv_ptrs_dev || !ar->status) return BILOCO_ERR_NULL;
+        if (ar->world < 2 || ar->world > 16 || ar->rank < 0 || ar->rank >= ar->world || (long long)M * N > ar->slot_elems) return BILOCO_ERR_SHAPE;
+        if (((uintptr_t)ar->recv_ptrs_dev & 7) || ((uintptr_t)ar->status & 3)) return BILOCO_ERR_ALIGN;
+        p.ar_recv = (uint2* const*)ar->recv_ptrs_dev;
+        p.ar_counter = (const uint32_t*)ar->status + 8;
+        p.ar_world = ar->world; p.ar_rank = ar->rank; p.ar_slot = ar->slot_elems;
+    }
     p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = (Rg + 31) / 32; p.Rpad = L.Rpad;
     p.ngroups = n_groups; p.Rg = Rg;
     for (int g = 0; g < 3; ++g) p.gtile[g] = gtile[g];
@@ -705,6 +720,17 @@ extern "C" int biloco_b200_fused_linear_rec(const void* W_codes, const void* W_s
                              scratch, scratch_bytes, M, A_rows, N, K, R, mode, epoch, stream);
 }
 
+extern "C" int biloco_b200_fused_linear_push(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                             const void* A_codes, const void* A_sf, const void* A_rec, const void* X_bf16,
+                                             const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16,
+                                             void* Y_f32, void* scratch, size_t scratch_bytes, int M, int A_rows, int N, int K,
+                                             int R, int mode, int epoch, void* const* recv_ptrs_dev, const int* ar_status, int world,
+                                             int rank, int slot_elems, biloco_stream_t stream) {
+    const ArPush ar = {recv_ptrs_dev, ar_status, world, rank, slot_elems};
+    return fused_linear_impl(W_codes, W_sf, W_tiled, alpha, A_codes, A_sf, A_rec, X_bf16, V_packed, U_col32, S_bf16, C_bf16, Y_f32,
+                             scratch, scratch_bytes, M, A_rows, N, K, R, mode, epoch, stream, 1, nullptr, &ar);
+}
+
 extern "C" int biloco_b200_fused_linear_grouped(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
                                                 const void* A_codes, const void* A_sf, const void* A_rec, const void* X_bf16,
                                                 const void* V_packed, const int32_t* U_col32, const void* S_bf16,
@@ -794,6 +820,7 @@ extern "C" int biloco_b200_fused_linear_noalloc(const void* W_codes, const void*
     p.partials = (float*)(sc + L.off_part);
     p.ztc_cnt = (uint32_t*)(sc + L.off_ztc);
     p.part_bytes = L.part_bytes;
+    p.ar_recv = nullptr; p.ar_counter = nullptr; p.ar_world = 0; p.ar_rank = 0; p.ar_slot = 0;
     p.M = M; p.N = N; p.K = K; p.R = R; p.Rw = L.Rw; p.Rpad = L.Rpad;
     p.ngroups = 1; p.Rg = R;
     for (int g = 0; g < 3; ++g) p.gtile[g] = 0x7fffffff;

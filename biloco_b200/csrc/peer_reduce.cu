@@ -44,6 +44,7 @@ struct ArArgs {
     unsigned long long wait_ns;
     int world, rank, count, slot_elems;
     int out_f32;
+    int pushed;               // the producer of `partial` has stored this rank's words into the peers' buffers already
 };
 
 __global__ void __launch_bounds__(AR_THREADS) peer_allreduce_kernel(ArArgs a) {
@@ -54,8 +55,8 @@ __global__ void __launch_bounds__(AR_THREADS) peer_allreduce_kernel(ArArgs a) {
     const int set = (int)(seq & 1u);
     const size_t set_off = (size_t)set * a.world * a.slot_elems;
     const int stride = gridDim.x * AR_THREADS;
-    // push
-    for (int i = blockIdx.x * AR_THREADS + threadIdx.x; i < a.count; i += stride) {
+    // push (unless the fused linear's epilogue has done it: biloco_b200_fused_linear_push)
+    for (int i = blockIdx.x * AR_THREADS + threadIdx.x; i < a.count && !a.pushed; i += stride) {
         const uint32_t bits = __float_as_uint(a.partial[i]);
         for (int p = 0; p < a.world; ++p) {
             if (p == a.rank) continue;
@@ -151,7 +152,7 @@ extern "C" int biloco_b200_peer_allreduce(const float* partial, const void* resi
                                           biloco_stream_t stream) {
     if (!partial || !out || !recv_ptrs_dev || !status) return BILOCO_ERR_NULL;
     if (world < 1 || world > AR_MAX_WORLD || rank < 0 || rank >= world || count < 1 || count > slot_elems) return BILOCO_ERR_SHAPE;
-    if (flags & ~BILOCO_OUT_FP32) return BILOCO_ERR_MODE;
+    if (flags & ~(BILOCO_OUT_FP32 | BILOCO_AR_PUSHED)) return BILOCO_ERR_MODE;
     if (((uintptr_t)partial & 3) || ((uintptr_t)recv_ptrs_dev & 7) || ((uintptr_t)status & 3)) return BILOCO_ERR_ALIGN;
     ArArgs a;
     a.partial = partial;
@@ -162,6 +163,7 @@ extern "C" int biloco_b200_peer_allreduce(const float* partial, const void* resi
     a.wait_ns = biloco_internal_wait_ns();
     a.world = world; a.rank = rank; a.count = count; a.slot_elems = slot_elems;
     a.out_f32 = (flags & BILOCO_OUT_FP32) ? 1 : 0;
+    a.pushed = (flags & BILOCO_AR_PUSHED) ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     int blocks = (count + AR_THREADS - 1) / AR_THREADS;
     if (blocks > 1184) blocks = 1184;                  // (eight CTAs per SM on 148 SMs; larger messages stride)

@@ -206,6 +206,7 @@ class BiLoCoGemm:
         self.epoch = 0
         self.residual = None      # optional bf16 [M, N] added before the single final rounding (e.g. a broadcast bias)
         self.fp32_out = False     # True: return the unrounded fp32 sum (partial outputs reduced across devices)
+        self.peer_push = None     # row-parallel shards: PeerAllReduce.push_args(); the epilogue then also stores its outputs to the peers
 
     def reset(self):
         """Clear the status words and counters (needed only after a launch whose status reported a failed wait;
@@ -253,7 +254,8 @@ class BiLoCoGemm:
         if self.residual is not None or self.fp32_out or out is not None or A_rec is not None:   # not expressible in the operator schemas
             return _ops._fused(A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32, self.z,
                                self.M, self.epoch, self.mode, C=self.residual, out=out, A_rec=A_rec,
-                               B_tiled=self.W_tiled if self.W_tiled.numel() else None, fp32_out=self.fp32_out)
+                               B_tiled=self.W_tiled if self.W_tiled.numel() else None, fp32_out=self.fp32_out,
+                               push=self.peer_push if self.fp32_out else None)
         a = (A_pad, self.W_fp4, A_sf, self.W_sf, self.alpha, X_bf16, self.V, self.S, self.U_col32)
         if self.mode == 2:
             return ops.biloco_gemm_mode2(*a, self.z, self.none, self.none, self.W_tiled, self.none, self.M, self.epoch)

@@ -58,7 +58,7 @@ def _check_fp4_operands(A, B, A_sf, B_sf, alpha, n_alpha=1):
 
 
 def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mode, C=None, out=None, B_tiled=None, fp32_out=False,
-           A_rec=None, group_rows=None):
+           A_rec=None, group_rows=None, push=None):
     """One launch of the fused linear. group_rows (list of ints) makes it a stacked launch of several linears that read
     the same activation: V and S hold the groups' ranks one after another, U_col32 each column's own group's words, alpha
     one scale per group (see biloco_b200_fused_linear_grouped)."""
@@ -97,7 +97,11 @@ def _fused(A, B, A_sf, B_sf, alpha, X, V, S, U_col32, scratch, m_rows, epoch, mo
             S.data_ptr() if R else None, C.data_ptr() if C is not None else None, D.data_ptr(),
             scratch.data_ptr(), scratch.numel() * scratch.element_size())
     with torch.cuda.device(A.device):
-        if group_rows is None:
+        if push is not None:      # (table of the peers' receive buffers, status words, world, rank, slot elements): see parallel.PeerAllReduce
+            _req(group_rows is None and fp32_out, "the epilogue push exists for single fp32-output launches")
+            rc = _lib.load().biloco_b200_fused_linear_push(*ptrs, m_rows, rows, N, K, R, mode, epoch, push[0], push[1], push[2], push[3],
+                                                           push[4], _stream())
+        elif group_rows is None:
             rc = _lib.load().biloco_b200_fused_linear_rec(*ptrs, m_rows, rows, N, K, R, mode, epoch, _stream())
         else:
             import ctypes

@@ -118,8 +118,14 @@ class PeerAllReduce:
             torch.cuda.synchronize(self.device)
         dist.barrier(group=group)          # every rank has mapped every buffer before anybody stores into one
 
-    def __call__(self, partial, residual=None, out=None, fp32_out=False):
-        """partial fp32 (contiguous, <= slot_elems elements) -> the sum over the ranks (+ residual bf16), bf16 or fp32, same shape."""
+    def push_args(self):
+        """What BiLoCoGemm.peer_push takes: the fused launch's epilogue then stores its outputs into the peers' buffers itself
+        (biloco_b200_fused_linear_push) and the call below only gathers (pushed=True)."""
+        return (self.table.data_ptr(), self.status.data_ptr(), self.world, self.rank, self.slot_elems)
+
+    def __call__(self, partial, residual=None, out=None, fp32_out=False, pushed=False):
+        """partial fp32 (contiguous, <= slot_elems elements) -> the sum over the ranks (+ residual bf16), bf16 or fp32, same shape.
+        pushed: the launch that produced `partial` has already stored it into the peers' buffers (push_args)."""
         from . import _lib
         assert partial.is_cuda and partial.dtype == torch.float32 and partial.is_contiguous() and partial.numel() <= self.slot_elems
         assert residual is None or (residual.dtype == torch.bfloat16 and residual.is_contiguous() and residual.numel() == partial.numel())
@@ -128,7 +134,7 @@ class PeerAllReduce:
         with torch.cuda.device(self.device):
             rc = _lib.load().biloco_b200_peer_allreduce(
                 partial.data_ptr(), residual.data_ptr() if residual is not None else None, out.data_ptr(), self.table.data_ptr(),
-                self.status.data_ptr(), self.world, self.rank, partial.numel(), self.slot_elems, 0x400 if fp32_out else 0,
+                self.status.data_ptr(), self.world, self.rank, partial.numel(), self.slot_elems, (0x400 if fp32_out else 0) | (1 if pushed else 0),
                 torch.cuda.current_stream().cuda_stream)
         _lib.check(rc, "peer_allreduce")
         return out
@@ -167,6 +173,7 @@ class ShardedBiLoCoLinear:
     """
 
     peer_allreduce = True      # row shards on CUDA under NCCL: the library's own one-launch all-reduce instead of ncclAllReduce + cast
+    epilogue_push = True       # ... with the transfer started by the fused launch's own epilogue (biloco_b200_fused_linear_push)
 
     def __init__(self, ops: dict, kind: str, M: int, group=None, presharded: bool = False, local_scale: bool = False):
         """ops: the operands of the whole layer (sharded here), or with presharded=True this rank's shard as it is.
@@ -211,12 +218,18 @@ class ShardedBiLoCoLinear:
             self.gemm.residual = residual if rank == 0 else None
         elif o.get("bias") is None:
             self.gemm.residual = None
+        red = None
+        if (self.kind == "row" and self.peer_allreduce and x.is_cuda and dist.is_initialized() and dist.get_world_size(self.group) > 1
+                and dist.get_backend(self.group) == "nccl"):
+            red = PeerAllReduce.for_group(self.group, x.device, self.M * self.N)
+            # the fused launch's epilogue stores its outputs to the peers itself (tile kernels; the gather follows below)
+            self.gemm.peer_push = red.push_args() if (self.epilogue_push and self.gemm.mode != 7) else None
         y = self.gemm(q["A"], q["A_sf"], q["X"], A_rec=q.get("A_rec")).view(-1, self.N)[: self.M]
         if self.kind == "row":
             y = y.contiguous()
             if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-                if self.peer_allreduce and y.is_cuda and dist.get_backend(self.group) == "nccl":
-                    return PeerAllReduce.for_group(self.group, y.device, y.numel())(y)      # fp32 partials in, bf16 sum out
+                if red is not None:
+                    return red(y, pushed=self.gemm.peer_push is not None)      # fp32 partials in, bf16 sum out
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)      # fp32 [M, N] over NVLink
             y = y.to(torch.bfloat16)
         return y

@@ -141,6 +141,7 @@ int biloco_b200_swiglu_act_quant(const void* GU_bf16, const void* smooth_bf16, v
  * out: bf16 (or fp32 with BILOCO_OUT_FP32 in flags); residual_bf16 may be NULL. status: int32 [16] on the device, zeroed
  * once before the first call and then left alone (word 8 is the call counter); word 0 becomes 1 when a poll ran out of
  * its time budget (BILOCO_OPT_WAIT_BUDGET_US; the call's output is then undefined). No counterpart in the reference. */
+#define BILOCO_AR_PUSHED 0x1          /* flags of biloco_b200_peer_allreduce: the partial's producer has pushed it already */
 size_t biloco_b200_peer_buffer_bytes(int world, int slot_elems);
 int biloco_b200_peer_buffer_create(size_t bytes, void** ptr, void* handle64);
 int biloco_b200_peer_buffer_open(const void* handle64, void** ptr);
@@ -148,6 +149,19 @@ int biloco_b200_peer_buffer_close(void* ptr);
 int biloco_b200_peer_buffer_destroy(void* ptr);
 int biloco_b200_peer_allreduce(const float* partial, const void* residual_bf16, void* out, void* const* recv_ptrs_dev, int* status,
                                int world, int rank, int count, int slot_elems, int flags, biloco_stream_t stream);
+
+/* biloco_b200_fused_linear_rec whose epilogue also PUSHES its fp32 outputs to the peers of a row-parallel group (schedules
+ * 2 / 4 / 5 with BILOCO_OUT_FP32 in `mode`): the thread that stores Y[m, n] also stores {value, call number} into this rank's
+ * slot of every peer's receive buffer (recv_ptrs_dev, ar_status, world, rank, slot_elems as for
+ * biloco_b200_peer_allreduce; M * N <= slot_elems), so the transfer over NVLink starts tile by tile with the epilogue
+ * instead of with a later launch. The all-reduce is completed by biloco_b200_peer_allreduce(..., flags | BILOCO_AR_PUSHED),
+ * issued next on the same stream with the same partial (Y) — it only gathers. No counterpart in the reference. */
+int biloco_b200_fused_linear_push(const void* W_codes, const void* W_sf, const void* W_tiled, const float* alpha,
+                                  const void* A_codes, const void* A_sf, const void* A_rec, const void* X_bf16,
+                                  const void* V_packed, const int32_t* U_col32, const void* S_bf16, const void* C_bf16,
+                                  void* Y_f32, void* scratch, size_t scratch_bytes, int M, int A_rows, int N, int K, int R,
+                                  int mode, int epoch, void* const* recv_ptrs_dev, const int* ar_status, int world, int rank,
+                                  int slot_elems, biloco_stream_t stream);
 
 /* Greedy sign peeling on the GPU:  W ~ sum_i S[i] u_i v_i^T + R  with u_i, v_i in {+-1}  (the decomposition that yields
  * the packed low-rank operands). R: fp32 [m][n] on the device, holds W on entry and the residual on return (updated in

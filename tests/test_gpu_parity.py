@@ -540,3 +540,46 @@ def test_fused_with_tensor_core_z_launch(kernel, lib, M, K, N, R, mode):
     finally:
         lib.biloco_b200_set_option(_lib.OPT_ZTC, -1)
     assert float((outs[1] - outs[0]).abs().max()) <= 2.0 ** -7 * float(outs[0].abs().max())      # (bf16 outputs: at most an ulp apart)
+
+
+@pytest.mark.parametrize("M,mode", [(1, 5), (1, 2), (8, 5), (32, 2)])
+def test_fused_epilogue_pushes_outputs_to_peer_buffers(kernel, lib, M, mode):
+    """Row-parallel use on one GPU: a 'group' of two whose second receive buffer is a local allocation. The fused launch's
+    epilogue (biloco_b200_fused_linear_push) must leave {fp32 output bits, call number 1} for every output element in this
+    rank's slot of the peer's buffer (set 1 of the two), and the output itself unchanged."""
+    import ctypes
+    K, N, R = (5120, 5120, 128) if mode == 5 else (2048, 1024, 128)      # (the cluster schedule needs enough tiles)
+    if mode not in kernel.supported_modes(M, N, K, R):
+        pytest.skip("schedule not available for this shape")
+    p = orc.random_problem(M, K, N, R, scales="random", seed=77 + M)
+    t = dev_problem(p)
+    world, slot = 2, M * N
+    nbytes = lib.biloco_b200_peer_buffer_bytes(world, slot)
+    bufs = []
+    for _ in range(2):
+        ptr, h = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+        assert lib.biloco_b200_peer_buffer_create(nbytes, ctypes.byref(ptr), h) == 0
+        bufs.append(ptr.value)
+    table = torch.tensor(bufs, dtype=torch.int64, device="cuda")
+    status = torch.zeros(16, dtype=torch.int32, device="cuda")
+    g = kernel.BiLoCoGemm(t["W"], t["W_sf"], t["alpha"], t["V_packed"], t["U_packed"], t["S"], M=M, mode=mode)
+    g.fp32_out = True
+    y_plain = g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].clone()
+    g.peer_push = (table.data_ptr(), status.data_ptr(), world, 0, slot)
+    y_push = g(t["A_pad"], t["A_sf"], t["X"]).view(-1, N)[:M].clone()
+    torch.cuda.synchronize()
+    assert g.status()[0] == 0
+    assert torch.equal(y_plain, y_push)
+    # peer buffer: [2 sets][world][slot] words of (value bits, call number); call 1 uses set 1, this rank is sender 0
+    words = torch.empty(2 * world * slot, 2, dtype=torch.int32, device="cuda")
+    assert lib.biloco_b200_peer_buffer_bytes(world, slot) == words.numel() * 4
+    # (the buffer is a raw allocation of the library: copy it into a tensor with the CUDA runtime that torch has loaded)
+    rt = ctypes.CDLL("libcudart.so.12")
+    assert rt.cudaMemcpy(ctypes.c_void_p(words.data_ptr()), ctypes.c_void_p(bufs[1]), ctypes.c_size_t(words.numel() * 4), 3) == 0    # device to device
+    torch.cuda.synchronize()
+    mine = words.view(2, world, slot, 2)[1, 0]
+    assert torch.equal(mine[:, 0].contiguous().view(torch.float32), y_push.reshape(-1)), "pushed values differ from the outputs"
+    assert bool((mine[:, 1] == 1).all()), "call number missing"
+    assert not words.view(2, world, slot, 2)[0].any() and not words.view(2, world, slot, 2)[1, 1].any()
+    for b in bufs:
+        assert lib.biloco_b200_peer_buffer_destroy(b) == 0
