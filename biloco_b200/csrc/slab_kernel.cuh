@@ -434,14 +434,18 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
     };
 
     // This CTA's share of 2^20 for the scratch's launch count (the shares of a launch add up to exactly 2^20 whatever the
-    // grid size). Added by the thread that has just read the count, not at the exit: bits 20.. change only when the LAST CTA
-    // has added, which is after every CTA has read, and a fire-and-forget add issued at the exit would be one more
-    // memory operation the grid's completion has to wait for.
+    // grid size; bits 20.. change only when the LAST CTA has added, which is after every CTA has read, so the add may come
+    // any time after this CTA's read). Added on the exit path; timing switch p.dbg & 4: by the thread that has just read
+    // the count instead (measured: no difference, 8.87 / 8.88 us per call). The switch is kept because the build WITHOUT
+    // it, early add only, ran at 10.2 us per call: with every instruction of this kernel executed once per launch, its
+    // speed depends on how the code happens to be laid out (no_instruction is among its largest stalls).
     auto count_launch = [&]() {
         const uint32_t share = (uint32_t)((((unsigned long long)(cta + 1)) << 20) / (unsigned)p.G) -
                                (uint32_t)((((unsigned long long)cta) << 20) / (unsigned)p.G);
         red_add_u32(p.z_counter + 8 + (cta & 7), share);
     };
+
+    const bool early_count = (p.dbg & 4) != 0;
 
     const bool has_rows = cta < p.Grows;
     if (!has_rows && (warp >= FIRST_SF_WARP && warp < FIRST_Z_WARP || warp >= MMA_WARP)) {
@@ -770,7 +774,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             if (lt == LR_THREADS - 1) {      // the launch number of this scratch (one reader per CTA: a hot line)
                 const uint4 c0 = ld_volatile_v4(p.z_counter + 8), c1 = ld_volatile_v4(p.z_counter + 12);
                 ctrl->seq = (((c0.x + c0.y) + (c0.z + c0.w)) + ((c1.x + c1.y) + (c1.z + c1.w))) >> 20;
-                    count_launch();
+                    if (early_count) count_launch();
             }
 #pragma unroll 1
             for (int row = 0; row < p.M; ++row) {
@@ -932,7 +936,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 if (lt == 0) {      // (behind this thread's own requests, so that it does not wait twice)
                     const uint4 c0 = ld_volatile_v4(p.z_counter + 8), c1 = ld_volatile_v4(p.z_counter + 12);
                     ctrl->seq = (((c0.x + c0.y) + (c0.z + c0.w)) + ((c1.x + c1.y) + (c1.z + c1.w))) >> 20;
-                    count_launch();
+                    if (early_count) count_launch();
                 }
                 if (lane + 96 < nch) {
                     int c = lane + 96 + rot;
@@ -946,7 +950,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             if (lt == 0 && !raw && !(single && nr > 0)) {
                 const uint4 c0 = ld_volatile_v4(p.z_counter + 8), c1 = ld_volatile_v4(p.z_counter + 12);
                 ctrl->seq = (((c0.x + c0.y) + (c0.z + c0.w)) + ((c1.x + c1.y) + (c1.z + c1.w))) >> 20;
-                    count_launch();
+                    if (early_count) count_launch();
             }
             if (lt == 0 && stamps) { stamps[3] = globaltimer_ns(); stamps[19] = (unsigned long long)clock64(); }
 #pragma unroll 1
@@ -1138,6 +1142,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         __syncthreads();
     }
     if (tid == 0) {
+        if ((p.R > 0 || RAW) && !early_count) count_launch();
         if (stamps) { stamps[9] = globaltimer_ns(); stamps[25] = (unsigned long long)clock64(); }
     }
     if (warp == MMA_WARP && has_rows) {
