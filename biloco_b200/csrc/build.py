@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 LIB = os.path.join(PKG, "libbiloco_b200.so")
 SOURCES = ["api.cu", "lowrank_ref.cu", "act_quant.cu", "decode_attn.cu", "fp4_gemm_simt.cu", "peel.cu", "peer_reduce.cu", "fused_linear.cu"]
-HEADERS = ["ptx.cuh", "schedule.h", "fused_cfg.cuh", "fused_lowrank.cuh", "fused_kernel.cuh", "ztc_kernel.cuh", "slab_kernel.cuh", "slab_host.cuh", "quant_math.cuh", os.path.join("..", "..", "include", "biloco_b200.h")]
+HEADERS = ["ptx.cuh", "schedule.h", "fused_cfg.cuh", "fused_lowrank.cuh", "fused_kernel.cuh", "ztc_kernel.cuh", "slab_kernel.cuh", "slab_plain_kernel.cuh", "slab_host.cuh", "quant_math.cuh", os.path.join("..", "..", "include", "biloco_b200.h")]
 
 
 def _nvcc():

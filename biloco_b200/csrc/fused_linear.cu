@@ -491,56 +491,60 @@ static int slab_launch(const void* W_slab, const float* alpha, const void* A_cod
     if (!W_slab) return BILOCO_ERR_NULL;
     if ((uintptr_t)W_slab & 15) return BILOCO_ERR_ALIGN;
     uint8_t* sc = (uint8_t*)scratch;
-    slab::SlabParams q;
-    q.W_slab = (const uint8_t*)W_slab;
-    q.A_codes = (const uint8_t*)A_codes;
-    q.A_sf = (const uint8_t*)A_sf;
-    q.alpha = alpha;
-    q.X = (const __nv_bfloat16*)X_bf16;
-    q.Vp = (const uint8_t*)V_packed;
-    q.Ucol = U_col32;
-    q.S = (const __nv_bfloat16*)S_bf16;
-    q.C = (const __nv_bfloat16*)C_bf16;
-    q.Y = Y;
-    q.status = (int32_t*)sc;
-    q.z_counter = (uint32_t*)(sc + L.off_zcnt);
-    q.zbuf = (float*)(sc + L.off_z);
-    q.M = M; q.N = N; q.K = K; q.R = R; q.Rw = L.Rw; q.Rpad = L.Rpad;
-    q.Rt = g.Rt; q.kg = g.kg; q.nkt = g.nkt; q.nsu = g.nsu; q.G = g.grid; q.Grows = g.G;
-    q.nsl = g.nsl;
-    q.ring = g_ring > 0 && g_ring < g.ring ? g_ring : g.ring;
-    q.stage_bytes = g.stage_bytes;
-    // (a shorter ring keeps the offsets computed for the full one: the stages simply stay unused)
-    q.nbp = g.nbp; q.atile_bytes = g.atile_bytes;
-    q.off_ring = g.off_ring; q.off_ctrl = g.off_ctrl; q.off_us = g.off_us; q.off_work = g.off_work; q.off_accp = g.off_accp;
-    q.xs_off = g.xs_off; q.off_asf = g.off_asf;
-    q.epoch = (uint32_t)epoch;
-    q.mode = mode;
-    q.wait_ns = g_wait_ns;
-    q.skip_publish_cta = g_skip_publish;
-    q.trigger = g_trigger >= 0 ? g_trigger : 1;      // (measured: 8.3 us per call at K = N = 5120 against 8.4 with 0)
-    q.inflight = g_inflight;
-    q.lut = g.lut;
-    q.dbg = g_dbg;
-    q.stamps = nullptr;
-    q.act_rec = (unsigned long long*)(sc + L.off_arec);
-    q.Xraw = nullptr; q.norm_w = nullptr; q.smooth = nullptr; q.w_gscale = nullptr; q.act_out = nullptr;
-    q.eps = 0.f; q.act_rule = 0; q.act_swiglu = 0;
-    if (act) {
-        q.Xraw = (const __nv_bfloat16*)act->Xraw;
-        q.norm_w = (const __nv_bfloat16*)act->norm_w;
-        q.smooth = (const __nv_bfloat16*)act->smooth;
-        q.w_gscale = act->w_gscale;
-        q.act_out = act->act_out;
-        q.eps = act->eps; q.act_rule = act->rule; q.act_swiglu = act->swiglu;
-    }
-    if (g_stamps && g_stamps_bytes >= (size_t)g.grid * slab::SLAB_STAMPS * 8) {
-        const size_t per = (size_t)g.grid * slab::SLAB_STAMPS, slots = g_stamps_bytes / (per * 8);
-        q.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
-    }
+    // the fields both forms of the kernel share (two parameter structs: see slab_plain_kernel.cuh)
+    auto fill = [&](auto& q, int stamp_words) {
+        q.W_slab = (const uint8_t*)W_slab;
+        q.A_codes = (const uint8_t*)A_codes;
+        q.A_sf = (const uint8_t*)A_sf;
+        q.alpha = alpha;
+        q.X = (const __nv_bfloat16*)X_bf16;
+        q.Vp = (const uint8_t*)V_packed;
+        q.Ucol = U_col32;
+        q.S = (const __nv_bfloat16*)S_bf16;
+        q.C = (const __nv_bfloat16*)C_bf16;
+        q.Y = Y;
+        q.status = (int32_t*)sc;
+        q.z_counter = (uint32_t*)(sc + L.off_zcnt);
+        q.zbuf = (float*)(sc + L.off_z);
+        q.M = M; q.N = N; q.K = K; q.R = R; q.Rw = L.Rw; q.Rpad = L.Rpad;
+        q.Rt = g.Rt; q.kg = g.kg; q.nkt = g.nkt; q.nsu = g.nsu; q.G = g.grid; q.Grows = g.G;
+        q.nsl = g.nsl;
+        q.ring = g_ring > 0 && g_ring < g.ring ? g_ring : g.ring;
+        q.stage_bytes = g.stage_bytes;
+        // (a shorter ring keeps the offsets computed for the full one: the stages simply stay unused)
+        q.nbp = g.nbp; q.atile_bytes = g.atile_bytes;
+        q.off_ring = g.off_ring; q.off_ctrl = g.off_ctrl; q.off_us = g.off_us; q.off_work = g.off_work; q.off_accp = g.off_accp;
+        q.xs_off = g.xs_off; q.off_asf = g.off_asf;
+        q.epoch = (uint32_t)epoch;
+        q.mode = mode;
+        q.wait_ns = g_wait_ns;
+        q.skip_publish_cta = g_skip_publish;
+        q.trigger = g_trigger >= 0 ? g_trigger : 1;      // (measured: 8.3 us per call at K = N = 5120 against 8.4 with 0)
+        q.inflight = g_inflight;
+        q.lut = g.lut;
+        q.dbg = g_dbg;
+        q.stamps = nullptr;
+        if (g_stamps && g_stamps_bytes >= (size_t)g.grid * stamp_words * 8) {
+            const size_t per = (size_t)g.grid * stamp_words, slots = g_stamps_bytes / (per * 8);
+            q.stamps = g_stamps + (g_stamps_seq++ % slots) * per;
+        }
+    };
     const bool pdl = g_use_pdl != 0 && !consume_relayout_mark(stream);
-    if (act) return M <= 1 ? slab::slab_launch_rows<1, true>(q, g, pdl, stream) : slab::slab_launch_rows<2, true>(q, g, pdl, stream);
-    return M <= 1 ? slab::slab_launch_rows<1, false>(q, g, pdl, stream) : slab::slab_launch_rows<2, false>(q, g, pdl, stream);
+    if (!act) {
+        slabp::SlabParams q;
+        fill(q, slabp::SLAB_STAMPS);
+        return M <= 1 ? slab::slabp_launch_rows<1>(q, g, pdl, stream) : slab::slabp_launch_rows<2>(q, g, pdl, stream);
+    }
+    slab::SlabParams q;
+    fill(q, slab::SLAB_STAMPS);
+    q.act_rec = (unsigned long long*)(sc + L.off_arec);
+    q.Xraw = (const __nv_bfloat16*)act->Xraw;
+    q.norm_w = (const __nv_bfloat16*)act->norm_w;
+    q.smooth = (const __nv_bfloat16*)act->smooth;
+    q.w_gscale = act->w_gscale;
+    q.act_out = act->act_out;
+    q.eps = act->eps; q.act_rule = act->rule; q.act_swiglu = act->swiglu;
+    return M <= 1 ? slab::slab_launch_rows<1, true>(q, g, pdl, stream) : slab::slab_launch_rows<2, true>(q, g, pdl, stream);
 }
 
 // Row-parallel use: where the epilogue pushes its fp32 outputs (peer_reduce.cu's receive buffers).

@@ -2,6 +2,7 @@
 // Included by fused_linear.cu (one translation unit: the launch options are shared).
 #pragma once
 #include "slab_kernel.cuh"
+#include "slab_plain_kernel.cuh"
 
 namespace biloco {
 namespace slab {
@@ -140,6 +141,35 @@ static int slab_launch_rows(const SlabParams& p, const Geo& g, bool pdl, cudaStr
     cfg.attrs = attr;
     cfg.numAttrs = na;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, slab_kernel<ROWS, RAW>, p);
+    return e == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
+}
+
+// The same for the plain form (slab_plain_kernel.cuh: activations quantised by the caller).
+template <int ROWS>
+static int slabp_launch_rows(const slabp::SlabParams& p, const Geo& g, bool pdl, cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(slabp::slab_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET) != cudaSuccess)
+            return BILOCO_ERR_CUDA;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)g.grid);
+    cfg.blockDim = dim3(slabp::NT);
+    cfg.dynamicSmemBytes = (size_t)g.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, slabp::slab_kernel<ROWS>, p);
     return e == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
