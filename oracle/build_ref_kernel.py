@@ -47,7 +47,8 @@ def run(cmd, **kw):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("BILOCO_REFERENCE", "/root/reference"),
+                    help="checkout of the reference (or set BILOCO_REFERENCE)")
     ap.add_argument("--work", default=None, help="scratch directory (default: a fresh temporary one)")
     a = ap.parse_args()
     ref = os.path.abspath(a.reference)
