@@ -64,36 +64,47 @@ __global__ void __launch_bounds__(AR_THREADS) peer_allreduce_kernel(ArArgs a) {
             asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(bits), "r"(seq) : "memory");
         }
     }
-    // gather, in rank order
+    // gather: the peers' words of an element are requested together (one local round trip per attempt, not one per peer),
+    // re-requested only where the flag is not there yet, and added in rank order once all have arrived
     const uint2* mine = a.recv[a.rank] + set_off;
     bool ok = true;
     for (int i = blockIdx.x * AR_THREADS + threadIdx.x; i < a.count && ok; i += stride) {
-        float sum = 0.f;
-        for (int p = 0; p < a.world && ok; ++p) {
-            float x;
-            if (p == a.rank) {
-                x = a.partial[i];
-            } else {
-                const uint2* src = mine + (size_t)p * a.slot_elems + i;
-                uint32_t v, f;
-                uint64_t t0 = 0;
-                for (uint32_t it = 0;; ++it) {
-                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(f) : "l"(src) : "memory");
-                    if (f == seq) break;
-                    if ((it & 63u) == 63u) {
-                        const uint64_t now = biloco::globaltimer_ns();
-                        if (t0 == 0) t0 = now;
-                        else if (now - t0 > a.wait_ns) { ok = false; break; }
-                    }
+        uint32_t val[AR_MAX_WORLD];
+        uint32_t need = 0u;
+#pragma unroll
+        for (int q = 0; q < AR_MAX_WORLD; ++q) {
+            val[q] = 0u;
+            if (q < a.world && q != a.rank) need |= 1u << q;
+        }
+        uint64_t t0 = 0;
+        for (uint32_t it = 0; need; ++it) {
+            uint32_t f[AR_MAX_WORLD];
+#pragma unroll
+            for (int q = 0; q < AR_MAX_WORLD; ++q) {
+                f[q] = 0u;
+                if (need & (1u << q)) {
+                    const uint2* src = mine + (size_t)q * a.slot_elems + i;
+                    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(val[q]), "=r"(f[q]) : "l"(src) : "memory");
                 }
-                x = __uint_as_float(v);
             }
-            sum = __fadd_rn(sum, x);
+#pragma unroll
+            for (int q = 0; q < AR_MAX_WORLD; ++q)
+                if ((need & (1u << q)) && f[q] == seq) need &= ~(1u << q);
+            if (need && (it & 63u) == 63u) {
+                const uint64_t now = biloco::globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > a.wait_ns) { ok = false; break; }
+            }
         }
         if (!ok) {
             if (atomicCAS(a.status, 0, 1) == 0) { a.status[1] = i; a.status[2] = (int)seq; a.status[3] = a.rank; }
             break;
         }
+        float sum = 0.f;
+        const float own = a.partial[i];
+#pragma unroll
+        for (int q = 0; q < AR_MAX_WORLD; ++q)
+            if (q < a.world) sum = __fadd_rn(sum, q == a.rank ? own : __uint_as_float(val[q]));
         if (a.residual) sum = __fadd_rn(sum, __bfloat162float(a.residual[i]));
         if (a.out_f32) reinterpret_cast<float*>(a.out)[i] = sum;
         else reinterpret_cast<__nv_bfloat16*>(a.out)[i] = __float2bfloat16_rn(sum);

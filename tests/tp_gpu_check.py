@@ -1,4 +1,4 @@
-"""Tensor-parallel check on real GPUs (one process per GPU, NCCL). Launched by tests/test_gpu_tp.py or by hand:
+"""Tensor-parallel check on real GPUs (one process per GPU, NCCL; 2 or 4 ranks). Launched by tests/test_gpu_tp.py or by hand:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 tests/tp_gpu_check.py
 
@@ -47,7 +47,14 @@ def main():
     lo, hi = parallel.shard_bounds(N, world, rank, 128)
     y_col = col(x)
     torch.cuda.synchronize()
-    assert torch.equal(y_col.view(torch.int16), y_full[:, lo:hi].contiguous().view(torch.int16)), "column shard differs"
+    # a column's arithmetic is the same in the shard and in the whole layer except for the order in which the K-split
+    # partial sums are added (the split follows the number of column tiles): equal bits at two ranks, where both split alike,
+    # and within a bf16 ulp of the largest output otherwise
+    ref_col = y_full[:, lo:hi].contiguous()
+    if world == 2:
+        assert torch.equal(y_col.view(torch.int16), ref_col.view(torch.int16)), "column shard differs"
+    else:
+        assert float((y_col.float() - ref_col.float()).abs().max()) <= 2.0 ** -7 * float(ref_col.float().abs().max()), "column shard differs"
 
     row = parallel.ShardedBiLoCoLinear(ops, "row", M)
     klo, khi = parallel.shard_bounds(K, world, rank, 256)
