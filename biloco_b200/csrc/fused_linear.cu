@@ -533,7 +533,8 @@ static int slab_launch(const void* W_slab, const float* alpha, const void* A_cod
     if (!act) {
         slabp::SlabParams q;
         fill(q, slabp::SLAB_STAMPS);
-        return M <= 1 ? slab::slabp_launch_rows<1>(q, g, pdl, stream) : slab::slabp_launch_rows<2>(q, g, pdl, stream);
+        return M <= 1 ? slab::slabp_launch_rows<1>(q, g, pdl, stream)
+                      : (M == 2 ? slab::slabp_launch_rows<2>(q, g, pdl, stream) : slab::slabp_launch_rows<4>(q, g, pdl, stream));
     }
     slab::SlabParams q;
     fill(q, slab::SLAB_STAMPS);

@@ -12,12 +12,12 @@ struct Geo {
     int grid;                       // CTAs launched: one per SM, the ones beyond G only take part in the z stage
     int nbp;                        // MMA N: kg * Rt rounded up to a multiple of 16
     int nsl, nr;                    // z stage: rank slices per activation row, most ranks of a slice
-    int rows;                       // 1 or 2 (template parameter)
+    int rows;                       // 1, 2 or 4 (template parameter; three rows run as four)
     int stage_bytes, ring, atile_bytes, lut;
     int off_ring, off_ctrl, off_us, off_work, off_accp, off_asf, xs_off, smem_bytes;
 };
 
-// Weight layout: depends on N, K and the SM count only (not on M), so one re-laid copy serves M = 1 and M = 2.
+// Weight layout: depends on N, K and the SM count only (not on M), so one re-laid copy serves every M the schedule takes.
 static bool slab_layout(int N, int K, int num_sms, Geo* g) {
     if (N < 8 || (N % 8) || K < 512 || (K % 512) || num_sms < 1) return false;      // (K / 256 must be even: a thread's span is pairs)
     int rt = (N + num_sms - 1) / num_sms;
@@ -38,9 +38,11 @@ static bool slab_layout(int N, int K, int num_sms, Geo* g) {
 }
 
 static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coresident, Geo* g, bool raw = false) {
-    if (M < 1 || M > 2 || R < 0) return false;
+    // (the raw-activation form exists for one and two rows)
+    if (M < 1 || M > (raw ? 2 : 4) || R < 0) return false;
     if (!slab_layout(N, K, num_sms, g)) return false;
-    g->rows = M;
+    g->rows = M <= 2 ? M : 4;
+    if (g->kg * g->rows > 32) return false;                                        // (operand rows: one TMEM lane quadrant)
     // One CTA per SM, always: with exactly as many CTAs as SMs every SM hosts one CTA of this launch beside one of the
     // next, and none hosts two of the same launch (which would take turns on the SM's tensor memory).
     g->grid = (R > 0 && g->G < num_sms) ? num_sms : g->G;

@@ -1,4 +1,4 @@
-// Row-slab schedule of the fused linear for one or two activation rows (mode 7).
+// Row-slab schedule of the fused linear for one to four activation rows (mode 7).
 //
 // The other schedules cut the weight into 128-row x 256-k units and share a tile's k-range between CTAs, which costs a
 // partial-sum exchange per launch. At one or two rows a launch is a dependency chain, not a stream (the weights are
@@ -51,7 +51,7 @@ constexpr int SET_COL0 = 256;            // set s at 256 + 64 s: the weights' sc
                                          // n % 32 in the lanes, n / 32 along the columns), the activations' in 32..47
 constexpr int SFA_OFF = 32;
 constexpr int SLAB_TMEM_COLS = 512;      // the accumulator D[128, N <= 256] takes columns 0..255
-constexpr int KG_MAX = 8;                // k-tiles per super-unit at most (activation-operand rows kg * M <= 16)
+constexpr int KG_MAX = 8;                // k-tiles per super-unit at most (activation-operand rows kg * ROWS <= 32: one TMEM lane quadrant)
 constexpr int MAX_RING = 12;
 constexpr int NRMAX = 8;                 // ranks per pass of the z stage
 constexpr int XW_MAX = 16;               // 32-bit activation words (pairs of bf16) a thread holds per 32-element segment
@@ -108,7 +108,7 @@ struct SCtrl {
     uint64_t acc_full;
     uint64_t tmem_ready;      // TMEM is allocated (the allocation waits for the previous kernel's CTA on this SM)
     float zred[LR_WARPS][NRMAX + 1];
-    float ztp[LR_WARPS][2];
+    float ztp[LR_WARPS][4];
     uint32_t tmem_base;
     uint32_t seq;             // launches completed on this scratch before this one (read once per CTA)
     volatile int abort;
@@ -305,6 +305,37 @@ __device__ __noinline__ void expand_padd(const float* zs, float* corrp, const ui
     }
 }
 
+// The same for four rows: the predicate of a sign bit is formed once and serves the four rows' adds (six instructions per
+// bit instead of twelve). Same order of additions per row as expand_padd.
+#define BILOCO_SPADD4(acc, w, mask, x0, x1, x2, x3)                                                                  \
+    asm("{\n\t.reg .pred p;\n\t.reg .b32 t;\n\tand.b32 t, %4, %5;\n\tsetp.ne.u32 p, t, 0;\n\t"                 \
+        "@p add.f32 %0, %0, %6;\n\t@p add.f32 %1, %1, %7;\n\t@p add.f32 %2, %2, %8;\n\t@p add.f32 %3, %3, %9;\n\t}" \
+        : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])                                                     \
+        : "r"(w), "r"(mask), "f"(x0), "f"(x1), "f"(x2), "f"(x3))
+__device__ __noinline__ void expand_padd4(const float* zs, float* corrp, const uint32_t* us, int nit, int Rt, int Rw, int Rpad, int lt) {
+#pragma unroll 1
+    for (int id = lt; id < nit; id += LR_THREADS) {
+        const int w = id / Rt, col = id - w * Rt;
+        float c0[4] = {0.f, 0.f, 0.f, 0.f}, c1[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t ub = us[id];
+        const float* zw = zs + 32 * w;
+#pragma unroll 1
+        for (int b = 0; b < 32; b += 4) {
+            const float4 z0 = *reinterpret_cast<const float4*>(zw + b);
+            const float4 z1 = *reinterpret_cast<const float4*>(zw + Rpad + b);
+            const float4 z2 = *reinterpret_cast<const float4*>(zw + 2 * Rpad + b);
+            const float4 z3 = *reinterpret_cast<const float4*>(zw + 3 * Rpad + b);
+            BILOCO_SPADD4(c0, ub, 1u, z0.x, z1.x, z2.x, z3.x);
+            BILOCO_SPADD4(c1, ub, 2u, z0.y, z1.y, z2.y, z3.y);
+            BILOCO_SPADD4(c0, ub, 4u, z0.z, z1.z, z2.z, z3.z);
+            BILOCO_SPADD4(c1, ub, 8u, z0.w, z1.w, z2.w, z3.w);
+            ub >>= 4;
+        }
+#pragma unroll
+        for (int m = 0; m < 4; ++m) corrp[(m * Rw + w) * Rt + col] = c0[m] + c1[m];
+    }
+}
+
 template <int ROWS>
 __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ SlabParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -476,9 +507,11 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             // Block scales: the four bytes of (k-tile kt, 64-k chunk a, row m) sit in atom 4 kt + a of the 128x4 layout.
             uint32_t* asf_w = reinterpret_cast<uint32_t*>(sm + p.off_asf);
             const int nsf = p.nkt * ROWS * 4;
-            uint32_t sfv[2];
+            constexpr int NSFV = ROWS <= 2 ? 2 : 4;     // scale words and code chunks a thread requests in one batch
+            constexpr int NU = ROWS <= 2 ? 4 : 8;
+            uint32_t sfv[NSFV];
 #pragma unroll
-            for (int r = 0; r < 2; ++r) {
+            for (int r = 0; r < NSFV; ++r) {
                 const int i = st + 128 * r;
                 sfv[r] = 0u;
                 if (i < nsf) {
@@ -491,10 +524,10 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             const int nchunks = p.nkt * p.M * 8;
             const int kbytes = p.K >> 1;
 #pragma unroll 1
-            for (int i0 = st; i0 < nchunks; i0 += 4 * 128) {
-                uint4 v[4];
+            for (int i0 = st; i0 < nchunks; i0 += NU * 128) {
+                uint4 v[NU];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < NU; ++u) {
                     const int i = i0 + 128 * u;
                     if (i < nchunks) {
                         const int c = i & 7, rest = i >> 3;
@@ -503,7 +536,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < NU; ++u) {
                     const int i = i0 + 128 * u;
                     if (i < nchunks) {
                         const int c = i & 7, rest = i >> 3;
@@ -514,10 +547,10 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 }
             }
 #pragma unroll
-            for (int r = 0; r < 2; ++r)
+            for (int r = 0; r < NSFV; ++r)
                 if (st + 128 * r < nsf) asf_w[st + 128 * r] = sfv[r];
 #pragma unroll 1
-            for (int i = st + 256; i < nsf; i += 128) {                 // (rows longer than 16384 elements)
+            for (int i = st + 128 * NSFV; i < nsf; i += 128) {          // (rows longer than 16384 elements)
                 const int a = i & 3, m = (i >> 2) % ROWS, kt = (i >> 2) / ROWS;
                 asf_w[i] = m < p.M ? ld_cg_u32(p.A_sf + ((size_t)(m >> 7) * (p.K >> 6) + (size_t)kt * 4 + a) * 512 + (m & 31) * 16 + ((m >> 5) & 3) * 4) : 0u;
             }
@@ -700,36 +733,80 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             named_bar_sync(3, LR_THREADS);                                      // ... by every thread
             phase = (ctrl->seq & 1u) ^ 1u;                                      // (a CTA without ranks has not looked yet)
             const int vpr = p.Rpad >> 2;
-            float zt[2] = {0.f, 0.f};
+            float zt[ROWS <= 2 ? 2 : ROWS];
+#pragma unroll
+            for (int m = 0; m < (ROWS <= 2 ? 2 : ROWS); ++m) zt[m] = 0.f;
             const int nvec = has_rows ? p.M * vpr : 0;                          // (a CTA without rows has no use for z)
+            if constexpr (ROWS <= 2) {
 #pragma unroll 1
-            for (int i = lt; i < nvec && good; i += LR_THREADS) {
-                const int m = i / vpr, j = i - m * vpr;
-                const int e0 = 4 * j;
-                const float* src = p.zbuf + (size_t)m * p.Rpad + e0;
-                uint4 v;
-                uint64_t t0 = 0;
+                for (int i = lt; i < nvec && good; i += LR_THREADS) {
+                    const int m = i / vpr, j = i - m * vpr;
+                    const int e0 = 4 * j;
+                    const float* src = p.zbuf + (size_t)m * p.Rpad + e0;
+                    uint4 v;
+                    uint64_t t0 = 0;
 #pragma unroll 1
-                for (uint32_t it = 0;; ++it) {
-                    v = ld_volatile_v4(src);
-                    const uint32_t bad = (e0 + 0 < p.R ? (v.x ^ phase) : 0u) | (e0 + 1 < p.R ? (v.y ^ phase) : 0u) |
-                                         (e0 + 2 < p.R ? (v.z ^ phase) : 0u) | (e0 + 3 < p.R ? (v.w ^ phase) : 0u);
-                    if (!(bad & 1u) || (p.dbg & 2)) break;
-                    if ((it & 15u) == 15u) {
-                        if (ctrl->abort) { good = false; break; }
-                        const uint64_t now = globaltimer_ns();
-                        if (t0 == 0) t0 = now;
-                        else if (now - t0 > p.wait_ns) { sfail(ctrl, p.status, p.epoch, ST_Z, 0); good = false; break; }
+                    for (uint32_t it = 0;; ++it) {
+                        v = ld_volatile_v4(src);
+                        const uint32_t bad = (e0 + 0 < p.R ? (v.x ^ phase) : 0u) | (e0 + 1 < p.R ? (v.y ^ phase) : 0u) |
+                                             (e0 + 2 < p.R ? (v.z ^ phase) : 0u) | (e0 + 3 < p.R ? (v.w ^ phase) : 0u);
+                        if (!(bad & 1u) || (p.dbg & 2)) break;
+                        if ((it & 15u) == 15u) {
+                            if (ctrl->abort) { good = false; break; }
+                            const uint64_t now = globaltimer_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > p.wait_ns) { sfail(ctrl, p.status, p.epoch, ST_Z, 0); good = false; break; }
+                        }
                     }
+                    float4 zz;
+                    zz.x = e0 + 0 < p.R ? __uint_as_float(v.x & ~1u) : 0.f;
+                    zz.y = e0 + 1 < p.R ? __uint_as_float(v.y & ~1u) : 0.f;
+                    zz.z = e0 + 2 < p.R ? __uint_as_float(v.z & ~1u) : 0.f;
+                    zz.w = e0 + 3 < p.R ? __uint_as_float(v.w & ~1u) : 0.f;
+                    *reinterpret_cast<float4*>(zs + (size_t)m * p.Rpad + e0) = zz;
+                    const float t = (zz.x + zz.y) + (zz.z + zz.w);
+                    if (m == 0) zt[0] += t; else zt[1] += t;
                 }
-                float4 zz;
-                zz.x = e0 + 0 < p.R ? __uint_as_float(v.x & ~1u) : 0.f;
-                zz.y = e0 + 1 < p.R ? __uint_as_float(v.y & ~1u) : 0.f;
-                zz.z = e0 + 2 < p.R ? __uint_as_float(v.z & ~1u) : 0.f;
-                zz.w = e0 + 3 < p.R ? __uint_as_float(v.w & ~1u) : 0.f;
-                *reinterpret_cast<float4*>(zs + (size_t)m * p.Rpad + e0) = zz;
-                const float t = (zz.x + zz.y) + (zz.z + zz.w);
-                if (m == 0) zt[0] += t; else zt[1] += t;
+            } else {
+                // More rows: a thread has several vectors; two are requested before either is examined (one round trip for
+                // both), and a vector is asked for again only while its marks are not this launch's.
+                auto settle = [&](int i, uint4 v) {
+                    const int m = i / vpr, j = i - m * vpr;
+                    const int e0 = 4 * j;
+                    const float* src = p.zbuf + (size_t)m * p.Rpad + e0;
+                    uint64_t t0 = 0;
+#pragma unroll 1
+                    for (uint32_t it = 0;; ++it) {
+                        const uint32_t bad = (e0 + 0 < p.R ? (v.x ^ phase) : 0u) | (e0 + 1 < p.R ? (v.y ^ phase) : 0u) |
+                                             (e0 + 2 < p.R ? (v.z ^ phase) : 0u) | (e0 + 3 < p.R ? (v.w ^ phase) : 0u);
+                        if (!(bad & 1u) || (p.dbg & 2)) break;
+                        if ((it & 15u) == 15u) {
+                            if (ctrl->abort) { good = false; break; }
+                            const uint64_t now = globaltimer_ns();
+                            if (t0 == 0) t0 = now;
+                            else if (now - t0 > p.wait_ns) { sfail(ctrl, p.status, p.epoch, ST_Z, 0); good = false; break; }
+                        }
+                        v = ld_volatile_v4(src);
+                    }
+                    float4 zz;
+                    zz.x = e0 + 0 < p.R ? __uint_as_float(v.x & ~1u) : 0.f;
+                    zz.y = e0 + 1 < p.R ? __uint_as_float(v.y & ~1u) : 0.f;
+                    zz.z = e0 + 2 < p.R ? __uint_as_float(v.z & ~1u) : 0.f;
+                    zz.w = e0 + 3 < p.R ? __uint_as_float(v.w & ~1u) : 0.f;
+                    *reinterpret_cast<float4*>(zs + (size_t)m * p.Rpad + e0) = zz;
+                    const float t = (zz.x + zz.y) + (zz.z + zz.w);
+#pragma unroll
+                    for (int mm = 0; mm < ROWS; ++mm) zt[mm] += mm == m ? t : 0.f;
+                };
+#pragma unroll 1
+                for (int i = lt; i < nvec && good; i += 2 * LR_THREADS) {
+                    const int i2 = i + LR_THREADS;
+                    const uint4 va = ld_volatile_v4(p.zbuf + (size_t)(i / vpr) * p.Rpad + 4 * (i % vpr));
+                    uint4 vb = make_uint4(0u, 0u, 0u, 0u);
+                    if (i2 < nvec) vb = ld_volatile_v4(p.zbuf + (size_t)(i2 / vpr) * p.Rpad + 4 * (i2 % vpr));
+                    settle(i, va);
+                    if (i2 < nvec && good) settle(i2, vb);
+                }
             }
 #pragma unroll
             for (int m = 0; m < ROWS; ++m) {
@@ -779,8 +856,10 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                         corrp[(m * p.Rw + w) * Rt + col] = c0 + c1;
                     }
                 }
-            } else {
+            } else if constexpr (ROWS <= 2) {
                 expand_padd<ROWS>(zs, corrp, us, nit, Rt, p.Rw, p.Rpad, lt);
+            } else {
+                expand_padd4(zs, corrp, us, nit, Rt, p.Rw, p.Rpad, lt);
             }
             if (lt == 0 && stamps) { stamps[6] = globaltimer_ns(); stamps[22] = (unsigned long long)clock64(); }
         }

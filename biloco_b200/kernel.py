@@ -139,7 +139,7 @@ def modes_for(M: int, rank: int, K: int = 5120):
     host-side checks (K must be a multiple of 256, N of 8)."""
     if not (1 <= M <= 32) or rank < 1 or K % 256 != 0:
         return []
-    return [m for m in IMPLEMENTED_MODES if (m != 5 or M <= 8) and (m != 7 or (M <= 2 and K % 512 == 0))]
+    return [m for m in IMPLEMENTED_MODES if (m != 5 or M <= 8) and (m != 7 or (M <= 4 and K % 512 == 0))]
 
 
 def supported_modes(M: int, N: int, K: int, rank: int, num_sms: int = 0):

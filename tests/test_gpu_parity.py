@@ -281,7 +281,8 @@ def _run_fused(kernel, p, M, N, launches=5):
 
 
 @pytest.mark.parametrize("M,N,K,R", [(1, 128, 256, 32), (1, 256, 512, 16), (2, 384, 1024, 40), (8, 1024, 2560, 128),
-                                     (32, 640, 768, 64), (16, 136, 256, 256)])
+                                     (32, 640, 768, 64), (16, 136, 256, 256), (4, 384, 1024, 40), (3, 1024, 2560, 200),
+                                     (4, 2560, 1536, 128), (3, 136, 512, 8)])
 def test_fused_small_shapes_random_scales(kernel, M, N, K, R):
     _run_fused(kernel, orc.random_problem(M, K, N, R, scales="random", seed=M * 7 + R), M, N)
 
@@ -294,7 +295,7 @@ def test_fused_reference_protocol(kernel, M, r):
     _run_fused(kernel, orc.random_problem(M, 5120, 5120, r), M, 5120)
 
 
-@pytest.mark.parametrize("M,r", [(1, 512), (8, 128), (32, 512)])
+@pytest.mark.parametrize("M,r", [(1, 512), (8, 128), (32, 512), (4, 512), (3, 512)])
 def test_fused_full_size_random_scales(kernel, M, r):
     _run_fused(kernel, orc.random_problem(M, 5120, 5120, r, scales="random", seed=1000 * M + r), M, 5120, launches=2)
 

@@ -35,10 +35,13 @@ def test_sf_bytes_and_mode_table(golden):
             assert kernel.DEFAULT_MODE[M][int(r)] in kernel.supported_modes(M, 5120, 5120, int(r), num_sms=148)
     assert kernel.modes_for(64, 512) == [] and kernel.modes_for(1, 512, K=5000) == []
     # mode 5 (cluster per tile) needs few enough tiles for >= 2 CTAs each and at most 8 rows
-    # mode 7 (row slabs) takes one or two rows, K a multiple of 512 and at most 128 weight rows per SM
+    # mode 7 (row slabs) takes one to four rows, K a multiple of 512 and at most 128 weight rows per SM
     assert kernel.supported_modes(1, 5120, 5120, 512, num_sms=148) == [2, 4, 5, 7]
     assert kernel.supported_modes(2, 5120, 5120, 1024, num_sms=148) == [2, 4, 5, 7]
-    assert kernel.supported_modes(4, 5120, 5120, 512, num_sms=148) == [2, 4, 5]
+    assert kernel.supported_modes(4, 5120, 5120, 512, num_sms=148) == [2, 4, 5, 7]
+    assert kernel.supported_modes(3, 5120, 5120, 256, num_sms=148) == [2, 4, 5, 7]
+    assert kernel.supported_modes(4, 5120, 5120, 1024, num_sms=148) == [2, 4, 5]
+    assert kernel.supported_modes(8, 5120, 5120, 512, num_sms=148) == [2, 4, 5]
     assert kernel.supported_modes(16, 5120, 5120, 512, num_sms=148) == [2, 4]
     assert kernel.supported_modes(1, 28672, 8192, 512, num_sms=148) == [2, 4]
     assert kernel.supported_modes(1, 5120, 768, 64, num_sms=148) == [2, 4, 5]
