@@ -49,6 +49,8 @@ static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coreside
     g->nsl = g->grid / M > 1 ? g->grid / M : 1;
     g->nr = R > 0 ? (R + g->nsl - 1) / g->nsl : 0;
     if (g->nr > 2 * NRMAX) return false;
+    // (more than two rows: the z stage is one pass over a staged row, the activation's scales one batch of requests)
+    if (g->rows > 2 && K / 256 > 2 * XW_MAX) return false;
     const int Rw = (R + 31) / 32, Rpad = Rw * 32;
     const int vt = g->nr * (K / 8);
     if (vt > VT_SLAB_MAX) return false;
@@ -66,7 +68,9 @@ static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coreside
     work = (work + 15) / 16 * 16;
     g->atile_bytes = (g->kg * g->rows + 7) / 8 * 1024;
     const int atiles = g->nsu * g->atile_bytes;
-    const int us = (Rw * g->Rt * 4 + 15) / 16 * 16, accp = g->kg * g->rows * g->nbp * 4;
+    // (more than two rows: the read-out area also holds the z stage's per-warp sums, 8 x 17 floats, while it is idle)
+    const int us = (Rw * g->Rt * 4 + 15) / 16 * 16;
+    const int accp = (g->rows > 2 && g->kg * g->rows * g->nbp * 4 < 1024) ? 1024 : g->kg * g->rows * g->nbp * 4;
     const int asf = g->nkt * g->rows * 16;
     const int fixed = atiles + 1024 + us + work + accp + asf;
     const int budget = (coresident ? CORESIDENT_SMEM : SMEM_BUDGET) - 1024;       // (alignment slack)

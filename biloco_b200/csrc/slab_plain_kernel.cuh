@@ -112,8 +112,11 @@ struct SCtrl {
     uint32_t tmem_base;
     uint32_t seq;             // launches completed on this scratch before this one (read once per CTA)
     volatile int abort;
+    // (behind the fields of the one- and two-row kernels, whose layout stays as it was measured)
+    uint64_t b_su[3];         // more than two rows: the activation codes of super-units 0..2 are in shared memory
 };
 static_assert(sizeof(SCtrl) <= 1024, "slab control block too large");
+static_assert(LR_WARPS * (2 * NRMAX + 1) * 4 <= 1024, "the z sums of the four-row kernel live in the read-out area (at least 1024 bytes there)");
 
 __device__ __noinline__ void sfail(SCtrl* ctrl, int32_t* status, uint32_t epoch, int code, int role) {
     ctrl->abort = 1;
@@ -277,6 +280,69 @@ __device__ __forceinline__ void zspan_rolled(const uint32_t* xs, int n2, const u
     plain += ps;
 }
 
+// Sixteen values at once (see reduce8). On return lane l holds the total of value
+// ((l >> 4) & 1) * 8 + ((l >> 3) & 1) * 4 + ((l >> 2) & 1) * 2 + ((l >> 1) & 1).
+__device__ __forceinline__ float reduce16(const float (&v)[2 * NRMAX], int lane) {
+    const bool h16 = lane & 16, h8 = lane & 8, h4 = lane & 4, h2 = lane & 2;
+    float a[8], b[4], c[2], d;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float give = h16 ? v[i] : v[i + 8], keep = h16 ? v[i + 8] : v[i];
+        a[i] = keep + __shfl_xor_sync(0xffffffffu, give, 16);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float give = h8 ? a[i] : a[i + 4], keep = h8 ? a[i + 4] : a[i];
+        b[i] = keep + __shfl_xor_sync(0xffffffffu, give, 8);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float give = h4 ? b[i] : b[i + 2], keep = h4 ? b[i + 2] : b[i];
+        c[i] = keep + __shfl_xor_sync(0xffffffffu, give, 4);
+    }
+    {
+        const float give = h2 ? c[0] : c[1], keep = h2 ? c[1] : c[0];
+        d = keep + __shfl_xor_sync(0xffffffffu, give, 2);
+    }
+    d += __shfl_xor_sync(0xffffffffu, d, 1);
+    return d;
+}
+
+// A thread's whole span (at most 32 activations, staged in shared memory) against up to sixteen ranks in one pass: one
+// chain of adds per rank (sixteen independent chains cover the add latency), the bit masks move instead of the sign words
+// (one shift per pair of activations for all ranks).
+__device__ __forceinline__ void zspan_rolled16(const uint32_t* xs, int n2, const uint32_t* vt, int words, int wi, int sh, int nr,
+                                               float (&sums)[2 * NRMAX], float& plain) {
+    uint32_t vw[2 * NRMAX];
+#pragma unroll
+    for (int q = 0; q < 2 * NRMAX; ++q) {
+        uint32_t lo = 0u, hi = 0u;
+        if (q < nr) {
+            lo = vt[q * words + wi];
+            if (sh + 2 * n2 > 32) hi = vt[q * words + wi + 1];
+        }
+        vw[q] = __funnelshift_r(lo, hi, sh);
+    }
+    float ps = 0.f;
+    uint32_t xn = xs[0];
+    uint32_t m0 = 1u;
+#pragma unroll 1
+    for (int i = 0; i < n2; ++i) {
+        const uint32_t xc = xn;
+        xn = xs[i + 1 < n2 ? i + 1 : i];
+        const float x0 = __uint_as_float(xc << 16), x1 = __uint_as_float(xc & 0xFFFF0000u);
+        const uint32_t m1 = m0 << 1;
+#pragma unroll
+        for (int q = 0; q < 2 * NRMAX; ++q) {
+            BILOCO_SPADD(sums[q], vw[q], m0, x0);
+            BILOCO_SPADD(sums[q], vw[q], m1, x1);
+        }
+        ps += x0 + x1;
+        m0 <<= 2;
+    }
+    plain += ps;
+}
+
 // Expansion without the table (ranks or rows for which the table would not fit): per item (rank word, column) 32 adds
 // under predicates taken from the word's bits. Not inlined (see zspan).
 template <int ROWS>
@@ -367,6 +433,10 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             mbar_init(smem_u32(&ctrl->sf_empty[q]), 1);
         }
         mbar_init(smem_u32(&ctrl->b_ready), 128);
+        if constexpr (ROWS > 2) {
+#pragma unroll 1
+            for (int q = 0; q < 3; ++q) mbar_init(smem_u32(&ctrl->b_su[q]), 128);
+        }
         mbar_init(smem_u32(&ctrl->acc_full), 1);
         mbar_init(smem_u32(&ctrl->tmem_ready), 1);
         ctrl->abort = 0;
@@ -422,11 +492,13 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         if (lane == 0 && stamps) { stamps[10] = globaltimer_ns(); stamps[26] = (unsigned long long)clock64(); }
         const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&ctrl->tmem_base);
         const uint32_t idesc = make_idesc_nvf4(128, p.nbp);
-        bool ok = swait(smem_u32(&ctrl->b_ready), 0, ctrl, p, ST_FULL, warp);
+        // (more than two rows: the activation tiles are announced super-unit by super-unit, the first three on their own)
+        bool ok = swait(smem_u32(ROWS > 2 ? &ctrl->b_su[0] : &ctrl->b_ready), 0, ctrl, p, ST_FULL, warp);
         if (lane == 0 && stamps) stamps[15] = globaltimer_ns();
 #pragma unroll 1
         for (int j = 0; ok && j < nsu; ++j) {
             const int slot = j % ring, set = j % NSETS;
+            if (ROWS > 2 && j > 0 && !swait(smem_u32(j < 3 ? &ctrl->b_su[j] : &ctrl->b_ready), 0, ctrl, p, ST_FULL, warp)) break;
             if (!swait(smem_u32(&ctrl->full[slot]), (j / ring) & 1, ctrl, p, ST_FULL, warp)) break;
             if (!swait(smem_u32(&ctrl->sf_full[set]), (j / NSETS) & 1, ctrl, p, ST_SF_FULL, warp)) break;
             tc_fence_after_sync();
@@ -523,8 +595,13 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             // activation codes: 16-byte chunk c of row m of k-tile kt -> tile kt / kg, row n = (kt % kg) * M + m, chunk c ^ (n & 7)
             const int nchunks = p.nkt * p.M * 8;
             const int kbytes = p.K >> 1;
+            // More than two rows: the tiles are announced super-unit by super-unit (the first three on their own), so that the
+            // first MMAs start when a quarter of the codes has arrived; a thread signals a super-unit once its next chunk
+            // lies behind it.
+            const int su_chunks = kg * p.M * 8, nsig = nsu < 3 ? nsu : 3;
+            int sj = 0;
 #pragma unroll 1
-            for (int i0 = st; i0 < nchunks; i0 += NU * 128) {
+            for (int i0 = st; i0 < nchunks || (ROWS > 2 && i0 == st); i0 += NU * 128) {      // (more rows: every thread makes the first trip)
                 uint4 v[NU];
 #pragma unroll
                 for (int u = 0; u < NU; ++u) {
@@ -533,6 +610,19 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                         const int c = i & 7, rest = i >> 3;
                         const int m = rest % p.M, kt = rest / p.M;
                         v[u] = ld_cg_v4(p.A_codes + (size_t)m * kbytes + kt * 128 + c * 16);
+                    }
+                }
+                if constexpr (ROWS > 2) {
+                    if (i0 == st) {
+                        // the scales were requested first: they go to shared memory and the first set to TMEM while the codes arrive
+#pragma unroll
+                        for (int r = 0; r < NSFV; ++r)
+                            if (st + 128 * r < nsf) asf_w[st + 128 * r] = sfv[r];
+                        named_bar_sync(2, 128);
+                        sfa_move(0, tmem);
+                        tc_wait_st();
+                        tc_fence_before_sync();
+                        mbar_arrive(smem_u32(&ctrl->sf_full[0]));
                     }
                 }
 #pragma unroll
@@ -544,21 +634,36 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                         const int j = kt / kg, g = kt - j * kg, n = g * ROWS + m;
                         *reinterpret_cast<uint4*>(atile + j * p.atile_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) * 16)) = v[u];
                     }
+                    if constexpr (ROWS > 2) {
+                        while (sj < nsig && (sj + 1) * su_chunks <= i + 128) {
+                            fence_proxy_async();
+                            mbar_arrive(smem_u32(&ctrl->b_su[sj]));
+                            ++sj;
+                        }
+                    }
                 }
             }
+            if constexpr (ROWS > 2) {
+                while (sj < nsig) {
+                    fence_proxy_async();
+                    mbar_arrive(smem_u32(&ctrl->b_su[sj]));
+                    ++sj;
+                }
+            } else {
 #pragma unroll
-            for (int r = 0; r < NSFV; ++r)
-                if (st + 128 * r < nsf) asf_w[st + 128 * r] = sfv[r];
+                for (int r = 0; r < NSFV; ++r)
+                    if (st + 128 * r < nsf) asf_w[st + 128 * r] = sfv[r];
 #pragma unroll 1
-            for (int i = st + 128 * NSFV; i < nsf; i += 128) {          // (rows longer than 16384 elements)
-                const int a = i & 3, m = (i >> 2) % ROWS, kt = (i >> 2) / ROWS;
-                asf_w[i] = m < p.M ? ld_cg_u32(p.A_sf + ((size_t)(m >> 7) * (p.K >> 6) + (size_t)kt * 4 + a) * 512 + (m & 31) * 16 + ((m >> 5) & 3) * 4) : 0u;
+                for (int i = st + 128 * NSFV; i < nsf; i += 128) {          // (rows longer than 16384 elements)
+                    const int a = i & 3, m = (i >> 2) % ROWS, kt = (i >> 2) / ROWS;
+                    asf_w[i] = m < p.M ? ld_cg_u32(p.A_sf + ((size_t)(m >> 7) * (p.K >> 6) + (size_t)kt * 4 + a) * 512 + (m & 31) * 16 + ((m >> 5) & 3) * 4) : 0u;
+                }
             }
             fence_proxy_async();                      // the activation tiles were written with ordinary stores
             mbar_arrive(smem_u32(&ctrl->b_ready));
-            named_bar_sync(2, 128);                   // the scales are in shared memory
+            if constexpr (ROWS <= 2) named_bar_sync(2, 128);      // the scales are in shared memory
 #pragma unroll 1
-            for (int j = 0; j < nfirst; ++j) {        // (set by set: the first MMAs start while the later sets are written)
+            for (int j = ROWS > 2 ? 1 : 0; j < nfirst; ++j) {     // (set by set: the first MMAs start while the later sets are written)
                 sfa_move(j, tmem);
                 tc_wait_st();
                 tc_fence_before_sync();
@@ -621,7 +726,9 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             cp_async_wait_all();
         }
         float s_coef[2] = {0.f, 0.f};                                        // (nr <= 2 * NRMAX: two passes at most)
-        if (lt < NRMAX) {
+        if (ROWS > 2) {                                                      // (one pass of up to sixteen ranks)
+            if (lt < 2 * NRMAX && lt < nr) s_coef[0] = __bfloat162float(p.S[ra + lt]);
+        } else if (lt < NRMAX) {
             if (lt < nr) s_coef[0] = __bfloat162float(p.S[ra + lt]);
             if (NRMAX + lt < nr) s_coef[1] = __bfloat162float(p.S[ra + NRMAX + lt]);
         }
@@ -681,49 +788,80 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 ctrl->seq = (((c0.x + c0.y) + (c0.z + c0.w)) + ((c1.x + c1.y) + (c1.z + c1.w))) >> 20;
             }
             if (lt == 0 && stamps) { stamps[3] = globaltimer_ns(); stamps[19] = (unsigned long long)clock64(); }
+            if constexpr (ROWS <= 2) {
 #pragma unroll 1
-            for (int ps = 0; ps * NRMAX < nr; ++ps) {
-                float sums[NRMAX];
+                for (int ps = 0; ps * NRMAX < nr; ++ps) {
+                    float sums[NRMAX];
 #pragma unroll
-                for (int q = 0; q < NRMAX; ++q) sums[q] = 0.f;
-                float plain = 0.f;
-                const int nq = nr - ps * NRMAX;                                  // ranks of this pass (may exceed NRMAX)
+                    for (int q = 0; q < NRMAX; ++q) sums[q] = 0.f;
+                    float plain = 0.f;
+                    const int nq = nr - ps * NRMAX;                                  // ranks of this pass (may exceed NRMAX)
 #pragma unroll 1
-                for (int s0 = 0; s0 < e; s0 += 2 * XW_MAX) {
-                    const int n2 = ((e - s0) < 2 * XW_MAX ? (e - s0) : 2 * XW_MAX) >> 1;      // pairs in this segment
-                    if (!single) {
+                    for (int s0 = 0; s0 < e; s0 += 2 * XW_MAX) {
+                        const int n2 = ((e - s0) < 2 * XW_MAX ? (e - s0) : 2 * XW_MAX) >> 1;      // pairs in this segment
+                        if (!single) {
 #pragma unroll
-                        for (int i = 0; i < XW_MAX; ++i) xw[i] = i < n2 ? ld_cg_u32(xrow + (s0 >> 1) + i) : 0u;
+                            for (int i = 0; i < XW_MAX; ++i) xw[i] = i < n2 ? ld_cg_u32(xrow + (s0 >> 1) + i) : 0u;
+                        }
+                        const int idx = lt * e + s0, wi = idx >> 5, sh = idx & 31;
+                        if (single) {
+                            if (nq <= 4) zspan_rolled<4>(mine, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
+                            else zspan_rolled<NRMAX>(mine, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
+                        } else if (nq <= 4) {
+                            zspan<4>(xw, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
+                        } else {
+                            zspan<NRMAX>(xw, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
+                        }
                     }
-                    const int idx = lt * e + s0, wi = idx >> 5, sh = idx & 31;
-                    if (single) {
-                        if (nq <= 4) zspan_rolled<4>(mine, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
-                        else zspan_rolled<NRMAX>(mine, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
-                    } else if (nq <= 4) {
-                        zspan<4>(xw, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
-                    } else {
-                        zspan<NRMAX>(xw, n2, vt, words, wi, sh, ps * NRMAX, nr, sums, plain);
+                    if (lt == 0 && stamps && ps == 0) stamps[26] = (unsigned long long)clock64();
+                    const float tot = reduce8(sums, lane);
+                    const int rl = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                    if ((lane & 3) == 0) ctrl->zred[lw][rl] = tot;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
+                    if (lane == 0) ctrl->zred[lw][NRMAX] = plain;
+                    named_bar_sync(3, LR_THREADS);
+                    if (lt == 0 && stamps && ps == 0) stamps[31] = (unsigned long long)clock64();
+                    phase = (ctrl->seq & 1u) ^ 1u;
+                    if (lt < NRMAX && ps * NRMAX + lt < nr) {
+                        float v = 0.f, a = 0.f;
+#pragma unroll
+                        for (int g = 0; g < LR_WARPS; ++g) { v += ctrl->zred[g][lt]; a += ctrl->zred[g][NRMAX]; }
+                        const float z = (2.f * v - a) * (ps == 0 ? s_coef[0] : s_coef[1]);
+                        if (cta != p.skip_publish_cta)
+                            p.zbuf[(size_t)zm * p.Rpad + ra + ps * NRMAX + lt] = __uint_as_float((__float_as_uint(z) & ~1u) | phase);
                     }
+                    if ((ps + 1) * NRMAX < nr) named_bar_sync(3, LR_THREADS);      // zred is reused by the next pass
                 }
-                if (lt == 0 && stamps && ps == 0) stamps[26] = (unsigned long long)clock64();
-                const float tot = reduce8(sums, lane);
-                const int rl = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-                if ((lane & 3) == 0) ctrl->zred[lw][rl] = tot;
+            } else {
+                // one pass over all ranks of the slice (at most sixteen, rows of at most 8192 elements: the launcher admits no others)
+                float sums[2 * NRMAX];
+#pragma unroll
+                for (int q = 0; q < 2 * NRMAX; ++q) sums[q] = 0.f;
+                float plain = 0.f;
+                if (nr > 0) {
+                    const int idx = lt * e;
+                    zspan_rolled16(mine, e >> 1, vt, words, idx >> 5, idx & 31, nr, sums, plain);
+                }
+                if (lt == 0 && stamps) stamps[26] = (unsigned long long)clock64();
+                float (*zr)[2 * NRMAX + 1] = reinterpret_cast<float (*)[2 * NRMAX + 1]>(accp);      // (the read-out area is idle until the MMAs are done)
+                const float tot = reduce16(sums, lane);
+                const int rl = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+                if ((lane & 1) == 0) zr[lw][rl] = tot;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) plain += __shfl_xor_sync(0xffffffffu, plain, o);
-                if (lane == 0) ctrl->zred[lw][NRMAX] = plain;
+                if (lane == 0) zr[lw][2 * NRMAX] = plain;
                 named_bar_sync(3, LR_THREADS);
-                if (lt == 0 && stamps && ps == 0) stamps[31] = (unsigned long long)clock64();
+                if (lt == 0 && stamps) stamps[31] = (unsigned long long)clock64();
                 phase = (ctrl->seq & 1u) ^ 1u;
-                if (lt < NRMAX && ps * NRMAX + lt < nr) {
+                if (lt < 2 * NRMAX && lt < nr) {
                     float v = 0.f, a = 0.f;
 #pragma unroll
-                    for (int g = 0; g < LR_WARPS; ++g) { v += ctrl->zred[g][lt]; a += ctrl->zred[g][NRMAX]; }
-                    const float z = (2.f * v - a) * (ps == 0 ? s_coef[0] : s_coef[1]);
+                    for (int g = 0; g < LR_WARPS; ++g) { v += zr[g][lt]; a += zr[g][2 * NRMAX]; }
+                    const float z = (2.f * v - a) * s_coef[0];
                     if (cta != p.skip_publish_cta)
-                        p.zbuf[(size_t)zm * p.Rpad + ra + ps * NRMAX + lt] = __uint_as_float((__float_as_uint(z) & ~1u) | phase);
+                        p.zbuf[(size_t)zm * p.Rpad + ra + lt] = __uint_as_float((__float_as_uint(z) & ~1u) | phase);
                 }
-                if ((ps + 1) * NRMAX < nr) named_bar_sync(3, LR_THREADS);      // zred is reused by the next pass
             }
             if (lt == 0 && stamps) { stamps[4] = globaltimer_ns(); stamps[20] = (unsigned long long)clock64(); }
             if (p.trigger == 1 && lt == 0) griddep_launch_dependents();

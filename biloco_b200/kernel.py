@@ -33,13 +33,13 @@ DEFAULT_MODE = {M: {r: (2 if (M > 8 or (M, r) in _MODE2_WINS) else 5) for r in R
 
 
 def default_mode(M: int, rank: int, ok, back_to_back: bool = True):
-    """The schedule BiLoCoGemm picks among the modes `ok` that the shape takes. Row slabs (mode 7) for one or two rows when
+    """The schedule BiLoCoGemm picks among the modes `ok` that the shape takes. Row slabs (mode 7) for one to four rows when
     the launches of a stream follow one another directly (the reference's measurement protocol, a chain of linears): a
     row-slab CTA takes the SM's whole tensor memory and relies on meeting exactly one CTA of the next launch on its SM.
     With other kernels in between (an activation quantiser per linear, the decode step) two CTAs of one launch can land
     on one SM and take turns (measured: 20.6 us per layer against 16.4 with the cluster schedule), so
     back_to_back=False keeps to the measured table of the other schedules; then the first that is available."""
-    if M <= 2 and 7 in ok and back_to_back:
+    if M <= 4 and 7 in ok and back_to_back:
         return 7
     mode = DEFAULT_MODE.get(M, {}).get(rank)
     return mode if mode in ok else ([m for m in ok if m != 7] or [None])[0]
