@@ -162,7 +162,7 @@ def tile_weights(B, B_sf):
 
 
 def tile_weights_slab(B, B_sf):
-    """Row-slab copy of the NVFP4 weight for the row-slab schedule (mode 7, one or two activation rows)."""
+    """Row-slab copy of the NVFP4 weight for the row-slab schedule (mode 7, one to four activation rows)."""
     N, K = B.size(0), B.size(1) * 2
     lib = _lib.load()
     with torch.cuda.device(B.device):

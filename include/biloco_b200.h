@@ -52,11 +52,12 @@ typedef struct CUstream_st* biloco_stream_t; /* same type as cudaStream_t */
 #define BILOCO_MODE_COUNTER 2
 #define BILOCO_MODE_OWNER 4
 #define BILOCO_MODE_CLUSTER 5
-/*   7: row slabs, for one or two activation rows: N is split only (CTA c owns the ceil8(N / SMs) weight rows c, all of K),
+/*   7: row slabs, for one to four activation rows: N is split only (CTA c owns the ceil8(N / SMs) weight rows c, all of K),
  *      so no partial sum leaves a CTA; the tensor-core tile's 128 rows hold the same weight rows for up to four
  *      consecutive k-tiles, matched by one activation-operand row per k-tile, and the diagonal blocks of the
  *      accumulator are summed in the epilogue. Needs the copy made by biloco_b200_tile_weights_slab as W_tiled,
- *      M <= 2, K % 512 == 0, N <= 128 * SMs, one column group. No counterpart in the reference. */
+ *      M <= 4 (three rows run as four; with three or four rows K <= 8192 and at most 16 ranks per z slice, i.e.
+ *      R <= 16 * floor(SMs / M)), K % 512 == 0, N <= 128 * SMs, one column group. No counterpart in the reference. */
 #define BILOCO_MODE_SLAB 7
 
 /* OR-ed to the mode: Y is fp32 [M,N] instead of bf16 (the unrounded sum). For partial outputs that are reduced across
