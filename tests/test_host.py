@@ -42,6 +42,11 @@ def test_sf_bytes_and_mode_table(golden):
     assert kernel.supported_modes(3, 5120, 5120, 256, num_sms=148) == [2, 4, 5, 7]
     assert kernel.supported_modes(4, 5120, 5120, 1024, num_sms=148) == [2, 4, 5]
     assert kernel.supported_modes(8, 5120, 5120, 512, num_sms=148) == [2, 4, 5]
+    # three and four rows: rows of at most 8192 elements, at most 16 ranks per z slice (148 // M slices per row), a ring of two stages
+    assert 7 in kernel.supported_modes(4, 5120, 5120, 576, num_sms=148) and 7 not in kernel.supported_modes(4, 5120, 5120, 600, num_sms=148)
+    assert 7 in kernel.supported_modes(3, 5120, 2560, 512, num_sms=148) and 7 not in kernel.supported_modes(3, 2560, 16384, 512, num_sms=148)
+    assert 7 not in kernel.supported_modes(4, 4096, 4096, 512, num_sms=148) and 7 in kernel.supported_modes(2, 4096, 4096, 512, num_sms=148)
+    assert kernel.default_mode(4, 512, [2, 4, 5, 7]) == 7 and kernel.default_mode(4, 512, [2, 4, 5, 7], back_to_back=False) == 5
     assert kernel.supported_modes(16, 5120, 5120, 512, num_sms=148) == [2, 4]
     assert kernel.supported_modes(1, 28672, 8192, 512, num_sms=148) == [2, 4]
     assert kernel.supported_modes(1, 5120, 768, 64, num_sms=148) == [2, 4, 5]
