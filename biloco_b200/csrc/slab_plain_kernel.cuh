@@ -571,6 +571,19 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             sfb_move(j, tmem);
         }
         tc_wait_st();
+        // One and two rows: where this thread's first activation chunks go in the operand tiles, worked out here, in front of
+        // the dependency wait (the quotient by kg, a run-time number, is about twenty dependent instructions: several hundred
+        // cycles that would otherwise sit between the arrival of the codes and the first MMA).
+        uint32_t cdst[4] = {0u, 0u, 0u, 0u};
+        if constexpr (ROWS <= 2) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = st + 128 * u, c = i & 7, rest = i >> 3;
+                const int m = rest % ROWS, kt = rest / ROWS;
+                const int j = kt / kg, g = kt - j * kg, n = g * ROWS + m;
+                cdst[u] = (uint32_t)(j * p.atile_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) * 16));
+            }
+        }
         if (st == 0 && stamps) { stamps[13] = globaltimer_ns(); stamps[29] = (unsigned long long)clock64(); }
         griddep_wait();
         if (st == 0 && stamps) { stamps[14] = globaltimer_ns(); stamps[30] = (unsigned long long)clock64(); }
@@ -608,7 +621,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                     const int i = i0 + 128 * u;
                     if (i < nchunks) {
                         const int c = i & 7, rest = i >> 3;
-                        const int m = rest % p.M, kt = rest / p.M;
+                        const int m = ROWS <= 2 ? rest % ROWS : rest % p.M, kt = ROWS <= 2 ? rest / ROWS : rest / p.M;      // (one, two rows: M = ROWS)
                         v[u] = ld_cg_v4(p.A_codes + (size_t)m * kbytes + kt * 128 + c * 16);
                     }
                 }
@@ -629,10 +642,14 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 for (int u = 0; u < NU; ++u) {
                     const int i = i0 + 128 * u;
                     if (i < nchunks) {
-                        const int c = i & 7, rest = i >> 3;
-                        const int m = rest % p.M, kt = rest / p.M;
-                        const int j = kt / kg, g = kt - j * kg, n = g * ROWS + m;
-                        *reinterpret_cast<uint4*>(atile + j * p.atile_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) * 16)) = v[u];
+                        if (ROWS <= 2 && i0 == st) {
+                            *reinterpret_cast<uint4*>(atile + cdst[u]) = v[u];
+                        } else {
+                            const int c = i & 7, rest = i >> 3;
+                            const int m = rest % p.M, kt = rest / p.M;
+                            const int j = kt / kg, g = kt - j * kg, n = g * ROWS + m;
+                            *reinterpret_cast<uint4*>(atile + j * p.atile_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) * 16)) = v[u];
+                        }
                     }
                     if constexpr (ROWS > 2) {
                         while (sj < nsig && (sj + 1) * su_chunks <= i + 128) {
