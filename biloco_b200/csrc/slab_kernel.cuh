@@ -325,17 +325,24 @@ __device__ __noinline__ void expand_padd(const float* zs, float* corrp, const ui
 // Raw-activation form: this CTA's share of the activation's 16-element blocks, [cta nblk / G, (cta + 1) nblk / G), quantised
 // by `nth` threads (whole warps; t = the thread's index among them) with a lane per element, each block published as two
 // 64-bit words that carry `mark` in their top 16 bits (layout: see SlabParams).
-__device__ __noinline__ void quantise_share(int t, int nth, int lane, int cta, const SlabParams& p, const uint8_t* xsb, float gs, uint32_t seq) {
-    const int kblocks = p.K >> 4, nblk = p.M * kblocks;
-    const int b0 = (int)((unsigned)cta * (unsigned)nblk / (unsigned)p.G), b1 = (int)((unsigned)(cta + 1) * (unsigned)nblk / (unsigned)p.G);
-    const int nl = ((b1 - b0) * 16 + 31) & ~31;      // (nblk <= 2048 and G <= 65535: the products fit 32 bits)
+// (The share's bounds are worked out by the caller in front of the dependency wait, and a block's row by comparison (the
+// raw form has one or two rows): a quotient by a run-time number is about twenty dependent instructions, several hundred
+// cycles on this kernel, and everything here sits between the activation's arrival and the first MMA.)
+__device__ __forceinline__ void share_bounds(int cta, const SlabParams& p, int& b0, int& b1) {
+    const int nblk = p.M * (p.K >> 4);               // (nblk <= 2048 and G <= 65535: the products fit 32 bits)
+    b0 = (int)((unsigned)cta * (unsigned)nblk / (unsigned)p.G);
+    b1 = (int)((unsigned)(cta + 1) * (unsigned)nblk / (unsigned)p.G);
+}
+__device__ __noinline__ void quantise_share(int t, int nth, int lane, int b0, int b1, const SlabParams& p, const uint8_t* xsb, float gs, uint32_t seq) {
+    const int kblocks = p.K >> 4;
+    const int nl = ((b1 - b0) * 16 + 31) & ~31;
     const unsigned long long mark = (unsigned long long)((seq + 1u) & 0xFFFFu) << 48;
 #pragma unroll 1
     for (int li = t; li < nl; li += nth) {
         const int b = b0 + (li >> 4), j = li & 15;
         float x = 0.f;
         if (b < b1) {
-            const int row = b / kblocks, kb = b - row * kblocks;
+            const int row = b >= kblocks ? 1 : 0, kb = b - row * kblocks;
             x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(xsb + (size_t)row * 2 * p.K)[kb * 16 + j]);
         }
         uint2 codes;
@@ -561,6 +568,10 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             sfb_move(j, tmem);
         }
         tc_wait_st();
+        // (raw form: this CTA's share of the blocks and the reciprocal that stands for the quotient by kg, see quantise_share)
+        int qb0 = 0, qb1 = 0;
+        float inv_kg = 0.f;
+        if constexpr (RAW) { share_bounds(cta, p, qb0, qb1); inv_kg = 1.f / (float)kg; }
         if (st == 0 && stamps) { stamps[13] = globaltimer_ns(); stamps[29] = (unsigned long long)clock64(); }
         griddep_wait();
         if (st == 0 && stamps) { stamps[14] = globaltimer_ns(); stamps[30] = (unsigned long long)clock64(); }
@@ -569,7 +580,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         // out must not leave the others at a barrier that has no time limit)
         if (raw) {
             asm volatile("bar.sync 5, 384;" ::: "memory");      // the low-rank threads have staged the activation and set the scale
-            quantise_share(st, 128, lane, cta, p, work + p.xs_off, ctrl->gs, ctrl->seq);
+            quantise_share(st, 128, lane, qb0, qb1, p, work + p.xs_off, ctrl->gs, ctrl->seq);
             if (st == 0 && stamps) stamps[47] = (unsigned long long)clock64();
         }
         if (ok && raw) {
@@ -609,8 +620,8 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 for (int u = 0; u < GMAX; ++u) {
                     const int b = b00 + 128 * u;
                     if (b < nblk) {
-                        const int row = b / kblocks, kb = b - row * kblocks;
-                        const int kt = kb >> 4, j = kt / kg, g = kt - j * kg, n = g * ROWS + row;
+                        const int row = b >= kblocks ? 1 : 0, kb = b - row * kblocks;
+                        const int kt = kb >> 4, j = (int)(((float)kt + 0.5f) * inv_kg), g = kt - j * kg, n = g * ROWS + row;      // (kt / kg, exact here)
                         const int byte = (kb & 15) * 8, c = byte >> 4;
                         const uint2 codes = make_uint2((uint32_t)w0[u], (uint32_t)((w0[u] >> 32) & 0xFFFFull) | ((uint32_t)(w1[u] & 0xFFFFull) << 16));
                         *reinterpret_cast<uint2*>(atile + j * p.atile_bytes + (n >> 3) * 1024 + (n & 7) * 128 + ((c ^ (n & 7)) * 16) + (byte & 8)) = codes;
@@ -754,6 +765,8 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
             if (NRMAX + lt < nr) s_coef[1] = __bfloat162float(p.S[ra + NRMAX + lt]);
         }
         named_bar_sync(3, LR_THREADS);
+        int qb0 = 0, qb1 = 0;                                                // (raw form, a CTA without weight rows: its share, see quantise_share)
+        if (RAW && !has_rows) share_bounds(cta, p, qb0, qb1);
 
         griddep_wait();            // everything below reads what earlier kernels of the stream wrote
         if (lt == 0 && stamps) { stamps[2] = globaltimer_ns(); stamps[18] = (unsigned long long)clock64(); }
@@ -896,7 +909,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 asm volatile("bar.sync 5, 384;" ::: "memory");
             } else {
                 named_bar_sync(3, LR_THREADS);
-                quantise_share(lt, LR_THREADS, lane, cta, p, xsb, ctrl->gs, ctrl->seq);
+                quantise_share(lt, LR_THREADS, lane, qb0, qb1, p, xsb, ctrl->gs, ctrl->seq);
             }
             if (lt == 0 && stamps) stamps[41] = (unsigned long long)clock64();
             if (lt == 0 && stamps) stamps[46] = (unsigned long long)clock64();

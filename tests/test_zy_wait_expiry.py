@@ -19,10 +19,11 @@ pytestmark = pytest.mark.gpu
 ST_Z = 105          # status code of the z poll (csrc/fused_cfg.cuh)
 
 
-def test_z_poll_runs_out_and_scratch_recovers():
+@pytest.mark.parametrize("M", [1, 4])        # (the four-row kernel has a z poll of its own: two vectors per round trip)
+def test_z_poll_runs_out_and_scratch_recovers(M):
     from biloco_b200 import _lib, kernel
     lib = _lib.load()
-    M, K, N, R = 1, 1024, 1024, 512        # (every CTA owns at least three ranks)
+    K, N, R = 1024, 1024, 512              # (every CTA owns at least three ranks)
     assert 7 in kernel.supported_modes(M, N, K, R)
     p = orc.random_problem(M, K, N, R, scales="random", seed=11)
     t = dev_problem(p)
