@@ -545,6 +545,10 @@ static int slab_launch(const void* W_slab, const float* alpha, const void* A_cod
     q.w_gscale = act->w_gscale;
     q.act_out = act->act_out;
     q.eps = act->eps; q.act_rule = act->rule; q.act_swiglu = act->swiglu;
+    // (the raw form's MMAs start ~6 us after the dependency wait: released at set-up, the next launch moves in as soon as the
+    // previous one has left and its weight burst is over before this launch fetches its late record; released after the
+    // z stage, as the plain form does, the burst lands on that fetch. Measured end to end: 13.85 against 14.56 us per layer.)
+    if (g_trigger < 0) q.trigger = 0;
     return M <= 1 ? slab::slab_launch_rows<1, true>(q, g, pdl, stream) : slab::slab_launch_rows<2, true>(q, g, pdl, stream);
 }
 
