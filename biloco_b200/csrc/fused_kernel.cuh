@@ -31,7 +31,10 @@ __device__ __forceinline__ void ar_push(const FusedParams& p, uint32_t seq, int 
     }
 }
 
-template <int MMA_N, int ROWS>
+// PUSH: the epilogue also stores its fp32 outputs into the peers' receive buffers (row-parallel use). An instantiation of its
+// own: compiled into the one kernel behind a run-time switch, the push cost every launch that does not use it (M = 32,
+// K = N = 5120, r = 512: 32.3 us per call with the switch, 29.7 without the code).
+template <int MMA_N, int ROWS, bool PUSH = false>
 __global__ void __launch_bounds__(NUM_THREADS, ctas_per_sm(ROWS))
 fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ FusedParams p) {
@@ -301,7 +304,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
         }
         if (p.trigger == 1 && tid == 0) griddep_launch_dependents();
         griddep_wait();            // (again, for the R == 0 path; a second wait returns at once)
-        if (p.ar_world > 1 && tid == 0) ctrl->ar_seq = (ld_volatile_u32(p.ar_counter) >> 20) + 1u;      // (read by the storing threads behind a barrier)
+        if (PUSH && tid == 0) ctrl->ar_seq = (ld_volatile_u32(p.ar_counter) >> 20) + 1u;      // (read by the storing threads behind a barrier)
         // Cluster mode: the other CTAs of the cluster deposit their partial sums in this (the finishing) CTA's work
         // area, which its z stage has been using until now: tell them it is free.
         if (p.cluster > 1 && (cta % p.cluster) == p.cluster - 1 && tid < p.cluster - 1)
@@ -395,7 +398,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                                 if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
                                 if (p.mode & 0x400) {
                                     reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
-                                    if (p.ar_world > 1) ar_push(p, ctrl->ar_seq, m * p.N + n, o);
+                                    if constexpr (PUSH) ar_push(p, ctrl->ar_seq, m * p.N + n, o);
                                 } else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
                             }
                         }
@@ -432,7 +435,7 @@ fused_linear_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
                             if (p.C) o += __bfloat162float(p.C[(size_t)m * p.N + n]);
                             if (p.mode & 0x400) {
                                 reinterpret_cast<float*>(p.Y)[(size_t)m * p.N + n] = o;
-                                if (p.ar_world > 1) ar_push(p, ctrl->ar_seq, m * p.N + n, o);
+                                if constexpr (PUSH) ar_push(p, ctrl->ar_seq, m * p.N + n, o);
                             } else p.Y[(size_t)m * p.N + n] = __float2bfloat16(o);
                         }
                     }

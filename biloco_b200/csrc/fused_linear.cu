@@ -303,9 +303,14 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM_BUDGET) != cudaSuccess ||
+            cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  SMEM_BUDGET) != cudaSuccess)
             return BILOCO_ERR_CUDA;
+        // (clusters of more than eight CTAs: query_active_clusters allows them for the plain instantiation)
+        if (cudaFuncSetAttribute(fused_linear_kernel<MMA_N, ROWS, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess)
+            cudaGetLastError();
         attr_set[dev] = true;
     }
     // z stage geometry: nsl rank slices per activation row, and shared memory for the sign words of one slice
@@ -406,7 +411,9 @@ static int launch(const CUtensorMap& tmW, const CUtensorMap& tmA, const FusedPar
     }
     cfg.attrs = attr;
     cfg.numAttrs = na;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, fused_linear_kernel<MMA_N, ROWS>, tmW, tmA, p);
+    // (the instantiation whose epilogue pushes to the peers only where a group of more than one rank is given)
+    const cudaError_t e = p.ar_world > 1 ? cudaLaunchKernelEx(&cfg, fused_linear_kernel<MMA_N, ROWS, true>, tmW, tmA, p)
+                                         : cudaLaunchKernelEx(&cfg, fused_linear_kernel<MMA_N, ROWS, false>, tmW, tmA, p);
     return e == cudaSuccess ? BILOCO_OK : BILOCO_ERR_CUDA;
 }
 
