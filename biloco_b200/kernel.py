@@ -21,13 +21,15 @@ RANKS = (16, 32, 64, 128, 256, 512, 1024)
 # Schedules implemented by the fused kernel (see include/biloco_b200.h, BILOCO_MODE_*).
 IMPLEMENTED_MODES = (2, 4, 5, 7)
 
-# Fastest implemented mode per (M, rank) on B200 at K = N = 5120, from `bench.py --M .. --r .. --mode ..` (us per call,
-# 64 distinct layers per step, mode 2 / mode 5; M = 16, 32: mode 2 only, expansion on the tensor cores):
-#   r = 128 : M=1 11.1/9.2   M=2 11.6/9.7   M=4 12.9/12.4  M=8 14.7/14.6  M=16 16.5  M=32 21.4
-#   r = 256 : M=1 11.6/9.6   M=2 12.5/10.6  M=4 14.6/14.3  M=8 16.8/16.2  M=16 19.3  M=32 25.6
-#   r = 512 : M=1 12.6/10.1  M=2 15.1/12.6  M=4 16.6/15.7  M=8 21.5/20.2  M=16 24.7  M=32 38.3
-#   r = 1024: M=1 15.1/14.2  M=2 17.6/18.3  M=4 21.4/21.2  M=8 29.9/31.5  M=16 38.9  M=32 67.6
-# Mode 5 does not take M > 8; mode 4 loses everywhere. Ranks below 128 were not measured and follow r = 128.
+# Time per call of every implemented mode per (M, rank) on B200 at K = N = 5120, HBM-cold, from `bench.py --table` (us;
+# mode 2 / mode 5 / mode 7 where the mode takes the point; M = 16, 32: mode 2 only, z stage and expansion on the tensor cores):
+#   r = 128 : M=1 11.3/9.6/8.5    M=2 12.0/9.7/8.5    M=4 12.9/12.7/10.5  M=8 14.7/14.7  M=16 20.4  M=32 25.0
+#   r = 256 : M=1 11.9/9.8/8.2    M=2 12.7/10.1/8.6   M=4 14.6/14.4/10.4  M=8 17.1/16.5  M=16 21.8  M=32 26.3
+#   r = 512 : M=1 12.7/10.2/8.9   M=2 14.7/12.6/9.4   M=4 16.9/16.0/10.7  M=8 21.6/20.4  M=16 24.4  M=32 29.9
+#   r = 1024: M=1 14.9/14.1/10.2  M=2 17.6/18.5/12.4  M=4 21.6/21.5       M=8 29.9/31.3  M=16 31.5  M=32 39.6
+# Mode 5 does not take M > 8, mode 7 not M > 4 (nor r = 1024 at M = 4); mode 4 loses everywhere. Ranks below 128 were not
+# measured and follow r = 128. DEFAULT_MODE is the table WITHOUT mode 7 (what a stream with other kernels between the linears
+# uses); default_mode() puts mode 7 in front of it for launches that follow one another directly.
 _MODE2_WINS = {(2, 1024), (8, 1024)}
 DEFAULT_MODE = {M: {r: (2 if (M > 8 or (M, r) in _MODE2_WINS) else 5) for r in RANKS} for M in (1, 2, 4, 8, 16, 32)}
 
