@@ -870,21 +870,32 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                     }
                 } else {
                     const uint4* xr = reinterpret_cast<const uint4*>(p.Xraw + (size_t)row * p.K);
+                    // (a thread's vectors are requested three at a time before any is used: one round trip per batch, not per vector)
 #pragma unroll 1
-                    for (int i = lt; i < kvec; i += LR_THREADS) {
-                        const uint4 a = ld_cg_v4(xr + i);
-                        uint4 c = make_uint4(0u, 0u, 0u, 0u);
-                        if (sv) c = sv[i];
-                        const uint32_t w[4] = {a.x, a.y, a.z, a.w}, sw[4] = {c.x, c.y, c.z, c.w};
-                        uint32_t o[4];
+                    for (int i0 = lt; i0 < kvec; i0 += 3 * LR_THREADS) {
+                        uint4 av[3];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float lo, hi;
-                            qm::unpack_smoothed(w[e], sw[e], sv != nullptr, lo, hi);
-                            amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
-                            o[e] = (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xFFFF0000u);
+                        for (int u = 0; u < 3; ++u)
+                            if (i0 + u * LR_THREADS < kvec) av[u] = ld_cg_v4(xr + i0 + u * LR_THREADS);
+#pragma unroll
+                        for (int u = 0; u < 3; ++u) {
+                            const int i = i0 + u * LR_THREADS;
+                            if (i < kvec) {
+                                const uint4 a = av[u];
+                                uint4 c = make_uint4(0u, 0u, 0u, 0u);
+                                if (sv) c = sv[i];
+                                const uint32_t w[4] = {a.x, a.y, a.z, a.w}, sw[4] = {c.x, c.y, c.z, c.w};
+                                uint32_t o[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float lo, hi;
+                                    qm::unpack_smoothed(w[e], sw[e], sv != nullptr, lo, hi);
+                                    amax = fmaxf(amax, fmaxf(fabsf(lo), fabsf(hi)));
+                                    o[e] = (__float_as_uint(lo) >> 16) | (__float_as_uint(hi) & 0xFFFF0000u);
+                                }
+                                dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                            }
                         }
-                        dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
             }
