@@ -60,23 +60,33 @@ static bool slab_geometry(int M, int N, int K, int R, int num_sms, bool coreside
     g->xs_off = (vt + 15) / 16 * 16;
     // (raw-activation form: all M rows of the activation are formed and staged there, whatever K and R are)
     const int zwork = raw ? g->xs_off + M * 2 * K : (R > 0 ? g->xs_off + (K / 256 <= 2 * XW_MAX ? 2 * K : 0) : 0);
-    int work = g->rows * Rpad * 4 + g->rows * Rw * g->Rt * 4;
-    // expansion by table (16 sums per group of four ranks: 16 bytes per rank and row) where the table is small
-    g->lut = (R > 0 && g->rows * Rpad * 16 <= 8192) ? 1 : 0;
-    if (g->lut) work += g->rows * Rpad * 16;
-    if (work < zwork) work = zwork;
-    work = (work + 15) / 16 * 16;
+    // expansion by table (16 sums per group of four ranks: 16 bytes per rank and row): always where the table is small, and
+    // up to 16 KB (two rows at r = 512, four at r = 256) where it costs no stage of the weight ring
+    const int work_plain = g->rows * Rpad * 4 + g->rows * Rw * g->Rt * 4, table = g->rows * Rpad * 16;
     g->atile_bytes = (g->kg * g->rows + 7) / 8 * 1024;
     const int atiles = g->nsu * g->atile_bytes;
     // (more than two rows: the read-out area also holds the z stage's per-warp sums, 8 x 17 floats, while it is idle)
     const int us = (Rw * g->Rt * 4 + 15) / 16 * 16;
     const int accp = (g->rows > 2 && g->kg * g->rows * g->nbp * 4 < 1024) ? 1024 : g->kg * g->rows * g->nbp * 4;
     const int asf = g->nkt * g->rows * 16;
-    const int fixed = atiles + 1024 + us + work + accp + asf;
     const int budget = (coresident ? CORESIDENT_SMEM : SMEM_BUDGET) - 1024;       // (alignment slack)
-    int ring = (budget - fixed) / g->stage_bytes;
-    if (ring > MAX_RING) ring = MAX_RING;
-    if (ring > g->nsu) ring = g->nsu;
+    auto ring_for = [&](int work_bytes, int* fixed_out) {
+        int w = work_bytes < zwork ? zwork : work_bytes;
+        w = (w + 15) / 16 * 16;
+        const int fixed = atiles + 1024 + us + w + accp + asf;
+        int r = (budget - fixed) / g->stage_bytes;
+        if (r > MAX_RING) r = MAX_RING;
+        if (r > g->nsu) r = g->nsu;
+        *fixed_out = w;
+        return r;
+    };
+    int work = 0, work_t = 0;
+    int ring = ring_for(work_plain, &work);
+    g->lut = 0;
+    if (R > 0 && table <= 16384) {
+        const int ring_t = ring_for(work_plain + table, &work_t);
+        if (table <= 8192 || ring_t == ring) { g->lut = 1; ring = ring_t; work = work_t; }
+    }
     if (ring < 1 || (ring < 2 && g->nsu >= 2)) return false;
     g->ring = ring;
     g->off_ring = atiles;
