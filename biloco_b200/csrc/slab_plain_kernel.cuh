@@ -495,11 +495,13 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
         // (more than two rows: the activation tiles are announced super-unit by super-unit, the first three on their own)
         bool ok = swait(smem_u32(ROWS > 2 ? &ctrl->b_su[0] : &ctrl->b_ready), 0, ctrl, p, ST_FULL, warp);
         if (lane == 0 && stamps) stamps[15] = globaltimer_ns();
+        int slot = 0;                    // (j % ring and the parity of j / ring, kept by counting: no quotient by a run-time number in front of an MMA)
+        uint32_t lap = 0u;
 #pragma unroll 1
         for (int j = 0; ok && j < nsu; ++j) {
-            const int slot = j % ring, set = j % NSETS;
+            const int set = j % NSETS;
             if (ROWS > 2 && j > 0 && !swait(smem_u32(j < 3 ? &ctrl->b_su[j] : &ctrl->b_ready), 0, ctrl, p, ST_FULL, warp)) break;
-            if (!swait(smem_u32(&ctrl->full[slot]), (j / ring) & 1, ctrl, p, ST_FULL, warp)) break;
+            if (!swait(smem_u32(&ctrl->full[slot]), lap, ctrl, p, ST_FULL, warp)) break;
             if (!swait(smem_u32(&ctrl->sf_full[set]), (j / NSETS) & 1, ctrl, p, ST_SF_FULL, warp)) break;
             tc_fence_after_sync();
             if (lane == 0) {
@@ -515,6 +517,7 @@ __global__ void __launch_bounds__(NT, 2) slab_kernel(const __grid_constant__ Sla
                 if (j == nsu - 1) tc_commit(smem_u32(&ctrl->acc_full));
             }
             __syncwarp();
+            if (++slot == ring) { slot = 0; lap ^= 1u; }
         }
         if (lane == 0 && stamps) { stamps[12] = globaltimer_ns(); stamps[28] = (unsigned long long)clock64(); }
     } else if (warp >= FIRST_SF_WARP && warp < FIRST_Z_WARP) {
