@@ -282,7 +282,10 @@ def _run_fused(kernel, p, M, N, launches=5):
 
 @pytest.mark.parametrize("M,N,K,R", [(1, 128, 256, 32), (1, 256, 512, 16), (2, 384, 1024, 40), (8, 1024, 2560, 128),
                                      (32, 640, 768, 64), (16, 136, 256, 256), (4, 384, 1024, 40), (3, 1024, 2560, 200),
-                                     (4, 2560, 1536, 128), (3, 136, 512, 8)])
+                                     (4, 2560, 1536, 128), (3, 136, 512, 8),
+                                     # rows of 7168 and 8192 elements: a z-stage thread's span is 28 / 32 activations (the fourth
+                                     # round of the row's staging, a sign word per span), 32 k-tiles of activation codes at four rows
+                                     (4, 1024, 8192, 64), (1, 1024, 8192, 64), (2, 2048, 8192, 96), (3, 512, 7168, 48)])
 def test_fused_small_shapes_random_scales(kernel, M, N, K, R):
     _run_fused(kernel, orc.random_problem(M, K, N, R, scales="random", seed=M * 7 + R), M, N)
 
